@@ -1,0 +1,69 @@
+"""ctypes binding of ``libaxs6_b200.so`` (see ``include/axs6_b200.h``).
+
+There is no CPU fallback: importing the package works without the library (so that host-side
+logic can be tested anywhere), but the first call of any op raises if the library is missing.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libaxs6_b200.so")
+
+F32, BF16 = 0, 1
+GRID_UNIFORM, GRID_NF5 = 0, 1
+ROUND_NEAREST, ROUND_STOCHASTIC = 0, 1
+LAYOUT_PLANES, LAYOUT_WIRE, LAYOUT_SPEC = 0, 1, 2
+FLAG_INPUT_VIA_BF16 = 1
+
+_i64, _int, _u32, _u64, _ptr = ctypes.c_int64, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p
+
+# name -> (restype, argtypes); mirrors include/axs6_b200.h one to one
+SIGNATURES = {
+    "axs6_strerror": (ctypes.c_char_p, [_int]),
+    "axs6_query": (_i64, [_int]),
+    "axs6_record_bytes": (_i64, [_int, _int]),
+    "axs6_fq": (_int, [_ptr, _ptr, _int, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _u32, _u64, _u64, _ptr]),
+    "axs6_fq_with_noise": (_int, [_ptr, _ptr, _int, _int, _i64, _i64, _i64, _i64, _int, _int, _u32, _ptr, _ptr]),
+    "axs6_pack": (_int, [_ptr, _int, _i64, _i64, _i64, _int, _int, _int, _u32, _u64, _u64, _ptr, _int,
+                         _ptr, _ptr, _ptr, _ptr]),
+    "axs6_unpack": (_int, [_int, _ptr, _ptr, _ptr, _ptr, _int, _i64, _i64, _i64, _int, _int, _ptr]),
+}
+
+_lib = None
+
+
+class Axs6Error(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+    def __init__(self, fn: str, status: int, text: str):
+        super().__init__(f"{fn} failed with status {status}: {text}")
+        self.status = status
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once; raise if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m axs6_b200.build` "
+                "(this package has no CPU or PyTorch fallback)")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(fn: str, status: int) -> None:
+    if status != 0:
+        raise Axs6Error(fn, status, load().axs6_strerror(status).decode())
+
+
+def launches() -> int:
+    """Number of kernels this process has launched through the library."""
+    return int(load().axs6_query(3))

@@ -1,0 +1,59 @@
+// Status text, device query and launch bookkeeping of the C ABI.
+#include <atomic>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace axs6 {
+
+static std::atomic<long long> g_launches{0};
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+const DeviceInfo &device_info()
+{
+    static DeviceInfo table[64];
+    static std::mutex mu;
+    static const DeviceInfo bad = {0, 0, 0};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return bad;
+    std::lock_guard<std::mutex> lock(mu);
+    DeviceInfo &d = table[dev];
+    if (!d.valid) {
+        int major = 0, sms = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            return bad;
+        d.ok = (major == 10) ? 1 : 0;
+        d.sms = sms;
+        d.valid = 1;
+    }
+    return d;
+}
+
+}  // namespace axs6
+
+AXS6_API const char *axs6_strerror(int status)
+{
+    switch (status) {
+    case AXS6_OK: return "ok";
+    case AXS6_ERR_ARG: return "invalid argument (null pointer, negative extent, bad enum or block size)";
+    case AXS6_ERR_ALIGN: return "pointer or leading dimension violates the required alignment";
+    case AXS6_ERR_DEVICE: return "current CUDA device is not compute capability 10.x (B200) or is unusable";
+    case AXS6_ERR_LAUNCH: return "kernel launch failed";
+    case AXS6_ERR_WORKSPACE: return "workspace missing or too small";
+    case AXS6_ERR_UNSUPPORTED: return "request not supported by this build";
+    default: return "unknown status";
+    }
+}
+
+AXS6_API int64_t axs6_query(int what)
+{
+    switch (what) {
+    case 0: { const axs6::DeviceInfo &d = axs6::device_info(); return d.valid && d.ok; }
+    case 1: { const axs6::DeviceInfo &d = axs6::device_info(); return d.valid ? d.sms : 0; }
+    case 2: return 1;
+    case 3: return axs6::g_launches.load(std::memory_order_relaxed);
+    default: return -1;
+    }
+}

@@ -1,0 +1,446 @@
+// Pack (values -> 6-bit codes + shared exponent) and unpack kernels and their C entry points.
+//
+// Roofline: HBM bandwidth.  Algorithmic bytes per block of B values:
+//   pack   B * sizeof(in)  +  record bytes (WIRE 1 + 3B/4, SPEC 2 + 3B/4)  or  1 + 2B (PLANES)
+//   unpack the mirror image.
+// Byte layouts: a CTA iteration owns 256*U consecutive chunks, i.e. a run of whole blocks
+// whose records are contiguous in the output.  Threads drop their 6 payload bytes (8 codes)
+// into a shared-memory image of that run, which is then moved with 128-bit accesses (the
+// run's size is a multiple of 16 bytes for every block size and layout).
+#include "quant_device.cuh"
+
+namespace axs6 {
+
+ChunkGeom make_geom(int64_t rows, int64_t cols, int block);
+
+struct CodecArgs {
+    const void *x;       // pack: values in;   unpack: unused
+    void *y;             // unpack: values out; pack: unused
+    int64_t ld;          // leading dimension of x / y
+    ChunkGeom g;
+    uint32_t via_bf16;
+    uint64_t seed, offset;
+    const float *noise;
+    uint8_t *p0, *p1, *p2;   // planes (exp, sign, mag) or p0 = records
+    int rec, hdr;            // record bytes and header bytes of the byte layout
+};
+
+constexpr int kPlanes = 0, kBytes = 1;
+constexpr int kU = 2;                               // chunks per thread per iteration
+constexpr int kStageBytes = kU * kThreads * 8;      // worst case: B = 8, 8-byte records
+
+// 8 codes (6 bits each) of one chunk.
+template <int GRID, int ROUND>
+__device__ __forceinline__ void chunk_codes(const uint32_t (&v)[8], uint32_t (&code)[8], int &se,
+                                            const uint8_t *rev, int lanes, const float (&u)[8])
+{
+    const uint32_t amax = group_max(chunk_amax_bits(v), lanes);
+    const Axs6Scale s = axs6_scale_codes(amax);
+    se = s.se;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t ab = v[i] & 0x7FFFFFFFu;
+        const float n = axs6_normalise(__uint_as_float(ab), s);
+        int m;
+        if (GRID == AXS6_GRID_NF5) {
+            const int idx = (ROUND == kNearest) ? axs6_nf5_index(n) : axs6_nf5_index_dithered(n, u[i]);
+            m = rev[idx];
+        } else {
+            m = (ROUND == kNearest) ? axs6_uniform_mag(n) : axs6_uniform_mag_stochastic(n, u[i]);
+        }
+        const uint32_t neg = (ab != 0u) ? (v[i] >> 31) : 0u;     // x < 0 is false for -0.0
+        code[i] = (neg << 5) | (uint32_t)m;
+    }
+}
+
+template <typename Tin, int GRID, int ROUND, int LAYOUT>
+__global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
+{
+    __shared__ __align__(16) uint8_t rev[GRID == AXS6_GRID_NF5 ? 1024 : 16];
+    __shared__ __align__(16) uint8_t stage[LAYOUT == kBytes ? kStageBytes : 16];
+    if (GRID == AXS6_GRID_NF5) build_reverse_lut(rev);
+    __syncthreads();
+
+    const int lanes = a.g.block / kChunk;
+    const int64_t total_blocks = a.g.total_chunks / lanes;
+    const int64_t step = (int64_t)gridDim.x * kThreads * kU;
+    for (int64_t base = (int64_t)blockIdx.x * kThreads * kU; base < a.g.total_chunks; base += step) {
+        uint32_t v[kU][8];
+        bool act[kU];
+#pragma unroll
+        for (int k = 0; k < kU; ++k) {
+            const int64_t c = base + (int64_t)k * kThreads + threadIdx.x;
+            act[k] = c < a.g.total_chunks;
+            int64_t xo = c * kChunk;
+            bool has = act[k];
+            if (!a.g.flat) {
+                const int64_t row = c / a.g.cpr;
+                const int64_t col0 = (c - row * a.g.cpr) * kChunk;
+                has = has && col0 < a.g.cols;
+                xo = row * a.ld + col0;
+            }
+            if (has) {
+                ChunkIO<Tin>::load(a.x, xo, v[k], a.via_bf16 != 0u);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[k][i] = 0u;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kU; ++k) {
+            const int64_t c = base + (int64_t)k * kThreads + threadIdx.x;
+            float u[8];
+            uint32_t code[8];
+            int se;
+            chunk_uniforms<ROUND>(u, c, act[k], a.seed, a.offset, a.noise);
+            chunk_codes<GRID, ROUND>(v[k], code, se, rev, lanes, u);
+            const int j = threadIdx.x & (lanes - 1);
+            if (LAYOUT == kPlanes) {
+                if (act[k]) {
+                    uint2 sg, mg;
+                    sg.x = (code[0] >> 5) | ((code[1] >> 5) << 8) | ((code[2] >> 5) << 16) | ((code[3] >> 5) << 24);
+                    sg.y = (code[4] >> 5) | ((code[5] >> 5) << 8) | ((code[6] >> 5) << 16) | ((code[7] >> 5) << 24);
+                    mg.x = (code[0] & 31u) | ((code[1] & 31u) << 8) | ((code[2] & 31u) << 16) | ((code[3] & 31u) << 24);
+                    mg.y = (code[4] & 31u) | ((code[5] & 31u) << 8) | ((code[6] & 31u) << 16) | ((code[7] & 31u) << 24);
+                    st_stream8(a.p1 + c * kChunk, sg);
+                    st_stream8(a.p2 + c * kChunk, mg);
+                    if (j == 0) a.p0[c / lanes] = (uint8_t)se;
+                }
+            } else {
+                const uint32_t lo = code[0] | (code[1] << 6) | (code[2] << 12) | (code[3] << 18) |
+                                    (code[4] << 24) | (code[5] << 30);
+                const uint32_t hi = (code[5] >> 2) | (code[6] << 4) | (code[7] << 10);
+                const int lb = (k * kThreads + (int)threadIdx.x) / lanes;
+                uint8_t *s = stage + lb * a.rec;
+                if (j == 0) {
+                    if (a.hdr == 1) {
+                        s[0] = (uint8_t)se;
+                    } else {
+                        s[0] = (uint8_t)((se << 2) & 0xFF);
+                        s[1] = (uint8_t)(se >> 6);
+                    }
+                }
+                s += a.hdr + 6 * j;
+                s[0] = (uint8_t)lo; s[1] = (uint8_t)(lo >> 8); s[2] = (uint8_t)(lo >> 16); s[3] = (uint8_t)(lo >> 24);
+                s[4] = (uint8_t)hi; s[5] = (uint8_t)(hi >> 8);
+            }
+        }
+        if (LAYOUT == kBytes) {
+            __syncthreads();
+            const int64_t blk0 = base / lanes;
+            int64_t nb = (int64_t)(kU * kThreads) / lanes;
+            if (nb > total_blocks - blk0) nb = total_blocks - blk0;
+            const int len = (int)(nb * a.rec);
+            uint8_t *dst = a.p0 + blk0 * a.rec;                 // 16-byte aligned by construction
+            const int nvec = len >> 4;
+            for (int i = threadIdx.x; i < nvec; i += kThreads)
+                st_stream16(dst + 16 * i, reinterpret_cast<const uint4 *>(stage)[i]);
+            for (int i = (nvec << 4) + threadIdx.x; i < len; i += kThreads) dst[i] = stage[i];
+            __syncthreads();
+        }
+    }
+}
+
+// One lane per value of the zero-padded row (any alignment).
+template <typename Tin, int GRID, int ROUND, int LAYOUT>
+__global__ void __launch_bounds__(kThreads) pack_generic_kernel(const CodecArgs a)
+{
+    __shared__ __align__(16) uint8_t rev[GRID == AXS6_GRID_NF5 ? 1024 : 16];
+    if (GRID == AXS6_GRID_NF5) build_reverse_lut(rev);
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    const int B = a.g.block;
+    const int64_t padded = a.g.cpr * kChunk;
+    const int64_t nblk = padded / B;
+    const int64_t tiles_per_row = (padded + 31) / 32;
+    const int64_t tiles = a.g.rows * tiles_per_row;
+    const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
+    for (int64_t t = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); t < tiles; t += warps) {
+        const int64_t row = t / tiles_per_row;
+        const int64_t pc = (t - row * tiles_per_row) * 32 + lane;
+        const bool in_pad = pc < padded;
+        const bool has = pc < a.g.cols;
+        const uint32_t v = has ? ChunkIO<Tin>::load1(a.x, row * a.ld + pc, a.via_bf16 != 0u) : 0u;
+        const uint32_t ab = v & 0x7FFFFFFFu;
+        const uint32_t amax = group_max(ab, B);
+        const Axs6Scale s = axs6_scale_codes(amax);
+        const float n = axs6_normalise(__uint_as_float(ab), s);
+        const float u = element_uniform<ROUND>(row * padded + pc, in_pad, a.seed, a.offset, a.noise);
+        int m;
+        if (GRID == AXS6_GRID_NF5) {
+            const int idx = (ROUND == kNearest) ? axs6_nf5_index(n) : axs6_nf5_index_dithered(n, u);
+            m = rev[idx];
+        } else {
+            m = (ROUND == kNearest) ? axs6_uniform_mag(n) : axs6_uniform_mag_stochastic(n, u);
+        }
+        const uint32_t neg = (ab != 0u) ? (v >> 31) : 0u;
+        const uint32_t code = (neg << 5) | (uint32_t)m;
+        const uint32_t next = __shfl_down_sync(0xFFFFFFFFu, code, 1);
+        const int i = (int)(pc % B);
+        const int64_t blk = row * nblk + pc / B;
+        if (!in_pad) continue;
+        if (LAYOUT == kPlanes) {
+            a.p1[row * padded + pc] = (uint8_t)neg;
+            a.p2[row * padded + pc] = (uint8_t)m;
+            if (i == 0) a.p0[blk] = (uint8_t)s.se;
+        } else {
+            uint8_t *r = a.p0 + blk * a.rec;
+            if (i == 0) {
+                if (a.hdr == 1) {
+                    r[0] = (uint8_t)s.se;
+                } else {
+                    r[0] = (uint8_t)((s.se << 2) & 0xFF);
+                    r[1] = (uint8_t)(s.se >> 6);
+                }
+            }
+            const int q = i & 3;
+            if (q != 3) {
+                const uint32_t b = (q == 0) ? (code | (next << 6)) : (q == 1) ? ((code >> 2) | (next << 4))
+                                                                              : ((code >> 4) | (next << 2));
+                r[a.hdr + (i >> 2) * 3 + q] = (uint8_t)b;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------ unpack
+template <typename Tout, int GRID, int LAYOUT>
+__global__ void __launch_bounds__(kThreads) unpack_vec_kernel(const CodecArgs a)
+{
+    __shared__ float lev[32];
+    __shared__ __align__(16) uint8_t stage[LAYOUT == kBytes ? kStageBytes : 16];
+    build_levels<GRID>(lev);
+    __syncthreads();
+
+    const int lanes = a.g.block / kChunk;
+    const int64_t total_blocks = a.g.total_chunks / lanes;
+    const int64_t step = (int64_t)gridDim.x * kThreads * kU;
+    for (int64_t base = (int64_t)blockIdx.x * kThreads * kU; base < a.g.total_chunks; base += step) {
+        if (LAYOUT == kBytes) {
+            const int64_t blk0 = base / lanes;
+            int64_t nb = (int64_t)(kU * kThreads) / lanes;
+            if (nb > total_blocks - blk0) nb = total_blocks - blk0;
+            const int len = (int)(nb * a.rec);
+            const uint8_t *src = a.p0 + blk0 * a.rec;
+            const int nvec = len >> 4;
+            for (int i = threadIdx.x; i < nvec; i += kThreads)
+                reinterpret_cast<uint4 *>(stage)[i] = ld_stream16(src + 16 * i);
+            for (int i = (nvec << 4) + threadIdx.x; i < len; i += kThreads) stage[i] = src[i];
+            __syncthreads();
+        }
+#pragma unroll
+        for (int k = 0; k < kU; ++k) {
+            const int64_t c = base + (int64_t)k * kThreads + threadIdx.x;
+            bool act = c < a.g.total_chunks;
+            int64_t yo = c * kChunk;
+            if (!a.g.flat) {
+                const int64_t row = c / a.g.cpr;
+                const int64_t col0 = (c - row * a.g.cpr) * kChunk;
+                act = act && col0 < a.g.cols;
+                yo = row * a.ld + col0;
+            }
+            if (!act) continue;
+            uint32_t se, neg[8], mag[8];
+            if (LAYOUT == kPlanes) {
+                se = a.p0[c / lanes];
+                const uint2 sg = ld_stream8(a.p1 + c * kChunk), mg = ld_stream8(a.p2 + c * kChunk);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    neg[i] = (sg.x >> (8 * i)) & 1u; neg[4 + i] = (sg.y >> (8 * i)) & 1u;
+                    mag[i] = (mg.x >> (8 * i)) & 31u; mag[4 + i] = (mg.y >> (8 * i)) & 31u;
+                }
+            } else {
+                const int j = threadIdx.x & (lanes - 1);
+                const int lb = (k * kThreads + (int)threadIdx.x) / lanes;
+                const uint8_t *s = stage + lb * a.rec;
+                se = (a.hdr == 1) ? (uint32_t)s[0] : (((uint32_t)s[0] | ((uint32_t)s[1] << 8)) >> 2) & 0xFFu;
+                s += a.hdr + 6 * j;
+                const uint32_t lo = (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
+                const uint32_t hi = (uint32_t)s[4] | ((uint32_t)s[5] << 8);
+                uint32_t code[8];
+                code[0] = lo & 63u; code[1] = (lo >> 6) & 63u; code[2] = (lo >> 12) & 63u; code[3] = (lo >> 18) & 63u;
+                code[4] = (lo >> 24) & 63u; code[5] = ((lo >> 30) | (hi << 2)) & 63u;
+                code[6] = (hi >> 4) & 63u; code[7] = (hi >> 10) & 63u;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { neg[i] = code[i] >> 5; mag[i] = code[i] & 31u; }
+            }
+            const float scale = axs6_scale_decode(se);
+            float y[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[i] = axs6_decode_value(neg[i], lev[mag[i]], scale);
+            ChunkIO<Tout>::store(a.y, yo, y);
+        }
+        if (LAYOUT == kBytes) __syncthreads();
+    }
+}
+
+template <typename Tout, int GRID, int LAYOUT>
+__global__ void __launch_bounds__(kThreads) unpack_generic_kernel(const CodecArgs a)
+{
+    __shared__ float lev[32];
+    build_levels<GRID>(lev);
+    __syncthreads();
+
+    const int B = a.g.block;
+    const int64_t padded = a.g.cpr * kChunk;
+    const int64_t nblk = padded / B;
+    const int64_t total = a.g.rows * a.g.cols;
+    const int64_t nthreads = (int64_t)gridDim.x * kThreads;
+    for (int64_t e = (int64_t)blockIdx.x * kThreads + threadIdx.x; e < total; e += nthreads) {
+        const int64_t row = e / a.g.cols;
+        const int64_t pc = e - row * a.g.cols;
+        const int i = (int)(pc % B);
+        const int64_t blk = row * nblk + pc / B;
+        uint32_t se, neg, mag;
+        if (LAYOUT == kPlanes) {
+            se = a.p0[blk];
+            neg = a.p1[row * padded + pc] & 1u;
+            mag = a.p2[row * padded + pc] & 31u;
+        } else {
+            const uint8_t *r = a.p0 + blk * a.rec;
+            se = (a.hdr == 1) ? (uint32_t)r[0] : (((uint32_t)r[0] | ((uint32_t)r[1] << 8)) >> 2) & 0xFFu;
+            const int bit = 6 * i, k = bit >> 3, sh = bit & 7;
+            uint32_t w = r[a.hdr + k];
+            if (sh > 2) w |= (uint32_t)r[a.hdr + k + 1] << 8;
+            const uint32_t code = (w >> sh) & 63u;
+            neg = code >> 5;
+            mag = code & 31u;
+        }
+        ChunkIO<Tout>::store1(a.y, row * a.ld + pc, axs6_decode_value(neg, lev[mag], axs6_scale_decode(se)));
+    }
+}
+
+// ------------------------------------------------------------------------------------------ host
+template <typename K>
+static int launch_codec(K kernel, const CodecArgs &a, int64_t items_per_cta, int64_t items, cudaStream_t stream)
+{
+    const DeviceInfo &d = device_info();
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm < 1)
+        return AXS6_ERR_LAUNCH;
+    int64_t ctas = (items + items_per_cta - 1) / items_per_cta;
+    const int64_t resident = (int64_t)d.sms * per_sm;
+    if (ctas > resident) ctas = resident;
+    if (ctas < 1) ctas = 1;
+    kernel<<<(unsigned)ctas, kThreads, 0, stream>>>(a);
+    count_launch();
+    return check_launch();
+}
+
+template <typename Tin, int GRID, int ROUND>
+static int launch_pack(const CodecArgs &a, bool planes, bool vec, cudaStream_t st)
+{
+    const int64_t tiles = a.g.rows * ((a.g.cpr * kChunk + 31) / 32);
+    if (vec) {
+        if (planes) return launch_codec(pack_vec_kernel<Tin, GRID, ROUND, kPlanes>, a, (int64_t)kThreads * kU, a.g.total_chunks, st);
+        return launch_codec(pack_vec_kernel<Tin, GRID, ROUND, kBytes>, a, (int64_t)kThreads * kU, a.g.total_chunks, st);
+    }
+    if (planes) return launch_codec(pack_generic_kernel<Tin, GRID, ROUND, kPlanes>, a, kThreads / 32, tiles, st);
+    return launch_codec(pack_generic_kernel<Tin, GRID, ROUND, kBytes>, a, kThreads / 32, tiles, st);
+}
+
+template <typename Tin>
+static int dispatch_pack(const CodecArgs &a, int grid, int round, bool planes, bool vec, cudaStream_t st)
+{
+#define AXS6_CASE(G, R) \
+    if (grid == G && round == R) return launch_pack<Tin, G, R>(a, planes, vec, st);
+    AXS6_CASE(AXS6_GRID_NF5, kNearest)
+    AXS6_CASE(AXS6_GRID_NF5, kPhilox)
+    AXS6_CASE(AXS6_GRID_NF5, kNoise)
+    AXS6_CASE(AXS6_GRID_UNIFORM, kNearest)
+    AXS6_CASE(AXS6_GRID_UNIFORM, kPhilox)
+    AXS6_CASE(AXS6_GRID_UNIFORM, kNoise)
+#undef AXS6_CASE
+    return AXS6_ERR_ARG;
+}
+
+template <typename Tout, int GRID>
+static int launch_unpack(const CodecArgs &a, bool planes, bool vec, cudaStream_t st)
+{
+    if (vec) {
+        if (planes) return launch_codec(unpack_vec_kernel<Tout, GRID, kPlanes>, a, (int64_t)kThreads * kU, a.g.total_chunks, st);
+        return launch_codec(unpack_vec_kernel<Tout, GRID, kBytes>, a, (int64_t)kThreads * kU, a.g.total_chunks, st);
+    }
+    const int64_t total = a.g.rows * a.g.cols;
+    if (planes) return launch_codec(unpack_generic_kernel<Tout, GRID, kPlanes>, a, kThreads, total, st);
+    return launch_codec(unpack_generic_kernel<Tout, GRID, kBytes>, a, kThreads, total, st);
+}
+
+static bool layout_ok(int layout) { return layout == AXS6_LAYOUT_PLANES || layout == AXS6_LAYOUT_WIRE || layout == AXS6_LAYOUT_SPEC; }
+
+}  // namespace axs6
+
+AXS6_API int64_t axs6_record_bytes(int layout, int block)
+{
+    if (!axs6::valid_block(block)) return 0;
+    if (layout == AXS6_LAYOUT_WIRE) return 1 + block * 3 / 4;
+    if (layout == AXS6_LAYOUT_SPEC) return 2 + block * 3 / 4;
+    return 0;
+}
+
+AXS6_API int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, int64_t ldx, int block, int grid,
+                         int rounding, uint32_t flags, uint64_t seed, uint64_t offset, const float *noise,
+                         int layout, void *out0, void *out1, void *out2, axs6_stream_t stream)
+{
+    using namespace axs6;
+    if (!valid_dtype(in_dtype) || !valid_block(block) || !layout_ok(layout)) return AXS6_ERR_ARG;
+    if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
+    if (rounding != AXS6_ROUND_NEAREST && rounding != AXS6_ROUND_STOCHASTIC) return AXS6_ERR_ARG;
+    if (rows < 0 || cols < 0 || ldx < cols) return AXS6_ERR_ARG;
+    if (flags & ~AXS6_FLAG_INPUT_VIA_BF16) return AXS6_ERR_ARG;
+    if (rows == 0 || cols == 0) return AXS6_OK;
+    const bool planes = layout == AXS6_LAYOUT_PLANES;
+    if (!x || !out0 || (planes && (!out1 || !out2))) return AXS6_ERR_ARG;
+    const DeviceInfo &d = device_info();
+    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+
+    const int round = rounding == AXS6_ROUND_NEAREST ? kNearest : (noise ? kNoise : kPhilox);
+    CodecArgs a;
+    a.x = x; a.y = nullptr; a.ld = ldx;
+    a.g = make_geom(rows, cols, block);
+    a.g.flat = (cols % block == 0 && ldx == cols) ? 1 : 0;
+    a.via_bf16 = (flags & AXS6_FLAG_INPUT_VIA_BF16) ? 1u : 0u;
+    a.seed = seed; a.offset = offset; a.noise = noise;
+    a.p0 = static_cast<uint8_t *>(out0); a.p1 = static_cast<uint8_t *>(out1); a.p2 = static_cast<uint8_t *>(out2);
+    a.rec = (int)axs6_record_bytes(layout, block);
+    a.hdr = layout == AXS6_LAYOUT_SPEC ? 2 : 1;
+    const bool vec = aligned16(x) && (cols % kChunk == 0) && (ldx % kChunk == 0) && aligned16(out0) &&
+                     (!planes || (aligned16(out1) && aligned16(out2))) && (round != kNoise || aligned16(noise));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return in_dtype == AXS6_F32 ? dispatch_pack<float>(a, grid, round, planes, vec, st)
+                                : dispatch_pack<__nv_bfloat16>(a, grid, round, planes, vec, st);
+}
+
+AXS6_API int axs6_unpack(int layout, const void *in0, const void *in1, const void *in2, void *y, int out_dtype,
+                           int64_t rows, int64_t cols, int64_t ldy, int block, int grid, axs6_stream_t stream)
+{
+    using namespace axs6;
+    if (!valid_dtype(out_dtype) || !valid_block(block) || !layout_ok(layout)) return AXS6_ERR_ARG;
+    if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
+    if (rows < 0 || cols < 0 || ldy < cols) return AXS6_ERR_ARG;
+    if (rows == 0 || cols == 0) return AXS6_OK;
+    const bool planes = layout == AXS6_LAYOUT_PLANES;
+    if (!y || !in0 || (planes && (!in1 || !in2))) return AXS6_ERR_ARG;
+    const DeviceInfo &d = device_info();
+    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+
+    CodecArgs a;
+    a.x = nullptr; a.y = y; a.ld = ldy;
+    a.g = make_geom(rows, cols, block);
+    a.g.flat = (cols % block == 0 && ldy == cols) ? 1 : 0;
+    a.via_bf16 = 0; a.seed = 0; a.offset = 0; a.noise = nullptr;
+    a.p0 = const_cast<uint8_t *>(static_cast<const uint8_t *>(in0));
+    a.p1 = const_cast<uint8_t *>(static_cast<const uint8_t *>(in1));
+    a.p2 = const_cast<uint8_t *>(static_cast<const uint8_t *>(in2));
+    a.rec = (int)axs6_record_bytes(layout, block);
+    a.hdr = layout == AXS6_LAYOUT_SPEC ? 2 : 1;
+    const bool vec = aligned16(y) && (cols % kChunk == 0) && (ldy % kChunk == 0) && aligned16(in0) &&
+                     (!planes || (aligned16(in1) && aligned16(in2)));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define AXS6_CASE(T, G) return launch_unpack<T, G>(a, planes, vec, st)
+    if (out_dtype == AXS6_F32) { if (grid == AXS6_GRID_NF5) AXS6_CASE(float, AXS6_GRID_NF5); AXS6_CASE(float, AXS6_GRID_UNIFORM); }
+    if (grid == AXS6_GRID_NF5) AXS6_CASE(__nv_bfloat16, AXS6_GRID_NF5);
+    AXS6_CASE(__nv_bfloat16, AXS6_GRID_UNIFORM);
+#undef AXS6_CASE
+}

@@ -1,0 +1,39 @@
+// Host-side plumbing shared by the translation units: status codes, device checks,
+// launch bookkeeping, and the device tables.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/axs6_b200.h"
+#include "axs6_math.cuh"
+#include "axs6_tables.cuh"
+
+#define AXS6_API extern "C" __attribute__((visibility("default")))
+
+namespace axs6 {
+
+// Per-device facts, looked up once per device.
+struct DeviceInfo {
+    int valid;     // 0 on a CUDA error while looking the device up
+    int ok;        // compute capability 10.x
+    int sms;       // multiprocessor count
+};
+
+const DeviceInfo &device_info();      // for the current device
+void count_launch(int n = 1);         // bookkeeping behind axs6_query(3)
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline int check_launch()
+{
+    return cudaGetLastError() == cudaSuccess ? AXS6_OK : AXS6_ERR_LAUNCH;
+}
+
+inline bool valid_block(int b) { return b == 8 || b == 16 || b == 32; }
+inline bool valid_dtype(int d) { return d == AXS6_F32 || d == AXS6_BF16; }
+
+// Codebook levels (fp32 bits) and LUT-index -> code table, baked into each module image.
+static __device__ __align__(16) const uint32_t g_codebook_bits[32] = AXS6_CODEBOOK_BITS_INIT;
+static __device__ __align__(16) const uint8_t g_reverse[1024] = AXS6_REVERSE_INIT;
+
+}  // namespace axs6

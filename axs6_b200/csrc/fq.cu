@@ -1,0 +1,234 @@
+// Fake-quantise kernels (NF5 and uniform grid) and their C entry points.
+//
+// One pass over HBM: every value is read once and written once.  Roofline: HBM bandwidth,
+// algorithmic bytes per value = sizeof(in) + sizeof(out).
+//   fq_vec_kernel      16-byte aligned tensors whose extents are multiples of 8 values: one
+//                      thread owns 8 consecutive values (128-bit streaming loads/stores), the
+//                      block amax is a 0..2-step xor shuffle, the NF5 reconstruction is one
+//                      gather from a 4 KB shared-memory LUT.  Persistent grid sized from the
+//                      occupancy of the instantiation, U independent chunks per thread in flight.
+//   fq_generic_kernel  any pointer alignment / extent: one lane per value, coalesced scalar
+//                      accesses, amax over B lanes.
+#include "quant_device.cuh"
+
+namespace axs6 {
+
+struct FqArgs {
+    const void *x;
+    void *y;
+    int64_t ldx, ldy;
+    ChunkGeom g;
+    uint32_t via_bf16;
+    uint64_t seed, offset;
+    const float *noise;
+};
+
+template <int GRID, int ROUND>
+__device__ __forceinline__ void fq_chunk(const uint32_t (&v)[8], float (&y)[8], const float *tab,
+                                         int lanes, const float (&u)[8])
+{
+    const uint32_t amax = group_max(chunk_amax_bits(v), lanes);
+    if (GRID == AXS6_GRID_NF5) {
+        const Axs6Scale s = axs6_scale_fq(amax);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float n = axs6_normalise(__uint_as_float(v[i] & 0x7FFFFFFFu), s);
+            const int idx = (ROUND == kNearest) ? axs6_nf5_index(n) : axs6_nf5_index_dithered(n, u[i]);
+            y[i] = axs6_fq_value(v[i], tab[idx], s.scale);
+        }
+    } else {
+        const Axs6Scale s = axs6_scale_codes(amax);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t ab = v[i] & 0x7FFFFFFFu;
+            const float n = axs6_normalise(__uint_as_float(ab), s);
+            const int m = (ROUND == kNearest) ? axs6_uniform_mag(n) : axs6_uniform_mag_stochastic(n, u[i]);
+            y[i] = axs6_decode_value((ab != 0u) ? (v[i] >> 31) : 0u, tab[m], s.scale);
+        }
+    }
+}
+
+template <typename Tin, typename Tout, int GRID, int ROUND, int U>
+__global__ void __launch_bounds__(kThreads) fq_vec_kernel(const FqArgs a)
+{
+    __shared__ float tab[GRID == AXS6_GRID_NF5 ? 1024 : 32];
+    if (GRID == AXS6_GRID_NF5) build_value_lut(tab); else build_levels<GRID>(tab);
+    __syncthreads();
+
+    const int lanes = a.g.block / kChunk;
+    const int64_t step = (int64_t)gridDim.x * kThreads * U;
+    for (int64_t base = (int64_t)blockIdx.x * kThreads * U; base < a.g.total_chunks; base += step) {
+        uint32_t v[U][8];
+        int64_t yo[U], cidx[U];
+        bool act[U];
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            const int64_t c = base + (int64_t)k * kThreads + threadIdx.x;
+            cidx[k] = c;
+            act[k] = c < a.g.total_chunks;
+            int64_t xo = c * kChunk;
+            yo[k] = xo;
+            if (!a.g.flat) {
+                const int64_t row = c / a.g.cpr;
+                const int64_t col0 = (c - row * a.g.cpr) * kChunk;
+                act[k] = act[k] && col0 < a.g.cols;
+                xo = row * a.ldx + col0;
+                yo[k] = row * a.ldy + col0;
+            }
+            if (act[k]) {
+                ChunkIO<Tin>::load(a.x, xo, v[k], a.via_bf16 != 0u);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[k][i] = 0u;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            float u[8], y[8];
+            chunk_uniforms<ROUND>(u, cidx[k], act[k], a.seed, a.offset, a.noise);
+            fq_chunk<GRID, ROUND>(v[k], y, tab, lanes, u);
+            if (act[k]) ChunkIO<Tout>::store(a.y, yo[k], y);
+        }
+    }
+}
+
+// One lane per value of the zero-padded row; a warp covers 32 consecutive padded columns.
+template <typename Tin, typename Tout, int GRID, int ROUND>
+__global__ void __launch_bounds__(kThreads) fq_generic_kernel(const FqArgs a)
+{
+    __shared__ float tab[GRID == AXS6_GRID_NF5 ? 1024 : 32];
+    if (GRID == AXS6_GRID_NF5) build_value_lut(tab); else build_levels<GRID>(tab);
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    const int64_t padded = a.g.cpr * kChunk;
+    const int64_t tiles_per_row = (padded + 31) / 32;
+    const int64_t tiles = a.g.rows * tiles_per_row;
+    const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
+    for (int64_t t = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); t < tiles; t += warps) {
+        const int64_t row = t / tiles_per_row;
+        const int64_t pc = (t - row * tiles_per_row) * 32 + lane;
+        const bool act = pc < a.g.cols;
+        const uint32_t v = act ? ChunkIO<Tin>::load1(a.x, row * a.ldx + pc, a.via_bf16 != 0u) : 0u;
+        const uint32_t ab = v & 0x7FFFFFFFu;
+        const uint32_t amax = group_max(ab, a.g.block);
+        const float u = element_uniform<ROUND>(row * padded + pc, act, a.seed, a.offset, a.noise);
+        float y;
+        if (GRID == AXS6_GRID_NF5) {
+            const Axs6Scale s = axs6_scale_fq(amax);
+            const float n = axs6_normalise(__uint_as_float(ab), s);
+            const int idx = (ROUND == kNearest) ? axs6_nf5_index(n) : axs6_nf5_index_dithered(n, u);
+            y = axs6_fq_value(v, tab[idx], s.scale);
+        } else {
+            const Axs6Scale s = axs6_scale_codes(amax);
+            const float n = axs6_normalise(__uint_as_float(ab), s);
+            const int m = (ROUND == kNearest) ? axs6_uniform_mag(n) : axs6_uniform_mag_stochastic(n, u);
+            y = axs6_decode_value((ab != 0u) ? (v >> 31) : 0u, tab[m], s.scale);
+        }
+        if (act) ChunkIO<Tout>::store1(a.y, row * a.ldy + pc, y);
+    }
+}
+
+template <typename K>
+static int launch_persistent(K kernel, const FqArgs &a, int64_t work_items_per_cta, int64_t work_items,
+                             cudaStream_t stream)
+{
+    const DeviceInfo &d = device_info();
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm < 1)
+        return AXS6_ERR_LAUNCH;
+    int64_t ctas = (work_items + work_items_per_cta - 1) / work_items_per_cta;
+    const int64_t resident = (int64_t)d.sms * per_sm;
+    if (ctas > resident) ctas = resident;
+    if (ctas < 1) ctas = 1;
+    kernel<<<(unsigned)ctas, kThreads, 0, stream>>>(a);
+    count_launch();
+    return check_launch();
+}
+
+template <typename Tin, typename Tout, int GRID, int ROUND>
+static int launch_fq(const FqArgs &a, bool vec, cudaStream_t stream)
+{
+    constexpr int U = 2;
+    if (vec)
+        return launch_persistent(fq_vec_kernel<Tin, Tout, GRID, ROUND, U>, a, (int64_t)kThreads * U,
+                                 a.g.total_chunks, stream);
+    const int64_t tiles = a.g.rows * ((a.g.cpr * kChunk + 31) / 32);
+    return launch_persistent(fq_generic_kernel<Tin, Tout, GRID, ROUND>, a, kThreads / 32, tiles, stream);
+}
+
+template <typename Tin, typename Tout>
+static int dispatch_fq(const FqArgs &a, int grid, int round, bool vec, cudaStream_t stream)
+{
+#define AXS6_CASE(G, R) \
+    if (grid == G && round == R) return launch_fq<Tin, Tout, G, R>(a, vec, stream);
+    AXS6_CASE(AXS6_GRID_NF5, kNearest)
+    AXS6_CASE(AXS6_GRID_NF5, kPhilox)
+    AXS6_CASE(AXS6_GRID_NF5, kNoise)
+    AXS6_CASE(AXS6_GRID_UNIFORM, kNearest)
+    AXS6_CASE(AXS6_GRID_UNIFORM, kPhilox)
+    AXS6_CASE(AXS6_GRID_UNIFORM, kNoise)
+#undef AXS6_CASE
+    return AXS6_ERR_ARG;
+}
+
+ChunkGeom make_geom(int64_t rows, int64_t cols, int block)
+{
+    ChunkGeom g;
+    g.rows = rows;
+    g.cols = cols;
+    g.block = block;
+    const int64_t nblk = (cols + block - 1) / block;
+    g.cpr = nblk * block / kChunk;
+    g.total_chunks = rows * g.cpr;
+    g.flat = 0;
+    return g;
+}
+
+static int fq_entry(const void *x, void *y, int in_dtype, int out_dtype, int64_t rows, int64_t cols,
+                    int64_t ldx, int64_t ldy, int block, int grid, int round, uint32_t flags,
+                    uint64_t seed, uint64_t offset, const float *noise, cudaStream_t stream)
+{
+    if (!valid_dtype(in_dtype) || !valid_dtype(out_dtype) || !valid_block(block)) return AXS6_ERR_ARG;
+    if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
+    if (rows < 0 || cols < 0 || ldx < cols || ldy < cols) return AXS6_ERR_ARG;
+    if (flags & ~AXS6_FLAG_INPUT_VIA_BF16) return AXS6_ERR_ARG;
+    if (rows == 0 || cols == 0) return AXS6_OK;
+    if (!x || !y) return AXS6_ERR_ARG;
+    if (round == kNoise && !noise) return AXS6_ERR_ARG;
+    const DeviceInfo &d = device_info();
+    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+
+    FqArgs a;
+    a.x = x; a.y = y; a.ldx = ldx; a.ldy = ldy;
+    a.g = make_geom(rows, cols, block);
+    a.g.flat = (cols % block == 0 && ldx == cols && ldy == cols) ? 1 : 0;
+    a.via_bf16 = (flags & AXS6_FLAG_INPUT_VIA_BF16) ? 1u : 0u;
+    a.seed = seed; a.offset = offset; a.noise = noise;
+    const bool vec = aligned16(x) && aligned16(y) && (cols % kChunk == 0) && (ldx % kChunk == 0) &&
+                     (ldy % kChunk == 0) && (round != kNoise || aligned16(noise));
+    if (in_dtype == AXS6_F32 && out_dtype == AXS6_F32) return dispatch_fq<float, float>(a, grid, round, vec, stream);
+    if (in_dtype == AXS6_F32 && out_dtype == AXS6_BF16) return dispatch_fq<float, __nv_bfloat16>(a, grid, round, vec, stream);
+    if (in_dtype == AXS6_BF16 && out_dtype == AXS6_F32) return dispatch_fq<__nv_bfloat16, float>(a, grid, round, vec, stream);
+    return dispatch_fq<__nv_bfloat16, __nv_bfloat16>(a, grid, round, vec, stream);
+}
+
+}  // namespace axs6
+
+AXS6_API int axs6_fq(const void *x, void *y, int in_dtype, int out_dtype, int64_t rows, int64_t cols,
+                       int64_t ldx, int64_t ldy, int block, int grid, int rounding, uint32_t flags,
+                       uint64_t seed, uint64_t offset, axs6_stream_t stream)
+{
+    if (rounding != AXS6_ROUND_NEAREST && rounding != AXS6_ROUND_STOCHASTIC) return AXS6_ERR_ARG;
+    return axs6::fq_entry(x, y, in_dtype, out_dtype, rows, cols, ldx, ldy, block, grid,
+                          rounding == AXS6_ROUND_NEAREST ? axs6::kNearest : axs6::kPhilox, flags, seed, offset,
+                          nullptr, static_cast<cudaStream_t>(stream));
+}
+
+AXS6_API int axs6_fq_with_noise(const void *x, void *y, int in_dtype, int out_dtype, int64_t rows,
+                                  int64_t cols, int64_t ldx, int64_t ldy, int block, int grid, uint32_t flags,
+                                  const float *noise, axs6_stream_t stream)
+{
+    return axs6::fq_entry(x, y, in_dtype, out_dtype, rows, cols, ldx, ldy, block, grid, axs6::kNoise, flags,
+                          0, 0, noise, static_cast<cudaStream_t>(stream));
+}

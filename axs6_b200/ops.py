@@ -1,0 +1,184 @@
+"""Tensor-level wrappers over the C ABI: argument checking, views, output allocation.
+
+Everything here is host plumbing; all arithmetic happens in the CUDA library.  Inputs must be
+CUDA tensors (fp32 or bf16); a CPU tensor raises ``RuntimeError`` -- there is no CPU path.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import (BF16, F32, FLAG_INPUT_VIA_BF16, GRID_NF5, GRID_UNIFORM, LAYOUT_PLANES, LAYOUT_SPEC,
+                   LAYOUT_WIRE, ROUND_NEAREST, ROUND_STOCHASTIC)
+
+VALID_BLOCK_SIZES = (8, 16, 32)
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+# Stochastic rounding: Philox stream keyed by torch's seed; the counter advances by the
+# number of draws of every call, so no two calls of a process reuse a draw and no device
+# sync is needed (the reference draws a seed with .item(), which synchronises).
+_philox_offset = 0
+
+
+def next_philox(n_draws: int) -> tuple[int, int]:
+    global _philox_offset
+    off = _philox_offset
+    _philox_offset += (n_draws + 3) // 4
+    return torch.initial_seed() & 0xFFFFFFFFFFFFFFFF, off
+
+
+def reset_philox(offset: int = 0) -> None:
+    global _philox_offset
+    _philox_offset = offset
+
+
+def _rounding(rounding: str) -> int:
+    if rounding == "nearest":
+        return ROUND_NEAREST
+    if rounding == "stochastic":
+        return ROUND_STOCHASTIC
+    raise ValueError(f"Unknown rounding mode: {rounding}")
+
+
+def _check_input(t: torch.Tensor, who: str) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{who} expects a torch.Tensor")
+    if not t.is_cuda:
+        raise RuntimeError(f"{who} requires a CUDA tensor")
+    if t.dim() == 0:
+        raise ValueError(f"{who} needs at least one dimension")
+
+
+def _as_rows(t: torch.Tensor) -> tuple[torch.Tensor, int, int, int]:
+    """-> (2-D view or copy with unit inner stride, rows, cols, leading dimension)."""
+    if t.dtype not in _DT:
+        t = t.float()
+    t2 = t.reshape(-1, t.shape[-1])
+    rows, cols = t2.shape
+    if cols > 0 and rows > 0 and (t2.stride(1) != 1 or (rows > 1 and t2.stride(0) < cols)):
+        t2 = t2.contiguous()
+    ld = t2.stride(0) if rows > 1 else cols
+    return t2, rows, cols, max(ld, cols)
+
+
+def _stream(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+class _on:
+    """Make `dev` current for the duration of a call (the library works on the current device)."""
+
+    def __init__(self, dev: torch.device):
+        self.dev = dev
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if self.dev.index is not None and self.dev.index != cur:
+            self.prev = cur
+            torch.cuda.set_device(self.dev)
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+
+
+def fake_quantize(x: torch.Tensor, block_size: int = 32, grid: int = GRID_NF5, rounding: str = "nearest",
+                  out_dtype: torch.dtype | None = None, via_bf16: bool = False,
+                  noise: torch.Tensor | None = None, who: str = "fake_quantize") -> torch.Tensor:
+    """One-pass fake-quantise of the last dimension in blocks; returns a new tensor."""
+    _check_input(x, who)
+    assert block_size in VALID_BLOCK_SIZES, f"block_size must be one of {VALID_BLOCK_SIZES}"
+    rnd = _rounding(rounding)
+    x2, rows, cols, ldx = _as_rows(x)
+    odt = out_dtype if out_dtype is not None else (x.dtype if x.dtype in _DT else torch.float32)
+    y = torch.empty((rows, cols), dtype=odt, device=x.device)
+    lib = _lib.load()
+    flags = FLAG_INPUT_VIA_BF16 if (via_bf16 and x2.dtype == torch.float32) else 0
+    with _on(x.device):
+        if noise is not None:
+            nz = noise.to(device=x.device, dtype=torch.float32).contiguous()
+            st = lib.axs6_fq_with_noise(x2.data_ptr(), y.data_ptr(), _DT[x2.dtype], _DT[odt], rows, cols, ldx, cols,
+                                        block_size, grid, flags, nz.data_ptr(), _stream(x.device))
+            _lib.check("axs6_fq_with_noise", st)
+        else:
+            seed, off = (0, 0)
+            if rnd == ROUND_STOCHASTIC:
+                seed, off = next_philox(rows * (-(-cols // block_size)) * block_size)
+            st = lib.axs6_fq(x2.data_ptr(), y.data_ptr(), _DT[x2.dtype], _DT[odt], rows, cols, ldx, cols,
+                             block_size, grid, rnd, flags, seed, off, _stream(x.device))
+            _lib.check("axs6_fq", st)
+    return y.reshape(x.shape)
+
+
+def record_bytes(layout: int, block_size: int) -> int:
+    return int(_lib.load().axs6_record_bytes(layout, block_size))
+
+
+def pack(x: torch.Tensor, block_size: int = 32, grid: int = GRID_NF5, rounding: str = "nearest",
+         layout: int = LAYOUT_PLANES, via_bf16: bool = False, noise: torch.Tensor | None = None,
+         who: str = "pack"):
+    """Quantise to codes.  PLANES -> (exponents u8 (rows, nblk), signs bool (rows, nblk, B),
+    magnitudes u8 (rows, nblk, B)); WIRE / SPEC -> flat uint8 tensor of block records."""
+    _check_input(x, who)
+    assert block_size in VALID_BLOCK_SIZES, f"block_size must be one of {VALID_BLOCK_SIZES}"
+    rnd = _rounding(rounding)
+    x2, rows, cols, ldx = _as_rows(x)
+    nblk = -(-cols // block_size)
+    dev = x.device
+    flags = FLAG_INPUT_VIA_BF16 if (via_bf16 and x2.dtype == torch.float32) else 0
+    if layout == LAYOUT_PLANES:
+        se = torch.empty((rows, nblk), dtype=torch.uint8, device=dev)
+        sg = torch.empty((rows, nblk, block_size), dtype=torch.bool, device=dev)
+        mg = torch.empty((rows, nblk, block_size), dtype=torch.uint8, device=dev)
+        outs = (se, sg, mg)
+        ptrs = (se.data_ptr(), sg.data_ptr(), mg.data_ptr())
+    else:
+        buf = torch.empty(rows * nblk * record_bytes(layout, block_size), dtype=torch.uint8, device=dev)
+        outs = buf
+        ptrs = (buf.data_ptr(), None, None)
+    nz = None
+    seed, off = 0, 0
+    if rnd == ROUND_STOCHASTIC:
+        if noise is not None:
+            nz = noise.to(device=dev, dtype=torch.float32).contiguous()
+        else:
+            seed, off = next_philox(rows * nblk * block_size)
+    with _on(dev):
+        st = _lib.load().axs6_pack(x2.data_ptr(), _DT[x2.dtype], rows, cols, ldx, block_size, grid, rnd, flags,
+                                   seed, off, nz.data_ptr() if nz is not None else None, layout,
+                                   ptrs[0], ptrs[1], ptrs[2], _stream(dev))
+    _lib.check("axs6_pack", st)
+    return outs
+
+
+def unpack(layout: int, parts, rows: int, cols: int, block_size: int = 32, grid: int = GRID_NF5,
+           out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Codes back to values, (rows, cols)."""
+    assert block_size in VALID_BLOCK_SIZES, f"block_size must be one of {VALID_BLOCK_SIZES}"
+    if layout == LAYOUT_PLANES:
+        se, sg, mg = parts
+        for t in (se, sg, mg):
+            _check_input(t, "unpack")
+        se, sg, mg = se.contiguous(), sg.contiguous(), mg.contiguous()
+        dev = mg.device
+        ptrs = (se.data_ptr(), sg.data_ptr(), mg.data_ptr())
+        keep = (se, sg, mg)
+    else:
+        buf = parts
+        _check_input(buf, "unpack")
+        buf = buf.contiguous()
+        nblk = -(-cols // block_size)
+        need = rows * nblk * record_bytes(layout, block_size)
+        if buf.numel() * buf.element_size() < need:
+            raise ValueError(f"buffer holds {buf.numel() * buf.element_size()} bytes, {need} needed")
+        dev = buf.device
+        ptrs = (buf.data_ptr(), None, None)
+        keep = (buf,)
+    y = torch.empty((rows, cols), dtype=out_dtype, device=dev)
+    with _on(dev):
+        st = _lib.load().axs6_unpack(layout, ptrs[0], ptrs[1], ptrs[2], y.data_ptr(), _DT[out_dtype], rows, cols,
+                                     cols, block_size, grid, _stream(dev))
+    _lib.check("axs6_unpack", st)
+    del keep
+    return y

@@ -1,0 +1,108 @@
+/*
+ * axs6_b200 -- C ABI of the B200 (sm_100a) implementation of the AXS-6 hot path.
+ *
+ * Every entry point takes plain device pointers and sizes, validates its arguments on
+ * the host before any launch, enqueues its work on the given CUDA stream and returns
+ * without synchronising.  Return value: AXS6_OK (0) or a negative AXS6_ERR_* code;
+ * axs6_strerror() gives the text.  The library never allocates device memory: every
+ * buffer, workspace included, belongs to the caller.  There is no CPU path: on a
+ * device that is not compute capability 10.x the calls return AXS6_ERR_DEVICE.
+ *
+ * Tensors are row-major 2-D views (rows, cols) with a leading dimension in ELEMENTS.
+ * The last dimension is cut into blocks of `block` (8, 16 or 32) values that share one
+ * 8-bit exponent; a ragged last block behaves as if zero-padded, exactly like the
+ * reference's F.pad.  "Reference" citations below are paths in the bwiemz/axs-6 tree.
+ */
+#ifndef AXS6_B200_H
+#define AXS6_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *axs6_stream_t; /* a cudaStream_t */
+
+enum { AXS6_F32 = 0, AXS6_BF16 = 1 };
+enum { AXS6_GRID_UNIFORM = 0, /* V1: 31 equal steps          (axs/core.py)                    */
+       AXS6_GRID_NF5 = 1 };   /* 32 half-normal levels via the 1024-entry LUT (axs/unified)   */
+enum { AXS6_ROUND_NEAREST = 0, AXS6_ROUND_STOCHASTIC = 1 };
+enum { AXS6_LAYOUT_PLANES = 0, /* AXSTensor planes: u8 exponent (rows,nblk), u8 sign and u8
+                                  magnitude (rows,nblk,block)      (axs/core.py:160-182)      */
+       AXS6_LAYOUT_WIRE = 1,   /* per block: 1 exponent byte + 6-bit codes, 25 B for block 32
+                                  (axs/unified/distributed.py:147-198)                        */
+       AXS6_LAYOUT_SPEC = 2 }; /* per block: u16 LE (exponent<<2 | config 0) + 6-bit codes,
+                                  26 B for block 32 (axs/core.py:97-118, FORMAT_SPEC.md:29-48) */
+
+/* flags */
+#define AXS6_FLAG_INPUT_VIA_BF16 1u /* round an fp32 input to bf16 before quantising: the
+                                       `weight.to(bfloat16)` of the mixed-precision Linear
+                                       (axs/unified/mixed_precision.py:96-100) fused in    */
+
+#define AXS6_OK 0
+#define AXS6_ERR_ARG (-1)         /* null pointer, negative size, bad enum, bad block size  */
+#define AXS6_ERR_ALIGN (-2)       /* pointer or leading dimension violates a stated alignment */
+#define AXS6_ERR_DEVICE (-3)      /* current device is not sm_100 / CUDA runtime error         */
+#define AXS6_ERR_LAUNCH (-4)      /* kernel launch failed                                       */
+#define AXS6_ERR_WORKSPACE (-5)   /* workspace missing or too small                             */
+#define AXS6_ERR_UNSUPPORTED (-6) /* valid request this build does not implement               */
+
+const char *axs6_strerror(int status);
+
+/* what: 0 = 1 if the current device can run the kernels (cc 10.x) else 0, 1 = SM count,
+ * 2 = ABI version, 3 = number of kernels launched by this process so far. */
+int64_t axs6_query(int what);
+
+/* Fake-quantise: y = dequantise(quantise(x)) in one pass.
+ * Replaces fused_fake_quantize (axs/unified/quantize_unified.py:121-204), the Triton
+ * launcher triton_fused_fake_quantize (axs/unified/triton_kernels.py:295-370) and, with
+ * grid = AXS6_GRID_UNIFORM, dequantize(quantize(x)) of axs/core.py:294-403 as used by
+ * axs/nn/functional.py:46-53.  Nearest rounding is bit-exact with the reference's eager
+ * CPU result.  Stochastic rounding draws U[0,1) per element from Philox4x32-10 keyed by
+ * `seed`, counter = `offset` + padded element index / 4.
+ * Any alignment is accepted; 16-byte aligned pointers with cols and both leading
+ * dimensions multiples of 8 elements take the vectorised path. */
+int axs6_fq(const void *x, void *y, int in_dtype, int out_dtype,
+            int64_t rows, int64_t cols, int64_t ldx, int64_t ldy,
+            int block, int grid, int rounding, uint32_t flags,
+            uint64_t seed, uint64_t offset, axs6_stream_t stream);
+
+/* Same arithmetic with the uniform draws supplied by the caller: `noise` holds fp32
+ * U[0,1) in the zero-padded (rows, nblk, block) layout, as torch.rand_like produces it in
+ * the reference (quantize_unified.py:186-189, core.py:351-355).  Makes the stochastic
+ * path bit-comparable. */
+int axs6_fq_with_noise(const void *x, void *y, int in_dtype, int out_dtype,
+                       int64_t rows, int64_t cols, int64_t ldx, int64_t ldy,
+                       int block, int grid, uint32_t flags,
+                       const float *noise, axs6_stream_t stream);
+
+/* Quantise to codes.  Replaces quantize_unified (axs/unified/quantize_unified.py:211-282),
+ * quantize (axs/core.py:294-369), _pack_gradient + _pack_to_flat_buffer
+ * (axs/unified/distributed.py:70-198) and AXSBlock.to_bytes (axs/core.py:97-118).
+ * layout PLANES: out0 = exponents u8 (rows*nblk), out1 = signs u8 (rows*nblk*block),
+ *                out2 = magnitudes u8 (rows*nblk*block).
+ * layout WIRE/SPEC: out0 = rows*nblk records of (1|2) + block*3/4 bytes; out1/out2 unused.
+ * `noise` (may be NULL) as in axs6_fq_with_noise; if NULL and rounding is stochastic the
+ * Philox stream (seed, offset) is used. */
+int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, int64_t ldx,
+              int block, int grid, int rounding, uint32_t flags,
+              uint64_t seed, uint64_t offset, const float *noise,
+              int layout, void *out0, void *out1, void *out2, axs6_stream_t stream);
+
+/* Codes back to values.  Replaces dequantize_unified (axs/unified/quantize_unified.py:285-308),
+ * dequantize (axs/core.py:372-403), _unpack_from_flat_buffer + _unpack_gradient
+ * (axs/unified/distributed.py:123-144, :201-232) and AXSBlock.from_bytes (axs/core.py:120-152).
+ * The fp32 result is bit-exact; out_dtype BF16 rounds it to nearest-even. */
+int axs6_unpack(int layout, const void *in0, const void *in1, const void *in2,
+                void *y, int out_dtype, int64_t rows, int64_t cols, int64_t ldy,
+                int block, int grid, axs6_stream_t stream);
+
+/* Bytes per block record of a byte layout (0 for PLANES or bad arguments). */
+int64_t axs6_record_bytes(int layout, int block);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AXS6_B200_H */

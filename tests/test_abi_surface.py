@@ -1,0 +1,68 @@
+"""The C-ABI library loads and exports every symbol the public header declares, and the ctypes
+binding covers the same set (no compute calls: runs without a GPU)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = set()
+    inc = os.path.join(ROOT, "include")
+    for f in os.listdir(inc):
+        if f.endswith(".h"):
+            text = open(os.path.join(inc, f)).read()
+            text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+            names |= set(re.findall(r"\b(axs6_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
+
+
+def test_header_declares_the_hot_path():
+    names = declared_symbols()
+    for must in ("axs6_fq", "axs6_fq_with_noise", "axs6_pack", "axs6_unpack", "axs6_strerror", "axs6_query"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    from axs6_b200 import _lib, build
+    path = build.build()
+    lib = ctypes.CDLL(path)
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} declared in include/ but not exported"
+    assert set(_lib.SIGNATURES) == set(declared_symbols())
+
+
+def test_host_only_entry_points():
+    from axs6_b200 import _lib
+    lib = _lib.load()
+    assert lib.axs6_strerror(0) == b"ok"
+    assert lib.axs6_strerror(-3).decode().startswith("current CUDA device")
+    assert lib.axs6_record_bytes(1, 32) == 25 and lib.axs6_record_bytes(2, 32) == 26
+    assert lib.axs6_record_bytes(1, 16) == 13 and lib.axs6_record_bytes(2, 8) == 8
+    assert lib.axs6_record_bytes(1, 12) == 0
+    assert lib.axs6_query(2) >= 1
+
+
+def test_ops_reject_cpu_tensors():
+    import torch
+    import importlib
+    qu = importlib.import_module("axs6_b200.unified.quantize_unified")
+    from axs6_b200 import core
+    with pytest.raises(RuntimeError, match="requires a CUDA tensor"):
+        qu.fused_fake_quantize(torch.randn(4, 32))
+    with pytest.raises(RuntimeError, match="requires a CUDA tensor"):
+        core.quantize(torch.randn(4, 32))
+
+
+def test_product_never_imports_the_oracle():
+    """The oracle is test infrastructure: nothing under the package may reference it."""
+    pkg = os.path.join(ROOT, "axs6_b200")
+    for root, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(root, f)).read()
+                assert not re.search(r"^\s*(import|from)\s+oracle\b", text, flags=re.M), f
+                assert "liboracle" not in text, f

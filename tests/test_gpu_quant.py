@@ -1,0 +1,335 @@
+"""GPU parity of the fake-quantise and codec kernels, called through the C ABI
+(axs6_b200.ops -> ctypes -> libaxs6_b200.so), against the golden vectors recorded from the
+reference and against the CPU oracle on seeded inputs.  Integer/byte results and fp32/bf16
+fake-quant outputs must be BIT-EXACT."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from gpu_util import assert_bits_equal, to_bits, to_cuda
+from helpers import (case_input, config1_input, config2_input, config3_input, expect_bits, fq_case_names, sha)
+
+pytestmark = pytest.mark.gpu
+
+from axs6_b200 import _lib, core, ops  # noqa: E402
+from axs6_b200.nn import functional as nnf  # noqa: E402
+from axs6_b200.unified import distributed as udist  # noqa: E402
+import importlib  # noqa: E402
+qu = importlib.import_module("axs6_b200.unified.quantize_unified")  # the package re-exports a function of the same name
+from axs6_b200.unified.triton_kernels import triton_fused_fake_quantize  # noqa: E402
+
+with open(os.path.join(os.path.dirname(__file__), "golden", "manifest.json")) as _f:
+    _MANIFEST = json.load(_f)
+_NEAREST = fq_case_names(_MANIFEST, stochastic=False)
+_STOCH = fq_case_names(_MANIFEST, stochastic=True)
+
+
+def test_library_reports_b200():
+    assert _lib.load().axs6_query(0) == 1
+    assert _lib.load().axs6_query(1) >= 100
+
+
+# ------------------------------------------------------------------ golden vectors, nearest
+@pytest.mark.parametrize("case", _NEAREST)
+def test_golden_nearest(case, fq_cases, manifest):
+    x, _, info = case_input(fq_cases, manifest, case)
+    B = info["block"]
+    xt = to_cuda(x)
+    before = _lib.launches()
+    y = qu.fused_fake_quantize(xt, B)
+    assert _lib.launches() == before + 1
+    assert y.dtype == xt.dtype and y.shape == xt.shape
+    assert_bits_equal(y, fq_cases[f"{case}.fq_nf5"], "fq_nf5")
+    # V1 fake-quantise: always fp32
+    y1 = nnf.fake_quantize(xt, B)
+    assert y1.dtype == torch.float32
+    assert_bits_equal(y1, fq_cases[f"{case}.deq_uni"], "fq_uniform")
+    for tag, qfn, dfn in (("nf5", qu.quantize_unified, qu.dequantize_unified), ("uni", core.quantize, core.dequantize)):
+        q = qfn(xt, B)
+        assert q.signs.dtype == torch.bool and q.magnitudes.dtype == torch.uint8
+        assert_bits_equal(q.shared_exponents, fq_cases[f"{case}.{tag}.se"], tag + ".se")
+        assert_bits_equal(q.magnitudes, fq_cases[f"{case}.{tag}.mag"], tag + ".mag")
+        assert_bits_equal(q.signs, fq_cases[f"{case}.{tag}.sign"], tag + ".sign")
+        d = dfn(q)
+        assert d.dtype == torch.float32 and d.shape == xt.shape
+        assert_bits_equal(d, fq_cases[f"{case}.deq_{tag}"], tag + ".deq")
+    if f"{case}.nf5.wire" in fq_cases.files:
+        w = udist.pack_wire(xt, B)
+        assert w.dtype == torch.int8
+        assert_bits_equal(w.view(torch.uint8), fq_cases[f"{case}.nf5.wire"], "wire")
+        back = udist.unpack_wire(w, xt.shape, B)
+        assert_bits_equal(back, fq_cases[f"{case}.deq_nf5"], "wire roundtrip")
+    if f"{case}.nf5.spec" in fq_cases.files:
+        s = core.tensor_to_bytes(xt, B, nf5=True)
+        assert_bits_equal(s, fq_cases[f"{case}.nf5.spec"], "spec")
+        back = core.tensor_from_bytes(s, xt.shape, B, nf5=True)
+        assert_bits_equal(back, fq_cases[f"{case}.deq_nf5"], "spec roundtrip")
+
+
+# ------------------------------------------------------------------ golden vectors, stochastic with given noise
+@pytest.mark.parametrize("case", _STOCH)
+def test_golden_stochastic_with_noise(case, fq_cases, manifest):
+    x, noise, info = case_input(fq_cases, manifest, case)
+    B = info["block"]
+    xt = to_cuda(x)
+    nz = torch.from_numpy(noise).cuda()
+    y = ops.fake_quantize(xt, B, ops.GRID_NF5, "stochastic", noise=nz)
+    assert_bits_equal(y, fq_cases[f"{case}.fq_nf5"], "fq_nf5 stochastic")
+    for tag, grid in (("nf5", ops.GRID_NF5), ("uni", ops.GRID_UNIFORM)):
+        se, sg, mg = ops.pack(xt, B, grid, "stochastic", ops.LAYOUT_PLANES, noise=nz)
+        assert_bits_equal(se, fq_cases[f"{case}.{tag}.se"], tag + ".se")
+        assert_bits_equal(mg, fq_cases[f"{case}.{tag}.mag"], tag + ".mag")
+        assert_bits_equal(sg, fq_cases[f"{case}.{tag}.sign"], tag + ".sign")
+    y1 = ops.fake_quantize(xt, B, ops.GRID_UNIFORM, "stochastic", out_dtype=torch.float32, noise=nz)
+    assert_bits_equal(y1, fq_cases[f"{case}.deq_uni"], "fq_uniform stochastic")
+
+
+# ------------------------------------------------------------------ BASELINE configs vs manifest hashes and oracle
+def test_config1(manifest):
+    x = config1_input()
+    y = qu.fused_fake_quantize(torch.from_numpy(x).cuda())
+    assert_bits_equal(y, oracle.fused_fake_quantize(x), "config1 vs oracle")
+    if sha(x) == manifest["hashes"]["config1.input"]:
+        assert sha(to_bits(y)) == manifest["hashes"]["config1.fq_nf5"]
+        y1 = nnf.fake_quantize(torch.from_numpy(x).cuda())
+        assert sha(to_bits(y1)) == manifest["hashes"]["config1.fq_uniform"]
+
+
+def test_config2_quarter_hashes(manifest):
+    xb = oracle.f32_to_bf16(config2_input(2048, 4096))
+    assert sha(xb) == manifest["hashes"]["config2_quarter.input"]
+    xt = to_cuda(xb)
+    w = udist.pack_wire(xt)
+    assert sha(to_bits(w.view(torch.uint8))) == manifest["hashes"]["config2_quarter.wire"]
+    back = udist.unpack_wire(w, xt.shape)
+    assert sha(to_bits(back)) == manifest["hashes"]["config2_quarter.roundtrip"]
+    assert sha(to_bits(qu.fused_fake_quantize(xt))) == manifest["hashes"]["config2_quarter.fq_nf5"]
+
+
+def test_config2_full_roundtrip_properties():
+    """8192x4096 bf16: fake-quant == unpack(pack) except at exact zeros, where the codec returns
+    +codebook[0]*scale (the reference's behaviour: sign bit clear, code 0 is not zero)."""
+    x = config2_input(8192, 4096)
+    xt = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    w = udist.pack_wire(xt)
+    assert w.numel() == 8192 * 128 * 25
+    back = udist.unpack_wire(w, xt.shape)
+    fq = qu.fused_fake_quantize(xt).float()
+    zero = xt == 0
+    assert int(zero.sum()) > 100000
+    assert torch.equal(back[~zero], fq[~zero])
+    assert bool((back[zero] > 0).all())
+    # sampled rows against the oracle, bit for bit
+    rows = np.random.default_rng(0).choice(8192, 256, replace=False)
+    xs = to_bits(xt[torch.from_numpy(rows).cuda()])
+    se, sg, mg = oracle.quantize(xs, 32, oracle.GRID_NF5)
+    want = oracle.dequantize(se, sg, mg, 4096, oracle.GRID_NF5)
+    assert_bits_equal(back[torch.from_numpy(rows).cuda()], want, "sampled rows")
+
+
+def test_config3_4096(manifest):
+    x = config3_input(4096, 4096)
+    assert sha(x) == manifest["hashes"]["config3_4096.input"]
+    xt = torch.from_numpy(x).cuda()
+    assert sha(to_bits(qu.fused_fake_quantize(xt))) == manifest["hashes"]["config3_4096.fq_nf5_f32"]
+    assert sha(to_bits(qu.fused_fake_quantize(xt.to(torch.bfloat16)))) == manifest["hashes"]["config3_4096.fq_nf5_bf16"]
+
+
+@pytest.mark.parametrize("shape", [(256, 256), (8192, 4096)])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_config3_vs_oracle(shape, dtype):
+    x = config3_input(*shape, seed=11)
+    xin = oracle.f32_to_bf16(x) if dtype == "bf16" else x
+    y = qu.fused_fake_quantize(to_cuda(xin))
+    assert_bits_equal(y, oracle.fused_fake_quantize(xin), f"{shape} {dtype}")
+    y1 = nnf.fake_quantize(to_cuda(xin))
+    assert_bits_equal(y1, oracle.fake_quantize_uniform(xin), f"uniform {shape} {dtype}")
+
+
+def test_config3_largest_properties():
+    """32768x8192 fp32 (1 GiB): size-independent properties plus sampled rows against the oracle."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    sig = 10 ** (torch.rand(32768, 1, generator=g, device="cuda") * 5 - 4)
+    x = torch.randn(32768, 8192, generator=g, device="cuda") * sig
+    y = qu.fused_fake_quantize(x)
+    # row-shard invariance: the result of a row range does not depend on the rest of the tensor
+    for lo, hi in ((0, 4096), (12288, 16384), (32768 - 4096, 32768)):
+        assert torch.equal(qu.fused_fake_quantize(x[lo:hi]), y[lo:hi])
+    # signs preserved, |y| <= block scale, zeros stay zeros
+    assert bool(((y == 0) | (torch.sign(y) == torch.sign(x))).all())
+    # sampled rows, bit-exact against the oracle
+    rows = torch.from_numpy(np.random.default_rng(1).choice(32768, 128, replace=False)).cuda()
+    assert_bits_equal(y[rows], oracle.fused_fake_quantize(x[rows].cpu().numpy()), "sampled rows")
+    del y
+    # power-of-two scaling commutes with the quantiser on bf16-representable data
+    xb = x[:8192].to(torch.bfloat16).float()
+    a = qu.fused_fake_quantize(xb * 8.0)
+    b = qu.fused_fake_quantize(xb) * 8.0
+    assert torch.equal(a, b)
+
+
+# ------------------------------------------------------------------ alignment / view handling
+@pytest.mark.parametrize("B", [8, 16, 32])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_unaligned_and_strided_views(B, dtype):
+    g = torch.Generator().manual_seed(B)
+    base = torch.randn(37, 200, generator=g).to(dtype)
+    bc = base.cuda()
+    for view in (lambda t: t[:, 1:129], lambda t: t[:, 8:136], lambda t: t[3:, :64], lambda t: t[:, 3:36],
+                 lambda t: t[::2, 16:144], lambda t: t.t()[:64, :32]):
+        v = view(bc)
+        want_in = to_bits(view(base).contiguous())
+        if dtype == torch.float32:
+            want_in = want_in.view(np.float32)
+        y = qu.fused_fake_quantize(v, B)
+        assert_bits_equal(y, oracle.fused_fake_quantize(want_in, B), "fq view")
+        se, sg, mg = ops.pack(v, B, ops.GRID_NF5, "nearest", ops.LAYOUT_PLANES)
+        ose, osg, omg = oracle.quantize(want_in, B, oracle.GRID_NF5)
+        assert_bits_equal(se, ose, "se view"); assert_bits_equal(mg, omg, "mag view"); assert_bits_equal(sg, osg, "sign view")
+        w = ops.pack(v, B, ops.GRID_NF5, "nearest", ops.LAYOUT_WIRE)
+        assert_bits_equal(w, oracle.pack_bytes(ose, osg, omg, oracle.LAYOUT_WIRE), "wire view")
+        s = ops.pack(v, B, ops.GRID_UNIFORM, "nearest", ops.LAYOUT_SPEC)
+        use, usg, umg = oracle.quantize(want_in, B, oracle.GRID_UNIFORM)
+        assert_bits_equal(s, oracle.pack_bytes(use, usg, umg, oracle.LAYOUT_SPEC), "spec view")
+
+
+def test_unaligned_byte_buffers():
+    """Byte records at an odd device address take the any-alignment kernels."""
+    x = torch.randn(19, 96, generator=torch.Generator().manual_seed(3))
+    xc = x.cuda()
+    ose, osg, omg = oracle.quantize(x.numpy(), 32, oracle.GRID_NF5)
+    want = oracle.pack_bytes(ose, osg, omg, oracle.LAYOUT_WIRE)
+    lib = _lib.load()
+    buf = torch.zeros(want.size + 64, dtype=torch.uint8, device="cuda")
+    st = lib.axs6_pack(xc.data_ptr(), 0, 19, 96, 96, 32, 1, 0, 0, 0, 0, None, 1, buf.data_ptr() + 3, None, None,
+                       torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    assert_bits_equal(buf[3:3 + want.size], want, "unaligned wire")
+    assert int(buf[:3].sum()) == 0 and int(buf[3 + want.size:].sum()) == 0      # nothing written outside
+    y = torch.empty(19, 96, device="cuda")
+    st = lib.axs6_unpack(1, buf.data_ptr() + 3, None, None, y.data_ptr(), 0, 19, 96, 96, 32, 1,
+                         torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    assert_bits_equal(y, oracle.dequantize(ose, osg, omg, 96, oracle.GRID_NF5), "unaligned unpack")
+
+
+def test_canary_no_out_of_bounds_writes():
+    """Outputs sit between guard regions that must stay untouched (ragged and aligned shapes)."""
+    for rows, cols in ((7, 100), (64, 256), (3, 8), (1, 1), (513, 40)):
+        for B in (8, 16, 32):
+            x = torch.randn(rows, cols, device="cuda")
+            n = rows * cols
+            buf = torch.full((n + 512,), 7.0, device="cuda")
+            y = buf[256:256 + n].view(rows, cols)
+            st = _lib.load().axs6_fq(x.data_ptr(), y.data_ptr(), 0, 0, rows, cols, cols, cols, B, 1, 0, 0, 0, 0,
+                                     torch.cuda.current_stream().cuda_stream)
+            assert st == 0
+            assert bool((buf[:256] == 7.0).all()) and bool((buf[256 + n:] == 7.0).all())
+            assert_bits_equal(y, oracle.fused_fake_quantize(x.cpu().numpy(), B), "canary result")
+
+
+def test_via_bf16_flag_equals_cast_then_quantise():
+    w = torch.randn(256, 512, generator=torch.Generator().manual_seed(9)) * 0.02
+    wc = w.cuda()
+    a = ops.fake_quantize(wc, 32, ops.GRID_NF5, "nearest", out_dtype=torch.bfloat16, via_bf16=True)
+    b = qu.fused_fake_quantize(wc.to(torch.bfloat16))
+    assert a.dtype == torch.bfloat16 and torch.equal(a, b)
+    assert_bits_equal(a, oracle.fused_fake_quantize(oracle.f32_to_bf16(w.numpy())), "via bf16 vs oracle")
+
+
+# ------------------------------------------------------------------ stochastic rounding statistics (Philox)
+def test_stochastic_statistics():
+    """Same checks as the reference's GPU tests (tests/test_triton_kernels.py:205-241)."""
+    torch.manual_seed(0)
+    x = torch.randn(512, 512, device="cuda")
+    near = qu.fused_fake_quantize(x, 32, "nearest")
+    st1 = qu.fused_fake_quantize(x, 32, "stochastic")
+    st2 = qu.fused_fake_quantize(x, 32, "stochastic")
+    assert not torch.equal(st1, near) and not torch.equal(st1, st2)
+    frac = float((st1 != near).float().mean())
+    assert 0.002 < frac < 0.05
+    mse_n = float(((near - x) ** 2).mean()); mse_s = float(((st1 - x) ** 2).mean())
+    assert 0.5 < mse_s / mse_n < 2.0
+    acc = torch.zeros_like(x)
+    for _ in range(20):
+        acc += qu.fused_fake_quantize(x, 32, "stochastic")
+    assert abs(float((acc / 20 - x).mean())) < 0.01
+    # every stochastic output is one of the two neighbouring levels of the nearest result's block grid
+    assert bool((torch.sign(st1) * torch.sign(x) >= 0).all())
+
+
+def test_stochastic_uniform_unbiased():
+    """V1 stochastic rounding is unbiased (reference: tests/test_quantize.py:53-62)."""
+    torch.manual_seed(1)
+    x = torch.randn(64, 256, device="cuda")
+    acc = torch.zeros_like(x)
+    for _ in range(200):
+        acc += core.dequantize(core.quantize(x, 32, "stochastic"))
+    assert abs(float((acc / 200 - x).mean())) < 0.005
+
+
+def test_stochastic_reproducible_under_seed():
+    x = torch.randn(128, 256, device="cuda")
+    torch.manual_seed(77); ops.reset_philox()
+    a = qu.fused_fake_quantize(x, 32, "stochastic")
+    torch.manual_seed(77); ops.reset_philox()
+    b = qu.fused_fake_quantize(x, 32, "stochastic")
+    assert torch.equal(a, b)
+
+
+def test_vector_and_generic_kernels_draw_same_philox_stream():
+    """The same (seed, offset) gives the same draws whichever kernel variant runs."""
+    x = torch.randn(64, 96, device="cuda")
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    y1 = torch.empty_like(x)
+    assert lib.axs6_fq(x.data_ptr(), y1.data_ptr(), 0, 0, 64, 96, 96, 96, 32, 1, 1, 0, 1234, 10, st) == 0
+    big = torch.empty(64 * 96 + 1, device="cuda")
+    xu = big[1:].view(64, 96); xu.copy_(x)                       # 4-byte aligned only -> generic kernel
+    y2 = torch.empty_like(big)[1:].view(64, 96)
+    assert lib.axs6_fq(xu.data_ptr(), y2.data_ptr(), 0, 0, 64, 96, 96, 96, 32, 1, 1, 0, 1234, 10, st) == 0
+    assert torch.equal(y1, y2)
+
+
+# ------------------------------------------------------------------ error conventions and edge sizes
+def test_error_conventions():
+    x = torch.randn(4, 32, device="cuda")
+    with pytest.raises(AssertionError):
+        qu.fused_fake_quantize(x, block_size=7)
+    with pytest.raises(AssertionError):
+        triton_fused_fake_quantize(x, block_size=64)
+    with pytest.raises(RuntimeError, match="requires a CUDA tensor"):
+        triton_fused_fake_quantize(torch.randn(4, 32))
+    with pytest.raises(RuntimeError, match="requires a CUDA tensor"):
+        qu.fused_fake_quantize(torch.randn(4, 32))
+    with pytest.raises(ValueError):
+        qu.fused_fake_quantize(x, 32, "banana")
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.axs6_fq(None, x.data_ptr(), 0, 0, 4, 32, 32, 32, 32, 1, 0, 0, 0, 0, st) == -1
+    assert lib.axs6_fq(x.data_ptr(), x.data_ptr(), 0, 0, 4, 32, 16, 32, 32, 1, 0, 0, 0, 0, st) == -1
+    assert lib.axs6_fq(x.data_ptr(), x.data_ptr(), 5, 0, 4, 32, 32, 32, 32, 1, 0, 0, 0, 0, st) == -1
+    assert lib.axs6_strerror(-1).decode().startswith("invalid argument")
+
+
+def test_empty_and_tiny():
+    e = torch.empty(0, 32, device="cuda")
+    assert qu.fused_fake_quantize(e).shape == (0, 32)
+    e2 = torch.empty(4, 0, device="cuda")
+    assert qu.fused_fake_quantize(e2).shape == (4, 0)
+    one = torch.tensor([0.3], device="cuda")
+    assert_bits_equal(qu.fused_fake_quantize(one), oracle.fused_fake_quantize(np.array([0.3], dtype=np.float32)), "1 value")
+    z = torch.zeros(5, 64, device="cuda")
+    assert bool((qu.fused_fake_quantize(z) == 0).all())
+    assert not bool(torch.signbit(qu.fused_fake_quantize(-z)).any())      # -0.0 -> +0.0
+
+
+def test_4d_and_fp16_inputs():
+    x = torch.randn(2, 3, 5, 48, generator=torch.Generator().manual_seed(4))
+    y = qu.fused_fake_quantize(x.cuda(), 16)
+    assert y.shape == x.shape
+    assert_bits_equal(y, oracle.fused_fake_quantize(x.numpy(), 16), "4-D")
