@@ -53,7 +53,13 @@ def _as_rows(t: torch.Tensor) -> tuple[torch.Tensor, int, int, int]:
     """-> (2-D view or copy with unit inner stride, rows, cols, leading dimension)."""
     if t.dtype not in _DT:
         t = t.float()
-    t2 = t.reshape(-1, t.shape[-1])
+    cols = t.shape[-1]
+    if t.numel() == 0:
+        rows = 1
+        for d in t.shape[:-1]:
+            rows *= d
+        return t.new_empty((rows, cols)), rows, cols, cols
+    t2 = t.reshape(-1, cols)
     rows, cols = t2.shape
     if cols > 0 and rows > 0 and (t2.stride(1) != 1 or (rows > 1 and t2.stride(0) < cols)):
         t2 = t2.contiguous()

@@ -1,0 +1,51 @@
+"""Runs ONE kernel of the library a few times on a small, larger-than-L2 case, for profilers.
+
+    python -m axs6_b200.profile_case {fq_f32|fq_bf16|pack_wire|unpack_wire} [launches]
+
+Device footprint stays under 1 GB so that a multi-pass capture finishes quickly.
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+from . import _lib
+
+
+def main() -> None:
+    what = sys.argv[1] if len(sys.argv) > 1 else "fq_f32"
+    n = int(sys.argv[2]) if len(sys.argv) > 2 else 3
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    rows, cols = 8192, 8192                       # 256 MiB fp32 / 128 MiB bf16: larger than the 126 MB L2
+    g = torch.Generator(device=dev).manual_seed(0)
+    st = torch.cuda.current_stream().cuda_stream
+    if what == "fq_f32":
+        x = torch.randn(rows, cols, generator=g, device=dev)
+        y = torch.empty_like(x)
+        run = lambda: lib.axs6_fq(x.data_ptr(), y.data_ptr(), 0, 0, rows, cols, cols, cols, 32, 1, 0, 0, 0, 0, st)
+    elif what == "fq_bf16":
+        x = torch.randn(rows, cols, generator=g, device=dev).to(torch.bfloat16)
+        y = torch.empty_like(x)
+        run = lambda: lib.axs6_fq(x.data_ptr(), y.data_ptr(), 1, 1, rows, cols, cols, cols, 32, 1, 0, 0, 0, 0, st)
+    elif what == "pack_wire":
+        x = torch.randn(rows, cols, generator=g, device=dev).to(torch.bfloat16)
+        w = torch.empty(rows * cols // 32 * 25, dtype=torch.uint8, device=dev)
+        run = lambda: lib.axs6_pack(x.data_ptr(), 1, rows, cols, cols, 32, 1, 0, 0, 0, 0, None, 1, w.data_ptr(), None, None, st)
+    elif what == "unpack_wire":
+        x = torch.randn(rows, cols, generator=g, device=dev).to(torch.bfloat16)
+        w = torch.empty(rows * cols // 32 * 25, dtype=torch.uint8, device=dev)
+        assert lib.axs6_pack(x.data_ptr(), 1, rows, cols, cols, 32, 1, 0, 0, 0, 0, None, 1, w.data_ptr(), None, None, st) == 0
+        y = torch.empty(rows, cols, device=dev)
+        run = lambda: lib.axs6_unpack(1, w.data_ptr(), None, None, y.data_ptr(), 0, rows, cols, cols, 32, 1, st)
+    else:
+        raise SystemExit(f"unknown case {what}")
+    for _ in range(n):
+        assert run() == 0
+    torch.cuda.synchronize()
+    print(f"{what}: {n} launches ok")
+
+
+if __name__ == "__main__":
+    main()

@@ -118,7 +118,7 @@ def test_config2_full_roundtrip_properties():
     w = udist.pack_wire(xt)
     assert w.numel() == 8192 * 128 * 25
     back = udist.unpack_wire(w, xt.shape)
-    fq = qu.fused_fake_quantize(xt).float()
+    fq = qu.fused_fake_quantize(xt.float())
     zero = xt == 0
     assert int(zero.sum()) > 100000
     assert torch.equal(back[~zero], fq[~zero])
