@@ -10,6 +10,10 @@ static std::atomic<long long> g_launches{0};
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+static std::atomic<long long> g_tune[8];
+
+int64_t tune_value(int key) { return (key >= 0 && key < 8) ? g_tune[key].load(std::memory_order_relaxed) : 0; }
+
 const DeviceInfo &device_info()
 {
     static DeviceInfo table[64];
@@ -56,4 +60,11 @@ AXS6_API int64_t axs6_query(int what)
     case 3: return axs6::g_launches.load(std::memory_order_relaxed);
     default: return -1;
     }
+}
+
+AXS6_API int axs6_tune(int key, int64_t value)
+{
+    if (key < 0 || key >= 8) return AXS6_ERR_ARG;
+    axs6::g_tune[key].store(value, std::memory_order_relaxed);
+    return AXS6_OK;
 }

@@ -113,11 +113,17 @@ AXS6_HD float axs6_pow2(int k)
 }
 
 struct Axs6Scale {
-    float scale;  // block scale S
+    float scale;  // block scale S = 2^k
     float inv;    // 1/S when `fast`, else unused
-    int fast;     // S and 1/S both normal powers of two: |x|/S == |x| * (1/S) under RN
+    int fast;     // k in [-116, 126]: S, 1/S, 1023/S and 31/S are all normal fp32 numbers
     int se;       // biased shared exponent byte (code paths)
 };
+
+// Why the fast path may fold the two roundings of trunc(RN(RN(|x| / S) * G)) (G = 1023 or 31)
+// into ONE product RN(|x| * (G / S)): G / S is exact in fp32 (G has at most 10 significant bits,
+// S is a power of two).  If |x| / S is representable the first rounding is the identity and both
+// expressions round the same real number.  If it is not, |x| / S < 2^-126, so both products are
+// below 2^-116 and truncate (or round) to index 0 alike.
 
 // Scale of the fused fake-quantise: S = exp2(floor(log2(max(amax, 2^-149))) + 1), S = 1 for an
 // all-zero block; no clamping of the exponent (quantize_unified.py:173-179).
@@ -127,7 +133,7 @@ AXS6_HD Axs6Scale axs6_scale_fq(uint32_t amax_bits)
     s.se = 0;
     if (amax_bits == 0u) { s.scale = 1.0f; s.inv = 1.0f; s.fast = 1; return s; }
     const int k = axs6_ref_floor_log2(amax_bits) + 1;
-    if (k >= -126 && k <= 126) {
+    if (k >= -116 && k <= 126) {
         s.scale = axs6_from_bits((uint32_t)(k + 127) << 23);
         s.inv = axs6_from_bits((uint32_t)(127 - k) << 23);
         s.fast = 1;
@@ -144,13 +150,14 @@ AXS6_HD Axs6Scale axs6_scale_fq(uint32_t amax_bits)
 AXS6_HD Axs6Scale axs6_scale_codes(uint32_t amax_bits)
 {
     Axs6Scale s;
-    int se = 0;
-    if (amax_bits != 0u) {
-        se = axs6_ref_floor_log2(amax_bits) + 1 + 127;
-        se = se < 0 ? 0 : (se > 255 ? 255 : se);
+    if (amax_bits == 0u) {      // every code of the block is 0 whatever the scale
+        s.se = 0; s.scale = axs6_pow2(-127); s.inv = 1.0f; s.fast = 1;
+        return s;
     }
+    int se = axs6_ref_floor_log2(amax_bits) + 1 + 127;
+    se = se < 0 ? 0 : (se > 255 ? 255 : se);
     s.se = se;
-    if (se >= 1 && se <= 253) {
+    if (se >= 11 && se <= 253) {
         s.scale = axs6_from_bits((uint32_t)se << 23);
         s.inv = axs6_from_bits((uint32_t)(254 - se) << 23);
         s.fast = 1;
@@ -191,6 +198,15 @@ AXS6_HD int axs6_nf5_index_dithered(float n, float u)
     return i > 1023 ? 1023 : i;
 }
 
+// Fast-path forms (block scale in the `fast` range, see Axs6Scale): one product, no clamps --
+// |x| < S guarantees an index below 1023 and a magnitude of at most 31.
+AXS6_HD int axs6_nf5_index_fast(float ax, float g_over_s) { return AXS6_TRUNC_I(AXS6_MUL(ax, g_over_s)); }
+#if defined(__CUDA_ARCH__)
+AXS6_HD int axs6_uniform_mag_fast(float ax, float g_over_s) { return __float2int_rn(AXS6_MUL(ax, g_over_s)); }
+#else
+AXS6_HD int axs6_uniform_mag_fast(float ax, float g_over_s) { return (int)nearbyintf(AXS6_MUL(ax, g_over_s)); }
+#endif
+
 // Uniform-grid magnitude: round-half-even of n * 31, or floor + (u < frac) (core.py:348-359).
 AXS6_HD int axs6_uniform_mag(float n)
 {
@@ -218,6 +234,14 @@ AXS6_HD float axs6_fq_value(uint32_t xbits, float level, float scale)
     if ((xbits & 0x7FFFFFFFu) == 0u) return AXS6_MUL(AXS6_MUL(0.0f, level), scale);
     const float v = AXS6_MUL(level, scale);
     return axs6_from_bits(axs6_to_bits(v) | (xbits & 0x80000000u));
+}
+
+// Same for a finite scale, branch-free: |y| = level * S, sign of x, +0 for x = +-0.
+AXS6_HD float axs6_fq_value_fast(float x, float level, float scale)
+{
+    const float v = AXS6_MUL(level, scale);
+    const float y = axs6_from_bits(axs6_to_bits(v) | (axs6_to_bits(x) & 0x80000000u));
+    return (x == 0.0f) ? 0.0f : y;
 }
 
 // where(sign, -v, v) with v = level * S (quantize_unified.py:300-302, core.py:388-389).

@@ -37,19 +37,37 @@ __device__ __forceinline__ void chunk_codes(const uint32_t (&v)[8], uint32_t (&c
     const uint32_t amax = group_max(chunk_amax_bits(v), lanes);
     const Axs6Scale s = axs6_scale_codes(amax);
     se = s.se;
+    if (s.fast) {
+        const float c = AXS6_MUL(s.inv, GRID == AXS6_GRID_NF5 ? 1023.0f : 31.0f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t ab = v[i] & 0x7FFFFFFFu;
-        const float n = axs6_normalise(__uint_as_float(ab), s);
-        int m;
-        if (GRID == AXS6_GRID_NF5) {
-            const int idx = (ROUND == kNearest) ? axs6_nf5_index(n) : axs6_nf5_index_dithered(n, u[i]);
-            m = rev[idx];
-        } else {
-            m = (ROUND == kNearest) ? axs6_uniform_mag(n) : axs6_uniform_mag_stochastic(n, u[i]);
+        for (int i = 0; i < 8; ++i) {
+            const float x = __uint_as_float(v[i]);
+            int m;
+            if (GRID == AXS6_GRID_NF5) {
+                const int idx = (ROUND == kNearest) ? axs6_nf5_index_fast(fabsf(x), c)
+                                                    : axs6_nf5_index_dithered(AXS6_MUL(fabsf(x), s.inv), u[i]);
+                m = rev[idx];
+            } else {
+                m = (ROUND == kNearest) ? axs6_uniform_mag_fast(fabsf(x), c)
+                                        : axs6_uniform_mag_stochastic(AXS6_MUL(fabsf(x), s.inv), u[i]);
+            }
+            code[i] = (uint32_t)m | (x < 0.0f ? 32u : 0u);          // x < 0 is false for -0.0
         }
-        const uint32_t neg = (ab != 0u) ? (v[i] >> 31) : 0u;     // x < 0 is false for -0.0
-        code[i] = (neg << 5) | (uint32_t)m;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t ab = v[i] & 0x7FFFFFFFu;
+            const float n = axs6_normalise(__uint_as_float(ab), s);
+            int m;
+            if (GRID == AXS6_GRID_NF5) {
+                const int idx = (ROUND == kNearest) ? axs6_nf5_index(n) : axs6_nf5_index_dithered(n, u[i]);
+                m = rev[idx];
+            } else {
+                m = (ROUND == kNearest) ? axs6_uniform_mag(n) : axs6_uniform_mag_stochastic(n, u[i]);
+            }
+            const uint32_t neg = (ab != 0u) ? (v[i] >> 31) : 0u;
+            code[i] = (neg << 5) | (uint32_t)m;
+        }
     }
 }
 
@@ -320,6 +338,8 @@ static int launch_codec(K kernel, const CodecArgs &a, int64_t items_per_cta, int
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm < 1)
         return AXS6_ERR_LAUNCH;
     int64_t ctas = (items + items_per_cta - 1) / items_per_cta;
+    const int64_t cap = tune_value(1);
+    if (cap > 0 && per_sm > cap) per_sm = (int)cap;
     const int64_t resident = (int64_t)d.sms * per_sm;
     if (ctas > resident) ctas = resident;
     if (ctas < 1) ctas = 1;

@@ -21,6 +21,7 @@ struct DeviceInfo {
 
 const DeviceInfo &device_info();      // for the current device
 void count_launch(int n = 1);         // bookkeeping behind axs6_query(3)
+int64_t tune_value(int key);          // axs6_tune() knobs (0 = default)
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -28,13 +28,19 @@ struct ChunkGeom {
 __device__ __forceinline__ uint4 ld_stream16(const void *p)
 {
     uint4 v;
-    asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];"
+#ifndef AXS6_LD_HINT
+#define AXS6_LD_HINT ".cs"
+#endif
+#ifndef AXS6_ST_HINT
+#define AXS6_ST_HINT ".cs"
+#endif
+    asm volatile("ld.global" AXS6_LD_HINT ".v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
 __device__ __forceinline__ void st_stream16(void *p, uint4 v)
 {
-    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};"
+    asm volatile("st.global" AXS6_ST_HINT ".v4.u32 [%0], {%1,%2,%3,%4};"
                  :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 __device__ __forceinline__ uint2 ld_stream8(const void *p)
@@ -93,8 +99,10 @@ template <> struct ChunkIO<__nv_bfloat16> {
         uint16_t *p = reinterpret_cast<uint16_t *>(base) + elem;
         uint32_t w[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-            w[i] = (uint32_t)axs6_f32_to_bf16_bits(y[2 * i]) | ((uint32_t)axs6_f32_to_bf16_bits(y[2 * i + 1]) << 16);
+        for (int i = 0; i < 4; ++i) {   // one cvt.rn.bf16x2.f32 per pair (round to nearest even)
+            const __nv_bfloat162 h = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t *>(&h);
+        }
         st_stream16(p, make_uint4(w[0], w[1], w[2], w[3]));
     }
     static __device__ __forceinline__ uint32_t load1(const void *base, int64_t elem, bool)
@@ -111,10 +119,10 @@ template <> struct ChunkIO<__nv_bfloat16> {
 // Works on |x| bit patterns: for non-negative floats the integer order is the float order.
 __device__ __forceinline__ uint32_t chunk_amax_bits(const uint32_t (&v)[8])
 {
-    uint32_t m = 0;
+    float m = 0.0f;                      // one FMNMX with |.| operand modifier per value
 #pragma unroll
-    for (int i = 0; i < 8; ++i) m = max(m, v[i] & 0x7FFFFFFFu);
-    return m;
+    for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(__uint_as_float(v[i])));
+    return __float_as_uint(m);
 }
 
 __device__ __forceinline__ uint32_t group_max(uint32_t m, int lanes)

@@ -251,6 +251,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     cpu = None
     if rank == 0:
         extra["codec"] = bench_codec(torch, lib, udist, dev, pk)
+        extra["fq_sweep"] = bench_sweep(torch, lib, dev, pk, x)
         if world == 1:
             cpu = cpu_baseline(x)
     del x, y
@@ -355,6 +356,44 @@ def bench_codec(torch, lib, udist, dev, pk) -> dict:
         res[name] = {"ms": ms, "GBps": gbs, "frac_of_hbm_peak": gbs / pk["hbm_gbs"], "algorithmic_bytes": nbytes}
     res["workload"] = "bf16 8192x4096 -> 25-byte wire records -> fp32, block 32 (4 rotating buffer sets, 4 x 227 MiB > L2)"
     return res
+
+
+def bench_sweep(torch, lib, dev, pk, x_big) -> list:
+    """Fake-quantise sweep (fp32 and bf16; 256^2, 4096^2, 8192x4096, 32768x8192).  Shapes smaller
+    than L2 rotate through slices of the 1 GiB tensor so that every launch reads cold data."""
+    stream = torch.cuda.current_stream().cuda_stream
+    out = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for dt_name, dt_code, esz in (("f32", 0, 4), ("bf16", 1, 2)):
+        src = x_big if dt_code == 0 else x_big.view(-1)[: x_big.numel() // 2].to(torch.bfloat16)
+        flat = src.view(-1)
+        dst = torch.empty_like(flat)
+        for rows, cols in ((256, 256), (4096, 4096), (8192, 4096), (32768, 8192)):
+            n = rows * cols
+            if n > flat.numel():
+                continue
+            slots = max(1, min(flat.numel() // n, 64))
+            iters = 30 if n >= (1 << 24) else 200
+
+            def run(i):
+                off = (i % slots) * n * esz
+                st = lib.axs6_fq(flat.data_ptr() + off, dst.data_ptr() + off, dt_code, dt_code, rows, cols, cols, cols,
+                                 BLOCK, 1, 0, 0, 0, 0, stream)
+                assert st == 0
+            for i in range(5):
+                run(i)
+            torch.cuda.synchronize()
+            e0.record()
+            for i in range(iters):
+                run(i)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            gbs = n * esz * 2 / (ms * 1e-3) / 1e9
+            out.append({"shape": f"{rows}x{cols}", "dtype": dt_name, "us": ms * 1e3, "GBps": gbs,
+                        "frac_of_hbm_peak": gbs / pk["hbm_gbs"], "rotating_slots": slots})
+        del dst
+    return out
 
 
 def bench_linear(args, rank, world, dev, pk):

@@ -55,6 +55,11 @@ const char *axs6_strerror(int status);
  * 2 = ABI version, 3 = number of kernels launched by this process so far. */
 int64_t axs6_query(int what);
 
+/* Performance knobs for experiments (process-wide, not needed for correct results):
+ * key 0 = cap on resident CTAs per SM of the fake-quantise kernels, key 1 = the same for the
+ * pack / unpack kernels; value 0 restores the built-in choice. */
+int axs6_tune(int key, int64_t value);
+
 /* Fake-quantise: y = dequantise(quantise(x)) in one pass.
  * Replaces fused_fake_quantize (axs/unified/quantize_unified.py:121-204), the Triton
  * launcher triton_fused_fake_quantize (axs/unified/triton_kernels.py:295-370) and, with
