@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libaxs6_b200.so")
 
 EXACT_SOURCES = ["abi.cu", "fq.cu", "codec.cu"]      # bit-exact arithmetic: no fma contraction
-FAST_SOURCES: list[str] = []                          # tensor-core kernels
+FAST_SOURCES: list[str] = ["gemm.cu"]                          # tensor-core kernels
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]

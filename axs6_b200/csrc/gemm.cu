@@ -1,0 +1,408 @@
+// bf16 x bf16 -> fp32-accumulate GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), fed
+// by TMA, for the three products of the AXS-6 Linear:
+//     forward   Y  = Xq  Wq^T      A = Xq (M x K, K-major)        B = Wq (N x K, K-major)
+//     dX        dX = Gq  Wq        A = Gq (M x N, K-major)        B = Wq (N x K, MN-major)
+//     dW        dW = Gq^T Xq       A = Gq (M x N, MN-major)       B = Xq (M x K, MN-major)
+// "K-major" = the contraction index is the contiguous one in global memory; "MN-major" = the
+// output index is contiguous.  Both are consumed in place: the shared-memory matrix descriptors
+// and the a_major / b_major bits of the instruction descriptor select the layout, so no operand
+// is ever transposed in HBM.
+//
+// Roofline: tensor pipe; 2*M*N*K flops per launch.
+//
+// One persistent CTA per SM, 192 threads:
+//   warp 0      TMA producer (one lane): 4-stage ring of {A 128x64, B 256x64} bf16 tiles, 128-byte
+//               swizzle, one mbarrier per stage armed with the stage's byte count
+//   warp 1      allocates TMEM (512 columns = two 128x256 fp32 accumulators); one lane issues
+//               tcgen05.mma (cta_group::1, M128 N256 K16) and commits stage-free / tile-done barriers
+//   warps 2..5  epilogue: tcgen05.ld of the finished accumulator (each warp its 32 TMEM lanes),
+//               bias add, conversion, 16-byte global stores; overlaps the next tile's main loop
+//               through the second accumulator.
+// Every wait on an mbarrier is bounded: after kSpinLimit polls the waiting role records an error
+// code in g_gemm_status and all roles leave their loops, TMEM is freed and the kernel returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace axs6 {
+namespace gemm {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;
+constexpr int kBBytes = BN * BK * 2;
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kThreadsGemm = 192;
+constexpr int kTmemCols = 512;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ int g_gemm_status;   // 0 = ok; otherwise the code of the first wait that gave up
+
+struct Params {
+    int M, N, K;              // C is M x N, contraction length K
+    int a_mn, b_mn;           // operand is MN-major
+    void *c;
+    long long ldc;
+    int c_bf16;               // output dtype: 1 bf16, 0 fp32
+    const float *bias;        // length N or null
+    int tiles_m, tiles_n;
+    uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;   // descriptor strides (bytes)
+};
+
+// ------------------------------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false if it gave up (status set) or if another role already failed.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code)
+{
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if (i > 64) {
+            __nanosleep(40);
+            if ((i & 255u) == 0u && *(volatile int *)&g_gemm_status != 0) return false;
+        }
+    }
+    atomicCAS(&g_gemm_status, 0, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Shared-memory matrix descriptor: start address, leading / stride byte offsets (all >> 4),
+// descriptor version 1 (sm_100), 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo)
+{
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor of tcgen05.mma kind::f16: D fp32, A and B bf16, optional MN-major
+// operands, N >> 3 at bit 17, M >> 4 at bit 24.
+__device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn)
+{
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+#define AXS6_TMEM_LD32(taddr, r)                                                                                      \
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                            \
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26," \
+                 "%27,%28,%29,%30,%31}, [%32];"                                                                        \
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),     \
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),            \
+                   "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),          \
+                   "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),          \
+                   "=r"(r[29]), "=r"(r[30]), "=r"(r[31])                                                               \
+                 : "r"(taddr))
+
+// ------------------------------------------------------------------------------------- kernel
+__global__ void __launch_bounds__(kThreadsGemm, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar0 = base + kStages * kStageBytes;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+    auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * kStages + a); };
+    auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * kStages + 2 + a); };
+    const uint32_t tmem_slot = bar0 + 8u * (2 * kStages + 4);
+    uint8_t *smem_gen = smem_raw + (base - smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(smem_gen + kStages * kStageBytes + 8 * (2 * kStages + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_kb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 128); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int m0 = (t / p.tiles_n) * BM, n0 = (t % p.tiles_n) * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, 1)) { ok = false; break; }
+                    mbar_expect_tx(full_bar(s), kStageBytes);
+                    const uint32_t sa = base + s * kStageBytes, sb = sa + kABytes;
+                    const int k0 = kb * BK;
+                    if (!p.a_mn) {
+                        tma_load_2d(sa, &map_a, full_bar(s), k0, m0);                  // box {64 k, 128 rows}
+                    } else {
+                        for (int j = 0; j < BM / 64; ++j)                              // boxes {64 m, 64 k}
+                            tma_load_2d(sa + j * (64 * BK * 2), &map_a, full_bar(s), m0 + 64 * j, k0);
+                    }
+                    if (!p.b_mn) {
+                        tma_load_2d(sb, &map_b, full_bar(s), k0, n0);                  // box {64 k, 256 rows}
+                    } else {
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(sb + j * (64 * BK * 2), &map_b, full_bar(s), n0 + 64 * j, k0);
+                    }
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(p.a_mn, p.b_mn);
+            int s = 0, acc = 0;
+            uint32_t ph = 0, aph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), aph ^ 1u, 2)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_bar(s), ph, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = base + s * kStageBytes, sb = sa + kABytes;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = smem_desc(sa + k * p.a_kstep, p.a_lbo, p.a_sbo);
+                        const uint64_t bd = smem_desc(sb + k * p.b_kstep, p.b_lbo, p.b_sbo);
+                        tc_mma(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(empty_bar(s));            // stage reusable once these MMAs have read it
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit(tfull_bar(acc));              // accumulator complete
+                acc ^= 1;
+                if (acc == 0) aph ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;                         // TMEM lane quarter this warp may read
+        int acc = 0;
+        uint32_t aph = 0;
+        bool ok = true;
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) && (p.ldc % 8 == 0);
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            const int m0 = (t / p.tiles_n) * BM, n0 = (t % p.tiles_n) * BN;
+            if (!mbar_wait(tfull_bar(acc), aph, 4)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                AXS6_TMEM_LD32(taddr + (uint32_t)(c * 32), r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int col0 = n0 + c * 32;
+                if (row < p.M && col0 < p.N) {
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                    if (p.bias) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
+                    }
+                    const bool full = col0 + 32 <= p.N;
+                    if (p.c_bf16) {
+                        __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.c) + (long long)row * p.ldc + col0;
+                        if (full && vec_ok) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+                                    w[j] = *reinterpret_cast<const uint32_t *>(&h);
+                                }
+                                *reinterpret_cast<uint4 *>(dst + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        } else {
+                            for (int i = 0; i < 32; ++i)
+                                if (col0 + i < p.N) dst[i] = __float2bfloat16_rn(v[i]);
+                        }
+                    } else {
+                        float *dst = reinterpret_cast<float *>(p.c) + (long long)row * p.ldc + col0;
+                        if (full && vec_ok) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                        } else {
+                            for (int i = 0; i < 32; ++i)
+                                if (col0 + i < p.N) dst[i] = v[i];
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(tempty_bar(acc));
+            acc ^= 1;
+            if (acc == 0) aph ^= 1u;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements per row, `rows` rows of `ld` elements,
+// box {64, box_rows}, 128-byte swizzle, out-of-bounds reads give zeros.
+static bool make_map(CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t rows, uint64_t ld, uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t gdim[2] = {inner, rows};
+    const cuuint64_t gstride[1] = {ld * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), gdim, gstride, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace gemm
+}  // namespace axs6
+
+// C[M,N] (+ bias[N]) = op(A) * op(B) with bf16 operands and fp32 accumulation.
+//   a_mn = 0: A is (M, K) row-major with leading dimension lda;  a_mn = 1: A is (K, M) row-major.
+//   b_mn = 0: B is (N, K) row-major with leading dimension ldb;  b_mn = 1: B is (K, N) row-major.
+AXS6_API int axs6_gemm_bf16(const void *a, const void *b, void *c, const float *bias, int64_t M, int64_t N, int64_t K,
+                            int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn, int c_dtype,
+                            axs6_stream_t stream)
+{
+    using namespace axs6;
+    using namespace axs6::gemm;
+    if (M < 0 || N < 0 || K < 0 || (a_mn & ~1) || (b_mn & ~1) || !valid_dtype(c_dtype)) return AXS6_ERR_ARG;
+    if (M == 0 || N == 0) return AXS6_OK;
+    if (!a || !b || !c || K == 0) return AXS6_ERR_ARG;
+    if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return AXS6_ERR_UNSUPPORTED;
+    if (lda < (a_mn ? M : K) || ldb < (b_mn ? N : K) || ldc < N) return AXS6_ERR_ARG;
+    if (!aligned16(a) || !aligned16(b) || (lda % 8) || (ldb % 8)) return AXS6_ERR_ALIGN;
+    const DeviceInfo &d = device_info();
+    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+
+    CUtensorMap ma, mb;
+    const bool oka = a_mn ? make_map(&ma, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64)
+                          : make_map(&ma, a, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM);
+    const bool okb = b_mn ? make_map(&mb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64)
+                          : make_map(&mb, b, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BN);
+    if (!oka || !okb) return AXS6_ERR_DEVICE;
+
+    Params p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.a_mn = a_mn; p.b_mn = b_mn;
+    p.c = c; p.ldc = ldc; p.c_bf16 = (c_dtype == AXS6_BF16) ? 1 : 0;
+    p.bias = bias;
+    p.tiles_m = (int)((M + BM - 1) / BM);
+    p.tiles_n = (int)((N + BN - 1) / BN);
+    // K-major, 128-byte swizzle: 8-row groups are 1024 B apart, a K step of 16 elements is 32 B.
+    // MN-major: 64-element chunks of the output index are one TMA box (64 k-rows x 128 B = 8192 B)
+    // apart, 8-k-row groups 1024 B apart, a K step of 16 rows is 2048 B.
+    p.a_lbo = a_mn ? 8192u : 0u; p.a_sbo = 1024u; p.a_kstep = a_mn ? 2048u : 32u;
+    p.b_lbo = b_mn ? 8192u : 0u; p.b_sbo = 1024u; p.b_kstep = b_mn ? 2048u : 32u;
+    if (tune_value(4)) p.a_lbo = p.b_lbo = (uint32_t)tune_value(4);
+    if (tune_value(5)) p.a_sbo = p.b_sbo = (uint32_t)tune_value(5);
+    if (tune_value(6)) { if (a_mn) p.a_kstep = (uint32_t)tune_value(6); if (b_mn) p.b_kstep = (uint32_t)tune_value(6); }
+
+    static bool attr_set[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+            return AXS6_ERR_LAUNCH;
+        attr_set[dev] = true;
+    }
+    int ctas = p.tiles_m * p.tiles_n;
+    if (ctas > d.sms) ctas = d.sms;
+    gemm_bf16_kernel<<<ctas, kThreadsGemm, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(ma, mb, p);
+    count_launch();
+    return check_launch();
+}
+
+// Reads (and clears) the device-side status word of the GEMM kernels: 0 = every wait completed,
+// otherwise the code of the first bounded wait that gave up (1 producer/stage-free, 2 MMA/accumulator-free,
+// 3 MMA/stage-full, 4 epilogue/accumulator-full).  Synchronises the device.
+AXS6_API int axs6_gemm_status(void)
+{
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, axs6::gemm::g_gemm_status, sizeof(int)) != cudaSuccess) return AXS6_ERR_DEVICE;
+    if (v != 0) cudaMemcpyToSymbol(axs6::gemm::g_gemm_status, &zero, sizeof(int));
+    return v;
+}

@@ -57,7 +57,8 @@ int64_t axs6_query(int what);
 
 /* Performance knobs for experiments (process-wide, not needed for correct results):
  * key 0 = cap on resident CTAs per SM of the fake-quantise kernels, key 1 = the same for the
- * pack / unpack kernels; value 0 restores the built-in choice. */
+ * pack / unpack kernels, keys 4-6 = overrides of the GEMM's shared-memory descriptor strides;
+ * value 0 restores the built-in choice. */
 int axs6_tune(int key, int64_t value);
 
 /* Fake-quantise: y = dequantise(quantise(x)) in one pass.
@@ -106,6 +107,28 @@ int axs6_unpack(int layout, const void *in0, const void *in1, const void *in2,
 
 /* Bytes per block record of a byte layout (0 for PLANES or bad arguments). */
 int64_t axs6_record_bytes(int layout, int block);
+
+/* C[M,N] (+ bias[N]) = op(A) * op(B): bf16 operands, fp32 accumulation in tensor memory
+ * (tcgen05), C stored as fp32 or bf16.  This is the GEMM under F.linear / torch.matmul / `@` in
+ * the reference's Linear functions (axs/unified/mixed_precision.py:108, :139, :145;
+ * axs/unified/functional_unified.py:123, :155-160; axs/nn/functional.py:121, :144-145), applied
+ * to operands that are already fake-quantised.
+ *   a_mn = 0: A is (M, K) row-major, leading dimension lda;  a_mn = 1: A is (K, M) row-major.
+ *   b_mn = 0: B is (N, K) row-major, leading dimension ldb;  b_mn = 1: B is (K, N) row-major.
+ * So forward = (0,0) with A = x_q, B = w_q;  dX = (0,1) with A = g_q, B = w_q;
+ * dW = (1,1) with A = g_q, B = x_q (contraction over the rows of both).
+ * A and B must be 16-byte aligned with leading dimensions multiples of 8 elements
+ * (AXS6_ERR_ALIGN otherwise); C may have any alignment. */
+int axs6_gemm_bf16(const void *a, const void *b, void *c, const float *bias,
+                   int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                   int a_mn, int b_mn, int c_dtype, axs6_stream_t stream);
+
+/* Device-side status of the GEMM kernels since the last call of this function: 0 = every
+ * wait inside the kernels completed; n > 0 = a bounded wait gave up (1 TMA producer waiting
+ * for a free stage, 2 MMA issuer waiting for a free accumulator, 3 MMA issuer waiting for a
+ * loaded stage, 4 epilogue waiting for a finished accumulator) and the result is invalid.
+ * Synchronises the device and clears the status. */
+int axs6_gemm_status(void);
 
 #ifdef __cplusplus
 }
