@@ -1,0 +1,216 @@
+// AXS-6 Linear forward and backward as sequences of library kernels on one stream:
+// fake-quantise the operands to bf16 (one HBM pass each), then the tcgen05 GEMMs.
+//
+//   forward   xq = FQ(bf16(x))  wq = FQ(bf16(w))  y = xq wq^T + bias
+//   backward  wq = FQ(bf16(w))  gq = FQ_stochastic(bf16(g))  dx = gq wq  dw = gq^T xq (fp32)
+//             db = column sums of the un-quantised g (fp32)
+// This is the graph of _AXSLinearBF16Function (axs/unified/mixed_precision.py:86-155).  xq is
+// materialised because backward needs it (the reference saves input_q); gq is materialised
+// because dx and dw must see the same stochastic rounding (the reference quantises once).
+// Also here: the cast kernel for operands that are not quantised and the column-sum kernels.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace axs6 {
+
+// ------------------------------------------------------------------------------ cast to bf16
+// y(bf16) = x (fp32 or bf16), row-major with leading dimensions; 8 values per thread when
+// aligned, scalar otherwise.
+template <typename Tin>
+__global__ void __launch_bounds__(256) cast_bf16_kernel(const Tin *x, __nv_bfloat16 *y, int64_t rows, int64_t cols,
+                                                        int64_t ldx, int64_t ldy, int vec)
+{
+    if (vec) {
+        const int64_t cpr = cols / 8, total = rows * cpr;
+        for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < total; c += (int64_t)gridDim.x * blockDim.x) {
+            const int64_t r = c / cpr, col = (c - r * cpr) * 8;
+            uint4 out;
+            if (sizeof(Tin) == 4) {
+                const float4 a = *reinterpret_cast<const float4 *>(x + r * ldx + col);
+                const float4 b = *reinterpret_cast<const float4 *>(x + r * ldx + col + 4);
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(a.x, a.y), h1 = __floats2bfloat162_rn(a.z, a.w);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(b.x, b.y), h3 = __floats2bfloat162_rn(b.z, b.w);
+                out = make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
+                                 *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
+            } else {
+                out = *reinterpret_cast<const uint4 *>(x + r * ldx + col);
+            }
+            *reinterpret_cast<uint4 *>(y + r * ldy + col) = out;
+        }
+    } else {
+        const int64_t total = rows * cols;
+        for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+            const int64_t r = e / cols, col = e - r * cols;
+            y[r * ldy + col] = __float2bfloat16_rn((float)x[r * ldx + col]);
+        }
+    }
+}
+
+static int cast_to_bf16(const void *x, int dtype, void *y, int64_t rows, int64_t cols, int64_t ldx, int64_t ldy,
+                        cudaStream_t st)
+{
+    const DeviceInfo &d = device_info();
+    const int vec = aligned16(x) && aligned16(y) && cols % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0;
+    int64_t items = vec ? rows * cols / 8 : rows * cols;
+    int64_t ctas = (items + 255) / 256;
+    if (ctas > (int64_t)d.sms * 8) ctas = (int64_t)d.sms * 8;
+    if (ctas < 1) ctas = 1;
+    if (dtype == AXS6_F32)
+        cast_bf16_kernel<float><<<(unsigned)ctas, 256, 0, st>>>(static_cast<const float *>(x), static_cast<__nv_bfloat16 *>(y), rows, cols, ldx, ldy, vec);
+    else
+        cast_bf16_kernel<__nv_bfloat16><<<(unsigned)ctas, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), static_cast<__nv_bfloat16 *>(y), rows, cols, ldx, ldy, vec);
+    count_launch();
+    return check_launch();
+}
+
+// ------------------------------------------------------------------------------ column sums
+// out[n] = sum over rows of g[row, n] in fp32, deterministic: phase 1 writes kSplits partial
+// sums per column (each over a contiguous row range, rows visited in order), phase 2 adds them.
+constexpr int kSplits = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const T *g, float *partial, int64_t rows, int64_t cols, int64_t ld)
+{
+    // CTA: 64 columns x (256/64 = 4 row lanes); grid (ceil(cols/64), kSplits)
+    __shared__ float red[4][64];
+    const int cx = threadIdx.x & 63, ry = threadIdx.x >> 6;
+    const int64_t col = (int64_t)blockIdx.x * 64 + cx;
+    const int64_t per = (rows + kSplits - 1) / kSplits;
+    const int64_t r0 = (int64_t)blockIdx.y * per;
+    const int64_t r1 = r0 + per < rows ? r0 + per : rows;
+    float acc = 0.0f;
+    if (col < cols)
+        for (int64_t r = r0 + ry; r < r1; r += 4) acc += (float)g[r * ld + col];
+    red[ry][cx] = acc;
+    __syncthreads();
+    if (ry == 0 && col < cols)
+        partial[(int64_t)blockIdx.y * cols + col] = (red[0][cx] + red[1][cx]) + (red[2][cx] + red[3][cx]);
+}
+
+__global__ void __launch_bounds__(256) colsum_final_kernel(const float *partial, float *out, int64_t cols)
+{
+    const int64_t col = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= cols) return;
+    float acc = 0.0f;
+    for (int s = 0; s < kSplits; ++s) acc += partial[(int64_t)s * cols + col];
+    out[col] = acc;
+}
+
+static int column_sums(const void *g, int dtype, float *out, float *partial, int64_t rows, int64_t cols, int64_t ld,
+                       cudaStream_t st)
+{
+    dim3 grid((unsigned)((cols + 63) / 64), kSplits);
+    if (dtype == AXS6_F32)
+        colsum_partial_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float *>(g), partial, rows, cols, ld);
+    else
+        colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(g), partial, rows, cols, ld);
+    colsum_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(partial, out, cols);
+    count_launch(2);
+    return check_launch();
+}
+
+static int64_t round_up8(int64_t v) { return (v + 7) / 8 * 8; }
+
+}  // namespace axs6
+
+AXS6_API int axs6_bias_grad(const void *g, int g_dtype, int64_t ldg, int64_t rows, int64_t cols, float *db,
+                            float *db_partial, axs6_stream_t stream)
+{
+    using namespace axs6;
+    if (!valid_dtype(g_dtype) || rows < 0 || cols < 0 || ldg < cols) return AXS6_ERR_ARG;
+    if (cols == 0) return AXS6_OK;
+    if (!g || !db) return AXS6_ERR_ARG;
+    if (!db_partial) return AXS6_ERR_WORKSPACE;
+    const DeviceInfo &d = device_info();
+    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+    return column_sums(g, g_dtype, db, db_partial, rows, cols, ldg, static_cast<cudaStream_t>(stream));
+}
+
+AXS6_API int64_t axs6_linear_workspace_bytes(int what, int64_t M, int64_t N, int64_t K)
+{
+    using namespace axs6;
+    if (M < 0 || N < 0 || K < 0) return -1;
+    switch (what) {
+    case 0: return M * round_up8(K) * 2;            // xq: bf16 (M, round_up(K, 8))
+    case 1: return N * round_up8(K) * 2;            // wq: bf16 (N, round_up(K, 8))
+    case 2: return M * round_up8(N) * 2;            // gq: bf16 (M, round_up(N, 8))
+    case 3: return (int64_t)kSplits * N * 4;        // column-sum partials
+    default: return -1;
+    }
+}
+
+AXS6_API int axs6_linear_fwd(const void *x, int x_dtype, int64_t ldx, const void *w, int w_dtype, int64_t ldw,
+                             const float *bias, void *y, int y_dtype, int64_t ldy, int64_t M, int64_t N, int64_t K,
+                             int block, int grid, uint32_t flags, void *xq, void *wq, axs6_stream_t stream)
+{
+    using namespace axs6;
+    if (!valid_dtype(x_dtype) || !valid_dtype(w_dtype) || !valid_dtype(y_dtype) || !valid_block(block)) return AXS6_ERR_ARG;
+    if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
+    if (M < 0 || N < 0 || K < 0 || ldx < K || ldw < K || ldy < N) return AXS6_ERR_ARG;
+    if (flags & ~(AXS6_LINEAR_QUANTIZE_INPUT)) return AXS6_ERR_ARG;
+    if (M == 0 || N == 0) return AXS6_OK;
+    if (!x || !w || !y || !xq || !wq || K == 0) return AXS6_ERR_ARG;
+    if (!aligned16(xq) || !aligned16(wq)) return AXS6_ERR_ALIGN;
+    const int64_t ldq = round_up8(K);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc = axs6_fq(w, wq, w_dtype, AXS6_BF16, N, K, ldw, ldq, block, grid, AXS6_ROUND_NEAREST,
+                     AXS6_FLAG_INPUT_VIA_BF16, 0, 0, stream);
+    if (rc) return rc;
+    if (flags & AXS6_LINEAR_QUANTIZE_INPUT)
+        rc = axs6_fq(x, xq, x_dtype, AXS6_BF16, M, K, ldx, ldq, block, grid, AXS6_ROUND_NEAREST,
+                     AXS6_FLAG_INPUT_VIA_BF16, 0, 0, stream);
+    else
+        rc = cast_to_bf16(x, x_dtype, xq, M, K, ldx, ldq, st);
+    if (rc) return rc;
+    return axs6_gemm_bf16(xq, wq, y, bias, M, N, K, ldq, ldq, ldy, 0, 0, y_dtype, stream);
+}
+
+AXS6_API int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void *xq, const void *w, int w_dtype,
+                             int64_t ldw, void *dx, int dx_dtype, int64_t lddx, float *dw, int64_t lddw, float *db,
+                             int64_t M, int64_t N, int64_t K, int block, int grid, uint32_t flags, uint64_t seed,
+                             uint64_t offset, const float *noise, void *gq, void *wq, float *db_partial,
+                             axs6_stream_t stream)
+{
+    using namespace axs6;
+    if (!valid_dtype(g_dtype) || !valid_dtype(w_dtype) || !valid_block(block)) return AXS6_ERR_ARG;
+    if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
+    if (M < 0 || N < 0 || K < 0 || ldg < N) return AXS6_ERR_ARG;
+    if (flags & ~(AXS6_LINEAR_QUANTIZE_GRAD)) return AXS6_ERR_ARG;
+    if (M == 0 || N == 0 || K == 0) return AXS6_OK;
+    if (!g || !gq) return AXS6_ERR_ARG;
+    if (dx && (!w || !wq || !valid_dtype(dx_dtype) || lddx < K || ldw < K)) return AXS6_ERR_ARG;
+    if (dw && (!xq || lddw < K)) return AXS6_ERR_ARG;
+    if (db && !db_partial) return AXS6_ERR_WORKSPACE;
+    if (!aligned16(gq) || (wq && !aligned16(wq)) || (xq && !aligned16(xq))) return AXS6_ERR_ALIGN;
+    const int64_t ldq = round_up8(K), ldgq = round_up8(N);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc;
+    if (flags & AXS6_LINEAR_QUANTIZE_GRAD) {
+        rc = noise ? axs6_fq_with_noise(g, gq, g_dtype, AXS6_BF16, M, N, ldg, ldgq, block, grid,
+                                        AXS6_FLAG_INPUT_VIA_BF16, noise, stream)
+                   : axs6_fq(g, gq, g_dtype, AXS6_BF16, M, N, ldg, ldgq, block, grid, AXS6_ROUND_STOCHASTIC,
+                             AXS6_FLAG_INPUT_VIA_BF16, seed, offset, stream);
+    } else {
+        rc = cast_to_bf16(g, g_dtype, gq, M, N, ldg, ldgq, st);
+    }
+    if (rc) return rc;
+    if (dx) {
+        rc = axs6_fq(w, wq, w_dtype, AXS6_BF16, N, K, ldw, ldq, block, grid, AXS6_ROUND_NEAREST,
+                     AXS6_FLAG_INPUT_VIA_BF16, 0, 0, stream);
+        if (rc) return rc;
+        // dx (M, K) = gq (M, N) * wq (N, K): contraction over N; wq is (contraction, output) row-major
+        rc = axs6_gemm_bf16(gq, wq, dx, nullptr, M, K, N, ldgq, ldq, lddx, 0, 1, dx_dtype, stream);
+        if (rc) return rc;
+    }
+    if (dw) {
+        // dw (N, K) = gq^T (N, M) * xq (M, K): contraction over M; both operands (contraction, output) row-major
+        rc = axs6_gemm_bf16(gq, xq, dw, nullptr, N, K, M, ldgq, ldq, lddw, 1, 1, AXS6_F32, stream);
+        if (rc) return rc;
+    }
+    if (db) {
+        rc = axs6_bias_grad(g, g_dtype, ldg, M, N, db, db_partial, stream);
+        if (rc) return rc;
+    }
+    return AXS6_OK;
+}

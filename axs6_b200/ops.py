@@ -188,3 +188,110 @@ def unpack(layout: int, parts, rows: int, cols: int, block_size: int = 32, grid:
     _lib.check("axs6_unpack", st)
     del keep
     return y
+
+
+# ------------------------------------------------------------------------------------------ linear
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, a_mn: bool = False,
+              b_mn: bool = False, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """C = op(A) op(B) on the tensor cores.  ``a`` is (M, K) (or (K, M) with ``a_mn``), ``b`` is
+    (N, K) (or (K, N) with ``b_mn``); both bf16, 2-D, unit inner stride."""
+    _check_input(a, "gemm_bf16")
+    _check_input(b, "gemm_bf16")
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
+    if a.stride(1) != 1 or a.stride(0) % 8 or a.data_ptr() % 16:
+        a = _padded_copy(a)
+    if b.stride(1) != 1 or b.stride(0) % 8 or b.data_ptr() % 16:
+        b = _padded_copy(b)
+    M, K = (a.shape[1], a.shape[0]) if a_mn else a.shape
+    N, K2 = (b.shape[1], b.shape[0]) if b_mn else b.shape
+    assert K == K2, "contraction lengths differ"
+    c = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    bias_f = None
+    if bias is not None:
+        bias_f = bias.to(device=a.device, dtype=torch.float32).contiguous()
+    with _on(a.device):
+        st = _lib.load().axs6_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(),
+                                        bias_f.data_ptr() if bias_f is not None else None, M, N, K,
+                                        a.stride(0) if a.shape[0] > 1 else max(a.shape[1], 8),
+                                        b.stride(0) if b.shape[0] > 1 else max(b.shape[1], 8), N,
+                                        int(a_mn), int(b_mn), _DT[out_dtype], _stream(a.device))
+    _lib.check("axs6_gemm_bf16", st)
+    return c
+
+
+def _padded_copy(t: torch.Tensor) -> torch.Tensor:
+    """Copy into a buffer whose rows start 16-byte aligned (row length rounded up to 8 elements)."""
+    rows, cols = t.shape
+    ld = (cols + 7) // 8 * 8
+    buf = torch.zeros((rows, ld), dtype=t.dtype, device=t.device)
+    buf[:, :cols].copy_(t)
+    return buf[:, :cols]
+
+
+def _ws(what: int, M: int, N: int, K: int, dev, dtype=torch.uint8) -> torch.Tensor:
+    n = int(_lib.load().axs6_linear_workspace_bytes(what, M, N, K))
+    return torch.empty(max(n, 16), dtype=torch.uint8, device=dev)
+
+
+def linear_fwd(x2: torch.Tensor, w: torch.Tensor, bias_f32: torch.Tensor | None, block_size: int, grid: int,
+               quantize_input: bool, out_dtype: torch.dtype):
+    """-> (y (M, N), xq workspace holding the bf16 activations that backward needs)."""
+    M, K = x2.shape
+    N = w.shape[0]
+    dev = x2.device
+    xq = _ws(0, M, N, K, dev)
+    wq = _ws(1, M, N, K, dev)
+    y = torch.empty((M, N), dtype=out_dtype, device=dev)
+    flags = _lib.LINEAR_QUANTIZE_INPUT if quantize_input else 0
+    with _on(dev):
+        st = _lib.load().axs6_linear_fwd(x2.data_ptr(), _DT[x2.dtype], x2.stride(0) if M > 1 else K,
+                                         w.data_ptr(), _DT[w.dtype], w.stride(0) if N > 1 else K,
+                                         bias_f32.data_ptr() if bias_f32 is not None else None,
+                                         y.data_ptr(), _DT[out_dtype], N, M, N, K, block_size, grid, flags,
+                                         xq.data_ptr(), wq.data_ptr(), _stream(dev))
+    _lib.check("axs6_linear_fwd", st)
+    return y, xq
+
+
+def linear_bwd(g2: torch.Tensor, xq: torch.Tensor, w: torch.Tensor, M: int, N: int, K: int, block_size: int,
+               grid: int, quantize_grad: bool, need_dx: bool, need_dw: bool, need_db: bool,
+               dx_dtype: torch.dtype = torch.bfloat16, noise: torch.Tensor | None = None):
+    """-> (dx (M, K) or None, dw fp32 (N, K) or None, db fp32 (N,) or None)."""
+    dev = g2.device
+    dx = torch.empty((M, K), dtype=dx_dtype, device=dev) if need_dx else None
+    dw = torch.empty((N, K), dtype=torch.float32, device=dev) if need_dw else None
+    db = torch.empty((N,), dtype=torch.float32, device=dev) if need_db else None
+    gq = _ws(2, M, N, K, dev)
+    wq = _ws(1, M, N, K, dev) if need_dx else None
+    part = _ws(3, M, N, K, dev) if need_db else None
+    seed, off = (0, 0)
+    nz = None
+    if quantize_grad:
+        if noise is not None:
+            nz = noise.to(device=dev, dtype=torch.float32).contiguous()
+        else:
+            seed, off = next_philox(M * (-(-N // block_size)) * block_size)
+    flags = _lib.LINEAR_QUANTIZE_GRAD if quantize_grad else 0
+    with _on(dev):
+        st = _lib.load().axs6_linear_bwd(
+            g2.data_ptr(), _DT[g2.dtype], g2.stride(0) if M > 1 else N, xq.data_ptr() if need_dw else None,
+            w.data_ptr(), _DT[w.dtype], w.stride(0) if N > 1 else K,
+            dx.data_ptr() if need_dx else None, _DT[dx_dtype], K, dw.data_ptr() if need_dw else None, K,
+            db.data_ptr() if need_db else None, M, N, K, block_size, grid, flags, seed, off,
+            nz.data_ptr() if nz is not None else None, gq.data_ptr(), wq.data_ptr() if wq is not None else None,
+            part.data_ptr() if part is not None else None, _stream(dev))
+    _lib.check("axs6_linear_bwd", st)
+    return dx, dw, db
+
+
+def bias_grad(g: torch.Tensor) -> torch.Tensor:
+    """fp32 column sums of a 2-D fp32 / bf16 gradient (deterministic order)."""
+    _check_input(g, "bias_grad")
+    g2, rows, cols, ld = _as_rows(g)
+    out = torch.empty((cols,), dtype=torch.float32, device=g.device)
+    part = _ws(3, 0, cols, 0, g.device)
+    with _on(g.device):
+        st = _lib.load().axs6_bias_grad(g2.data_ptr(), _DT[g2.dtype], ld, rows, cols, out.data_ptr(), part.data_ptr(),
+                                        _stream(g.device))
+    _lib.check("axs6_bias_grad", st)
+    return out

@@ -1,0 +1,147 @@
+"""AXS-6 Linear with bf16 tensor-core compute and fp32 master weights.
+
+Same names, arguments and dtypes as ``axs/unified/mixed_precision.py``: the autograd function
+(:65-155), ``axs_linear_mixed_precision`` (:158-185), the module ``AXSLinearMixedPrecision``
+(:193-269) and ``convert_to_axs_mixed_precision`` (:277-349).  Forward and backward each run as
+one C-ABI call: fake-quantise kernels for the operands, then the tcgen05 GEMMs.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..core import DEFAULT_BLOCK_SIZE, VALID_BLOCK_SIZES
+
+# Test hook: when set to a tensor, the next backward uses these U[0,1) draws for the gradient's
+# stochastic rounding (padded (M, nblk, block) layout) instead of the Philox stream.
+_noise_for_next_backward: torch.Tensor | None = None
+
+
+def _rows(t: torch.Tensor) -> torch.Tensor:
+    t2 = t.reshape(-1, t.shape[-1])
+    if t2.dtype not in (torch.float32, torch.bfloat16):
+        t2 = t2.float()
+    if t2.stride(-1) != 1 or (t2.shape[0] > 1 and t2.stride(0) < t2.shape[1]):
+        t2 = t2.contiguous()
+    return t2
+
+
+class _AXSLinearBF16Function(torch.autograd.Function):
+    """Forward: cast to bf16, NF5 fake-quantise weight (always) and input (optionally), bf16
+    GEMM with fp32 accumulation, bf16 output.  Saved: the quantised bf16 input, the leaf weight,
+    the bias.  Backward: recompute the quantised weight, stochastic fake-quantise of the bf16
+    gradient, dX in bf16, dW and db in fp32 (mixed_precision.py:86-155)."""
+
+    @staticmethod
+    def forward(ctx, input, weight, bias, block_size, quantize_input, quantize_grad):
+        if not input.is_cuda:
+            raise RuntimeError("axs_linear_mixed_precision requires CUDA tensors")
+        assert block_size in VALID_BLOCK_SIZES, f"block_size must be one of {VALID_BLOCK_SIZES}"
+        x2 = _rows(input)
+        w = weight if weight.dtype in (torch.float32, torch.bfloat16) else weight.float()
+        w = w if w.stride(-1) == 1 else w.contiguous()
+        b32 = bias.to(torch.bfloat16).float().contiguous() if bias is not None else None   # F.linear sees bf16(bias)
+        y, xq = ops.linear_fwd(x2, w, b32, block_size, ops.GRID_NF5, bool(quantize_input), torch.bfloat16)
+        ctx.save_for_backward(xq, weight, bias)
+        ctx.block_size = block_size
+        ctx.quantize_grad = bool(quantize_grad)
+        ctx.in_shape = input.shape
+        return y.reshape(*input.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        global _noise_for_next_backward
+        xq, weight, bias = ctx.saved_tensors
+        N, K = weight.shape
+        g2 = _rows(grad_output)
+        M = g2.shape[0]
+        w = weight if weight.dtype in (torch.float32, torch.bfloat16) else weight.float()
+        w = w if w.stride(-1) == 1 else w.contiguous()
+        noise, _noise_for_next_backward = _noise_for_next_backward, None
+        dx, dw, db = ops.linear_bwd(g2, xq, w, M, N, K, ctx.block_size, ops.GRID_NF5, ctx.quantize_grad,
+                                    ctx.needs_input_grad[0], ctx.needs_input_grad[1],
+                                    bias is not None and ctx.needs_input_grad[2], torch.bfloat16, noise)
+        if dx is not None:
+            dx = dx.reshape(ctx.in_shape)
+        return dx, dw, db, None, None, None
+
+
+def axs_linear_mixed_precision(input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                               block_size: int = DEFAULT_BLOCK_SIZE, quantize_input: bool = True,
+                               quantize_grad: bool = True) -> torch.Tensor:
+    """bf16 output ``(*, out_features)``; fp32 weight gradient (mixed_precision.py:158-185)."""
+    return _AXSLinearBF16Function.apply(input, weight, bias, block_size, quantize_input, quantize_grad)
+
+
+class AXSLinearMixedPrecision(nn.Module):
+    """Drop-in ``nn.Linear`` replacement: fp32 master weights, AXS-6 NF5 fake-quantised bf16
+    compute (mixed_precision.py:193-269).  ``_warmup_active`` bypasses quantisation."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True,
+                 block_size: int = DEFAULT_BLOCK_SIZE, quantize_input: bool = True,
+                 quantize_grad: bool = True) -> None:
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.block_size = block_size
+        self.quantize_input = quantize_input
+        self.quantize_grad = quantize_grad
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        if bias:
+            self.bias = nn.Parameter(torch.empty(out_features))
+        else:
+            self.register_parameter("bias", None)
+        self._warmup_active: bool = False
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
+        if self.bias is not None:
+            bound = 1 / math.sqrt(self.weight.shape[1])
+            nn.init.uniform_(self.bias, -bound, bound)
+
+    def forward(self, input: torch.Tensor) -> torch.Tensor:
+        if self._warmup_active:
+            return F.linear(input.to(torch.bfloat16), self.weight.to(torch.bfloat16),
+                            self.bias.to(torch.bfloat16) if self.bias is not None else None)
+        return axs_linear_mixed_precision(input, self.weight, self.bias, self.block_size, self.quantize_input,
+                                          self.quantize_grad)
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, "
+                f"bias={self.bias is not None}, block_size={self.block_size}, "
+                f"quant_input={self.quantize_input}, quant_grad={self.quantize_grad}, mixed_precision=bf16")
+
+
+def convert_to_axs_mixed_precision(model: nn.Module, block_size: int = DEFAULT_BLOCK_SIZE,
+                                   quantize_input: bool = True, quantize_grad: bool = True,
+                                   skip_layers: set[str] | None = None, inplace: bool = False) -> nn.Module:
+    """Swap every ``nn.Linear`` for :class:`AXSLinearMixedPrecision`, keeping the parameters
+    (mixed_precision.py:277-349)."""
+    import copy
+    if not inplace:
+        model = copy.deepcopy(model)
+    skip = skip_layers or set()
+
+    def swap(parent: nn.Module, prefix: str) -> None:
+        for name, child in list(parent.named_children()):
+            full = f"{prefix}.{name}" if prefix else name
+            if full in skip:
+                continue
+            if isinstance(child, nn.Linear) and not isinstance(child, AXSLinearMixedPrecision):
+                new = AXSLinearMixedPrecision(child.in_features, child.out_features, child.bias is not None,
+                                              block_size, quantize_input, quantize_grad)
+                new = new.to(child.weight.device)
+                new.weight = child.weight
+                if child.bias is not None:
+                    new.bias = child.bias
+                setattr(parent, name, new)
+            else:
+                swap(child, full)
+
+    swap(model, "")
+    return model

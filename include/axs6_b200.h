@@ -41,6 +41,9 @@ enum { AXS6_LAYOUT_PLANES = 0, /* AXSTensor planes: u8 exponent (rows,nblk), u8 
                                        `weight.to(bfloat16)` of the mixed-precision Linear
                                        (axs/unified/mixed_precision.py:96-100) fused in    */
 
+#define AXS6_LINEAR_QUANTIZE_INPUT 1u /* fake-quantise the activations (else only cast to bf16) */
+#define AXS6_LINEAR_QUANTIZE_GRAD 2u  /* fake-quantise the upstream gradient, stochastic rounding */
+
 #define AXS6_OK 0
 #define AXS6_ERR_ARG (-1)         /* null pointer, negative size, bad enum, bad block size  */
 #define AXS6_ERR_ALIGN (-2)       /* pointer or leading dimension violates a stated alignment */
@@ -129,6 +132,45 @@ int axs6_gemm_bf16(const void *a, const void *b, void *c, const float *bias,
  * loaded stage, 4 epilogue waiting for a finished accumulator) and the result is invalid.
  * Synchronises the device and clears the status. */
 int axs6_gemm_status(void);
+
+/* AXS-6 Linear with bf16 tensor-core compute: the graph of _AXSLinearBF16Function
+ * (axs/unified/mixed_precision.py:86-155), also reached through accelerated_linear /
+ * triton_fused_linear (axs/unified/backend.py:540-618, axs/unified/triton_kernels.py:385-482).
+ *
+ * Forward:  xq = FQ(bf16(x)) (or bf16(x) without AXS6_LINEAR_QUANTIZE_INPUT), wq = FQ(bf16(w)),
+ *           y (M,N) = xq wq^T + bias, fp32 accumulation, y stored as y_dtype.
+ * x is (M,K), w is (N,K); bias (fp32, length N) may be NULL.  xq and wq are caller-owned bf16
+ * buffers of axs6_linear_workspace_bytes(0 | 1, M, N, K) bytes, 16-byte aligned, row length
+ * round_up(K, 8); xq must be kept for the backward call (the reference saves input_q). */
+int axs6_linear_fwd(const void *x, int x_dtype, int64_t ldx, const void *w, int w_dtype, int64_t ldw,
+                    const float *bias, void *y, int y_dtype, int64_t ldy,
+                    int64_t M, int64_t N, int64_t K, int block, int grid, uint32_t flags,
+                    void *xq, void *wq, axs6_stream_t stream);
+
+/* Backward:  wq = FQ(bf16(w)) (recomputed, mixed_precision.py:130), gq = FQ_stochastic(bf16(g))
+ *            (or bf16(g) without AXS6_LINEAR_QUANTIZE_GRAD, :133-136), dx (M,K) = gq wq stored as
+ *            dx_dtype (:139), dw (N,K) = gq^T xq in fp32 (:145), db (N) = column sums of the
+ *            un-quantised g in fp32 (:150).  Any of dx, dw, db may be NULL (not needed).
+ * `noise` (may be NULL): U[0,1) draws for the gradient in the padded (M, nblk, block) layout,
+ * instead of the Philox stream (seed, offset).  Workspaces: gq = what 2, wq = what 1,
+ * db_partial = what 3 of axs6_linear_workspace_bytes (db_partial only if db is given). */
+int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void *xq,
+                    const void *w, int w_dtype, int64_t ldw,
+                    void *dx, int dx_dtype, int64_t lddx, float *dw, int64_t lddw, float *db,
+                    int64_t M, int64_t N, int64_t K, int block, int grid, uint32_t flags,
+                    uint64_t seed, uint64_t offset, const float *noise,
+                    void *gq, void *wq, float *db_partial, axs6_stream_t stream);
+
+/* Bias gradient: db[n] = sum over rows of g[row, n], accumulated in fp32 in a fixed order
+ * (deterministic).  Replaces grad_output.float().sum(dim=...) of the Linear backward
+ * (axs/unified/mixed_precision.py:149-153, axs/unified/functional_unified.py:161-165,
+ * axs/nn/functional.py:146).  db_partial: caller-owned scratch of
+ * axs6_linear_workspace_bytes(3, 0, cols, 0) bytes that holds the per-row-range partial sums. */
+int axs6_bias_grad(const void *g, int g_dtype, int64_t ldg, int64_t rows, int64_t cols,
+                   float *db, float *db_partial, axs6_stream_t stream);
+
+/* Bytes of a caller-owned work buffer: what 0 = xq, 1 = wq, 2 = gq, 3 = db_partial. */
+int64_t axs6_linear_workspace_bytes(int what, int64_t M, int64_t N, int64_t K);
 
 #ifdef __cplusplus
 }

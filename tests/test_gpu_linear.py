@@ -1,0 +1,201 @@
+"""GPU parity of the tensor-core GEMM and the AXS-6 Linear (forward + backward), through the
+C ABI.  Tolerance (stated by the task): relative Frobenius error <= 1e-3 against an fp32 matmul
+of the dequantised operands; checked here on the fp32 accumulator output.  bf16 outputs are
+compared with the bf16 rounding of that reference (a bf16 rounding alone costs ~1.7e-3
+relative Frobenius, so they are held to 4e-3)."""
+import importlib
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from gpu_util import to_bits, to_cuda
+
+pytestmark = pytest.mark.gpu
+
+from axs6_b200 import _lib, ops  # noqa: E402
+
+mp = importlib.import_module("axs6_b200.unified.mixed_precision")
+qu = importlib.import_module("axs6_b200.unified.quantize_unified")
+
+TOL = 1e-3
+TOL_BF16_OUT = 4e-3
+
+
+def rel(a: torch.Tensor, b: torch.Tensor) -> float:
+    a, b = a.detach().double(), b.detach().double()
+    return float((a - b).norm() / b.norm())
+
+
+def gemm_status_ok():
+    assert _lib.load().axs6_gemm_status() == 0, "a bounded wait inside the GEMM kernel gave up"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (1000, 776, 520), (1, 8, 8), (130, 40, 72),
+                                   (2048, 1024, 4096)])
+def test_gemm_against_fp32_matmul(M, N, K, a_mn, b_mn):
+    g = torch.Generator().manual_seed(M * 7 + N * 3 + K + a_mn * 2 + b_mn)
+    A = torch.randn((K, M) if a_mn else (M, K), generator=g).to(torch.bfloat16)
+    B = torch.randn((K, N) if b_mn else (N, K), generator=g).to(torch.bfloat16)
+    if (A.shape[1] % 8) or (B.shape[1] % 8):
+        pytest.skip("operand rows are not 16-byte multiples; covered through the padded path below")
+    C = ops.gemm_bf16(A.cuda(), B.cuda(), a_mn=bool(a_mn), b_mn=bool(b_mn))
+    gemm_status_ok()
+    Af = A.float().t() if a_mn else A.float()
+    Bf = B.float() if b_mn else B.float().t()
+    ref = (Af.double() @ Bf.double())
+    assert rel(C.cpu(), ref) < 1e-5
+
+
+def test_gemm_ragged_operands_and_bias_and_bf16_out():
+    g = torch.Generator().manual_seed(1)
+    A = torch.randn(77, 50, generator=g).to(torch.bfloat16)       # rows of 100 bytes: needs the padded copy
+    B = torch.randn(33, 50, generator=g).to(torch.bfloat16)
+    bias = torch.randn(33, generator=g)
+    C = ops.gemm_bf16(A.cuda(), B.cuda(), bias=bias.cuda())
+    gemm_status_ok()
+    ref = A.double() @ B.double().t() + bias.double()
+    assert rel(C.cpu(), ref) < 1e-5
+    Cb = ops.gemm_bf16(A.cuda(), B.cuda(), bias=bias.cuda(), out_dtype=torch.bfloat16)
+    assert Cb.dtype == torch.bfloat16
+    assert torch.equal(Cb.cpu(), C.cpu().to(torch.bfloat16))      # same accumulator, rounded once
+
+
+def test_gemm_rejects_misaligned_operands():
+    lib = _lib.load()
+    a = torch.zeros(64, 72, dtype=torch.bfloat16, device="cuda")
+    c = torch.zeros(64, 64, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.axs6_gemm_bf16(a.data_ptr() + 2, a.data_ptr(), c.data_ptr(), None, 64, 64, 64, 72, 72, 64, 0, 0, 0, st) == -2
+    assert lib.axs6_gemm_bf16(a.data_ptr(), a.data_ptr(), c.data_ptr(), None, 64, 64, 64, 68, 72, 64, 0, 0, 0, st) == -2
+    assert lib.axs6_gemm_bf16(None, a.data_ptr(), c.data_ptr(), None, 64, 64, 64, 72, 72, 64, 0, 0, 0, st) == -1
+
+
+def _oracle_linear(x, w, b, g, noise, qin, qgrad, block=32):
+    """fp32/fp64 restatement of the mixed-precision graph (mixed_precision.py:96-150) on the CPU
+    oracle: returns y, dx, dw, db in float64 computed from the dequantised bf16 operands."""
+    xb = oracle.f32_to_bf16(x) if x.dtype == np.float32 else x
+    wb = oracle.f32_to_bf16(w)
+    xq = oracle.bf16_to_f32(oracle.fused_fake_quantize(xb, block) if qin else xb)
+    wq = oracle.bf16_to_f32(oracle.fused_fake_quantize(wb, block))
+    y = xq.astype(np.float64) @ wq.astype(np.float64).T
+    if b is not None:
+        y = y + oracle.bf16_to_f32(oracle.f32_to_bf16(b)).astype(np.float64)
+    gb = oracle.f32_to_bf16(g)
+    gq = oracle.bf16_to_f32(oracle.fused_fake_quantize(gb, block, noise) if qgrad else gb)
+    dx = gq.astype(np.float64) @ wq.astype(np.float64)
+    dw = gq.astype(np.float64).T @ xq.astype(np.float64)
+    db = g.astype(np.float64).sum(0)
+    return y, dx, dw, db
+
+
+@pytest.mark.parametrize("M,K,N,bias,qin,qgrad", [(256, 128, 96, True, True, True), (40, 96, 64, True, True, False),
+                                                 (48, 128, 32, False, False, True), (24, 50, 24, True, True, True),
+                                                 (1024, 1024, 1024, True, True, True)])
+def test_linear_mixed_precision_vs_oracle(M, K, N, bias, qin, qgrad):
+    rng = np.random.default_rng(M + K + N)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    w = (rng.standard_normal((N, K), dtype=np.float32) * 0.05)
+    b = (rng.standard_normal(N, dtype=np.float32) * 0.1) if bias else None
+    g = rng.standard_normal((M, N), dtype=np.float32)
+    nblk = -(-N // 32)
+    noise = (rng.integers(0, 1 << 24, size=M * nblk * 32).astype(np.float32) * np.float32(2.0 ** -24))
+    xt = torch.from_numpy(x).cuda().requires_grad_(True)
+    wt = torch.from_numpy(w).cuda().requires_grad_(True)
+    bt = torch.from_numpy(b).cuda().requires_grad_(True) if bias else None
+    y = mp.axs_linear_mixed_precision(xt, wt, bt, 32, qin, qgrad)
+    assert y.dtype == torch.bfloat16 and y.shape == (M, N)
+    mp._noise_for_next_backward = torch.from_numpy(noise).cuda() if qgrad else None
+    y.backward(torch.from_numpy(g).cuda().to(torch.bfloat16))
+    gemm_status_ok()
+    # gradient fed to backward is bf16(g): db is the column sum of exactly that tensor
+    g_b = oracle.bf16_to_f32(oracle.f32_to_bf16(g))
+    ry, rdx, rdw, rdb = _oracle_linear(x, w, b, g_b, noise if qgrad else None, qin, qgrad)
+    assert wt.grad.dtype == torch.float32 and xt.grad.dtype == torch.float32
+    assert rel(y.float().cpu(), torch.from_numpy(ry)) < TOL_BF16_OUT
+    assert rel(xt.grad.cpu(), torch.from_numpy(rdx)) < TOL_BF16_OUT       # dX is produced in bf16
+    assert rel(wt.grad.cpu(), torch.from_numpy(rdw)) < TOL                # dW: fp32 accumulator
+    if bias:
+        assert bt.grad.dtype == torch.float32
+        assert rel(bt.grad.cpu(), torch.from_numpy(rdb)) < 1e-5
+
+
+def test_linear_fp32_accumulator_meets_1e_minus_3():
+    """The stated GEMM bar, on the accumulator: y (fp32 out) and dX (fp32 out) against the fp32
+    matmul of the dequantised operands."""
+    rng = np.random.default_rng(5)
+    M, K, N = 512, 1024, 768
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    w = rng.standard_normal((N, K), dtype=np.float32) * 0.02
+    g = rng.standard_normal((M, N), dtype=np.float32)
+    xt, wt = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    y, xq = ops.linear_fwd(xt, wt, None, 32, ops.GRID_NF5, True, torch.float32)
+    dx, dw, _ = ops.linear_bwd(torch.from_numpy(g).cuda(), xq, wt, M, N, K, 32, ops.GRID_NF5, False, True, True, False,
+                               torch.float32)
+    gemm_status_ok()
+    ry, rdx, rdw, _ = _oracle_linear(x, w, None, g, None, True, False)
+    assert rel(y.cpu(), torch.from_numpy(ry)) < 1e-5
+    assert rel(dx.cpu(), torch.from_numpy(rdx)) < 1e-5
+    assert rel(dw.cpu(), torch.from_numpy(rdw)) < 1e-5
+
+
+def test_linear_golden_from_reference(linear_cases, manifest):
+    """Cases recorded by running the reference's mixed-precision Function on the CPU (with the
+    same stochastic draws): outputs agree within the bf16-output tolerance, dtypes as the reference."""
+    for name in ("lin_mixed_a", "lin_mixed_b", "lin_mixed_c"):
+        info = manifest["cases"][name]
+        M = int(np.prod(info["M"])); K = info["K"]; N = info["N"]
+        xb = linear_cases[f"{name}.x"]
+        x = to_cuda(xb.view(np.float32) if xb.dtype == np.uint32 else xb).reshape(*info["M"], K).requires_grad_(True)
+        w = to_cuda(linear_cases[f"{name}.w"].view(np.float32)).reshape(N, K).requires_grad_(True)
+        b = to_cuda(linear_cases[f"{name}.b"].view(np.float32)).requires_grad_(True) if info["bias"] else None
+        g = to_cuda(linear_cases[f"{name}.g"].view(np.float32)).reshape(*info["M"], N)
+        y = mp.axs_linear_mixed_precision(x, w, b, 32, info["quantize_input"], info["quantize_grad"])
+        assert str(y.dtype).endswith(info["y_dtype"])
+        mp._noise_for_next_backward = torch.from_numpy(linear_cases[f"{name}.noise"]).cuda() if info["quantize_grad"] else None
+        y.backward(g.to(y.dtype))
+        mp._noise_for_next_backward = None
+        gemm_status_ok()
+        want_y = torch.from_numpy(linear_cases[f"{name}.y"].view(np.float32)).reshape(y.shape)
+        want_dx = torch.from_numpy(linear_cases[f"{name}.dx"].view(np.float32)).reshape(x.shape)
+        want_dw = torch.from_numpy(linear_cases[f"{name}.dw"].view(np.float32)).reshape(N, K)
+        assert rel(y.float().cpu(), want_y) < TOL_BF16_OUT, name
+        assert rel(x.grad.float().cpu(), want_dx) < TOL_BF16_OUT, name
+        assert rel(w.grad.cpu(), want_dw) < TOL, name
+        assert str(w.grad.dtype).endswith(info["dw_dtype"]) and str(x.grad.dtype).endswith(info["dx_dtype"])
+        if info["bias"]:
+            want_db = torch.from_numpy(linear_cases[f"{name}.db"].view(np.float32))
+            assert rel(b.grad.cpu(), want_db) < 1e-5, name
+
+
+def test_module_and_conversion():
+    torch.manual_seed(0)
+    lin = mp.AXSLinearMixedPrecision(128, 64).cuda()
+    x = torch.randn(4, 10, 128, device="cuda", requires_grad=True)
+    y = lin(x)
+    assert y.shape == (4, 10, 64) and y.dtype == torch.bfloat16
+    y.float().sum().backward()
+    assert lin.weight.grad.dtype == torch.float32 and lin.bias.grad.dtype == torch.float32 and x.grad.shape == x.shape
+    lin._warmup_active = True
+    assert torch.equal(lin(x), torch.nn.functional.linear(x.to(torch.bfloat16), lin.weight.to(torch.bfloat16),
+                                                          lin.bias.to(torch.bfloat16)))
+    net = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 8)).cuda()
+    conv = mp.convert_to_axs_mixed_precision(net)
+    assert isinstance(conv[0], mp.AXSLinearMixedPrecision) and isinstance(conv[2], mp.AXSLinearMixedPrecision)
+    assert conv(torch.randn(5, 32, device="cuda")).shape == (5, 8)
+    with pytest.raises(RuntimeError, match="requires CUDA tensors"):
+        mp.axs_linear_mixed_precision(torch.randn(2, 32), torch.randn(4, 32))
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (33, 70), (1000, 64), (16384, 4096)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_bias_grad_column_sums(rows, cols, dtype):
+    g = torch.randn(rows, cols, generator=torch.Generator().manual_seed(rows + cols)).to(dtype)
+    out = ops.bias_grad(g.cuda())
+    assert out.dtype == torch.float32 and out.shape == (cols,)
+    ref = g.double().sum(0)
+    assert float((out.cpu().double() - ref).abs().max()) <= 1e-5 * max(1.0, float(ref.abs().max())) * (rows ** 0.5)
+    again = ops.bias_grad(g.cuda())
+    assert torch.equal(out, again)          # fixed summation order
