@@ -35,6 +35,7 @@ SIGNATURES = {
     "axs6_gemm_status": (_int, []),
     "axs6_linear_workspace_bytes": (_i64, [_int, _i64, _i64, _i64]),
     "axs6_bias_grad": (_int, [_ptr, _int, _i64, _i64, _i64, _ptr, _ptr, _ptr]),
+    "axs6_bias_grad_static": (_int, [_ptr, _int, _i64, _i64, _i64, _ptr, _ptr]),
     "axs6_linear_fwd": (_int, [_ptr, _int, _i64, _ptr, _int, _i64, _ptr, _ptr, _int, _i64, _i64, _i64, _i64,
                                _int, _int, _u32, _ptr, _ptr, _ptr]),
     "axs6_linear_bwd": (_int, [_ptr, _int, _i64, _ptr, _ptr, _int, _i64, _ptr, _int, _i64, _ptr, _i64, _ptr,

@@ -47,6 +47,7 @@ AXS6_API const char *axs6_strerror(int status)
     case AXS6_ERR_LAUNCH: return "kernel launch failed";
     case AXS6_ERR_WORKSPACE: return "workspace missing or too small";
     case AXS6_ERR_UNSUPPORTED: return "request not supported by this build";
+    case AXS6_ERR_TOO_LARGE: return "size exceeds the fixed capacity of an entry point that allocates nothing";
     default: return "unknown status";
     }
 }

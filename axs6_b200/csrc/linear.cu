@@ -10,6 +10,8 @@
 // Also here: the cast kernel for operands that are not quantised and the column-sum kernels.
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace axs6 {
@@ -213,4 +215,45 @@ AXS6_API int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void
         if (rc) return rc;
     }
     return AXS6_OK;
+}
+
+// ------------------------------------------------------------------------------ bias gradient, no allocation
+// Scratch for axs6_bias_grad_static: the per-row-range partial sums live in this fixed array
+// instead of a caller-supplied buffer.  It is part of the module image, so every GPU that loads
+// the library carries these 2 MiB until the process exits.
+namespace axs6 {
+constexpr int64_t kStaticMaxCols = 16384;
+static __device__ __align__(256) float g_bias_grad_scratch[kSplits * kStaticMaxCols];
+}  // namespace axs6
+
+AXS6_API int axs6_bias_grad_static(const void *g, int g_dtype, int64_t ldg, int64_t rows, int64_t cols, float *db,
+                                   axs6_stream_t stream)
+{
+    using namespace axs6;
+    if (!valid_dtype(g_dtype) || rows < 0 || cols < 0 || ldg < cols) return AXS6_ERR_ARG;
+    if (cols > kStaticMaxCols) return AXS6_ERR_TOO_LARGE;
+    if (cols == 0) return AXS6_OK;
+    if (!g || !db) return AXS6_ERR_ARG;
+    const DeviceInfo &d = device_info();
+    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+
+    // In host code the array's name is only a handle; the address the kernels need comes from
+    // cudaGetSymbolAddress, looked up once per device while that device is current.
+    static float *scratch_of_device[64];
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return AXS6_ERR_DEVICE;
+    float *scratch;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!scratch_of_device[dev]) {
+            void *ptr = nullptr;
+            if (cudaGetSymbolAddress(&ptr, g_bias_grad_scratch) != cudaSuccess || !ptr) return AXS6_ERR_DEVICE;
+            scratch_of_device[dev] = static_cast<float *>(ptr);
+        }
+        scratch = scratch_of_device[dev];
+    }
+    // Nothing has to start at zero: the first kernel writes every partial sum of the `cols`
+    // columns before the second one reads them, so whatever the previous call left is overwritten.
+    return column_sums(g, g_dtype, db, scratch, rows, cols, ldg, static_cast<cudaStream_t>(stream));
 }

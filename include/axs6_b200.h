@@ -51,6 +51,7 @@ enum { AXS6_LAYOUT_PLANES = 0, /* AXSTensor planes: u8 exponent (rows,nblk), u8 
 #define AXS6_ERR_LAUNCH (-4)      /* kernel launch failed                                       */
 #define AXS6_ERR_WORKSPACE (-5)   /* workspace missing or too small                             */
 #define AXS6_ERR_UNSUPPORTED (-6) /* valid request this build does not implement               */
+#define AXS6_ERR_TOO_LARGE (-7)   /* size beyond the fixed capacity of a *_static entry point   */
 
 const char *axs6_strerror(int status);
 
@@ -168,6 +169,26 @@ int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void *xq,
  * axs6_linear_workspace_bytes(3, 0, cols, 0) bytes that holds the per-row-range partial sums. */
 int axs6_bias_grad(const void *g, int g_dtype, int64_t ldg, int64_t rows, int64_t cols,
                    float *db, float *db_partial, axs6_stream_t stream);
+
+/* Bias gradient for callers that cannot hand over a scratch buffer.  (No counterpart in the
+ * reference: its bias gradient is a torch reduction that allocates freely.)
+ * Same result as axs6_bias_grad, bit for bit, but the partial sums go to a fixed 2 MiB array
+ * inside the library instead of `db_partial`, and the call performs no cudaMalloc / cudaFree
+ * and uses no allocating library routine.  Meant for hosts that own no device allocator at
+ * the point of the call: a plugin behind cgo / JNI / ctypes that is given input and output
+ * pointers only, or a serving process whose memory plan was fixed at start-up and which has
+ * handed all remaining HBM to its own pool, where a late cudaMalloc fails or stalls every
+ * stream with its implicit synchronisation.
+ *   - cols <= 16384, otherwise AXS6_ERR_TOO_LARGE; any number of rows.
+ *   - The first call on each device looks up the array's device address (that device must be
+ *     current, as for every call); make that first call before any stream capture begins.
+ *   - All calls on a device share the one array.  It keeps the previous call's contents, which
+ *     is harmless because each call overwrites every entry it later reads; but two calls whose
+ *     kernels overlap on the GPU (different streams, no ordering) race on it and give garbage.
+ *     Order them on one stream or with events.
+ *   - The array stays resident on every GPU that loads the library until the process exits. */
+int axs6_bias_grad_static(const void *g, int g_dtype, int64_t ldg, int64_t rows, int64_t cols,
+                          float *db, axs6_stream_t stream);
 
 /* Bytes of a caller-owned work buffer: what 0 = xq, 1 = wq, 2 = gq, 3 = db_partial. */
 int64_t axs6_linear_workspace_bytes(int what, int64_t M, int64_t N, int64_t K);
