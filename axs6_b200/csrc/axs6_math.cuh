@@ -290,5 +290,5 @@ AXS6_HD Axs6Philox axs6_philox(uint64_t counter, uint64_t key)
     return o;
 }
 
-// 24 random bits -> U[0,1) on the 2^-24 grid (the grid torch.rand uses for fp32).
-AXS6_HD float axs6_u01(uint32_t r) { return (float)(r >> 8) * 5.9604644775390625e-8f; }
+// 16 random bits -> the midpoints (h + 0.5) / 65536 of a 2^-16 grid on (0, 1): mean exactly 1/2.
+AXS6_HD float axs6_u01_16(uint32_t h) { return ((float)h + 0.5f) * 1.52587890625e-5f; }

@@ -23,6 +23,7 @@ struct CodecArgs {
     const float *noise;
     uint8_t *p0, *p1, *p2;   // planes (exp, sign, mag) or p0 = records
     int rec, hdr;            // record bytes and header bytes of the byte layout
+    int lanes_log2;          // log2(block / 8): lanes that share one block
 };
 
 constexpr int kPlanes = 0, kBytes = 1;
@@ -79,9 +80,12 @@ __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
     if (GRID == AXS6_GRID_NF5) build_reverse_lut(rev);
     __syncthreads();
 
-    const int lanes = a.g.block / kChunk;
-    const int64_t total_blocks = a.g.total_chunks / lanes;
+    const int lg = a.lanes_log2, lanes = 1 << lg;
+    const int64_t total_blocks = a.g.total_chunks >> lg;
     const int64_t step = (int64_t)gridDim.x * kThreads * kU;
+    const int j = threadIdx.x & (lanes - 1);
+    const int lb_thread = (int)threadIdx.x >> lg;           // block of this thread inside a 256-chunk group
+    const int blocks_per_group = kThreads >> lg;
     for (int64_t base = (int64_t)blockIdx.x * kThreads * kU; base < a.g.total_chunks; base += step) {
         uint32_t v[kU][8];
         bool act[kU];
@@ -112,7 +116,6 @@ __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
             int se;
             chunk_uniforms<ROUND>(u, c, act[k], a.seed, a.offset, a.noise);
             chunk_codes<GRID, ROUND>(v[k], code, se, rev, lanes, u);
-            const int j = threadIdx.x & (lanes - 1);
             if (LAYOUT == kPlanes) {
                 if (act[k]) {
                     uint2 sg, mg;
@@ -122,13 +125,13 @@ __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
                     mg.y = (code[4] & 31u) | ((code[5] & 31u) << 8) | ((code[6] & 31u) << 16) | ((code[7] & 31u) << 24);
                     st_stream8(a.p1 + c * kChunk, sg);
                     st_stream8(a.p2 + c * kChunk, mg);
-                    if (j == 0) a.p0[c / lanes] = (uint8_t)se;
+                    if (j == 0) a.p0[c >> lg] = (uint8_t)se;
                 }
             } else {
                 const uint32_t lo = code[0] | (code[1] << 6) | (code[2] << 12) | (code[3] << 18) |
                                     (code[4] << 24) | (code[5] << 30);
                 const uint32_t hi = (code[5] >> 2) | (code[6] << 4) | (code[7] << 10);
-                const int lb = (k * kThreads + (int)threadIdx.x) / lanes;
+                const int lb = k * blocks_per_group + lb_thread;
                 uint8_t *s = stage + lb * a.rec;
                 if (j == 0) {
                     if (a.hdr == 1) {
@@ -145,10 +148,10 @@ __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
         }
         if (LAYOUT == kBytes) {
             __syncthreads();
-            const int64_t blk0 = base / lanes;
-            int64_t nb = (int64_t)(kU * kThreads) / lanes;
-            if (nb > total_blocks - blk0) nb = total_blocks - blk0;
-            const int len = (int)(nb * a.rec);
+            const int64_t blk0 = base >> lg;
+            int nb = (kU * kThreads) >> lg;
+            if ((int64_t)nb > total_blocks - blk0) nb = (int)(total_blocks - blk0);
+            const int len = nb * a.rec;
             uint8_t *dst = a.p0 + blk0 * a.rec;                 // 16-byte aligned by construction
             const int nvec = len >> 4;
             for (int i = threadIdx.x; i < nvec; i += kThreads)
@@ -231,15 +234,18 @@ __global__ void __launch_bounds__(kThreads) unpack_vec_kernel(const CodecArgs a)
     build_levels<GRID>(lev);
     __syncthreads();
 
-    const int lanes = a.g.block / kChunk;
-    const int64_t total_blocks = a.g.total_chunks / lanes;
+    const int lg = a.lanes_log2, lanes = 1 << lg;
+    const int64_t total_blocks = a.g.total_chunks >> lg;
     const int64_t step = (int64_t)gridDim.x * kThreads * kU;
+    const int j = threadIdx.x & (lanes - 1);
+    const int lb_thread = (int)threadIdx.x >> lg;
+    const int blocks_per_group = kThreads >> lg;
     for (int64_t base = (int64_t)blockIdx.x * kThreads * kU; base < a.g.total_chunks; base += step) {
         if (LAYOUT == kBytes) {
-            const int64_t blk0 = base / lanes;
-            int64_t nb = (int64_t)(kU * kThreads) / lanes;
-            if (nb > total_blocks - blk0) nb = total_blocks - blk0;
-            const int len = (int)(nb * a.rec);
+            const int64_t blk0 = base >> lg;
+            int nb = (kU * kThreads) >> lg;
+            if ((int64_t)nb > total_blocks - blk0) nb = (int)(total_blocks - blk0);
+            const int len = nb * a.rec;
             const uint8_t *src = a.p0 + blk0 * a.rec;
             const int nvec = len >> 4;
             for (int i = threadIdx.x; i < nvec; i += kThreads)
@@ -261,7 +267,7 @@ __global__ void __launch_bounds__(kThreads) unpack_vec_kernel(const CodecArgs a)
             if (!act) continue;
             uint32_t se, neg[8], mag[8];
             if (LAYOUT == kPlanes) {
-                se = a.p0[c / lanes];
+                se = a.p0[c >> lg];
                 const uint2 sg = ld_stream8(a.p1 + c * kChunk), mg = ld_stream8(a.p2 + c * kChunk);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -269,8 +275,7 @@ __global__ void __launch_bounds__(kThreads) unpack_vec_kernel(const CodecArgs a)
                     mag[i] = (mg.x >> (8 * i)) & 31u; mag[4 + i] = (mg.y >> (8 * i)) & 31u;
                 }
             } else {
-                const int j = threadIdx.x & (lanes - 1);
-                const int lb = (k * kThreads + (int)threadIdx.x) / lanes;
+                const int lb = k * blocks_per_group + lb_thread;
                 const uint8_t *s = stage + lb * a.rec;
                 se = (a.hdr == 1) ? (uint32_t)s[0] : (((uint32_t)s[0] | ((uint32_t)s[1] << 8)) >> 2) & 0xFFu;
                 s += a.hdr + 6 * j;
@@ -425,6 +430,7 @@ AXS6_API int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, 
     a.p0 = static_cast<uint8_t *>(out0); a.p1 = static_cast<uint8_t *>(out1); a.p2 = static_cast<uint8_t *>(out2);
     a.rec = (int)axs6_record_bytes(layout, block);
     a.hdr = layout == AXS6_LAYOUT_SPEC ? 2 : 1;
+    a.lanes_log2 = block == 32 ? 2 : (block == 16 ? 1 : 0);
     const bool vec = aligned16(x) && (cols % kChunk == 0) && (ldx % kChunk == 0) && aligned16(out0) &&
                      (!planes || (aligned16(out1) && aligned16(out2))) && (round != kNoise || aligned16(noise));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -455,6 +461,7 @@ AXS6_API int axs6_unpack(int layout, const void *in0, const void *in1, const voi
     a.p2 = const_cast<uint8_t *>(static_cast<const uint8_t *>(in2));
     a.rec = (int)axs6_record_bytes(layout, block);
     a.hdr = layout == AXS6_LAYOUT_SPEC ? 2 : 1;
+    a.lanes_log2 = block == 32 ? 2 : (block == 16 ? 1 : 0);
     const bool vec = aligned16(y) && (cols % kChunk == 0) && (ldy % kChunk == 0) && aligned16(in0) &&
                      (!planes || (aligned16(in1) && aligned16(in2)));
     cudaStream_t st = static_cast<cudaStream_t>(stream);

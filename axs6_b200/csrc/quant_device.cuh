@@ -138,10 +138,10 @@ __device__ __forceinline__ void chunk_uniforms(float (&u)[8], int64_t chunk, boo
                                                uint64_t seed, uint64_t offset, const float *noise)
 {
     if (ROUND == kPhilox) {
-        const uint64_t ctr = offset + (uint64_t)chunk * 2u;
-        const Axs6Philox a = axs6_philox(ctr, seed), b = axs6_philox(ctr + 1u, seed);
+        // one Philox4x32-10 block per chunk: eight 16-bit draws
+        const Axs6Philox a = axs6_philox(offset + (uint64_t)chunk, seed);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { u[i] = axs6_u01(a.r[i]); u[4 + i] = axs6_u01(b.r[i]); }
+        for (int i = 0; i < 4; ++i) { u[2 * i] = axs6_u01_16(a.r[i] & 0xFFFFu); u[2 * i + 1] = axs6_u01_16(a.r[i] >> 16); }
     } else if (ROUND == kNoise) {
         if (active) {
             const float4 a = *reinterpret_cast<const float4 *>(noise + chunk * 8);
@@ -160,8 +160,9 @@ __device__ __forceinline__ float element_uniform(int64_t padded_index, bool acti
                                                  uint64_t seed, uint64_t offset, const float *noise)
 {
     if (ROUND == kPhilox) {
-        const Axs6Philox a = axs6_philox(offset + (uint64_t)(padded_index >> 2), seed);
-        return axs6_u01(a.r[padded_index & 3]);
+        const Axs6Philox a = axs6_philox(offset + (uint64_t)(padded_index >> 3), seed);
+        const uint32_t w = a.r[(padded_index & 7) >> 1];
+        return axs6_u01_16((padded_index & 1) ? (w >> 16) : (w & 0xFFFFu));
     }
     if (ROUND == kNoise) return active ? noise[padded_index] : 0.0f;
     return 0.0f;

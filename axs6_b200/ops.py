@@ -23,7 +23,7 @@ _philox_offset = 0
 def next_philox(n_draws: int) -> tuple[int, int]:
     global _philox_offset
     off = _philox_offset
-    _philox_offset += (n_draws + 3) // 4
+    _philox_offset += (n_draws + 7) // 8
     return torch.initial_seed() & 0xFFFFFFFFFFFFFFFF, off
 
 

@@ -1,6 +1,6 @@
 """Runs ONE kernel of the library a few times on a small, larger-than-L2 case, for profilers.
 
-    python -m axs6_b200.profile_case {fq_f32|fq_bf16|pack_wire|unpack_wire} [launches]
+    python -m axs6_b200.profile_case {fq_f32|fq_bf16|fq_bf16_stochastic|pack_wire|unpack_wire|gemm_fwd|gemm_dx|gemm_dw} [launches]
 
 Device footprint stays under 1 GB so that a multi-pass capture finishes quickly.
 """
@@ -39,11 +39,25 @@ def main() -> None:
         assert lib.axs6_pack(x.data_ptr(), 1, rows, cols, cols, 32, 1, 0, 0, 0, 0, None, 1, w.data_ptr(), None, None, st) == 0
         y = torch.empty(rows, cols, device=dev)
         run = lambda: lib.axs6_unpack(1, w.data_ptr(), None, None, y.data_ptr(), 0, rows, cols, cols, 32, 1, st)
+    elif what == "fq_bf16_stochastic":
+        x = torch.randn(rows, cols, generator=g, device=dev).to(torch.bfloat16)
+        y = torch.empty_like(x)
+        run = lambda: lib.axs6_fq(x.data_ptr(), y.data_ptr(), 1, 1, rows, cols, cols, cols, 32, 1, 1, 0, 99, 0, st)
+    elif what in ("gemm_fwd", "gemm_dx", "gemm_dw"):
+        M, N, K = 8192, 4096, 4096                 # operands 64 + 32 MiB, output 64 MiB
+        a_mn, b_mn = {"gemm_fwd": (0, 0), "gemm_dx": (0, 1), "gemm_dw": (1, 1)}[what]
+        a = torch.randn((K, M) if a_mn else (M, K), generator=g, device=dev).to(torch.bfloat16)
+        b = torch.randn((K, N) if b_mn else (N, K), generator=g, device=dev).to(torch.bfloat16)
+        c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        run = lambda: lib.axs6_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), None, M, N, K, a.stride(0), b.stride(0),
+                                         N, a_mn, b_mn, 1, st)
     else:
         raise SystemExit(f"unknown case {what}")
     for _ in range(n):
         assert run() == 0
     torch.cuda.synchronize()
+    if what.startswith("gemm"):
+        assert lib.axs6_gemm_status() == 0
     print(f"{what}: {n} launches ok")
 
 

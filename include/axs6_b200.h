@@ -70,8 +70,8 @@ int axs6_tune(int key, int64_t value);
  * launcher triton_fused_fake_quantize (axs/unified/triton_kernels.py:295-370) and, with
  * grid = AXS6_GRID_UNIFORM, dequantize(quantize(x)) of axs/core.py:294-403 as used by
  * axs/nn/functional.py:46-53.  Nearest rounding is bit-exact with the reference's eager
- * CPU result.  Stochastic rounding draws U[0,1) per element from Philox4x32-10 keyed by
- * `seed`, counter = `offset` + padded element index / 4.
+ * CPU result.  Stochastic rounding draws one 16-bit uniform per element from Philox4x32-10 keyed
+ * by `seed`: counter = `offset` + padded element index / 8, eight draws per 128-bit block.
  * Any alignment is accepted; 16-byte aligned pointers with cols and both leading
  * dimensions multiples of 8 elements take the vectorised path. */
 int axs6_fq(const void *x, void *y, int in_dtype, int out_dtype,
