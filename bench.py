@@ -292,7 +292,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
 
 # DRAM bytes (read + write) of one launch of the headline kernel from the ncu capture summarised
 # under profiles/ (captured on a 4096 x 8192 case and scaled by rows; traffic grows with rows).
-TRAFFIC_BYTES_PER_LAUNCH: dict[int, float] = {}
+TRAFFIC_BYTES_PER_LAUNCH: dict[int, float] = {32768: 4 * 486.1e6, 16384: 2 * 486.1e6, 8192: 486.1e6, 4096: 243.05e6}
 
 
 def cpu_baseline(x) -> dict:
