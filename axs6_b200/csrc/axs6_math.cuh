@@ -207,6 +207,22 @@ AXS6_HD int axs6_uniform_mag_fast(float ax, float g_over_s) { return __float2int
 AXS6_HD int axs6_uniform_mag_fast(float ax, float g_over_s) { return (int)nearbyintf(AXS6_MUL(ax, g_over_s)); }
 #endif
 
+// Dithered index for draws that come from the library's own generator (no bit-level
+// counterpart in the reference, whose draws come from torch's generator): the same dither of
+// +-0.5 LUT steps, evaluated as ONE fused multiply-add trunc(|x| * (1023 / S) + (u - 0.5)).  The
+// sum lies in (-0.5, 1023.5), so truncation already lands in [0, 1023].
+#if defined(__CUDA_ARCH__)
+AXS6_HD int axs6_nf5_index_dithered_fast(float ax, float g_over_s, float u)
+{
+    return __float2int_rz(__fmaf_rn(ax, g_over_s, AXS6_SUB(u, 0.5f)));
+}
+#else
+AXS6_HD int axs6_nf5_index_dithered_fast(float ax, float g_over_s, float u)
+{
+    return (int)fmaf(ax, g_over_s, u - 0.5f);
+}
+#endif
+
 // Uniform-grid magnitude: round-half-even of n * 31, or floor + (u < frac) (core.py:348-359).
 AXS6_HD int axs6_uniform_mag(float n)
 {

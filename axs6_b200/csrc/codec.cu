@@ -46,7 +46,8 @@ __device__ __forceinline__ void chunk_codes(const uint32_t (&v)[8], uint32_t (&c
             int m;
             if (GRID == AXS6_GRID_NF5) {
                 const int idx = (ROUND == kNearest) ? axs6_nf5_index_fast(fabsf(x), c)
-                                                    : axs6_nf5_index_dithered(AXS6_MUL(fabsf(x), s.inv), u[i]);
+                              : (ROUND == kPhilox) ? axs6_nf5_index_dithered_fast(fabsf(x), c, u[i])
+                                                   : axs6_nf5_index_dithered(AXS6_MUL(fabsf(x), s.inv), u[i]);
                 m = rev[idx];
             } else {
                 m = (ROUND == kNearest) ? axs6_uniform_mag_fast(fabsf(x), c)
@@ -190,7 +191,9 @@ __global__ void __launch_bounds__(kThreads) pack_generic_kernel(const CodecArgs 
         const float u = element_uniform<ROUND>(row * padded + pc, in_pad, a.seed, a.offset, a.noise);
         int m;
         if (GRID == AXS6_GRID_NF5) {
-            const int idx = (ROUND == kNearest) ? axs6_nf5_index(n) : axs6_nf5_index_dithered(n, u);
+            const int idx = (ROUND == kNearest) ? axs6_nf5_index(n)
+                          : (ROUND == kPhilox && s.fast) ? axs6_nf5_index_dithered_fast(__uint_as_float(ab), AXS6_MUL(s.inv, 1023.0f), u)
+                                                         : axs6_nf5_index_dithered(n, u);
             m = rev[idx];
         } else {
             m = (ROUND == kNearest) ? axs6_uniform_mag(n) : axs6_uniform_mag_stochastic(n, u);

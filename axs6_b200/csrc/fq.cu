@@ -38,7 +38,8 @@ __device__ __forceinline__ void fq_chunk(const uint32_t (&v)[8], float (&y)[8], 
             for (int i = 0; i < 8; ++i) {
                 const float x = __uint_as_float(v[i]);
                 const int idx = (ROUND == kNearest) ? axs6_nf5_index_fast(fabsf(x), c)
-                                                    : axs6_nf5_index_dithered(AXS6_MUL(fabsf(x), s.inv), u[i]);
+                              : (ROUND == kPhilox) ? axs6_nf5_index_dithered_fast(fabsf(x), c, u[i])
+                                                   : axs6_nf5_index_dithered(AXS6_MUL(fabsf(x), s.inv), u[i]);
                 y[i] = axs6_fq_value_fast(x, tab[idx], s.scale);
             }
         } else {
@@ -141,7 +142,9 @@ __global__ void __launch_bounds__(kThreads) fq_generic_kernel(const FqArgs a)
         if (GRID == AXS6_GRID_NF5) {
             const Axs6Scale s = axs6_scale_fq(amax);
             const float n = axs6_normalise(__uint_as_float(ab), s);
-            const int idx = (ROUND == kNearest) ? axs6_nf5_index(n) : axs6_nf5_index_dithered(n, u);
+            const int idx = (ROUND == kNearest) ? axs6_nf5_index(n)
+                          : (ROUND == kPhilox && s.fast) ? axs6_nf5_index_dithered_fast(__uint_as_float(ab), AXS6_MUL(s.inv, 1023.0f), u)
+                                                         : axs6_nf5_index_dithered(n, u);
             y = axs6_fq_value(v, tab[idx], s.scale);
         } else {
             const Axs6Scale s = axs6_scale_codes(amax);
