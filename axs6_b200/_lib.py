@@ -16,7 +16,8 @@ GRID_UNIFORM, GRID_NF5 = 0, 1
 ROUND_NEAREST, ROUND_STOCHASTIC = 0, 1
 LAYOUT_PLANES, LAYOUT_WIRE, LAYOUT_SPEC = 0, 1, 2
 FLAG_INPUT_VIA_BF16 = 1
-LINEAR_QUANTIZE_INPUT, LINEAR_QUANTIZE_GRAD = 1, 2
+FLAG_OUTPUT_TF32 = 2
+LINEAR_QUANTIZE_INPUT, LINEAR_QUANTIZE_GRAD, LINEAR_COMPUTE_TF32, LINEAR_BIAS_FROM_QUANTIZED = 1, 2, 4, 8
 
 _i64, _int, _u32, _u64, _ptr = ctypes.c_int64, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p
 
@@ -32,6 +33,7 @@ SIGNATURES = {
                          _ptr, _ptr, _ptr, _ptr]),
     "axs6_unpack": (_int, [_int, _ptr, _ptr, _ptr, _ptr, _int, _i64, _i64, _i64, _int, _int, _ptr]),
     "axs6_gemm_bf16": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
+    "axs6_gemm_tf32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "axs6_gemm_status": (_int, []),
     "axs6_linear_workspace_bytes": (_i64, [_int, _i64, _i64, _i64]),
     "axs6_bias_grad": (_int, [_ptr, _int, _i64, _i64, _i64, _ptr, _ptr, _ptr]),
@@ -39,7 +41,8 @@ SIGNATURES = {
     "axs6_linear_fwd": (_int, [_ptr, _int, _i64, _ptr, _int, _i64, _ptr, _ptr, _int, _i64, _i64, _i64, _i64,
                                _int, _int, _u32, _ptr, _ptr, _ptr]),
     "axs6_linear_bwd": (_int, [_ptr, _int, _i64, _ptr, _ptr, _int, _i64, _ptr, _int, _i64, _ptr, _i64, _ptr,
-                               _i64, _i64, _i64, _int, _int, _u32, _u64, _u64, _ptr, _ptr, _ptr, _ptr, _ptr]),
+                               _i64, _i64, _i64, _int, _int, _u32, _u64, _u64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr]),
+    "axs6_transpose_f32": (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
 }
 
 _lib = None

@@ -19,9 +19,18 @@ struct FqArgs {
     int64_t ldx, ldy;
     ChunkGeom g;
     uint32_t via_bf16;
+    uint32_t out_tf32;       // round fp32 results to the nearest TF32 value
     uint64_t seed, offset;
     const float *noise;
 };
+
+// Nearest TF32 value (10-bit mantissa, ties away from zero), returned as fp32.
+__device__ __forceinline__ float round_tf32(float v)
+{
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return __uint_as_float(r);
+}
 
 template <int GRID, int ROUND>
 __device__ __forceinline__ void fq_chunk(const uint32_t (&v)[8], float (&y)[8], const float *tab,
@@ -112,6 +121,10 @@ __global__ void __launch_bounds__(kThreads) fq_vec_kernel(const FqArgs a)
             float u[8], y[8];
             chunk_uniforms<ROUND>(u, cidx[k], act[k], a.seed, a.offset, a.noise);
             fq_chunk<GRID, ROUND>(v[k], y, tab, lanes, u);
+            if (sizeof(Tout) == 4 && a.out_tf32) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) y[i] = round_tf32(y[i]);
+            }
             if (act[k]) ChunkIO<Tout>::store(a.y, yo[k], y);
         }
     }
@@ -152,6 +165,7 @@ __global__ void __launch_bounds__(kThreads) fq_generic_kernel(const FqArgs a)
             const int m = (ROUND == kNearest) ? axs6_uniform_mag(n) : axs6_uniform_mag_stochastic(n, u);
             y = axs6_decode_value((ab != 0u) ? (v >> 31) : 0u, tab[m], s.scale);
         }
+        if (sizeof(Tout) == 4 && a.out_tf32) y = round_tf32(y);
         if (act) ChunkIO<Tout>::store1(a.y, row * a.ldy + pc, y);
     }
 }
@@ -231,7 +245,7 @@ static int fq_entry(const void *x, void *y, int in_dtype, int out_dtype, int64_t
     if (!valid_dtype(in_dtype) || !valid_dtype(out_dtype) || !valid_block(block)) return AXS6_ERR_ARG;
     if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
     if (rows < 0 || cols < 0 || ldx < cols || ldy < cols) return AXS6_ERR_ARG;
-    if (flags & ~AXS6_FLAG_INPUT_VIA_BF16) return AXS6_ERR_ARG;
+    if (flags & ~(AXS6_FLAG_INPUT_VIA_BF16 | AXS6_FLAG_OUTPUT_TF32)) return AXS6_ERR_ARG;
     if (rows == 0 || cols == 0) return AXS6_OK;
     if (!x || !y) return AXS6_ERR_ARG;
     if (round == kNoise && !noise) return AXS6_ERR_ARG;
@@ -243,6 +257,7 @@ static int fq_entry(const void *x, void *y, int in_dtype, int out_dtype, int64_t
     a.g = make_geom(rows, cols, block);
     a.g.flat = (cols % block == 0 && ldx == cols && ldy == cols) ? 1 : 0;
     a.via_bf16 = (flags & AXS6_FLAG_INPUT_VIA_BF16) ? 1u : 0u;
+    a.out_tf32 = (flags & AXS6_FLAG_OUTPUT_TF32) ? 1u : 0u;
     a.seed = seed; a.offset = offset; a.noise = noise;
     const bool vec = aligned16(x) && aligned16(y) && (cols % kChunk == 0) && (ldx % kChunk == 0) &&
                      (ldy % kChunk == 0) && (round != kNoise || aligned16(noise));

@@ -8,6 +8,11 @@
 // and the a_major / b_major bits of the instruction descriptor select the layout, so no operand
 // is ever transposed in HBM.
 //
+// The same kernel is instantiated for fp32 operands consumed as TF32 (kind::tf32: the tensor
+// core reads 10 mantissa bits), used by the fp32 Linear paths where bf16 operands would miss the
+// 1e-3 accuracy bar.  Tile geometry in BYTES is identical (rows of 128 B, K step of 32 B), so
+// a k-block is 64 bf16 or 32 fp32 values.
+//
 // Roofline: tensor pipe; 2*M*N*K flops per launch.
 //
 // One persistent CTA per SM, 192 threads:
@@ -49,6 +54,8 @@ struct Params {
     const float *bias;        // length N or null
     int tiles_m, tiles_n;
     uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;   // descriptor strides (bytes)
+    int bk;                   // values per k-block: 64 (bf16) or 32 (tf32)
+    uint32_t mn_box_bytes;    // bytes of one MN-major TMA box: 128 B x bk rows
 };
 
 // ------------------------------------------------------------------------------------- PTX helpers
@@ -101,11 +108,17 @@ __device__ __forceinline__ void tc_commit(uint32_t bar)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+template <bool kTf32>
 __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+    if (kTf32)
+        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                     " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+                     ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+    else
+        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                     " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                     ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 // Shared-memory matrix descriptor: start address, leading / stride byte offsets (all >> 4),
@@ -116,11 +129,12 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
            (1ull << 46) | (2ull << 61);
 }
 
-// Instruction descriptor of tcgen05.mma kind::f16: D fp32, A and B bf16, optional MN-major
-// operands, N >> 3 at bit 17, M >> 4 at bit 24.
-__device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn)
+// Instruction descriptor of tcgen05.mma: D fp32 (bit 4), A and B format at bits 7 and 10
+// (kind::f16: 1 = bf16; kind::tf32: 2 = tf32), optional MN-major operands (bits 15, 16),
+// N >> 3 at bit 17, M >> 4 at bit 24.
+__device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn, uint32_t fmt)
 {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
            ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
@@ -136,8 +150,9 @@ __device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn)
                  : "r"(taddr))
 
 // ------------------------------------------------------------------------------------- kernel
+template <bool kTf32>
 __global__ void __launch_bounds__(kThreadsGemm, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -152,7 +167,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = p.tiles_m * p.tiles_n;
-    const int num_kb = (p.K + BK - 1) / BK;
+    const int num_kb = (p.K + p.bk - 1) / p.bk;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -181,18 +196,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, 1)) { ok = false; break; }
                     mbar_expect_tx(full_bar(s), kStageBytes);
                     const uint32_t sa = base + s * kStageBytes, sb = sa + kABytes;
-                    const int k0 = kb * BK;
+                    const int k0 = kb * p.bk;
                     if (!p.a_mn) {
                         tma_load_2d(sa, &map_a, full_bar(s), k0, m0);                  // box {64 k, 128 rows}
                     } else {
-                        for (int j = 0; j < BM / 64; ++j)                              // boxes {64 m, 64 k}
-                            tma_load_2d(sa + j * (64 * BK * 2), &map_a, full_bar(s), m0 + 64 * j, k0);
+                        const int per_box = p.bk;                                      // output indices per 128-byte row (= 128 / element size)
+                        for (int j = 0; j < BM / per_box; ++j)                         // boxes {128 B of m, bk rows of k}
+                            tma_load_2d(sa + j * p.mn_box_bytes, &map_a, full_bar(s), m0 + per_box * j, k0);
                     }
                     if (!p.b_mn) {
                         tma_load_2d(sb, &map_b, full_bar(s), k0, n0);                  // box {64 k, 256 rows}
                     } else {
-                        for (int j = 0; j < BN / 64; ++j)
-                            tma_load_2d(sb + j * (64 * BK * 2), &map_b, full_bar(s), n0 + 64 * j, k0);
+                        const int per_box = p.bk;
+                        for (int j = 0; j < BN / per_box; ++j)
+                            tma_load_2d(sb + j * p.mn_box_bytes, &map_b, full_bar(s), n0 + per_box * j, k0);
                     }
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
@@ -201,7 +218,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = instr_desc(p.a_mn, p.b_mn);
+            const uint32_t idesc = instr_desc(p.a_mn, p.b_mn, kTf32 ? 2u : 1u);
             int s = 0, acc = 0;
             uint32_t ph = 0, aph = 0;
             bool ok = true;
@@ -214,10 +231,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     tc_fence_after();
                     const uint32_t sa = base + s * kStageBytes, sb = sa + kABytes;
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k) {
+                    for (int k = 0; k < 4; ++k) {                  // four 32-byte K steps per 128-byte row
                         const uint64_t ad = smem_desc(sa + k * p.a_kstep, p.a_lbo, p.a_sbo);
                         const uint64_t bd = smem_desc(sb + k * p.b_kstep, p.b_lbo, p.b_sbo);
-                        tc_mma(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+                        tc_mma<kTf32>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     tc_commit(empty_bar(s));            // stage reusable once these MMAs have read it
                     if (++s == kStages) { s = 0; ph ^= 1u; }
@@ -322,19 +339,77 @@ static EncodeTiledFn encode_fn()
     return fn;
 }
 
-// 2-D bf16 tensor map: `inner` contiguous elements per row, `rows` rows of `ld` elements,
-// box {64, box_rows}, 128-byte swizzle, out-of-bounds reads give zeros.
-static bool make_map(CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t rows, uint64_t ld, uint32_t box_rows)
+// 2-D tensor map over rows of `inner` contiguous values (`esize` bytes each, `ld` values apart):
+// box = {128 bytes, box_rows}, 128-byte swizzle, out-of-bounds reads give zeros.
+static bool make_map(CUtensorMap *map, const void *ptr, int esize, uint64_t inner, uint64_t rows, uint64_t ld,
+                     uint32_t box_rows)
 {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t gdim[2] = {inner, rows};
-    const cuuint64_t gstride[1] = {ld * 2};
-    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint64_t gstride[1] = {ld * (uint64_t)esize};
+    const cuuint32_t box[2] = {(cuuint32_t)(128 / esize), box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), gdim, gstride, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    return fn(map, esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+              const_cast<void *>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool kTf32>
+static int launch_gemm(const void *a, const void *b, void *c, const float *bias, int64_t M, int64_t N, int64_t K,
+                       int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn, int c_dtype, cudaStream_t stream)
+{
+    constexpr int esize = kTf32 ? 4 : 2;
+    constexpr int bk = 128 / esize;                     // values per k-block
+    if (M < 0 || N < 0 || K < 0 || (a_mn & ~1) || (b_mn & ~1) || !valid_dtype(c_dtype)) return AXS6_ERR_ARG;
+    if (M == 0 || N == 0) return AXS6_OK;
+    if (!a || !b || !c || K == 0) return AXS6_ERR_ARG;
+    if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return AXS6_ERR_UNSUPPORTED;
+    if (lda < (a_mn ? M : K) || ldb < (b_mn ? N : K) || ldc < N) return AXS6_ERR_ARG;
+    if (!aligned16(a) || !aligned16(b) || (lda * esize) % 16 || (ldb * esize) % 16) return AXS6_ERR_ALIGN;
+    const DeviceInfo &d = device_info();
+    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+
+    CUtensorMap ma, mb;
+    const bool oka = a_mn ? make_map(&ma, a, esize, (uint64_t)M, (uint64_t)K, (uint64_t)lda, bk)
+                          : make_map(&ma, a, esize, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM);
+    const bool okb = b_mn ? make_map(&mb, b, esize, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, bk)
+                          : make_map(&mb, b, esize, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BN);
+    if (!oka || !okb) return AXS6_ERR_DEVICE;
+
+    Params p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.a_mn = a_mn; p.b_mn = b_mn;
+    p.c = c; p.ldc = ldc; p.c_bf16 = (c_dtype == AXS6_BF16) ? 1 : 0;
+    p.bias = bias;
+    p.tiles_m = (int)((M + BM - 1) / BM);
+    p.tiles_n = (int)((N + BN - 1) / BN);
+    p.bk = bk;
+    p.mn_box_bytes = 128u * bk;
+    // K-major, 128-byte swizzle: 8-row groups are 1024 B apart, one MMA K step is 32 B.
+    // MN-major: 128-byte chunks of the output index are one TMA box (bk k-rows x 128 B) apart,
+    // groups of 8 k-rows 1024 B apart, one MMA K step (32 B / esize rows) is that many rows x 128 B.
+    const uint32_t mn_kstep = (32u / esize) * 128u;
+    p.a_lbo = a_mn ? p.mn_box_bytes : 0u; p.a_sbo = 1024u; p.a_kstep = a_mn ? mn_kstep : 32u;
+    p.b_lbo = b_mn ? p.mn_box_bytes : 0u; p.b_sbo = 1024u; p.b_kstep = b_mn ? mn_kstep : 32u;
+    if (tune_value(4)) p.a_lbo = p.b_lbo = (uint32_t)tune_value(4);
+    if (tune_value(5)) p.a_sbo = p.b_sbo = (uint32_t)tune_value(5);
+    if (tune_value(6)) { if (a_mn) p.a_kstep = (uint32_t)tune_value(6); if (b_mn) p.b_kstep = (uint32_t)tune_value(6); }
+
+    static bool attr_set[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(gemm_kernel<kTf32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+            return AXS6_ERR_LAUNCH;
+        attr_set[dev] = true;
+    }
+    int ctas = p.tiles_m * p.tiles_n;
+    if (ctas > d.sms) ctas = d.sms;
+    gemm_kernel<kTf32><<<ctas, kThreadsGemm, kSmemBytes, stream>>>(ma, mb, p);
+    count_launch();
+    return check_launch();
 }
 
 }  // namespace gemm
@@ -347,53 +422,19 @@ AXS6_API int axs6_gemm_bf16(const void *a, const void *b, void *c, const float *
                             int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn, int c_dtype,
                             axs6_stream_t stream)
 {
-    using namespace axs6;
-    using namespace axs6::gemm;
-    if (M < 0 || N < 0 || K < 0 || (a_mn & ~1) || (b_mn & ~1) || !valid_dtype(c_dtype)) return AXS6_ERR_ARG;
-    if (M == 0 || N == 0) return AXS6_OK;
-    if (!a || !b || !c || K == 0) return AXS6_ERR_ARG;
-    if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return AXS6_ERR_UNSUPPORTED;
-    if (lda < (a_mn ? M : K) || ldb < (b_mn ? N : K) || ldc < N) return AXS6_ERR_ARG;
-    if (!aligned16(a) || !aligned16(b) || (lda % 8) || (ldb % 8)) return AXS6_ERR_ALIGN;
-    const DeviceInfo &d = device_info();
-    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+    return axs6::gemm::launch_gemm<false>(a, b, c, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, c_dtype,
+                                          static_cast<cudaStream_t>(stream));
+}
 
-    CUtensorMap ma, mb;
-    const bool oka = a_mn ? make_map(&ma, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64)
-                          : make_map(&ma, a, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM);
-    const bool okb = b_mn ? make_map(&mb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64)
-                          : make_map(&mb, b, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BN);
-    if (!oka || !okb) return AXS6_ERR_DEVICE;
-
-    Params p;
-    p.M = (int)M; p.N = (int)N; p.K = (int)K;
-    p.a_mn = a_mn; p.b_mn = b_mn;
-    p.c = c; p.ldc = ldc; p.c_bf16 = (c_dtype == AXS6_BF16) ? 1 : 0;
-    p.bias = bias;
-    p.tiles_m = (int)((M + BM - 1) / BM);
-    p.tiles_n = (int)((N + BN - 1) / BN);
-    // K-major, 128-byte swizzle: 8-row groups are 1024 B apart, a K step of 16 elements is 32 B.
-    // MN-major: 64-element chunks of the output index are one TMA box (64 k-rows x 128 B = 8192 B)
-    // apart, 8-k-row groups 1024 B apart, a K step of 16 rows is 2048 B.
-    p.a_lbo = a_mn ? 8192u : 0u; p.a_sbo = 1024u; p.a_kstep = a_mn ? 2048u : 32u;
-    p.b_lbo = b_mn ? 8192u : 0u; p.b_sbo = 1024u; p.b_kstep = b_mn ? 2048u : 32u;
-    if (tune_value(4)) p.a_lbo = p.b_lbo = (uint32_t)tune_value(4);
-    if (tune_value(5)) p.a_sbo = p.b_sbo = (uint32_t)tune_value(5);
-    if (tune_value(6)) { if (a_mn) p.a_kstep = (uint32_t)tune_value(6); if (b_mn) p.b_kstep = (uint32_t)tune_value(6); }
-
-    static bool attr_set[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-            return AXS6_ERR_LAUNCH;
-        attr_set[dev] = true;
-    }
-    int ctas = p.tiles_m * p.tiles_n;
-    if (ctas > d.sms) ctas = d.sms;
-    gemm_bf16_kernel<<<ctas, kThreadsGemm, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(ma, mb, p);
-    count_launch();
-    return check_launch();
+// Same with fp32 operands consumed as TF32 by the tensor cores (the low 13 mantissa bits of each
+// operand value are ignored; pre-round the operands to TF32 for round-to-nearest behaviour).
+AXS6_API int axs6_gemm_tf32(const void *a, const void *b, void *c, const float *bias, int64_t M, int64_t N, int64_t K,
+                            int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn, int c_dtype,
+                            axs6_stream_t stream)
+{
+    if (a_mn || b_mn) return AXS6_ERR_UNSUPPORTED;      // kind::tf32 gives zeros for MN-major operands on sm_100
+    return axs6::gemm::launch_gemm<true>(a, b, c, bias, M, N, K, lda, ldb, ldc, 0, 0, c_dtype,
+                                         static_cast<cudaStream_t>(stream));
 }
 
 // Reads (and clears) the device-side status word of the GEMM kernels: 0 = every wait completed,

@@ -66,6 +66,66 @@ static int cast_to_bf16(const void *x, int dtype, void *y, int64_t rows, int64_t
     return check_launch();
 }
 
+// y(fp32, rounded to the nearest TF32 value) = x (fp32 or bf16): the operand copy of the TF32
+// Linear for tensors that are not quantised.
+template <typename Tin>
+__global__ void __launch_bounds__(256) cast_tf32_kernel(const Tin *x, float *y, int64_t rows, int64_t cols,
+                                                        int64_t ldx, int64_t ldy)
+{
+    const int64_t total = rows * cols;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = e / cols, col = e - r * cols;
+        uint32_t t;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"((float)x[r * ldx + col]));
+        y[r * ldy + col] = __uint_as_float(t);
+    }
+}
+
+static int cast_to_tf32(const void *x, int dtype, void *y, int64_t rows, int64_t cols, int64_t ldx, int64_t ldy,
+                        cudaStream_t st)
+{
+    const DeviceInfo &d = device_info();
+    int64_t ctas = (rows * cols + 255) / 256;
+    if (ctas > (int64_t)d.sms * 8) ctas = (int64_t)d.sms * 8;
+    if (ctas < 1) ctas = 1;
+    if (dtype == AXS6_F32)
+        cast_tf32_kernel<float><<<(unsigned)ctas, 256, 0, st>>>(static_cast<const float *>(x), static_cast<float *>(y), rows, cols, ldx, ldy);
+    else
+        cast_tf32_kernel<__nv_bfloat16><<<(unsigned)ctas, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), static_cast<float *>(y), rows, cols, ldx, ldy);
+    count_launch();
+    return check_launch();
+}
+
+// ------------------------------------------------------------------------------ fp32 transpose
+// out (cols, rows) = in (rows, cols)^T through 32 x 33 shared-memory tiles.  The TF32 tensor-core
+// instruction takes K-major operands only, so the two backward products of the fp32 graph read
+// transposed copies of their operands.
+__global__ void __launch_bounds__(256) transpose_f32_kernel(const float *in, float *out, int64_t rows, int64_t cols,
+                                                            int64_t ldin, int64_t ldout)
+{
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;       // 32 x 8
+    const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
+    for (int i = ty; i < 32; i += 8) {
+        const int64_t r = r0 + i, c = c0 + tx;
+        tile[i][tx] = (r < rows && c < cols) ? in[r * ldin + c] : 0.0f;
+    }
+    __syncthreads();
+    for (int i = ty; i < 32; i += 8) {
+        const int64_t c = c0 + i, r = r0 + tx;
+        if (c < cols && r < rows) out[c * ldout + r] = tile[tx][i];
+    }
+}
+
+static int transpose_f32(const float *in, float *out, int64_t rows, int64_t cols, int64_t ldin, int64_t ldout, cudaStream_t st)
+{
+    dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
+    if (grid.y > 65535u) return AXS6_ERR_UNSUPPORTED;
+    transpose_f32_kernel<<<grid, 256, 0, st>>>(in, out, rows, cols, ldin, ldout);
+    count_launch();
+    return check_launch();
+}
+
 // ------------------------------------------------------------------------------ column sums
 // out[n] = sum over rows of g[row, n] in fp32, deterministic: phase 1 writes kSplits partial
 // sums per column (each over a contiguous row range, rows visited in order), phase 2 adds them.
@@ -113,6 +173,7 @@ static int column_sums(const void *g, int dtype, float *out, float *partial, int
 }
 
 static int64_t round_up8(int64_t v) { return (v + 7) / 8 * 8; }
+static int64_t round_up4(int64_t v) { return (v + 3) / 4 * 4; }
 
 }  // namespace axs6
 
@@ -138,6 +199,10 @@ AXS6_API int64_t axs6_linear_workspace_bytes(int what, int64_t M, int64_t N, int
     case 1: return N * round_up8(K) * 2;            // wq: bf16 (N, round_up(K, 8))
     case 2: return M * round_up8(N) * 2;            // gq: bf16 (M, round_up(N, 8))
     case 3: return (int64_t)kSplits * N * 4;        // column-sum partials
+    case 4: return M * round_up4(K) * 4;            // xq of the TF32 path: fp32 (M, round_up(K, 4))
+    case 5: return N * round_up4(K) * 4;            // wq, TF32 path
+    case 6: return M * round_up4(N) * 4;            // gq, TF32 path
+    case 7: return (K * round_up4(N) + N * round_up4(M) + K * round_up4(M)) * 4;   // transposes, TF32 backward
     default: return -1;
     }
 }
@@ -150,12 +215,27 @@ AXS6_API int axs6_linear_fwd(const void *x, int x_dtype, int64_t ldx, const void
     if (!valid_dtype(x_dtype) || !valid_dtype(w_dtype) || !valid_dtype(y_dtype) || !valid_block(block)) return AXS6_ERR_ARG;
     if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
     if (M < 0 || N < 0 || K < 0 || ldx < K || ldw < K || ldy < N) return AXS6_ERR_ARG;
-    if (flags & ~(AXS6_LINEAR_QUANTIZE_INPUT)) return AXS6_ERR_ARG;
+    if (flags & ~(AXS6_LINEAR_QUANTIZE_INPUT | AXS6_LINEAR_COMPUTE_TF32)) return AXS6_ERR_ARG;
     if (M == 0 || N == 0) return AXS6_OK;
     if (!x || !w || !y || !xq || !wq || K == 0) return AXS6_ERR_ARG;
     if (!aligned16(xq) || !aligned16(wq)) return AXS6_ERR_ALIGN;
-    const int64_t ldq = round_up8(K);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (flags & AXS6_LINEAR_COMPUTE_TF32) {
+        // fp32 graph (axs/unified/functional_unified.py:107-131, axs/nn/functional.py:101-129): operands
+        // fake-quantised in fp32, rounded to TF32, product on the TF32 tensor cores
+        const int64_t ld4 = round_up4(K);
+        int rc4 = axs6_fq(w, wq, w_dtype, AXS6_F32, N, K, ldw, ld4, block, grid, AXS6_ROUND_NEAREST,
+                          AXS6_FLAG_OUTPUT_TF32, 0, 0, stream);
+        if (rc4) return rc4;
+        if (flags & AXS6_LINEAR_QUANTIZE_INPUT)
+            rc4 = axs6_fq(x, xq, x_dtype, AXS6_F32, M, K, ldx, ld4, block, grid, AXS6_ROUND_NEAREST,
+                          AXS6_FLAG_OUTPUT_TF32, 0, 0, stream);
+        else
+            rc4 = cast_to_tf32(x, x_dtype, xq, M, K, ldx, ld4, st);
+        if (rc4) return rc4;
+        return axs6_gemm_tf32(xq, wq, y, bias, M, N, K, ld4, ld4, ldy, 0, 0, y_dtype, stream);
+    }
+    const int64_t ldq = round_up8(K);
     int rc = axs6_fq(w, wq, w_dtype, AXS6_BF16, N, K, ldw, ldq, block, grid, AXS6_ROUND_NEAREST,
                      AXS6_FLAG_INPUT_VIA_BF16, 0, 0, stream);
     if (rc) return rc;
@@ -172,22 +252,65 @@ AXS6_API int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void
                              int64_t ldw, void *dx, int dx_dtype, int64_t lddx, float *dw, int64_t lddw, float *db,
                              int64_t M, int64_t N, int64_t K, int block, int grid, uint32_t flags, uint64_t seed,
                              uint64_t offset, const float *noise, void *gq, void *wq, float *db_partial,
-                             axs6_stream_t stream)
+                             void *tf32_scratch, axs6_stream_t stream)
 {
     using namespace axs6;
     if (!valid_dtype(g_dtype) || !valid_dtype(w_dtype) || !valid_block(block)) return AXS6_ERR_ARG;
     if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
     if (M < 0 || N < 0 || K < 0 || ldg < N) return AXS6_ERR_ARG;
-    if (flags & ~(AXS6_LINEAR_QUANTIZE_GRAD)) return AXS6_ERR_ARG;
+    if (flags & ~(AXS6_LINEAR_QUANTIZE_GRAD | AXS6_LINEAR_COMPUTE_TF32 | AXS6_LINEAR_BIAS_FROM_QUANTIZED)) return AXS6_ERR_ARG;
     if (M == 0 || N == 0 || K == 0) return AXS6_OK;
     if (!g || !gq) return AXS6_ERR_ARG;
     if (dx && (!w || !wq || !valid_dtype(dx_dtype) || lddx < K || ldw < K)) return AXS6_ERR_ARG;
     if (dw && (!xq || lddw < K)) return AXS6_ERR_ARG;
     if (db && !db_partial) return AXS6_ERR_WORKSPACE;
     if (!aligned16(gq) || (wq && !aligned16(wq)) || (xq && !aligned16(xq))) return AXS6_ERR_ALIGN;
-    const int64_t ldq = round_up8(K), ldgq = round_up8(N);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int rc;
+    if (flags & AXS6_LINEAR_COMPUTE_TF32) {
+        // fp32 graph (axs/unified/functional_unified.py:134-170, axs/nn/functional.py:131-148)
+        const int64_t ld4 = round_up4(K), ldg4 = round_up4(N);
+        if (flags & AXS6_LINEAR_QUANTIZE_GRAD) {
+            rc = noise ? axs6_fq_with_noise(g, gq, g_dtype, AXS6_F32, M, N, ldg, ldg4, block, grid,
+                                            AXS6_FLAG_OUTPUT_TF32, noise, stream)
+                       : axs6_fq(g, gq, g_dtype, AXS6_F32, M, N, ldg, ldg4, block, grid, AXS6_ROUND_STOCHASTIC,
+                                 AXS6_FLAG_OUTPUT_TF32, seed, offset, stream);
+        } else {
+            rc = cast_to_tf32(g, g_dtype, gq, M, N, ldg, ldg4, st);
+        }
+        if (rc) return rc;
+        if ((dx || dw) && !tf32_scratch) return AXS6_ERR_WORKSPACE;
+        const int64_t ldn4 = round_up4(N), ldm4 = round_up4(M);
+        float *wqT = static_cast<float *>(tf32_scratch);          // (K, N)
+        float *gqT = wqT + K * ldn4;                               // (N, M)
+        float *xqT = gqT + N * ldm4;                               // (K, M)
+        if (dx) {
+            rc = axs6_fq(w, wq, w_dtype, AXS6_F32, N, K, ldw, ld4, block, grid, AXS6_ROUND_NEAREST,
+                         AXS6_FLAG_OUTPUT_TF32, 0, 0, stream);
+            if (rc) return rc;
+            rc = transpose_f32(static_cast<const float *>(wq), wqT, N, K, ld4, ldn4, st);
+            if (rc) return rc;
+            // dx (M, K) = gq (M, N) * wq (N, K) = gq * (wq^T)^T with both operands K-major
+            rc = axs6_gemm_tf32(gq, wqT, dx, nullptr, M, K, N, ldg4, ldn4, lddx, 0, 0, dx_dtype, stream);
+            if (rc) return rc;
+        }
+        if (dw) {
+            rc = transpose_f32(static_cast<const float *>(gq), gqT, M, N, ldg4, ldm4, st);
+            if (rc) return rc;
+            rc = transpose_f32(static_cast<const float *>(xq), xqT, M, K, ld4, ldm4, st);
+            if (rc) return rc;
+            // dw (N, K) = gq^T (N, M) * xq (M, K)
+            rc = axs6_gemm_tf32(gqT, xqT, dw, nullptr, N, K, M, ldm4, ldm4, lddw, 0, 0, AXS6_F32, stream);
+            if (rc) return rc;
+        }
+        if (db) {
+            rc = (flags & AXS6_LINEAR_BIAS_FROM_QUANTIZED) ? axs6_bias_grad(gq, AXS6_F32, ldg4, M, N, db, db_partial, stream)
+                                                           : axs6_bias_grad(g, g_dtype, ldg, M, N, db, db_partial, stream);
+            if (rc) return rc;
+        }
+        return AXS6_OK;
+    }
+    const int64_t ldq = round_up8(K), ldgq = round_up8(N);
     if (flags & AXS6_LINEAR_QUANTIZE_GRAD) {
         rc = noise ? axs6_fq_with_noise(g, gq, g_dtype, AXS6_BF16, M, N, ldg, ldgq, block, grid,
                                         AXS6_FLAG_INPUT_VIA_BF16, noise, stream)
@@ -211,7 +334,8 @@ AXS6_API int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void
         if (rc) return rc;
     }
     if (db) {
-        rc = axs6_bias_grad(g, g_dtype, ldg, M, N, db, db_partial, stream);
+        rc = (flags & AXS6_LINEAR_BIAS_FROM_QUANTIZED) ? axs6_bias_grad(gq, AXS6_BF16, ldgq, M, N, db, db_partial, stream)
+                                                       : axs6_bias_grad(g, g_dtype, ldg, M, N, db, db_partial, stream);
         if (rc) return rc;
     }
     return AXS6_OK;
@@ -256,4 +380,16 @@ AXS6_API int axs6_bias_grad_static(const void *g, int g_dtype, int64_t ldg, int6
     // Nothing has to start at zero: the first kernel writes every partial sum of the `cols`
     // columns before the second one reads them, so whatever the previous call left is overwritten.
     return column_sums(g, g_dtype, db, scratch, rows, cols, ldg, static_cast<cudaStream_t>(stream));
+}
+
+AXS6_API int axs6_transpose_f32(const float *in, float *out, int64_t rows, int64_t cols, int64_t ldin, int64_t ldout,
+                                axs6_stream_t stream)
+{
+    using namespace axs6;
+    if (rows < 0 || cols < 0 || ldin < cols || ldout < rows) return AXS6_ERR_ARG;
+    if (rows == 0 || cols == 0) return AXS6_OK;
+    if (!in || !out) return AXS6_ERR_ARG;
+    const DeviceInfo &d = device_info();
+    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+    return transpose_f32(in, out, rows, cols, ldin, ldout, static_cast<cudaStream_t>(stream));
 }

@@ -41,7 +41,7 @@ def run(args, rank: int, world: int, dev, pk: dict, steps: int | None = None) ->
     def bwd(i):
         st = lib.axs6_linear_bwd(go.data_ptr(), 1, N, xq.data_ptr(), w.data_ptr(), 0, K, dx.data_ptr(), 1, K,
                                  dws[i % 2].data_ptr(), K, db.data_ptr(), M, N, K, BLOCK, 1, 2, 1234, i * (M * N // 8),
-                                 None, gq.data_ptr(), wq.data_ptr(), part.data_ptr(), stream)
+                                 None, gq.data_ptr(), wq.data_ptr(), part.data_ptr(), None, stream)
         assert st == 0, st
 
     pending = [None, None]

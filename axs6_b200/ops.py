@@ -194,13 +194,20 @@ def unpack(layout: int, parts, rows: int, cols: int, block_size: int = 32, grid:
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, a_mn: bool = False,
               b_mn: bool = False, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
     """C = op(A) op(B) on the tensor cores.  ``a`` is (M, K) (or (K, M) with ``a_mn``), ``b`` is
-    (N, K) (or (K, N) with ``b_mn``); both bf16, 2-D, unit inner stride."""
+    (N, K) (or (K, N) with ``b_mn``); 2-D, unit inner stride; both bf16 (bf16 tensor cores) or both
+    fp32 (consumed as TF32)."""
     _check_input(a, "gemm_bf16")
     _check_input(b, "gemm_bf16")
-    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
-    if a.stride(1) != 1 or a.stride(0) % 8 or a.data_ptr() % 16:
+    assert a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float32) and a.dim() == 2 and b.dim() == 2
+    if a.dtype == torch.float32:          # the TF32 instruction takes K-major operands only
+        if a_mn:
+            a, a_mn = transpose_f32(a), False
+        if b_mn:
+            b, b_mn = transpose_f32(b), False
+    per16 = 16 // a.element_size()
+    if a.stride(1) != 1 or a.stride(0) % per16 or a.data_ptr() % 16:
         a = _padded_copy(a)
-    if b.stride(1) != 1 or b.stride(0) % 8 or b.data_ptr() % 16:
+    if b.stride(1) != 1 or b.stride(0) % per16 or b.data_ptr() % 16:
         b = _padded_copy(b)
     M, K = (a.shape[1], a.shape[0]) if a_mn else a.shape
     N, K2 = (b.shape[1], b.shape[0]) if b_mn else b.shape
@@ -209,13 +216,14 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None
     bias_f = None
     if bias is not None:
         bias_f = bias.to(device=a.device, dtype=torch.float32).contiguous()
+    fn = _lib.load().axs6_gemm_bf16 if a.dtype == torch.bfloat16 else _lib.load().axs6_gemm_tf32
     with _on(a.device):
-        st = _lib.load().axs6_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(),
-                                        bias_f.data_ptr() if bias_f is not None else None, M, N, K,
-                                        a.stride(0) if a.shape[0] > 1 else max(a.shape[1], 8),
-                                        b.stride(0) if b.shape[0] > 1 else max(b.shape[1], 8), N,
-                                        int(a_mn), int(b_mn), _DT[out_dtype], _stream(a.device))
-    _lib.check("axs6_gemm_bf16", st)
+        st = fn(a.data_ptr(), b.data_ptr(), c.data_ptr(),
+                bias_f.data_ptr() if bias_f is not None else None, M, N, K,
+                a.stride(0) if a.shape[0] > 1 else max(a.shape[1], 8),
+                b.stride(0) if b.shape[0] > 1 else max(b.shape[1], 8), N,
+                int(a_mn), int(b_mn), _DT[out_dtype], _stream(a.device))
+    _lib.check("axs6_gemm", st)
     return c
 
 
@@ -234,15 +242,16 @@ def _ws(what: int, M: int, N: int, K: int, dev, dtype=torch.uint8) -> torch.Tens
 
 
 def linear_fwd(x2: torch.Tensor, w: torch.Tensor, bias_f32: torch.Tensor | None, block_size: int, grid: int,
-               quantize_input: bool, out_dtype: torch.dtype):
-    """-> (y (M, N), xq workspace holding the bf16 activations that backward needs)."""
+               quantize_input: bool, out_dtype: torch.dtype, tf32: bool = False):
+    """-> (y (M, N), xq workspace holding the quantised activations that backward needs).
+    ``tf32``: the fp32 graph (operands fake-quantised in fp32, TF32 tensor cores) instead of bf16."""
     M, K = x2.shape
     N = w.shape[0]
     dev = x2.device
-    xq = _ws(0, M, N, K, dev)
-    wq = _ws(1, M, N, K, dev)
+    xq = _ws(4 if tf32 else 0, M, N, K, dev)
+    wq = _ws(5 if tf32 else 1, M, N, K, dev)
     y = torch.empty((M, N), dtype=out_dtype, device=dev)
-    flags = _lib.LINEAR_QUANTIZE_INPUT if quantize_input else 0
+    flags = (_lib.LINEAR_QUANTIZE_INPUT if quantize_input else 0) | (_lib.LINEAR_COMPUTE_TF32 if tf32 else 0)
     with _on(dev):
         st = _lib.load().axs6_linear_fwd(x2.data_ptr(), _DT[x2.dtype], x2.stride(0) if M > 1 else K,
                                          w.data_ptr(), _DT[w.dtype], w.stride(0) if N > 1 else K,
@@ -255,15 +264,17 @@ def linear_fwd(x2: torch.Tensor, w: torch.Tensor, bias_f32: torch.Tensor | None,
 
 def linear_bwd(g2: torch.Tensor, xq: torch.Tensor, w: torch.Tensor, M: int, N: int, K: int, block_size: int,
                grid: int, quantize_grad: bool, need_dx: bool, need_dw: bool, need_db: bool,
-               dx_dtype: torch.dtype = torch.bfloat16, noise: torch.Tensor | None = None):
+               dx_dtype: torch.dtype = torch.bfloat16, noise: torch.Tensor | None = None, tf32: bool = False,
+               bias_from_quantized: bool = False):
     """-> (dx (M, K) or None, dw fp32 (N, K) or None, db fp32 (N,) or None)."""
     dev = g2.device
     dx = torch.empty((M, K), dtype=dx_dtype, device=dev) if need_dx else None
     dw = torch.empty((N, K), dtype=torch.float32, device=dev) if need_dw else None
     db = torch.empty((N,), dtype=torch.float32, device=dev) if need_db else None
-    gq = _ws(2, M, N, K, dev)
-    wq = _ws(1, M, N, K, dev) if need_dx else None
+    gq = _ws(6 if tf32 else 2, M, N, K, dev)
+    wq = _ws(5 if tf32 else 1, M, N, K, dev) if need_dx else None
     part = _ws(3, M, N, K, dev) if need_db else None
+    tscr = _ws(7, M, N, K, dev) if (tf32 and (need_dx or need_dw)) else None
     seed, off = (0, 0)
     nz = None
     if quantize_grad:
@@ -271,7 +282,8 @@ def linear_bwd(g2: torch.Tensor, xq: torch.Tensor, w: torch.Tensor, M: int, N: i
             nz = noise.to(device=dev, dtype=torch.float32).contiguous()
         else:
             seed, off = next_philox(M * (-(-N // block_size)) * block_size)
-    flags = _lib.LINEAR_QUANTIZE_GRAD if quantize_grad else 0
+    flags = (_lib.LINEAR_QUANTIZE_GRAD if quantize_grad else 0) | (_lib.LINEAR_COMPUTE_TF32 if tf32 else 0) | \
+            (_lib.LINEAR_BIAS_FROM_QUANTIZED if bias_from_quantized else 0)
     with _on(dev):
         st = _lib.load().axs6_linear_bwd(
             g2.data_ptr(), _DT[g2.dtype], g2.stride(0) if M > 1 else N, xq.data_ptr() if need_dw else None,
@@ -279,7 +291,8 @@ def linear_bwd(g2: torch.Tensor, xq: torch.Tensor, w: torch.Tensor, M: int, N: i
             dx.data_ptr() if need_dx else None, _DT[dx_dtype], K, dw.data_ptr() if need_dw else None, K,
             db.data_ptr() if need_db else None, M, N, K, block_size, grid, flags, seed, off,
             nz.data_ptr() if nz is not None else None, gq.data_ptr(), wq.data_ptr() if wq is not None else None,
-            part.data_ptr() if part is not None else None, _stream(dev))
+            part.data_ptr() if part is not None else None, tscr.data_ptr() if tscr is not None else None,
+            _stream(dev))
     _lib.check("axs6_linear_bwd", st)
     return dx, dw, db
 
@@ -295,3 +308,19 @@ def bias_grad(g: torch.Tensor) -> torch.Tensor:
                                         _stream(g.device))
     _lib.check("axs6_bias_grad", st)
     return out
+
+
+def transpose_f32(t: torch.Tensor) -> torch.Tensor:
+    """(rows, cols) fp32 -> contiguous-row (cols, rows) copy whose rows start 16-byte aligned."""
+    _check_input(t, "transpose_f32")
+    assert t.dtype == torch.float32 and t.dim() == 2
+    if t.stride(1) != 1:
+        t = t.contiguous()
+    rows, cols = t.shape
+    ld = (rows + 3) // 4 * 4
+    out = torch.empty((cols, ld), dtype=torch.float32, device=t.device)
+    with _on(t.device):
+        st = _lib.load().axs6_transpose_f32(t.data_ptr(), out.data_ptr(), rows, cols, t.stride(0) if rows > 1 else cols,
+                                            ld, _stream(t.device))
+    _lib.check("axs6_transpose_f32", st)
+    return out[:, :rows]

@@ -40,6 +40,40 @@ def accelerated_fake_quantize(tensor: torch.Tensor, block_size: int = DEFAULT_BL
     return fused_fake_quantize(tensor, block_size, rounding)
 
 
+def accelerated_linear(input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                       block_size: int = DEFAULT_BLOCK_SIZE, quantize_input: bool = True) -> torch.Tensor:
+    """FQ(input) @ FQ(weight)^T + bias, forward only (reference: backend.py:540-618).  fp32
+    tensors run the fp32 graph on the TF32 tensor cores and return fp32; bf16 input with bf16
+    weight runs on the bf16 tensor cores and returns bf16."""
+    if not input.is_cuda:
+        raise RuntimeError("accelerated_linear requires CUDA tensors")
+    x2 = input.reshape(-1, input.shape[-1])
+    if x2.dtype not in (torch.float32, torch.bfloat16):
+        x2 = x2.float()
+    if x2.stride(-1) != 1 or (x2.shape[0] > 1 and x2.stride(0) < x2.shape[1]):
+        x2 = x2.contiguous()
+    w = weight if weight.dtype in (torch.float32, torch.bfloat16) else weight.float()
+    w = w if w.stride(-1) == 1 else w.contiguous()
+    all_bf16 = x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    b32 = bias.float().contiguous() if bias is not None else None
+    y, _ = ops.linear_fwd(x2, w, b32, block_size, ops.GRID_NF5, bool(quantize_input),
+                          torch.bfloat16 if all_bf16 else torch.float32, tf32=not all_bf16)
+    return y.reshape(*input.shape[:-1], weight.shape[0])
+
+
+def accelerated_matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a (*, K) @ b (K, N)`` on the tensor cores, fp32 result (reference: backend.py:621-671; no
+    quantisation step -- the operands are expected to be fake-quantised already).  fp32 operands
+    are consumed as TF32, bf16 operands as bf16; ``b`` is read in place (no transpose copy)."""
+    if not a.is_cuda:
+        raise RuntimeError("accelerated_matmul requires CUDA tensors")
+    a2 = a.reshape(-1, a.shape[-1])
+    if a2.dtype != b.dtype or a2.dtype not in (torch.float32, torch.bfloat16):
+        a2, b = a2.float(), b.float()
+    out = ops.gemm_bf16(a2, b.reshape(-1, b.shape[-1]), a_mn=False, b_mn=True, out_dtype=torch.float32)
+    return out.reshape(*a.shape[:-1], b.shape[-1])
+
+
 def backend_info() -> dict[str, object]:
     """Diagnostics in the spirit of backend.py:678-691."""
     cuda = torch.cuda.is_available()

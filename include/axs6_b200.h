@@ -41,8 +41,16 @@ enum { AXS6_LAYOUT_PLANES = 0, /* AXSTensor planes: u8 exponent (rows,nblk), u8 
                                        `weight.to(bfloat16)` of the mixed-precision Linear
                                        (axs/unified/mixed_precision.py:96-100) fused in    */
 
+#define AXS6_FLAG_OUTPUT_TF32 2u     /* round an fp32 result to the nearest TF32 value (10-bit
+                                       mantissa) so that a kind::tf32 GEMM reads it exactly     */
+
 #define AXS6_LINEAR_QUANTIZE_INPUT 1u /* fake-quantise the activations (else only cast to bf16) */
 #define AXS6_LINEAR_QUANTIZE_GRAD 2u  /* fake-quantise the upstream gradient, stochastic rounding */
+#define AXS6_LINEAR_COMPUTE_TF32 4u   /* fp32 graph: operands fake-quantised in fp32 (no bf16 cast),
+                                         rounded to TF32, products on the TF32 tensor cores; work
+                                         buffers are fp32 (workspace codes 4, 5, 6)              */
+#define AXS6_LINEAR_BIAS_FROM_QUANTIZED 8u /* db sums the QUANTISED gradient, as the fp32 reference
+                                         functions do (functional_unified.py:151, :161-165)      */
 
 #define AXS6_OK 0
 #define AXS6_ERR_ARG (-1)         /* null pointer, negative size, bad enum, bad block size  */
@@ -127,6 +135,24 @@ int axs6_gemm_bf16(const void *a, const void *b, void *c, const float *bias,
                    int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                    int a_mn, int b_mn, int c_dtype, axs6_stream_t stream);
 
+/* Same product with fp32 operands that the tensor cores consume as TF32 (kind::tf32): 10 mantissa
+ * bits of every operand value are used, the rest is ignored.  For the fp32 Linear paths
+ * (axs/unified/functional_unified.py:123, :155-160; axs/nn/functional.py:121, :144-145;
+ * axs/unified/backend.py:540-618), where bf16 operands would exceed the 1e-3 error bar.  Operands
+ * 16-byte aligned, leading dimensions multiples of 4 elements.  AXS6_FLAG_OUTPUT_TF32 of
+ * axs6_fq produces operands already rounded to nearest TF32.  Only K-major operands
+ * (a_mn = b_mn = 0): the TF32 instruction does not take MN-major ones (AXS6_ERR_UNSUPPORTED);
+ * axs6_transpose_f32 makes the copy. */
+int axs6_gemm_tf32(const void *a, const void *b, void *c, const float *bias,
+                   int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                   int a_mn, int b_mn, int c_dtype, axs6_stream_t stream);
+
+/* out (cols, rows) = in (rows, cols) transposed, fp32.  Plumbing for the TF32 products, which
+ * need K-major operands (replaces the `.t().contiguous()` of
+ * axs/unified/functional_unified.py:157-158). */
+int axs6_transpose_f32(const float *in, float *out, int64_t rows, int64_t cols,
+                       int64_t ldin, int64_t ldout, axs6_stream_t stream);
+
 /* Device-side status of the GEMM kernels since the last call of this function: 0 = every
  * wait inside the kernels completed; n > 0 = a bounded wait gave up (1 TMA producer waiting
  * for a free stage, 2 MMA issuer waiting for a free accumulator, 3 MMA issuer waiting for a
@@ -140,6 +166,9 @@ int axs6_gemm_status(void);
  *
  * Forward:  xq = FQ(bf16(x)) (or bf16(x) without AXS6_LINEAR_QUANTIZE_INPUT), wq = FQ(bf16(w)),
  *           y (M,N) = xq wq^T + bias, fp32 accumulation, y stored as y_dtype.
+ * With AXS6_LINEAR_COMPUTE_TF32 the same call runs the fp32 graph of _AXSLinearUnifiedFunction
+ * (axs/unified/functional_unified.py:89-170) and, with grid = AXS6_GRID_UNIFORM, of
+ * _AXSLinearFunction (axs/nn/functional.py:93-148): no bf16 cast, TF32 products.
  * x is (M,K), w is (N,K); bias (fp32, length N) may be NULL.  xq and wq are caller-owned bf16
  * buffers of axs6_linear_workspace_bytes(0 | 1, M, N, K) bytes, 16-byte aligned, row length
  * round_up(K, 8); xq must be kept for the backward call (the reference saves input_q). */
@@ -154,13 +183,14 @@ int axs6_linear_fwd(const void *x, int x_dtype, int64_t ldx, const void *w, int 
  *            un-quantised g in fp32 (:150).  Any of dx, dw, db may be NULL (not needed).
  * `noise` (may be NULL): U[0,1) draws for the gradient in the padded (M, nblk, block) layout,
  * instead of the Philox stream (seed, offset).  Workspaces: gq = what 2, wq = what 1,
- * db_partial = what 3 of axs6_linear_workspace_bytes (db_partial only if db is given). */
+ * db_partial = what 3 of axs6_linear_workspace_bytes (db_partial only if db is given);
+ * tf32_scratch = what 7, only for AXS6_LINEAR_COMPUTE_TF32 (transposed operand copies), else NULL. */
 int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void *xq,
                     const void *w, int w_dtype, int64_t ldw,
                     void *dx, int dx_dtype, int64_t lddx, float *dw, int64_t lddw, float *db,
                     int64_t M, int64_t N, int64_t K, int block, int grid, uint32_t flags,
                     uint64_t seed, uint64_t offset, const float *noise,
-                    void *gq, void *wq, float *db_partial, axs6_stream_t stream);
+                    void *gq, void *wq, float *db_partial, void *tf32_scratch, axs6_stream_t stream);
 
 /* Bias gradient: db[n] = sum over rows of g[row, n], accumulated in fp32 in a fixed order
  * (deterministic).  Replaces grad_output.float().sum(dim=...) of the Linear backward
@@ -190,7 +220,8 @@ int axs6_bias_grad(const void *g, int g_dtype, int64_t ldg, int64_t rows, int64_
 int axs6_bias_grad_static(const void *g, int g_dtype, int64_t ldg, int64_t rows, int64_t cols,
                           float *db, axs6_stream_t stream);
 
-/* Bytes of a caller-owned work buffer: what 0 = xq, 1 = wq, 2 = gq, 3 = db_partial. */
+/* Bytes of a caller-owned work buffer: what 0 = xq, 1 = wq, 2 = gq (bf16 compute), 3 = db_partial,
+ * 4 = xq, 5 = wq, 6 = gq of the AXS6_LINEAR_COMPUTE_TF32 graph (fp32), 7 = its tf32_scratch. */
 int64_t axs6_linear_workspace_bytes(int what, int64_t M, int64_t N, int64_t K);
 
 #ifdef __cplusplus

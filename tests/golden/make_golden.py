@@ -314,9 +314,7 @@ def main() -> None:
                                    "bias": bias, "quantize_input": qin, "quantize_grad": qgrad}
 
     for tag, fn in (("mixed", ref_mp.axs_linear_mixed_precision), ("unified", ref_fu.axs_linear_unified),
-                    ("v1", None)):
-        if fn is None:
-            continue
+                    ("v1", ref_nnf.axs_linear)):
         add_linear(f"lin_{tag}_a", fn, (40,), 96, 64, torch.float32, True, True, True)
         add_linear(f"lin_{tag}_b", fn, (3, 16), 128, 32, torch.bfloat16 if tag == "mixed" else torch.float32,
                    False, True, False)

@@ -199,3 +199,143 @@ def test_bias_grad_column_sums(rows, cols, dtype):
     assert float((out.cpu().double() - ref).abs().max()) <= 1e-5 * max(1.0, float(ref.abs().max())) * (rows ** 0.5)
     again = ops.bias_grad(g.cuda())
     assert torch.equal(out, again)          # fixed summation order
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 32), (256, 512, 512), (1000, 776, 516), (2048, 1024, 2048)])
+def test_gemm_tf32_against_fp32_matmul(M, N, K, a_mn, b_mn):
+    """fp32 operands consumed as TF32: operands pre-rounded to TF32 must give an fp32-exact
+    product; raw fp32 operands stay within the 1e-3 bar."""
+    g = torch.Generator().manual_seed(M + N + K + a_mn * 2 + b_mn)
+    A = torch.randn((K, M) if a_mn else (M, K), generator=g)
+    B = torch.randn((K, N) if b_mn else (N, K), generator=g)
+    def tf32(t):            # keep 10 mantissa bits, round to nearest (ties away)
+        return ((t.view(torch.int32) + 0x1000) & ~0x1FFF).view(torch.float32)
+    At, Bt = tf32(A), tf32(B)
+    C = ops.gemm_bf16(At.cuda(), Bt.cuda(), a_mn=bool(a_mn), b_mn=bool(b_mn))    # MN-major fp32 operands go through a transposed copy
+    gemm_status_ok()
+    Af = At.t() if a_mn else At
+    Bf = Bt if b_mn else Bt.t()
+    assert rel(C.cpu(), Af.double() @ Bf.double()) < 1e-5
+    C2 = ops.gemm_bf16(A.cuda(), B.cuda(), a_mn=bool(a_mn), b_mn=bool(b_mn))
+    Af = A.t() if a_mn else A
+    Bf = B if b_mn else B.t()
+    assert rel(C2.cpu(), Af.double() @ Bf.double()) < TOL
+
+
+def test_fq_tf32_rounded_output():
+    x = torch.randn(64, 256, generator=torch.Generator().manual_seed(8)).cuda()
+    lib = _lib.load()
+    y = torch.empty_like(x)
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.axs6_fq(x.data_ptr(), y.data_ptr(), 0, 0, 64, 256, 256, 256, 32, 1, 0, 2, 0, 0, st) == 0
+    ref = qu.fused_fake_quantize(x)
+    want = ((ref.view(torch.int32) + 0x1000) & ~0x1FFF).view(torch.float32)
+    assert torch.equal(y, want)
+    assert int((y.view(torch.int32) & 0x1FFF).abs().max()) == 0
+
+
+# ------------------------------------------------------------------ fp32 graphs (TF32 tensor cores)
+fu = importlib.import_module("axs6_b200.unified.functional_unified")
+nnf = importlib.import_module("axs6_b200.nn.functional")
+ub = importlib.import_module("axs6_b200.unified.backend")
+tk = importlib.import_module("axs6_b200.unified.triton_kernels")
+_lf = importlib.import_module("axs6_b200._linear_fn")
+
+
+@pytest.mark.parametrize("family", ["unified", "v1"])
+def test_fp32_linear_golden_from_reference(family, linear_cases, manifest):
+    """Cases recorded from the reference's fp32 autograd functions on the CPU (same stochastic
+    draws): y, dx, dw, db within 1e-3 relative Frobenius; fp32 everywhere."""
+    fn = fu.axs_linear_unified if family == "unified" else nnf.axs_linear
+    for name in (f"lin_{family}_a", f"lin_{family}_b", f"lin_{family}_c"):
+        info = manifest["cases"][name]
+        K, N = info["K"], info["N"]
+        x = to_cuda(linear_cases[f"{name}.x"].view(np.float32)).reshape(*info["M"], K).requires_grad_(True)
+        w = to_cuda(linear_cases[f"{name}.w"].view(np.float32)).reshape(N, K).requires_grad_(True)
+        b = to_cuda(linear_cases[f"{name}.b"].view(np.float32)).requires_grad_(True) if info["bias"] else None
+        g = to_cuda(linear_cases[f"{name}.g"].view(np.float32)).reshape(*info["M"], N)
+        y = fn(x, w, b, 32, info["quantize_input"], info["quantize_grad"])
+        assert y.dtype == torch.float32
+        _lf._noise_for_next_backward = torch.from_numpy(linear_cases[f"{name}.noise"]).cuda() if info["quantize_grad"] else None
+        y.backward(g)
+        _lf._noise_for_next_backward = None
+        gemm_status_ok()
+        for got, key in ((y, "y"), (x.grad, "dx"), (w.grad, "dw")):
+            want = torch.from_numpy(linear_cases[f"{name}.{key}"].view(np.float32)).reshape(got.shape)
+            assert got.dtype == torch.float32
+            assert rel(got.cpu(), want) < TOL, (name, key, rel(got.cpu(), want))
+        if info["bias"]:
+            want = torch.from_numpy(linear_cases[f"{name}.db"].view(np.float32))
+            assert rel(b.grad.cpu(), want) < TOL, name            # column sums of the quantised (TF32-rounded) gradient
+
+
+def test_accelerated_linear_and_fused_linear_vs_oracle():
+    """Forward-only entry points against the fp32 matmul of the oracle's fake-quantised
+    operands; shapes as in the reference's fused-linear tests (ragged K, batched input, M = 1)."""
+    rng = np.random.default_rng(21)
+    for shape, K, N, bias, qin in (((64,), 128, 96, True, True), ((4, 8), 33, 20, False, True), ((2, 3, 5), 50, 17, True, True),
+                                   ((1,), 100, 64, True, False), ((7,), 127, 40, False, True), ((16,), 255, 33, True, True)):
+        x = rng.standard_normal((*shape, K), dtype=np.float32)
+        w = rng.standard_normal((N, K), dtype=np.float32) * 0.1
+        b = rng.standard_normal(N, dtype=np.float32) if bias else None
+        xq = oracle.fused_fake_quantize(x.reshape(-1, K)) if qin else x.reshape(-1, K)
+        wq = oracle.fused_fake_quantize(w)
+        ref = xq.astype(np.float64) @ wq.astype(np.float64).T + (b.astype(np.float64) if bias else 0.0)
+        ref = torch.from_numpy(ref).reshape(*shape, N)
+        xt, wt = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+        bt = torch.from_numpy(b).cuda() if bias else None
+        for fn in (ub.accelerated_linear, tk.triton_fused_linear):
+            y = fn(xt, wt, bt, 32, qin)
+            assert y.dtype == torch.float32 and y.shape == ref.shape and y.is_contiguous()
+            assert rel(y.cpu(), ref) < TOL
+    gemm_status_ok()
+    with pytest.raises(ValueError, match="block_size=32"):
+        tk.triton_fused_linear(xt, wt, None, 16)
+    with pytest.raises(RuntimeError, match="requires CUDA tensors"):
+        tk.triton_fused_linear(torch.randn(2, 32), torch.randn(4, 32))
+    yb = tk.triton_fused_linear(xt.to(torch.bfloat16), wt)
+    assert yb.dtype == torch.bfloat16
+
+
+def test_accelerated_matmul():
+    g = torch.Generator().manual_seed(2)
+    a = torch.randn(3, 40, 96, generator=g)
+    b = torch.randn(96, 56, generator=g)
+    out = ub.accelerated_matmul(a.cuda(), b.cuda())
+    gemm_status_ok()
+    assert out.dtype == torch.float32 and out.shape == (3, 40, 56)
+    assert rel(out.cpu(), a.double() @ b.double()) < TOL
+    outb = ub.accelerated_matmul(a.cuda().to(torch.bfloat16), b.cuda().to(torch.bfloat16))
+    assert outb.dtype == torch.float32
+    assert rel(outb.cpu(), a.to(torch.bfloat16).double() @ b.to(torch.bfloat16).double()) < 1e-5
+    m = fu.axs_matmul_unified(a.cuda(), b.cuda())
+    aq = oracle.fused_fake_quantize(a.numpy()); bq = oracle.fused_fake_quantize(b.numpy())
+    assert rel(m.cpu(), torch.from_numpy(aq.astype(np.float64) @ bq.astype(np.float64))) < TOL
+
+
+def test_fp32_modules_train_a_step():
+    torch.manual_seed(3)
+    um = importlib.import_module("axs6_b200.unified.modules_unified")
+    nm = importlib.import_module("axs6_b200.nn.modules")
+    for cls in (um.AXSLinearUnified, nm.AXSLinear):
+        lin = cls(64, 32).cuda()
+        x = torch.randn(10, 64, device="cuda", requires_grad=True)
+        y = lin(x)
+        assert y.dtype == torch.float32 and y.shape == (10, 32)
+        y.sum().backward()
+        assert lin.weight.grad.shape == (32, 64) and lin.bias.grad.shape == (32,) and x.grad.shape == x.shape
+        # straight-through: with an all-ones upstream gradient db is the row count (quantised ones are exact)
+        assert torch.allclose(lin.bias.grad, torch.full((32,), 10.0, device="cuda"), rtol=0.05)
+    net = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 8)).cuda()
+    conv = um.convert_to_axs_unified(net)
+    assert isinstance(conv[0], um.AXSLinearUnified) and conv(torch.randn(5, 32, device="cuda")).shape == (5, 8)
+
+
+def test_tf32_entry_rejects_mn_major():
+    lib = _lib.load()
+    a = torch.zeros(64, 64, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.axs6_gemm_tf32(a.data_ptr(), a.data_ptr(), a.data_ptr(), None, 64, 64, 64, 64, 64, 64, 0, 1, 0, st) == -6
+    t = ops.transpose_f32(torch.arange(35 * 50, dtype=torch.float32, device="cuda").reshape(35, 50))
+    assert torch.equal(t, torch.arange(35 * 50, dtype=torch.float32, device="cuda").reshape(35, 50).t())
