@@ -39,3 +39,140 @@ def _unpack_gradient(shared_exponents, signs, magnitudes, original_shape, block_
     y = ops.unpack(ops.LAYOUT_PLANES, (shared_exponents, signs, magnitudes), rows, original_shape[-1], block_size,
                    ops.GRID_NF5, torch.float32)
     return y.reshape(original_shape)
+
+
+# ---------------------------------------------------------------------------------------------
+# Row sharding and gradient exchange (host logic over torch.distributed)
+# ---------------------------------------------------------------------------------------------
+import math
+from dataclasses import dataclass
+from typing import Any, Callable
+
+import torch.distributed as dist
+
+
+def shard_rows(rows: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous row range [start, stop) of `rank`: blocks never cross a row, so fake-quantise,
+    pack and unpack shard by rows with no exchange of data.  The first ``rows % world`` ranks
+    take one extra row."""
+    base, extra = divmod(rows, world)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+class CudaCodec:
+    """The three codec operations the gradient hooks need, on the CUDA kernels."""
+
+    def __init__(self, block_size: int = DEFAULT_BLOCK_SIZE):
+        self.block_size = block_size
+
+    def pack(self, flat: torch.Tensor) -> torch.Tensor:
+        """1-D tensor -> uint8 wire records of its zero-padded blocks."""
+        return ops.pack(flat.reshape(1, -1), self.block_size, ops.GRID_NF5, "nearest", ops.LAYOUT_WIRE, who="pack")
+
+    def unpack(self, buf: torch.Tensor, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        out_dt = dtype if dtype in (torch.float32, torch.bfloat16) else torch.float32
+        y = ops.unpack(ops.LAYOUT_WIRE, buf, 1, numel, self.block_size, ops.GRID_NF5, out_dt)
+        return y.reshape(-1).to(dtype)
+
+    def roundtrip(self, flat: torch.Tensor) -> torch.Tensor:
+        """unpack(pack(flat)): what a peer would reconstruct from this rank's records."""
+        return self.unpack(self.pack(flat), flat.numel(), flat.dtype)
+
+
+@dataclass
+class HookState:
+    """State object for the communication hooks: the process group and the codec."""
+    group: Any = None
+    codec: Any = None
+
+    def resolve(self):
+        group = self.group if self.group is not None else dist.group.WORLD
+        return group, (self.codec if self.codec is not None else CudaCodec())
+
+
+def _state(state) -> tuple[Any, Any]:
+    if isinstance(state, HookState):
+        return state.resolve()
+    group = state if (state is not None and isinstance(state, dist.ProcessGroup)) else dist.group.WORLD
+    return group, CudaCodec()
+
+
+def _allreduce_mean(flat: torch.Tensor, group, world: int) -> "torch.futures.Future[torch.Tensor]":
+    fut = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group, async_op=True).get_future()
+
+    def done(f):
+        v = f.value()
+        v = v[0] if isinstance(v, list) else v
+        return v.div_(world)
+
+    return fut.then(done)
+
+
+def axs6_gradient_hook(state: Any, bucket) -> "torch.futures.Future[torch.Tensor]":
+    """DDP communication hook with the semantics of the reference's ``axs6_gradient_hook``
+    (distributed.py:239-305): every rank replaces its flat gradient bucket by its AXS-6 NF5
+    reconstruction (pack -> unpack, block 32 over the zero-padded flat buffer), the reconstructions
+    are all-reduced in the gradient's own dtype and divided by the world size."""
+    group, codec = _state(state)
+    world = dist.get_world_size(group)
+    grad = bucket.buffer()
+    recon = codec.roundtrip(grad.reshape(-1)).to(grad.dtype)
+    return _allreduce_mean(recon, group, world)
+
+
+def axs6_gradient_hook_packed(state: Any, bucket) -> "torch.futures.Future[torch.Tensor]":
+    """Compressed exchange: each rank packs its bucket to 25-byte records (6.25 bits per value on
+    the wire), the records are all-gathered, and every rank unpacks all of them and averages.
+
+    Same name and registration as the reference's packed hook (distributed.py:308-367) but not
+    its arithmetic: the reference all-reduces the bit-packed bytes as integers and averages
+    them, which mixes unrelated bit fields; here the result is exactly the mean of the ranks'
+    reconstructions, i.e. identical to :func:`axs6_gradient_hook` up to summation order."""
+    group, codec = _state(state)
+    world = dist.get_world_size(group)
+    grad = bucket.buffer()
+    numel, dtype = grad.numel(), grad.dtype
+    mine = codec.pack(grad.reshape(-1))
+    gathered = torch.empty(world * mine.numel(), dtype=mine.dtype, device=mine.device)
+    fut = dist.all_gather_into_tensor(gathered, mine, group=group, async_op=True).get_future()
+
+    def done(f):
+        acc = None
+        for r in range(world):
+            part = codec.unpack(gathered[r * mine.numel():(r + 1) * mine.numel()], numel, torch.float32)
+            acc = part if acc is None else acc.add_(part)
+        return acc.div_(world).to(dtype)
+
+    return fut.then(done)
+
+
+class AXS6GradCompressor:
+    """Manual-loop counterpart of the hooks (reference: distributed.py:374-440).
+    ``packed=False``: all-reduce of the local reconstructions; ``packed=True``: all-gather of the
+    packed records (see :func:`axs6_gradient_hook_packed` for how this differs from the reference)."""
+
+    def __init__(self, process_group=None, block_size: int = DEFAULT_BLOCK_SIZE, packed: bool = False,
+                 codec=None) -> None:
+        self.group = process_group
+        self.block_size = block_size
+        self.packed = packed
+        self.codec = codec
+
+    def compress_and_allreduce(self, grad: torch.Tensor) -> torch.Tensor:
+        group = self.group if self.group is not None else dist.group.WORLD
+        codec = self.codec if self.codec is not None else CudaCodec(self.block_size)
+        world = dist.get_world_size(group)
+        flat = grad.reshape(-1)
+        if not self.packed:
+            recon = codec.roundtrip(flat).to(grad.dtype)
+            dist.all_reduce(recon, op=dist.ReduceOp.SUM, group=group)
+            return recon.div_(world).reshape(grad.shape)
+        mine = codec.pack(flat)
+        gathered = torch.empty(world * mine.numel(), dtype=mine.dtype, device=mine.device)
+        dist.all_gather_into_tensor(gathered, mine, group=group)
+        acc = None
+        for r in range(world):
+            part = codec.unpack(gathered[r * mine.numel():(r + 1) * mine.numel()], flat.numel(), torch.float32)
+            acc = part if acc is None else acc.add_(part)
+        return acc.div_(world).to(grad.dtype).reshape(grad.shape)

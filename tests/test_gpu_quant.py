@@ -333,3 +333,31 @@ def test_4d_and_fp16_inputs():
     y = qu.fused_fake_quantize(x.cuda(), 16)
     assert y.shape == x.shape
     assert_bits_equal(y, oracle.fused_fake_quantize(x.numpy(), 16), "4-D")
+
+
+def test_gradient_hooks_on_one_gpu_rank():
+    """The DDP hooks with the CUDA codec in a world of one NCCL rank: the result is this rank's own
+    AXS-6 reconstruction, bit for bit what the oracle's pack -> unpack gives (incl. the non-zero
+    reconstruction of exact zeros)."""
+    import torch.distributed as dist
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", str(29400 + os.getpid() % 500))
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    try:
+        class Bucket:
+            def __init__(self, t): self.t = t
+            def buffer(self): return self.t
+        rng = np.random.default_rng(4)
+        g = rng.standard_normal(100003, dtype=np.float32) * 1e-3
+        g[::97] = 0.0
+        se, sg, mg = oracle.quantize(g.reshape(1, -1), 32, oracle.GRID_NF5)
+        want = oracle.dequantize(se, sg, mg, g.size, oracle.GRID_NF5).reshape(-1)
+        for hook in (udist.axs6_gradient_hook, udist.axs6_gradient_hook_packed):
+            out = hook(None, Bucket(torch.from_numpy(g).cuda())).wait()
+            assert out.shape == (g.size,) and out.dtype == torch.float32
+            assert_bits_equal(out, want, hook.__name__)
+        c = udist.AXS6GradCompressor(packed=True)
+        out = c.compress_and_allreduce(torch.from_numpy(g).cuda().reshape(-1, 7)[:1000])
+        assert out.shape == (1000, 7)
+    finally:
+        dist.destroy_process_group()
