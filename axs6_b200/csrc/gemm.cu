@@ -149,6 +149,58 @@ __device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn, uint32_t fmt)
                    "=r"(r[29]), "=r"(r[30]), "=r"(r[31])                                                               \
                  : "r"(taddr))
 
+// Drains one 128 x 256 fp32 accumulator: this thread owns TMEM lane (= output row) `row` and walks
+// the 256 columns in chunks of 32 (tcgen05.ld 32x32b.x32), adds the bias, converts and stores.
+__device__ __forceinline__ void epilogue_tile(const Params &p, uint32_t taddr, int row, int n0, bool vec_ok)
+{
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        AXS6_TMEM_LD32(taddr + (uint32_t)(c * 32), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            if (p.bias) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
+            }
+            const bool full = col0 + 32 <= p.N;
+            if (p.c_bf16) {
+                __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.c) + (long long)row * p.ldc + col0;
+                if (full && vec_ok) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+                            w[j] = *reinterpret_cast<const uint32_t *>(&h);
+                        }
+                        *reinterpret_cast<uint4 *>(dst + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                } else {
+                    for (int i = 0; i < 32; ++i)
+                        if (col0 + i < p.N) dst[i] = __float2bfloat16_rn(v[i]);
+                }
+            } else {
+                float *dst = reinterpret_cast<float *>(p.c) + (long long)row * p.ldc + col0;
+                if (full && vec_ok) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                } else {
+                    for (int i = 0; i < 32; ++i)
+                        if (col0 + i < p.N) dst[i] = v[i];
+                }
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------- kernel
 template <bool kTf32>
 __global__ void __launch_bounds__(kThreadsGemm, 1)
@@ -258,52 +310,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                AXS6_TMEM_LD32(taddr + (uint32_t)(c * 32), r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int col0 = n0 + c * 32;
-                if (row < p.M && col0 < p.N) {
-                    float v[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-                    if (p.bias) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
-                    }
-                    const bool full = col0 + 32 <= p.N;
-                    if (p.c_bf16) {
-                        __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.c) + (long long)row * p.ldc + col0;
-                        if (full && vec_ok) {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                uint32_t w[4];
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    const __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
-                                    w[j] = *reinterpret_cast<const uint32_t *>(&h);
-                                }
-                                *reinterpret_cast<uint4 *>(dst + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
-                            }
-                        } else {
-                            for (int i = 0; i < 32; ++i)
-                                if (col0 + i < p.N) dst[i] = __float2bfloat16_rn(v[i]);
-                        }
-                    } else {
-                        float *dst = reinterpret_cast<float *>(p.c) + (long long)row * p.ldc + col0;
-                        if (full && vec_ok) {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                        } else {
-                            for (int i = 0; i < 32; ++i)
-                                if (col0 + i < p.N) dst[i] = v[i];
-                        }
-                    }
-                }
-            }
+            epilogue_tile(p, taddr, row, n0, vec_ok);
             tc_fence_before();
             mbar_arrive(tempty_bar(acc));
             acc ^= 1;
@@ -316,6 +323,196 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------- 2-CTA kernel
+// Pairs of CTAs (cluster of 2, on neighbouring SMs) share one 256 x 256 output tile with
+// tcgen05.mma.cta_group::2: each CTA stages ITS 128 rows of A and ITS 128-wide half of B (32 KB per
+// k-block instead of 48 KB), the leader CTA (cluster rank 0) issues M256 N256 K16 instructions
+// that read both CTAs' shared memory and write 128 accumulator rows into each CTA's TMEM.
+// Less shared-memory traffic per flop and a 6-deep ring in the same shared-memory budget.
+//   * every TMA load (no multicast) of either CTA reports its bytes to the LEADER's stage
+//     barrier, which the leader arms with the bytes of both CTAs;
+//   * "stage free" and "accumulator ready" are committed by the leader to its own barrier and,
+//     with a second tcgen05.commit, to the peer's barrier at the same offset;
+//   * "accumulator drained" arrives on the leader's barrier from the epilogue warps of both CTAs.
+// All waits are bounded as in the 1-CTA kernel.
+#ifndef AXS6_STAGES2
+#define AXS6_STAGES2 6
+#endif
+constexpr int kStages2 = AXS6_STAGES2;
+constexpr int kA2Bytes = 128 * BK * 2;                  // this CTA's 128 rows of A
+constexpr int kB2Bytes = 128 * BK * 2;                  // this CTA's 128 output columns of B
+constexpr int kStage2Bytes = kA2Bytes + kB2Bytes;
+constexpr int kSmem2Bytes = kStages2 * kStage2Bytes + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_commit2(uint32_t bar_cluster)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void tc_mma2(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsGemm, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar0 = base + kStages2 * kStage2Bytes;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kStages2 + s); };
+    auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * kStages2 + a); };
+    auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * kStages2 + 2 + a); };
+    const uint32_t tmem_slot = bar0 + 8u * (2 * kStages2 + 4);
+    uint8_t *smem_gen = smem_raw + (base - smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(smem_gen + kStages2 * kStage2Bytes + 8 * (2 * kStages2 + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();            // 0 = leader
+    const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+    const int tiles_m = (p.M + 255) / 256, tiles_n = p.tiles_n;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages2; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        // accumulator drained: one arrival per epilogue warp of both CTAs (on the leader's barrier)
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                  // both CTAs' barriers exist before any remote signal
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+                const int m0 = (t / tiles_n) * 256 + (int)rank * 128;
+                const int n0 = (t % tiles_n) * 256 + (int)rank * 128;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, 1)) { ok = false; break; }
+                    const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+                    if (rank == 0) mbar_expect_tx(full_bar(s), 2 * kStage2Bytes);
+                    const uint32_t sa = base + s * kStage2Bytes, sb = sa + kA2Bytes;
+                    const int k0 = kb * BK;
+                    if (!p.a_mn) {
+                        tma_load_2d_pair(sa, &map_a, lead_full, k0, m0);
+                    } else {
+                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(sa + j * 8192, &map_a, lead_full, m0 + 64 * j, k0);
+                    }
+                    if (!p.b_mn) {
+                        tma_load_2d_pair(sb, &map_b, lead_full, k0, n0);
+                    } else {
+                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(sb + j * 8192, &map_b, lead_full, n0 + 64 * j, k0);
+                    }
+                    if (++s == kStages2) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            // M = 256 (>> 4 = 16) over the pair, N = 256
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
+                                   ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            int s = 0, acc = 0;
+            uint32_t ph = 0, aph = 0;
+            bool ok = true;
+            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+                if (!mbar_wait(tempty_bar(acc), aph ^ 1u, 2)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_bar(s), ph, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = base + s * kStage2Bytes, sb = sa + kA2Bytes;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t ad = smem_desc(sa + k * p.a_kstep, p.a_lbo, p.a_sbo);
+                        const uint64_t bd = smem_desc(sb + k * p.b_kstep, p.b_lbo, p.b_sbo);
+                        tc_mma2(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit2(empty_bar(s));                       // frees the stage here ...
+                    tc_commit2(map_to_cta(empty_bar(s), 1));        // ... and in the peer
+                    if (++s == kStages2) { s = 0; ph ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit2(tfull_bar(acc));
+                tc_commit2(map_to_cta(tfull_bar(acc), 1));
+                acc ^= 1;
+                if (acc == 0) aph ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+        const int q = warp & 3;
+        int acc = 0;
+        uint32_t aph = 0;
+        bool ok = true;
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) && (p.ldc % 8 == 0);
+        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+            const int m0 = (t / tiles_n) * 256 + (int)rank * 128, n0 = (t % tiles_n) * 256;
+            if (!mbar_wait(tfull_bar(acc), aph, 4)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+            epilogue_tile(p, taddr, row, n0, vec_ok);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+            acc ^= 1;
+            if (acc == 0) aph ^= 1u;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                  // the peer's shared memory and barriers stay alive until both are done
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
 
@@ -371,11 +568,17 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     const DeviceInfo &d = device_info();
     if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
 
+    // bf16: CTA pairs on 256 x 256 tiles when there are enough of them to fill the GPU
+    // (tune key 7: 1 forces the single-CTA kernel, 2 forces pairs)
+    const int64_t pair_tiles = ((M + 255) / 256) * ((N + BN - 1) / BN);
+    const int64_t mode = tune_value(7);
+    const bool pairs = !kTf32 && mode != 1 && (mode == 2 || pair_tiles >= d.sms / 2);
+
     CUtensorMap ma, mb;
     const bool oka = a_mn ? make_map(&ma, a, esize, (uint64_t)M, (uint64_t)K, (uint64_t)lda, bk)
                           : make_map(&ma, a, esize, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM);
     const bool okb = b_mn ? make_map(&mb, b, esize, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, bk)
-                          : make_map(&mb, b, esize, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BN);
+                          : make_map(&mb, b, esize, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, pairs ? 128 : BN);
     if (!oka || !okb) return AXS6_ERR_DEVICE;
 
     Params p;
@@ -404,6 +607,18 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
         if (cudaFuncSetAttribute(gemm_kernel<kTf32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
             return AXS6_ERR_LAUNCH;
         attr_set[dev] = true;
+    }
+    if (pairs) {
+        static bool attr2_set[64];
+        if (dev >= 0 && dev < 64 && !attr2_set[dev]) {
+            if (cudaFuncSetAttribute(gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2Bytes) != cudaSuccess)
+                return AXS6_ERR_LAUNCH;
+            attr2_set[dev] = true;
+        }
+        int clusters = (int)(pair_tiles < d.sms / 2 ? pair_tiles : d.sms / 2);
+        gemm2_kernel<<<2 * clusters, kThreadsGemm, kSmem2Bytes, stream>>>(ma, mb, p);
+        count_launch();
+        return check_launch();
     }
     int ctas = p.tiles_m * p.tiles_n;
     if (ctas > d.sms) ctas = d.sms;
