@@ -55,6 +55,7 @@ struct Params {
     int tiles_m, tiles_n;
     uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;   // descriptor strides (bytes)
     int bk;                   // values per k-block: 64 (bf16) or 32 (tf32)
+    int splits;               // split-K factor of the 2-CTA kernel (1 or 2); 2 = fp32 output accumulated with red.add
     uint32_t mn_box_bytes;    // bytes of one MN-major TMA box: 128 B x bk rows
 };
 
@@ -151,7 +152,8 @@ __device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn, uint32_t fmt)
 
 // Drains one 128 x 256 fp32 accumulator: this thread owns TMEM lane (= output row) `row` and walks
 // the 256 columns in chunks of 32 (tcgen05.ld 32x32b.x32), adds the bias, converts and stores.
-__device__ __forceinline__ void epilogue_tile(const Params &p, uint32_t taddr, int row, int n0, bool vec_ok)
+__device__ __forceinline__ void epilogue_tile(const Params &p, uint32_t taddr, int row, int n0, bool vec_ok,
+                                              bool accumulate = false, bool add_bias = true)
 {
 #pragma unroll 1
     for (int c = 0; c < BN / 32; ++c) {
@@ -163,7 +165,7 @@ __device__ __forceinline__ void epilogue_tile(const Params &p, uint32_t taddr, i
             float v[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-            if (p.bias) {
+            if (p.bias && add_bias) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
                     if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
@@ -185,6 +187,19 @@ __device__ __forceinline__ void epilogue_tile(const Params &p, uint32_t taddr, i
                 } else {
                     for (int i = 0; i < 32; ++i)
                         if (col0 + i < p.N) dst[i] = __float2bfloat16_rn(v[i]);
+                }
+            } else if (accumulate) {
+                // split-K partial: add into the zero-initialised fp32 output.  With two partials the
+                // result does not depend on their order (0 + a + b == 0 + b + a exactly).
+                float *dst = reinterpret_cast<float *>(p.c) + (long long)row * p.ldc + col0;
+                if (full && vec_ok) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * i), "f"(v[4 * i]),
+                                     "f"(v[4 * i + 1]), "f"(v[4 * i + 2]), "f"(v[4 * i + 3]) : "memory");
+                } else {
+                    for (int i = 0; i < 32; ++i)
+                        if (col0 + i < p.N) atomicAdd(dst + i, v[i]);
                 }
             } else {
                 float *dst = reinterpret_cast<float *>(p.c) + (long long)row * p.ldc + col0;
@@ -402,8 +417,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     const uint32_t rank = cluster_ctarank();            // 0 = leader
     const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
     const int tiles_m = (p.M + 255) / 256, tiles_n = p.tiles_n;
-    const int num_tiles = tiles_m * tiles_n;
-    const int num_kb = (p.K + BK - 1) / BK;
+    const int splits = p.splits;
+    const int num_tiles = tiles_m * tiles_n * splits;     // work units: (tile, K range)
+    const int total_kb = (p.K + BK - 1) / BK;
+    auto kb_begin = [&](int t) { return (int)(((long long)(t % splits) * total_kb) / splits); };
+    auto kb_end = [&](int t) { return (int)(((long long)(t % splits + 1) * total_kb) / splits); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages2; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -429,9 +447,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             uint32_t ph = 0;
             bool ok = true;
             for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-                const int m0 = (t / tiles_n) * 256 + (int)rank * 128;
-                const int n0 = (t % tiles_n) * 256 + (int)rank * 128;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int tile = t / splits;
+                const int m0 = (tile / tiles_n) * 256 + (int)rank * 128;
+                const int n0 = (tile % tiles_n) * 256 + (int)rank * 128;
+                for (int kb = kb_begin(t); kb < kb_end(t); ++kb) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, 1)) { ok = false; break; }
                     const uint32_t lead_full = map_to_cta(full_bar(s), 0);
                     if (rank == 0) mbar_expect_tx(full_bar(s), 2 * kStage2Bytes);
@@ -464,7 +483,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                 if (!mbar_wait(tempty_bar(acc), aph ^ 1u, 2)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int kb0 = kb_begin(t);
+                for (int kb = kb0; kb < kb_end(t); ++kb) {
                     if (!mbar_wait(full_bar(s), ph, 3)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = base + s * kStage2Bytes, sb = sa + kA2Bytes;
@@ -472,7 +492,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                     for (int k = 0; k < 4; ++k) {
                         const uint64_t ad = smem_desc(sa + k * p.a_kstep, p.a_lbo, p.a_sbo);
                         const uint64_t bd = smem_desc(sb + k * p.b_kstep, p.b_lbo, p.b_sbo);
-                        tc_mma2(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+                        tc_mma2(d_tmem, ad, bd, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
                     }
                     tc_commit2(empty_bar(s));                       // frees the stage here ...
                     tc_commit2(map_to_cta(empty_bar(s), 1));        // ... and in the peer
@@ -493,12 +513,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         bool ok = true;
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) && (p.ldc % 8 == 0);
         for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-            const int m0 = (t / tiles_n) * 256 + (int)rank * 128, n0 = (t % tiles_n) * 256;
+            const int tile = t / splits;
+            const int m0 = (tile / tiles_n) * 256 + (int)rank * 128, n0 = (tile % tiles_n) * 256;
             if (!mbar_wait(tfull_bar(acc), aph, 4)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-            epilogue_tile(p, taddr, row, n0, vec_ok);
+            epilogue_tile(p, taddr, row, n0, vec_ok, splits > 1, (t % splits) == 0);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
@@ -590,6 +611,11 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     p.tiles_n = (int)((N + BN - 1) / BN);
     p.bk = bk;
     p.mn_box_bytes = 128u * bk;
+    // Split K in two (fp32 output only): available through tune key 3 = 2.  Measured on the
+    // 4096 x 4096 x 16384 weight-gradient product (256 tile pairs on 74 clusters = 3.46 waves) it is
+    // slower than not splitting (452 vs 436 us: the zero-fill and the red.add traffic cost more than
+    // the better-filled last wave gains), so it is never chosen automatically.
+    p.splits = (pairs && c_dtype == AXS6_F32 && tune_value(3) == 2 && K >= 16 * BK) ? 2 : 1;
     // K-major, 128-byte swizzle: 8-row groups are 1024 B apart, one MMA K step is 32 B.
     // MN-major: 128-byte chunks of the output index are one TMA box (bk k-rows x 128 B) apart,
     // groups of 8 k-rows 1024 B apart, one MMA K step (32 B / esize rows) is that many rows x 128 B.
@@ -615,7 +641,11 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
                 return AXS6_ERR_LAUNCH;
             attr2_set[dev] = true;
         }
-        int clusters = (int)(pair_tiles < d.sms / 2 ? pair_tiles : d.sms / 2);
+        const int64_t units = pair_tiles * p.splits;
+        int clusters = (int)(units < d.sms / 2 ? units : d.sms / 2);
+        if (p.splits > 1 &&
+            cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess)
+            return AXS6_ERR_LAUNCH;
         gemm2_kernel<<<2 * clusters, kThreadsGemm, kSmem2Bytes, stream>>>(ma, mb, p);
         count_launch();
         return check_launch();

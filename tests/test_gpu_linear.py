@@ -339,3 +339,25 @@ def test_tf32_entry_rejects_mn_major():
     assert lib.axs6_gemm_tf32(a.data_ptr(), a.data_ptr(), a.data_ptr(), None, 64, 64, 64, 64, 64, 64, 0, 1, 0, st) == -6
     t = ops.transpose_f32(torch.arange(35 * 50, dtype=torch.float32, device="cuda").reshape(35, 50))
     assert torch.equal(t, torch.arange(35 * 50, dtype=torch.float32, device="cuda").reshape(35, 50).t())
+
+
+def test_split_k_weight_gradient_product_is_deterministic_and_accurate():
+    """The optional split-K mode of the 2-CTA kernel (fp32 output, red.add onto a zeroed buffer):
+    two partials commute, so the result is reproducible."""
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(12)
+    M, N, K = 1024, 1024, 4096                       # 16 tile pairs
+    A = torch.randn(K, M, generator=g).to(torch.bfloat16).cuda()
+    B = torch.randn(K, N, generator=g).to(torch.bfloat16).cuda()
+    ref = (A.float().t().double() @ B.float().double()).cpu()
+    outs = []
+    try:
+        lib.axs6_tune(7, 2)                          # pairs
+        for mode in (2, 2, 1):                       # split, split again, no split
+            lib.axs6_tune(3, mode)
+            outs.append(ops.gemm_bf16(A, B, a_mn=True, b_mn=True))
+    finally:
+        lib.axs6_tune(7, 0); lib.axs6_tune(3, 0)
+    gemm_status_ok()
+    assert torch.equal(outs[0], outs[1])
+    assert rel(outs[0].cpu(), ref) < 1e-5 and rel(outs[2].cpu(), ref) < 1e-5
