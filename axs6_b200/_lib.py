@@ -18,6 +18,7 @@ LAYOUT_PLANES, LAYOUT_WIRE, LAYOUT_SPEC = 0, 1, 2
 FLAG_INPUT_VIA_BF16 = 1
 FLAG_OUTPUT_TF32 = 2
 LINEAR_QUANTIZE_INPUT, LINEAR_QUANTIZE_GRAD, LINEAR_COMPUTE_TF32, LINEAR_BIAS_FROM_QUANTIZED = 1, 2, 4, 8
+LINEAR_BIAS_VIA_BF16 = 16
 
 _i64, _int, _u32, _u64, _ptr = ctypes.c_int64, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p
 

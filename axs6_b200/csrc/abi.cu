@@ -1,6 +1,8 @@
 // Status text, device query and launch bookkeeping of the C ABI.
 #include <atomic>
+#include <map>
 #include <mutex>
+#include <utility>
 
 #include "common.cuh"
 
@@ -13,6 +15,21 @@ void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 static std::atomic<long long> g_tune[8];
 
 int64_t tune_value(int key) { return (key >= 0 && key < 8) ? g_tune[key].load(std::memory_order_relaxed) : 0; }
+
+int cached_occupancy(const void *kernel, int threads)
+{
+    static std::map<std::pair<const void *, int>, int> cache;
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find({kernel, dev});
+    if (it != cache.end()) return it->second;
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess) per_sm = 0;
+    cache[{kernel, dev}] = per_sm;
+    return per_sm;
+}
 
 const DeviceInfo &device_info()
 {

@@ -342,9 +342,8 @@ template <typename K>
 static int launch_codec(K kernel, const CodecArgs &a, int64_t items_per_cta, int64_t items, cudaStream_t stream)
 {
     const DeviceInfo &d = device_info();
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm < 1)
-        return AXS6_ERR_LAUNCH;
+    int per_sm = cached_occupancy(reinterpret_cast<const void *>(kernel), kThreads);
+    if (per_sm < 1) return AXS6_ERR_LAUNCH;
     int64_t ctas = (items + items_per_cta - 1) / items_per_cta;
     const int64_t cap = tune_value(1);
     if (cap > 0 && per_sm > cap) per_sm = (int)cap;

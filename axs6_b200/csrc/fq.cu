@@ -178,9 +178,8 @@ static int launch_persistent(K kernel, const FqArgs &a, int64_t work_items_per_c
                              int want_per_sm, cudaStream_t stream)
 {
     const DeviceInfo &d = device_info();
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm < 1)
-        return AXS6_ERR_LAUNCH;
+    int per_sm = cached_occupancy(reinterpret_cast<const void *>(kernel), kThreads);
+    if (per_sm < 1) return AXS6_ERR_LAUNCH;
     int64_t ctas = (work_items + work_items_per_cta - 1) / work_items_per_cta;
     const int64_t cap = tune_value(0) > 0 ? tune_value(0) : want_per_sm;
     if (cap > 0 && per_sm > cap) per_sm = (int)cap;

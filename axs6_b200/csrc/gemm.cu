@@ -52,6 +52,7 @@ struct Params {
     long long ldc;
     int c_bf16;               // output dtype: 1 bf16, 0 fp32
     const float *bias;        // length N or null
+    int bias_bf16;            // round each bias value to bf16 before adding (F.linear with a bf16 bias)
     int tiles_m, tiles_n;
     uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;   // descriptor strides (bytes)
     int bk;                   // values per k-block: 64 (bf16) or 32 (tf32)
@@ -168,7 +169,10 @@ __device__ __forceinline__ void epilogue_tile(const Params &p, uint32_t taddr, i
             if (p.bias && add_bias) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
-                    if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
+                    if (col0 + i < p.N) {
+                        const float bv = __ldg(p.bias + col0 + i);
+                        v[i] += p.bias_bf16 ? __bfloat162float(__float2bfloat16_rn(bv)) : bv;
+                    }
             }
             const bool full = col0 + 32 <= p.N;
             if (p.c_bf16) {
@@ -233,8 +237,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(smem_gen + kStages * kStageBytes + 8 * (2 * kStages + 4));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_tiles = p.tiles_m * p.tiles_n;
-    const int num_kb = (p.K + p.bk - 1) / p.bk;
+    const int splits = p.splits;
+    const int num_tiles = p.tiles_m * p.tiles_n * splits;  // work units: (tile, K range)
+    const int total_kb = (p.K + p.bk - 1) / p.bk;
+    auto kb_begin = [&](int t) { return (int)(((long long)(t % splits) * total_kb) / splits); };
+    auto kb_end = [&](int t) { return (int)(((long long)(t % splits + 1) * total_kb) / splits); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -258,8 +265,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             uint32_t ph = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                const int m0 = (t / p.tiles_n) * BM, n0 = (t % p.tiles_n) * BN;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int tile = t / splits;
+                const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+                for (int kb = kb_begin(t); kb < kb_end(t); ++kb) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, 1)) { ok = false; break; }
                     mbar_expect_tx(full_bar(s), kStageBytes);
                     const uint32_t sa = base + s * kStageBytes, sb = sa + kABytes;
@@ -293,7 +301,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 if (!mbar_wait(tempty_bar(acc), aph ^ 1u, 2)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int kb0 = kb_begin(t);
+                for (int kb = kb0; kb < kb_end(t); ++kb) {
                     if (!mbar_wait(full_bar(s), ph, 3)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = base + s * kStageBytes, sb = sa + kABytes;
@@ -301,7 +310,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     for (int k = 0; k < 4; ++k) {                  // four 32-byte K steps per 128-byte row
                         const uint64_t ad = smem_desc(sa + k * p.a_kstep, p.a_lbo, p.a_sbo);
                         const uint64_t bd = smem_desc(sb + k * p.b_kstep, p.b_lbo, p.b_sbo);
-                        tc_mma<kTf32>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+                        tc_mma<kTf32>(d_tmem, ad, bd, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
                     }
                     tc_commit(empty_bar(s));            // stage reusable once these MMAs have read it
                     if (++s == kStages) { s = 0; ph ^= 1u; }
@@ -320,12 +329,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         bool ok = true;
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) && (p.ldc % 8 == 0);
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-            const int m0 = (t / p.tiles_n) * BM, n0 = (t % p.tiles_n) * BN;
+            const int tile = t / splits;
+            const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
             if (!mbar_wait(tfull_bar(acc), aph, 4)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-            epilogue_tile(p, taddr, row, n0, vec_ok);
+            epilogue_tile(p, taddr, row, n0, vec_ok, splits > 1, (t % splits) == 0);
             tc_fence_before();
             mbar_arrive(tempty_bar(acc));
             acc ^= 1;
@@ -576,7 +586,8 @@ static bool make_map(CUtensorMap *map, const void *ptr, int esize, uint64_t inne
 
 template <bool kTf32>
 static int launch_gemm(const void *a, const void *b, void *c, const float *bias, int64_t M, int64_t N, int64_t K,
-                       int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn, int c_dtype, cudaStream_t stream)
+                       int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn, int c_dtype, int bias_via_bf16,
+                       cudaStream_t stream)
 {
     constexpr int esize = kTf32 ? 4 : 2;
     constexpr int bk = 128 / esize;                     // values per k-block
@@ -607,6 +618,7 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     p.a_mn = a_mn; p.b_mn = b_mn;
     p.c = c; p.ldc = ldc; p.c_bf16 = (c_dtype == AXS6_BF16) ? 1 : 0;
     p.bias = bias;
+    p.bias_bf16 = bias_via_bf16;
     p.tiles_m = (int)((M + BM - 1) / BM);
     p.tiles_n = (int)((N + BN - 1) / BN);
     p.bk = bk;
@@ -616,6 +628,19 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     // slower than not splitting (452 vs 436 us: the zero-fill and the red.add traffic cost more than
     // the better-filled last wave gains), so it is never chosen automatically.
     p.splits = (pairs && c_dtype == AXS6_F32 && tune_value(3) == 2 && K >= 16 * BK) ? 2 : 1;
+    // Few output tiles but a long contraction (the weight gradient of a small layer: 1024 x 1024 from
+    // 8192 rows is 32 tiles for 148 SMs): split K so that about one work unit per SM exists; the
+    // partial products are added into the zero-filled fp32 output with red.add.  The order of more than
+    // two partials is not fixed, so results can differ in the last bits between runs; tune key 3 = 1
+    // turns this off.
+    if (!pairs && c_dtype == AXS6_F32 && tune_value(3) != 1) {
+        const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+        int64_t want = d.sms / tiles;
+        const int64_t max_by_k = K / (8 * bk);
+        if (want > max_by_k) want = max_by_k;
+        if (want > 16) want = 16;
+        if (want >= 2) p.splits = (int)want;
+    }
     // K-major, 128-byte swizzle: 8-row groups are 1024 B apart, one MMA K step is 32 B.
     // MN-major: 128-byte chunks of the output index are one TMA box (bk k-rows x 128 B) apart,
     // groups of 8 k-rows 1024 B apart, one MMA K step (32 B / esize rows) is that many rows x 128 B.
@@ -650,14 +675,29 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
         count_launch();
         return check_launch();
     }
-    int ctas = p.tiles_m * p.tiles_n;
+    int ctas = p.tiles_m * p.tiles_n * p.splits;
     if (ctas > d.sms) ctas = d.sms;
+    if (p.splits > 1 &&
+        cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess)
+        return AXS6_ERR_LAUNCH;
     gemm_kernel<kTf32><<<ctas, kThreadsGemm, kSmemBytes, stream>>>(ma, mb, p);
     count_launch();
     return check_launch();
 }
 
 }  // namespace gemm
+
+int gemm_launch(bool tf32, const void *a, const void *b, void *c, const float *bias, int64_t M, int64_t N, int64_t K,
+                int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn, int c_dtype, int bias_via_bf16,
+                cudaStream_t stream)
+{
+    if (tf32) {
+        if (a_mn || b_mn) return AXS6_ERR_UNSUPPORTED;
+        return gemm::launch_gemm<true>(a, b, c, bias, M, N, K, lda, ldb, ldc, 0, 0, c_dtype, bias_via_bf16, stream);
+    }
+    return gemm::launch_gemm<false>(a, b, c, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, c_dtype, bias_via_bf16, stream);
+}
+
 }  // namespace axs6
 
 // C[M,N] (+ bias[N]) = op(A) * op(B) with bf16 operands and fp32 accumulation.
@@ -667,7 +707,7 @@ AXS6_API int axs6_gemm_bf16(const void *a, const void *b, void *c, const float *
                             int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn, int c_dtype,
                             axs6_stream_t stream)
 {
-    return axs6::gemm::launch_gemm<false>(a, b, c, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, c_dtype,
+    return axs6::gemm::launch_gemm<false>(a, b, c, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, c_dtype, 0,
                                           static_cast<cudaStream_t>(stream));
 }
 
@@ -678,7 +718,7 @@ AXS6_API int axs6_gemm_tf32(const void *a, const void *b, void *c, const float *
                             axs6_stream_t stream)
 {
     if (a_mn || b_mn) return AXS6_ERR_UNSUPPORTED;      // kind::tf32 gives zeros for MN-major operands on sm_100
-    return axs6::gemm::launch_gemm<true>(a, b, c, bias, M, N, K, lda, ldb, ldc, 0, 0, c_dtype,
+    return axs6::gemm::launch_gemm<true>(a, b, c, bias, M, N, K, lda, ldb, ldc, 0, 0, c_dtype, 0,
                                          static_cast<cudaStream_t>(stream));
 }
 

@@ -215,7 +215,7 @@ AXS6_API int axs6_linear_fwd(const void *x, int x_dtype, int64_t ldx, const void
     if (!valid_dtype(x_dtype) || !valid_dtype(w_dtype) || !valid_dtype(y_dtype) || !valid_block(block)) return AXS6_ERR_ARG;
     if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
     if (M < 0 || N < 0 || K < 0 || ldx < K || ldw < K || ldy < N) return AXS6_ERR_ARG;
-    if (flags & ~(AXS6_LINEAR_QUANTIZE_INPUT | AXS6_LINEAR_COMPUTE_TF32)) return AXS6_ERR_ARG;
+    if (flags & ~(AXS6_LINEAR_QUANTIZE_INPUT | AXS6_LINEAR_COMPUTE_TF32 | AXS6_LINEAR_BIAS_VIA_BF16)) return AXS6_ERR_ARG;
     if (M == 0 || N == 0) return AXS6_OK;
     if (!x || !w || !y || !xq || !wq || K == 0) return AXS6_ERR_ARG;
     if (!aligned16(xq) || !aligned16(wq)) return AXS6_ERR_ALIGN;
@@ -245,7 +245,8 @@ AXS6_API int axs6_linear_fwd(const void *x, int x_dtype, int64_t ldx, const void
     else
         rc = cast_to_bf16(x, x_dtype, xq, M, K, ldx, ldq, st);
     if (rc) return rc;
-    return axs6_gemm_bf16(xq, wq, y, bias, M, N, K, ldq, ldq, ldy, 0, 0, y_dtype, stream);
+    return gemm_launch(false, xq, wq, y, bias, M, N, K, ldq, ldq, ldy, 0, 0, y_dtype,
+                       (flags & AXS6_LINEAR_BIAS_VIA_BF16) ? 1 : 0, st);
 }
 
 AXS6_API int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void *xq, const void *w, int w_dtype,

@@ -79,10 +79,11 @@ class _on:
         self.prev = None
 
     def __enter__(self):
-        cur = torch.cuda.current_device()
-        if self.dev.index is not None and self.dev.index != cur:
-            self.prev = cur
-            torch.cuda.set_device(self.dev)
+        if self.dev.index is not None:
+            cur = torch.cuda.current_device()
+            if self.dev.index != cur:
+                self.prev = cur
+                torch.cuda.set_device(self.dev)
 
     def __exit__(self, *exc):
         if self.prev is not None:
@@ -236,22 +237,54 @@ def _padded_copy(t: torch.Tensor) -> torch.Tensor:
     return buf[:, :cols]
 
 
+def _r8(v: int) -> int:
+    return (v + 7) // 8 * 8
+
+
+def _r4(v: int) -> int:
+    return (v + 3) // 4 * 4
+
+
+def _ws_bytes(what: int, M: int, N: int, K: int) -> int:
+    """Python twin of axs6_linear_workspace_bytes (saves a library call per buffer)."""
+    if what == 0: return M * _r8(K) * 2
+    if what == 1: return N * _r8(K) * 2
+    if what == 2: return M * _r8(N) * 2
+    if what == 3: return 32 * N * 4
+    if what == 4: return M * _r4(K) * 4
+    if what == 5: return N * _r4(K) * 4
+    if what == 6: return M * _r4(N) * 4
+    if what == 7: return (K * _r4(N) + N * _r4(M) + K * _r4(M)) * 4
+    raise ValueError(what)
+
+
 def _ws(what: int, M: int, N: int, K: int, dev, dtype=torch.uint8) -> torch.Tensor:
-    n = int(_lib.load().axs6_linear_workspace_bytes(what, M, N, K))
-    return torch.empty(max(n, 16), dtype=torch.uint8, device=dev)
+    return torch.empty(max(_ws_bytes(what, M, N, K), 16), dtype=torch.uint8, device=dev)
+
+
+def _carve(dev, sizes: list[int]) -> list[int]:
+    """One allocation for several 256-byte aligned scratch regions; returns (keep-alive tensor, pointers)."""
+    offs, total = [], 0
+    for n in sizes:
+        offs.append(total)
+        total += (max(n, 16) + 255) // 256 * 256
+    buf = torch.empty(total, dtype=torch.uint8, device=dev)
+    base = buf.data_ptr()
+    return buf, [base + o for o in offs]
 
 
 def linear_fwd(x2: torch.Tensor, w: torch.Tensor, bias_f32: torch.Tensor | None, block_size: int, grid: int,
-               quantize_input: bool, out_dtype: torch.dtype, tf32: bool = False):
+               quantize_input: bool, out_dtype: torch.dtype, tf32: bool = False, bias_via_bf16: bool = False):
     """-> (y (M, N), xq workspace holding the quantised activations that backward needs).
     ``tf32``: the fp32 graph (operands fake-quantised in fp32, TF32 tensor cores) instead of bf16."""
     M, K = x2.shape
     N = w.shape[0]
     dev = x2.device
-    xq = _ws(4 if tf32 else 0, M, N, K, dev)
-    wq = _ws(5 if tf32 else 1, M, N, K, dev)
+    xq = torch.empty(max(_ws_bytes(4 if tf32 else 0, M, N, K), 16), dtype=torch.uint8, device=dev)
+    wq = torch.empty(max(_ws_bytes(5 if tf32 else 1, M, N, K), 16), dtype=torch.uint8, device=dev)
     y = torch.empty((M, N), dtype=out_dtype, device=dev)
-    flags = (_lib.LINEAR_QUANTIZE_INPUT if quantize_input else 0) | (_lib.LINEAR_COMPUTE_TF32 if tf32 else 0)
+    flags = (_lib.LINEAR_QUANTIZE_INPUT if quantize_input else 0) | (_lib.LINEAR_COMPUTE_TF32 if tf32 else 0) | \
+            (_lib.LINEAR_BIAS_VIA_BF16 if bias_via_bf16 else 0)
     with _on(dev):
         st = _lib.load().axs6_linear_fwd(x2.data_ptr(), _DT[x2.dtype], x2.stride(0) if M > 1 else K,
                                          w.data_ptr(), _DT[w.dtype], w.stride(0) if N > 1 else K,
@@ -271,10 +304,11 @@ def linear_bwd(g2: torch.Tensor, xq: torch.Tensor, w: torch.Tensor, M: int, N: i
     dx = torch.empty((M, K), dtype=dx_dtype, device=dev) if need_dx else None
     dw = torch.empty((N, K), dtype=torch.float32, device=dev) if need_dw else None
     db = torch.empty((N,), dtype=torch.float32, device=dev) if need_db else None
-    gq = _ws(6 if tf32 else 2, M, N, K, dev)
-    wq = _ws(5 if tf32 else 1, M, N, K, dev) if need_dx else None
-    part = _ws(3, M, N, K, dev) if need_db else None
-    tscr = _ws(7, M, N, K, dev) if (tf32 and (need_dx or need_dw)) else None
+    keep, (p_gq, p_wq, p_part, p_tscr) = _carve(dev, [
+        _ws_bytes(6 if tf32 else 2, M, N, K),
+        _ws_bytes(5 if tf32 else 1, M, N, K) if need_dx else 0,
+        _ws_bytes(3, M, N, K) if need_db else 0,
+        _ws_bytes(7, M, N, K) if (tf32 and (need_dx or need_dw)) else 0])
     seed, off = (0, 0)
     nz = None
     if quantize_grad:
@@ -290,10 +324,10 @@ def linear_bwd(g2: torch.Tensor, xq: torch.Tensor, w: torch.Tensor, M: int, N: i
             w.data_ptr(), _DT[w.dtype], w.stride(0) if N > 1 else K,
             dx.data_ptr() if need_dx else None, _DT[dx_dtype], K, dw.data_ptr() if need_dw else None, K,
             db.data_ptr() if need_db else None, M, N, K, block_size, grid, flags, seed, off,
-            nz.data_ptr() if nz is not None else None, gq.data_ptr(), wq.data_ptr() if wq is not None else None,
-            part.data_ptr() if part is not None else None, tscr.data_ptr() if tscr is not None else None,
-            _stream(dev))
+            nz.data_ptr() if nz is not None else None, p_gq, p_wq if need_dx else None,
+            p_part if need_db else None, p_tscr if (tf32 and (need_dx or need_dw)) else None, _stream(dev))
     _lib.check("axs6_linear_bwd", st)
+    del keep
     return dx, dw, db
 
 

@@ -44,8 +44,11 @@ class _AXSLinearBF16Function(torch.autograd.Function):
         x2 = _rows(input)
         w = weight if weight.dtype in (torch.float32, torch.bfloat16) else weight.float()
         w = w if w.stride(-1) == 1 else w.contiguous()
-        b32 = bias.to(torch.bfloat16).float().contiguous() if bias is not None else None   # F.linear sees bf16(bias)
-        y, xq = ops.linear_fwd(x2, w, b32, block_size, ops.GRID_NF5, bool(quantize_input), torch.bfloat16)
+        b32 = None
+        if bias is not None:                      # F.linear sees bf16(bias): rounded inside the GEMM epilogue
+            b32 = bias if (bias.dtype == torch.float32 and bias.is_contiguous()) else bias.float().contiguous()
+        y, xq = ops.linear_fwd(x2, w, b32, block_size, ops.GRID_NF5, bool(quantize_input), torch.bfloat16,
+                               bias_via_bf16=True)
         ctx.save_for_backward(xq, weight, bias)
         ctx.block_size = block_size
         ctx.quantize_grad = bool(quantize_grad)

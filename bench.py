@@ -19,6 +19,7 @@ Prints ONE JSON line on rank 0:
   cpu_baseline  the CPU oracle (a port of the reference's eager algorithm, C + OpenMP) on a
              bounded row sample of the same tensor, on this box's host cores
   codec, linear   the two other metrics of the path (pack->unpack GB/s, fused-linear TFLOP/s)
+  fq_sweep, minigpt   the fake-quantise sweep (fp32 + bf16) and the MiniGPT-style training step
 `--impl reference` times the CPU oracle alone (the reference is pure Python/torch and does not
 travel to the GPU box; the oracle is its pinned C restatement) and prints the same line shape.
 """
@@ -263,6 +264,15 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     except Exception as e:          # the linear metric is reported separately; never hide the headline
         if rank == 0:
             extra["linear"] = {"error": repr(e)}
+
+    try:
+        from axs6_b200 import minigpt_bench
+        mg = minigpt_bench.run(args, rank, world, dev)
+        if rank == 0:
+            extra["minigpt"] = mg
+    except Exception as e:
+        if rank == 0:
+            extra["minigpt"] = {"error": repr(e)}
 
     if rank == 0:
         line = {

@@ -49,6 +49,8 @@ enum { AXS6_LAYOUT_PLANES = 0, /* AXSTensor planes: u8 exponent (rows,nblk), u8 
 #define AXS6_LINEAR_COMPUTE_TF32 4u   /* fp32 graph: operands fake-quantised in fp32 (no bf16 cast),
                                          rounded to TF32, products on the TF32 tensor cores; work
                                          buffers are fp32 (workspace codes 4, 5, 6)              */
+#define AXS6_LINEAR_BIAS_VIA_BF16 16u  /* forward: add bf16(bias) instead of bias, as F.linear does with
+                                         `bias.to(bfloat16)` (mixed_precision.py:108)                 */
 #define AXS6_LINEAR_BIAS_FROM_QUANTIZED 8u /* db sums the QUANTISED gradient, as the fp32 reference
                                          functions do (functional_unified.py:151, :161-165)      */
 

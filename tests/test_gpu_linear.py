@@ -361,3 +361,27 @@ def test_split_k_weight_gradient_product_is_deterministic_and_accurate():
     gemm_status_ok()
     assert torch.equal(outs[0], outs[1])
     assert rel(outs[0].cpu(), ref) < 1e-5 and rel(outs[2].cpu(), ref) < 1e-5
+
+
+def test_minigpt_block_trains_with_axs6_linears():
+    """A decoder block built on AXSLinearMixedPrecision: forward/backward run, gradients reach every
+    parameter, a few AdamW steps reduce the loss (convergence smoke test in the spirit of
+    tests/test_mixed_precision.py:286-348 of the reference)."""
+    mg = importlib.import_module("axs6_b200.minigpt_bench")
+    torch.manual_seed(0)
+    blk = mg.Block(lambda i, o, bias=True: mp.AXSLinearMixedPrecision(i, o, bias=bias)).cuda()
+    head = mp.AXSLinearMixedPrecision(mg.D_MODEL, 64).cuda()
+    params = list(blk.parameters()) + list(head.parameters())
+    opt = torch.optim.AdamW(params, lr=1e-3)
+    x = torch.randn(2, 128, mg.D_MODEL, device="cuda").to(torch.bfloat16)
+    y = torch.randint(0, 64, (2 * 128,), device="cuda")
+    losses = []
+    for _ in range(12):
+        opt.zero_grad()
+        loss = torch.nn.functional.cross_entropy(head(blk(x)).float().view(-1, 64), y)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    assert all(p.grad is not None for p in params)
+    assert losses[-1] < losses[0] * 0.9
+    gemm_status_ok()
