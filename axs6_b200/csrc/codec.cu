@@ -394,6 +394,170 @@ static int launch_unpack(const CodecArgs &a, bool planes, bool vec, cudaStream_t
     return launch_codec(unpack_generic_kernel<Tout, GRID, kBytes>, a, kThreads, total, st);
 }
 
+// ------------------------------------------------------------------------------------------ bf16 fast pack
+// Specialised pack for the common case bf16 input, NF5 grid, nearest rounding, block 32, byte
+// layouts, 16-byte aligned and contiguous: ONE THREAD PER BLOCK and integer arithmetic on the
+// bf16 bit patterns.  About 10 instructions per value instead of 25 (the general kernel is bound
+// by instruction issue, not by HBM).
+//
+// Why integers suffice: a bf16 value is (128 + m) * 2^(e - 134) with a 7-bit m.  For a block whose
+// largest magnitude has exponent field E the scale is 2^(E - 126) (the top-of-binade exponent bump
+// of the fp32 path cannot occur: the low 16 mantissa bits are zero), and
+//     idx = trunc(|x| / S * 1023) = ((128 + m) * 1023) >> (8 + j),   j = E - e,
+// exactly, because the fp32 product has only 18 significant bits.  idx = 0 for j >= 10.  So the
+// 5-bit code depends on (j, m) only: key = ((E << 7) | 127) - |x|_bits = j * 128 + (127 - m) indexes a
+// 1280-entry table; keys beyond it (small or zero values, denormals) give code 0.  Taken for
+// E in [11, 252]; an all-zero block is a record of zeros; anything else (denormal-range or
+// near-overflow block maxima) takes the per-value path of the general formulas.
+constexpr int kFastBlocks = 256;         // blocks (threads) per CTA iteration
+constexpr int kKeyLimit = 1280;
+
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    asm("max.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t min_u16x2(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    asm("min.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+template <int HDR>
+__global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_kernel(const uint16_t *__restrict__ x,
+                                                                       uint8_t *__restrict__ out, int64_t nblocks)
+{
+    constexpr int REC = HDR + 24;
+    __shared__ __align__(16) uint8_t table[kKeyLimit + 16];
+    __shared__ __align__(16) uint8_t stage[2][kFastBlocks * REC];
+    for (int key = threadIdx.x; key <= kKeyLimit; key += kFastBlocks) {
+        uint8_t code = 0;
+        if (key < kKeyLimit) {
+            const int j = key >> 7, m = 127 - (key & 127);
+            code = g_reverse[((128 + m) * 1023) >> (8 + j)];
+        }
+        table[key] = code;
+    }
+    __syncthreads();
+
+    int buf = 0;
+    const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
+    for (int64_t grp = blockIdx.x; grp < groups; grp += gridDim.x, buf ^= 1) {
+        const int64_t b = grp * kFastBlocks + threadIdx.x;
+        uint8_t *rec = &stage[buf][threadIdx.x * REC];
+        if (b < nblocks) {
+            uint32_t w[16];
+            const uint4 *src = reinterpret_cast<const uint4 *>(x + b * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 v = src[i];
+                w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+            }
+            uint32_t mx = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) mx = max_u16x2(mx, w[i] & 0x7FFF7FFFu);
+            const uint32_t amax16 = max(mx & 0xFFFFu, mx >> 16);
+            const uint32_t ef = amax16 >> 7;
+            if (amax16 == 0u || (ef >= 11u && ef <= 252u)) {
+                const uint32_t se = amax16 ? ef + 1u : 0u;
+                const uint32_t a1 = amax16 ? ((ef << 7) | 127u) : 0x7FFFu;
+                const uint32_t a2 = a1 | (a1 << 16);
+                const uint32_t lim2 = (uint32_t)kKeyLimit | ((uint32_t)kKeyLimit << 16);
+                uint32_t pay[6];
+#pragma unroll
+                for (int gq = 0; gq < 8; ++gq) {                 // 4 values -> one 24-bit group
+                    const uint32_t wa = w[2 * gq], wb = w[2 * gq + 1];
+                    const uint32_t ma = wa & 0x7FFF7FFFu, mb = wb & 0x7FFF7FFFu;
+                    const uint32_t ka = min_u16x2(a2 - ma, lim2), kb = min_u16x2(a2 - mb, lim2);
+                    const uint32_t c0 = table[ka & 0xFFFFu], c1 = table[ka >> 16];
+                    const uint32_t c2 = table[kb & 0xFFFFu], c3 = table[kb >> 16];
+                    uint32_t g = c0 | (c1 << 6) | (c2 << 12) | (c3 << 18);
+                    // sign bits of the non-zero values: bit 15 / 31 of (w & (|w| + 0x7FFF)) per half
+                    const uint32_t ta = wa & (ma + 0x7FFF7FFFu), tb = wb & (mb + 0x7FFF7FFFu);
+                    // bytes 1, 3 of ta and 1, 3 of tb, each replicated from its top bit: 0x00 or 0xFF per value
+                    uint32_t r;
+                    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(ta), "r"(tb), "r"(0xFDB9u));
+                    g |= (r & 0x00020820u) | ((r >> 8) & 0x00800000u);   // sign bits at 5, 11, 17 and 23
+                    // append the 24-bit group to the 192-bit payload
+                    if ((gq & 3) == 0) { pay[(gq >> 2) * 3] = g; }
+                    else if ((gq & 3) == 1) { pay[(gq >> 2) * 3] |= g << 24; pay[(gq >> 2) * 3 + 1] = g >> 8; }
+                    else if ((gq & 3) == 2) { pay[(gq >> 2) * 3 + 1] |= g << 16; pay[(gq >> 2) * 3 + 2] = g >> 16; }
+                    else { pay[(gq >> 2) * 3 + 2] |= g << 8; }
+                }
+                if (HDR == 1) {
+                    rec[0] = (uint8_t)se;
+                } else {
+                    rec[0] = (uint8_t)((se << 2) & 0xFFu);
+                    rec[1] = (uint8_t)(se >> 6);
+                }
+#pragma unroll
+                for (int i = 0; i < 6; ++i) {
+                    rec[HDR + 4 * i] = (uint8_t)pay[i];
+                    rec[HDR + 4 * i + 1] = (uint8_t)(pay[i] >> 8);
+                    rec[HDR + 4 * i + 2] = (uint8_t)(pay[i] >> 16);
+                    rec[HDR + 4 * i + 3] = (uint8_t)(pay[i] >> 24);
+                }
+            } else {
+                // rare block: the general fp32 formulas, one value at a time, straight into the record
+                const uint32_t amax_bits = amax16 << 16;
+                const Axs6Scale sc = axs6_scale_codes(amax_bits);
+                if (HDR == 1) {
+                    rec[0] = (uint8_t)sc.se;
+                } else {
+                    rec[0] = (uint8_t)((sc.se << 2) & 0xFF);
+                    rec[1] = (uint8_t)(sc.se >> 6);
+                }
+                uint32_t acc = 0;
+                int nb = 0, o = HDR;
+#pragma unroll 1
+                for (int i = 0; i < 32; ++i) {
+                    const uint32_t bits = (uint32_t)x[b * 32 + i] << 16;
+                    const uint32_t ab = bits & 0x7FFFFFFFu;
+                    const int idx = axs6_nf5_index(axs6_normalise(__uint_as_float(ab), sc));
+                    const uint32_t code = (uint32_t)g_reverse[idx] | ((ab != 0u && (bits >> 31)) ? 32u : 0u);
+                    acc |= code << nb;
+                    nb += 6;
+                    while (nb >= 8) { rec[o++] = (uint8_t)acc; acc >>= 8; nb -= 8; }
+                }
+            }
+        }
+        __syncthreads();
+        // move this iteration's records (contiguous, 16-byte aligned: 256 * REC is a multiple of 16)
+        const int64_t blk0 = grp * kFastBlocks;
+        int64_t nb = nblocks - blk0;
+        if (nb > kFastBlocks) nb = kFastBlocks;
+        const int len = (int)nb * REC;
+        uint8_t *dst = out + blk0 * REC;
+        const int nvec = len >> 4;
+        for (int i = threadIdx.x; i < nvec; i += kFastBlocks)
+            st_stream16(dst + 16 * i, reinterpret_cast<const uint4 *>(stage[buf])[i]);
+        for (int i = (nvec << 4) + threadIdx.x; i < len; i += kFastBlocks) dst[i] = stage[buf][i];
+        // the other buffer is written next; this one again only after the next __syncthreads
+    }
+}
+
+static int launch_pack_fast(const void *x, void *out, int64_t nblocks, int hdr, cudaStream_t st)
+{
+    const DeviceInfo &d = device_info();
+    const void *fn = hdr == 1 ? reinterpret_cast<const void *>(pack_bf16_nf5_b32_kernel<1>)
+                              : reinterpret_cast<const void *>(pack_bf16_nf5_b32_kernel<2>);
+    int per_sm = cached_occupancy(fn, kFastBlocks);
+    if (per_sm < 1) return AXS6_ERR_LAUNCH;
+    const int64_t cap = tune_value(1);
+    if (cap > 0 && per_sm > cap) per_sm = (int)cap;
+    int64_t ctas = (nblocks + kFastBlocks - 1) / kFastBlocks;
+    if (ctas > (int64_t)d.sms * per_sm) ctas = (int64_t)d.sms * per_sm;
+    if (ctas < 1) ctas = 1;
+    if (hdr == 1)
+        pack_bf16_nf5_b32_kernel<1><<<(unsigned)ctas, kFastBlocks, 0, st>>>(static_cast<const uint16_t *>(x), static_cast<uint8_t *>(out), nblocks);
+    else
+        pack_bf16_nf5_b32_kernel<2><<<(unsigned)ctas, kFastBlocks, 0, st>>>(static_cast<const uint16_t *>(x), static_cast<uint8_t *>(out), nblocks);
+    count_launch();
+    return check_launch();
+}
+
 static bool layout_ok(int layout) { return layout == AXS6_LAYOUT_PLANES || layout == AXS6_LAYOUT_WIRE || layout == AXS6_LAYOUT_SPEC; }
 
 }  // namespace axs6
@@ -436,6 +600,9 @@ AXS6_API int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, 
     const bool vec = aligned16(x) && (cols % kChunk == 0) && (ldx % kChunk == 0) && aligned16(out0) &&
                      (!planes || (aligned16(out1) && aligned16(out2))) && (round != kNoise || aligned16(noise));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (vec && !planes && a.g.flat && in_dtype == AXS6_BF16 && grid == AXS6_GRID_NF5 && round == kNearest && block == 32 &&
+        tune_value(2) != 1)
+        return launch_pack_fast(x, out0, rows * (cols / 32), a.hdr, st);
     return in_dtype == AXS6_F32 ? dispatch_pack<float>(a, grid, round, planes, vec, st)
                                 : dispatch_pack<__nv_bfloat16>(a, grid, round, planes, vec, st);
 }
