@@ -562,6 +562,80 @@ static bool layout_ok(int layout) { return layout == AXS6_LAYOUT_PLANES || layou
 
 }  // namespace axs6
 
+// ------------------------------------------------------------------------------------------ planes <-> records
+// One thread per block: planes (exponent, sign, magnitude bytes) to a byte record or back, no
+// arithmetic on values.  The counterpart of _pack_to_flat_buffer / _unpack_from_flat_buffer
+// (axs/unified/distributed.py:147-232) and of AXSBlock.to_bytes / from_bytes (axs/core.py:97-152)
+// for callers that already hold an AXSTensor.
+namespace axs6 {
+
+__global__ void __launch_bounds__(256) planes_to_records_kernel(const uint8_t *se, const uint8_t *sg, const uint8_t *mg,
+                                                               uint8_t *out, int64_t nblocks, int B, int hdr)
+{
+    const int rec = hdr + B * 3 / 4;
+    for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += (int64_t)gridDim.x * blockDim.x) {
+        uint8_t *r = out + b * rec;
+        const uint32_t e = se[b];
+        if (hdr == 1) {
+            r[0] = (uint8_t)e;
+        } else {
+            r[0] = (uint8_t)((e << 2) & 0xFFu);
+            r[1] = (uint8_t)(e >> 6);
+        }
+        for (int g = 0; g < B / 4; ++g) {
+            uint32_t v = 0;
+            for (int i = 0; i < 4; ++i) {
+                const int64_t o = b * B + 4 * g + i;
+                v |= (((uint32_t)(sg[o] & 1u) << 5) | (uint32_t)(mg[o] & 31u)) << (6 * i);
+            }
+            r[hdr + 3 * g] = (uint8_t)v; r[hdr + 3 * g + 1] = (uint8_t)(v >> 8); r[hdr + 3 * g + 2] = (uint8_t)(v >> 16);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) records_to_planes_kernel(const uint8_t *in, uint8_t *se, uint8_t *sg, uint8_t *mg,
+                                                               int64_t nblocks, int B, int hdr)
+{
+    const int rec = hdr + B * 3 / 4;
+    for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += (int64_t)gridDim.x * blockDim.x) {
+        const uint8_t *r = in + b * rec;
+        se[b] = (hdr == 1) ? r[0] : (uint8_t)((((uint32_t)r[0] | ((uint32_t)r[1] << 8)) >> 2) & 0xFFu);
+        for (int g = 0; g < B / 4; ++g) {
+            const uint32_t v = (uint32_t)r[hdr + 3 * g] | ((uint32_t)r[hdr + 3 * g + 1] << 8) | ((uint32_t)r[hdr + 3 * g + 2] << 16);
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t code = (v >> (6 * i)) & 63u;
+                sg[b * B + 4 * g + i] = (uint8_t)(code >> 5);
+                mg[b * B + 4 * g + i] = (uint8_t)(code & 31u);
+            }
+        }
+    }
+}
+
+}  // namespace axs6
+
+AXS6_API int axs6_repack(int to_records, int layout, int block, int64_t nblocks, void *exponents, void *signs,
+                         void *magnitudes, void *records, axs6_stream_t stream)
+{
+    using namespace axs6;
+    if (!valid_block(block) || (layout != AXS6_LAYOUT_WIRE && layout != AXS6_LAYOUT_SPEC) || nblocks < 0) return AXS6_ERR_ARG;
+    if (nblocks == 0) return AXS6_OK;
+    if (!exponents || !signs || !magnitudes || !records) return AXS6_ERR_ARG;
+    const DeviceInfo &d = device_info();
+    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+    int64_t ctas = (nblocks + 255) / 256;
+    if (ctas > (int64_t)d.sms * 8) ctas = (int64_t)d.sms * 8;
+    const int hdr = layout == AXS6_LAYOUT_SPEC ? 2 : 1;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (to_records)
+        planes_to_records_kernel<<<(unsigned)ctas, 256, 0, st>>>(static_cast<const uint8_t *>(exponents), static_cast<const uint8_t *>(signs),
+                                                                 static_cast<const uint8_t *>(magnitudes), static_cast<uint8_t *>(records), nblocks, block, hdr);
+    else
+        records_to_planes_kernel<<<(unsigned)ctas, 256, 0, st>>>(static_cast<const uint8_t *>(records), static_cast<uint8_t *>(exponents),
+                                                                 static_cast<uint8_t *>(signs), static_cast<uint8_t *>(magnitudes), nblocks, block, hdr);
+    count_launch();
+    return check_launch();
+}
+
 AXS6_API int64_t axs6_record_bytes(int layout, int block)
 {
     if (!axs6::valid_block(block)) return 0;

@@ -667,7 +667,9 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
             attr2_set[dev] = true;
         }
         const int64_t units = pair_tiles * p.splits;
-        int clusters = (int)(units < d.sms / 2 ? units : d.sms / 2);
+        // tune key 8: SMs to leave to other work (a collective running on another stream)
+        const int64_t usable = d.sms - (tune_value(8) > 0 && tune_value(8) < d.sms - 2 ? tune_value(8) : 0);
+        int clusters = (int)(units < usable / 2 ? units : usable / 2);
         if (p.splits > 1 &&
             cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess)
             return AXS6_ERR_LAUNCH;
@@ -676,7 +678,10 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
         return check_launch();
     }
     int ctas = p.tiles_m * p.tiles_n * p.splits;
-    if (ctas > d.sms) ctas = d.sms;
+    {
+        const int64_t usable = d.sms - (tune_value(8) > 0 && tune_value(8) < d.sms - 2 ? tune_value(8) : 0);
+        if (ctas > usable) ctas = (int)usable;
+    }
     if (p.splits > 1 &&
         cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess)
         return AXS6_ERR_LAUNCH;

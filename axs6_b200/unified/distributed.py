@@ -41,6 +41,33 @@ def _unpack_gradient(shared_exponents, signs, magnitudes, original_shape, block_
     return y.reshape(original_shape)
 
 
+def _pack_to_flat_buffer(shared_exponents: torch.Tensor, signs: torch.Tensor, magnitudes: torch.Tensor) -> torch.Tensor:
+    """Planes -> flat int8 buffer of wire records (reference: distributed.py:147-198)."""
+    rows, num_blocks, block_size = magnitudes.shape
+    se = shared_exponents.contiguous()
+    sg = signs.contiguous()
+    mg = magnitudes.contiguous()
+    rec = 1 + block_size * 3 // 4
+    out = torch.empty(rows * num_blocks * rec, dtype=torch.uint8, device=mg.device)
+    st = ops._lib.load().axs6_repack(1, ops.LAYOUT_WIRE, block_size, rows * num_blocks, se.data_ptr(), sg.data_ptr(),
+                                     mg.data_ptr(), out.data_ptr(), torch.cuda.current_stream(mg.device).cuda_stream)
+    ops._lib.check("axs6_repack", st)
+    return out.view(torch.int8)
+
+
+def _unpack_from_flat_buffer(buffer: torch.Tensor, rows: int, num_blocks: int, block_size: int):
+    """Flat wire records -> (exponents u8, signs bool, magnitudes u8) (reference: distributed.py:201-232)."""
+    buf = buffer.contiguous()
+    dev = buf.device
+    se = torch.empty((rows, num_blocks), dtype=torch.uint8, device=dev)
+    sg = torch.empty((rows, num_blocks, block_size), dtype=torch.bool, device=dev)
+    mg = torch.empty((rows, num_blocks, block_size), dtype=torch.uint8, device=dev)
+    st = ops._lib.load().axs6_repack(0, ops.LAYOUT_WIRE, block_size, rows * num_blocks, se.data_ptr(), sg.data_ptr(),
+                                     mg.data_ptr(), buf.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+    ops._lib.check("axs6_repack", st)
+    return se, sg, mg
+
+
 # ---------------------------------------------------------------------------------------------
 # Row sharding and gradient exchange (host logic over torch.distributed)
 # ---------------------------------------------------------------------------------------------

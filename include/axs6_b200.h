@@ -72,7 +72,8 @@ int64_t axs6_query(int what);
 /* Performance knobs for experiments (process-wide, not needed for correct results):
  * key 0 = cap on resident CTAs per SM of the fake-quantise kernels, key 1 = the same for the
  * pack / unpack kernels, key 2 = 1 disables the specialised bf16 pack kernel, key 3 = 2 turns on split-K (two partials, fp32 output) in the bf16 GEMM, keys 4-6 = overrides
- * of the GEMM's shared-memory descriptor strides, key 7 = GEMM kernel (1 single-CTA, 2 CTA pairs);
+ * of the GEMM's shared-memory descriptor strides, key 7 = GEMM kernel (1 single-CTA, 2 CTA pairs), key 8 = SMs the GEMM leaves free (for a collective
+ * on another stream);
  * value 0 restores the built-in choice. */
 int axs6_tune(int key, int64_t value);
 
@@ -119,6 +120,13 @@ int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, int64_t l
 int axs6_unpack(int layout, const void *in0, const void *in1, const void *in2,
                 void *y, int out_dtype, int64_t rows, int64_t cols, int64_t ldy,
                 int block, int grid, axs6_stream_t stream);
+
+/* Planes <-> byte records without touching values: to_records = 1 packs (exponents, signs,
+ * magnitudes) of `nblocks` blocks into WIRE or SPEC records, to_records = 0 unpacks them.
+ * Replaces _pack_to_flat_buffer / _unpack_from_flat_buffer (axs/unified/distributed.py:147-232)
+ * and AXSBlock.to_bytes / from_bytes (axs/core.py:97-152) for data already held as planes. */
+int axs6_repack(int to_records, int layout, int block, int64_t nblocks,
+                void *exponents, void *signs, void *magnitudes, void *records, axs6_stream_t stream);
 
 /* Bytes per block record of a byte layout (0 for PLANES or bad arguments). */
 int64_t axs6_record_bytes(int layout, int block);

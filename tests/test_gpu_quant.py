@@ -361,3 +361,18 @@ def test_gradient_hooks_on_one_gpu_rank():
         assert out.shape == (1000, 7)
     finally:
         dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("B", [8, 16, 32])
+def test_planes_to_records_and_back(B):
+    """The reference-named helpers for data already held as planes."""
+    x = torch.randn(21, 96, generator=torch.Generator().manual_seed(B))
+    se, sg, mg, shape = udist._pack_gradient(x.cuda(), B)
+    buf = udist._pack_to_flat_buffer(se, sg, mg)
+    ose, osg, omg = oracle.quantize(x.numpy(), B, oracle.GRID_NF5)
+    assert buf.dtype == torch.int8
+    assert_bits_equal(buf.view(torch.uint8), oracle.pack_bytes(ose, osg, omg, oracle.LAYOUT_WIRE), "records from planes")
+    se2, sg2, mg2 = udist._unpack_from_flat_buffer(buf, 21, 96 // B, B)
+    assert torch.equal(se2, se) and torch.equal(sg2, sg) and torch.equal(mg2, mg) and sg2.dtype == torch.bool
+    back = udist._unpack_gradient(se2, sg2, mg2, shape, B)
+    assert_bits_equal(back, oracle.dequantize(ose, osg, omg, 96, oracle.GRID_NF5), "values from planes")
