@@ -153,11 +153,12 @@ __device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn, uint32_t fmt)
 
 // Drains one 128 x 256 fp32 accumulator: this thread owns TMEM lane (= output row) `row` and walks
 // the 256 columns in chunks of 32 (tcgen05.ld 32x32b.x32), adds the bias, converts and stores.
+template <int TN = BN>
 __device__ __forceinline__ void epilogue_tile(const Params &p, uint32_t taddr, int row, int n0, bool vec_ok,
                                               bool accumulate = false, bool add_bias = true)
 {
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = 0; c < TN / 32; ++c) {
         uint32_t r[32];
         AXS6_TMEM_LD32(taddr + (uint32_t)(c * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -363,14 +364,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 //     with a second tcgen05.commit, to the peer's barrier at the same offset;
 //   * "accumulator drained" arrives on the leader's barrier from the epilogue warps of both CTAs.
 // All waits are bounded as in the 1-CTA kernel.
-#ifndef AXS6_STAGES2
-#define AXS6_STAGES2 6
-#endif
-constexpr int kStages2 = AXS6_STAGES2;
-constexpr int kA2Bytes = 128 * BK * 2;                  // this CTA's 128 rows of A
-constexpr int kB2Bytes = 128 * BK * 2;                  // this CTA's 128 output columns of B
-constexpr int kStage2Bytes = kA2Bytes + kB2Bytes;
-constexpr int kSmem2Bytes = kStages2 * kStage2Bytes + 1024 + 256;
+// Tile width TN is 256, or 128 for problems whose 256-wide tiles fill the last wave of clusters badly
+// (e.g. a 4096 x 4096 weight gradient: 256 tile pairs on 74 clusters = 3.46 waves; 512 narrower
+// pairs = 6.92 waves).
+template <int TN> struct Pair {
+    static constexpr int kStages = TN == 256 ? 6 : 8;
+    static constexpr int kABytes = 128 * BK * 2;               // this CTA's 128 rows of A
+    static constexpr int kBBytes = (TN / 2) * BK * 2;          // this CTA's half of the TN output columns of B
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
 
 __device__ __forceinline__ uint32_t cluster_ctarank()
 {
@@ -409,9 +412,11 @@ __device__ __forceinline__ void tc_mma2(uint32_t tmem_d, uint64_t adesc, uint64_
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+template <int TN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsGemm, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p)
 {
+    constexpr int kStages2 = Pair<TN>::kStages, kA2Bytes = Pair<TN>::kABytes, kStage2Bytes = Pair<TN>::kStageBytes;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar0 = base + kStages2 * kStage2Bytes;
@@ -426,7 +431,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();            // 0 = leader
     const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
-    const int tiles_m = (p.M + 255) / 256, tiles_n = p.tiles_n;
+    const int tiles_m = (p.M + 255) / 256, tiles_n = (p.N + TN - 1) / TN;
     const int splits = p.splits;
     const int num_tiles = tiles_m * tiles_n * splits;     // work units: (tile, K range)
     const int total_kb = (p.K + BK - 1) / BK;
@@ -459,7 +464,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
                 const int tile = t / splits;
                 const int m0 = (tile / tiles_n) * 256 + (int)rank * 128;
-                const int n0 = (tile % tiles_n) * 256 + (int)rank * 128;
+                const int n0 = (tile % tiles_n) * TN + (int)rank * (TN / 2);
                 for (int kb = kb_begin(t); kb < kb_end(t); ++kb) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, 1)) { ok = false; break; }
                     const uint32_t lead_full = map_to_cta(full_bar(s), 0);
@@ -474,7 +479,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                     if (!p.b_mn) {
                         tma_load_2d_pair(sb, &map_b, lead_full, k0, n0);
                     } else {
-                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(sb + j * 8192, &map_b, lead_full, n0 + 64 * j, k0);
+                        for (int j = 0; j < TN / 128; ++j) tma_load_2d_pair(sb + j * 8192, &map_b, lead_full, n0 + 64 * j, k0);
                     }
                     if (++s == kStages2) { s = 0; ph ^= 1u; }
                 }
@@ -483,16 +488,16 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader CTA only)
         if (lane == 0 && rank == 0) {
-            // M = 256 (>> 4 = 16) over the pair, N = 256
+            // M = 256 (>> 4 = 16) over the pair, N = TN
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
-                                   ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+                                   ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
             int s = 0, acc = 0;
             uint32_t ph = 0, aph = 0;
             bool ok = true;
             for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
                 if (!mbar_wait(tempty_bar(acc), aph ^ 1u, 2)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * TN);
                 const int kb0 = kb_begin(t);
                 for (int kb = kb0; kb < kb_end(t); ++kb) {
                     if (!mbar_wait(full_bar(s), ph, 3)) { ok = false; break; }
@@ -524,12 +529,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) && (p.ldc % 8 == 0);
         for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
             const int tile = t / splits;
-            const int m0 = (tile / tiles_n) * 256 + (int)rank * 128, n0 = (tile % tiles_n) * 256;
+            const int m0 = (tile / tiles_n) * 256 + (int)rank * 128, n0 = (tile % tiles_n) * TN;
             if (!mbar_wait(tfull_bar(acc), aph, 4)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-            epilogue_tile(p, taddr, row, n0, vec_ok, splits > 1, (t % splits) == 0);
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TN);
+            epilogue_tile<TN>(p, taddr, row, n0, vec_ok, splits > 1, (t % splits) == 0);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
@@ -602,15 +607,28 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
 
     // bf16: CTA pairs on 256 x 256 tiles when there are enough of them to fill the GPU
     // (tune key 7: 1 forces the single-CTA kernel, 2 forces pairs)
-    const int64_t pair_tiles = ((M + 255) / 256) * ((N + BN - 1) / BN);
+    int64_t pair_tiles = ((M + 255) / 256) * ((N + BN - 1) / BN);
     const int64_t mode = tune_value(7);
-    const bool pairs = !kTf32 && mode != 1 && (mode == 2 || pair_tiles >= d.sms / 2);
+    const bool pairs = !kTf32 && mode != 1 && (mode == 2 || mode == 3 || pair_tiles >= d.sms / 2);
+    // 128-wide tiles: only through tune key 7 = 3.  Measured on the 4096 x 4096 x 16384 weight-gradient
+    // product they fill the waves better (6.92 of 7 instead of 3.46 of 4) but run at 806 instead of
+    // 1246 TFLOP/s: the per-k-block costs of the single producer and issuer threads no longer hide.
+    bool narrow = false;
+    if (pairs) {
+        const int64_t clusters = d.sms / 2;
+        const int64_t narrow_tiles = ((M + 255) / 256) * ((N + 127) / 128);
+        const double eff_wide = (double)pair_tiles / (double)(((pair_tiles + clusters - 1) / clusters) * clusters);
+        const double eff_narrow = (double)narrow_tiles / (double)(((narrow_tiles + clusters - 1) / clusters) * clusters);
+        narrow = mode == 3;
+        (void)eff_wide; (void)eff_narrow;
+        if (narrow) pair_tiles = narrow_tiles;
+    }
 
     CUtensorMap ma, mb;
     const bool oka = a_mn ? make_map(&ma, a, esize, (uint64_t)M, (uint64_t)K, (uint64_t)lda, bk)
                           : make_map(&ma, a, esize, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM);
     const bool okb = b_mn ? make_map(&mb, b, esize, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, bk)
-                          : make_map(&mb, b, esize, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, pairs ? 128 : BN);
+                          : make_map(&mb, b, esize, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, pairs ? (narrow ? 64 : 128) : BN);
     if (!oka || !okb) return AXS6_ERR_DEVICE;
 
     Params p;
@@ -662,7 +680,8 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     if (pairs) {
         static bool attr2_set[64];
         if (dev >= 0 && dev < 64 && !attr2_set[dev]) {
-            if (cudaFuncSetAttribute(gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2Bytes) != cudaSuccess)
+            if (cudaFuncSetAttribute(gemm2_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, Pair<256>::kSmemBytes) != cudaSuccess ||
+                cudaFuncSetAttribute(gemm2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Pair<128>::kSmemBytes) != cudaSuccess)
                 return AXS6_ERR_LAUNCH;
             attr2_set[dev] = true;
         }
@@ -673,7 +692,10 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
         if (p.splits > 1 &&
             cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess)
             return AXS6_ERR_LAUNCH;
-        gemm2_kernel<<<2 * clusters, kThreadsGemm, kSmem2Bytes, stream>>>(ma, mb, p);
+        if (narrow)
+            gemm2_kernel<128><<<2 * clusters, kThreadsGemm, Pair<128>::kSmemBytes, stream>>>(ma, mb, p);
+        else
+            gemm2_kernel<256><<<2 * clusters, kThreadsGemm, Pair<256>::kSmemBytes, stream>>>(ma, mb, p);
         count_launch();
         return check_launch();
     }

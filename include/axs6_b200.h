@@ -72,7 +72,7 @@ int64_t axs6_query(int what);
 /* Performance knobs for experiments (process-wide, not needed for correct results):
  * key 0 = cap on resident CTAs per SM of the fake-quantise kernels, key 1 = the same for the
  * pack / unpack kernels, key 2 = 1 disables the specialised bf16 pack kernel, key 3 = 2 turns on split-K (two partials, fp32 output) in the bf16 GEMM, keys 4-6 = overrides
- * of the GEMM's shared-memory descriptor strides, key 7 = GEMM kernel (1 single-CTA, 2 CTA pairs), key 8 = SMs the GEMM leaves free (for a collective
+ * of the GEMM's shared-memory descriptor strides, key 7 = GEMM kernel (1 single-CTA, 2 CTA pairs, 3 CTA pairs with 128-wide tiles), key 8 = SMs the GEMM leaves free (for a collective
  * on another stream);
  * value 0 restores the built-in choice. */
 int axs6_tune(int key, int64_t value);
