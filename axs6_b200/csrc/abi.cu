@@ -31,6 +31,29 @@ int cached_occupancy(const void *kernel, int threads)
     return per_sm;
 }
 
+// ---- Philox epoch: a device-resident addend to the counter offset of every stochastic kernel -------
+__device__ unsigned long long g_philox_epoch;
+
+__global__ void philox_epoch_kernel(unsigned long long delta, int reset)
+{
+    g_philox_epoch = reset ? 0ull : g_philox_epoch + delta;
+}
+
+const unsigned long long *philox_epoch_ptr()
+{
+    static const unsigned long long *table[64];
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!table[dev]) {
+        void *ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_philox_epoch) != cudaSuccess) return nullptr;
+        table[dev] = static_cast<const unsigned long long *>(ptr);
+    }
+    return table[dev];
+}
+
 const DeviceInfo &device_info()
 {
     static DeviceInfo table[64];
@@ -85,4 +108,14 @@ AXS6_API int axs6_tune(int key, int64_t value)
     if (key < 0 || key >= 8) return AXS6_ERR_ARG;
     axs6::g_tune[key].store(value, std::memory_order_relaxed);
     return AXS6_OK;
+}
+
+AXS6_API int axs6_philox_advance(uint64_t delta, int reset, axs6_stream_t stream)
+{
+    const axs6::DeviceInfo &d = axs6::device_info();
+    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+    if (!axs6::philox_epoch_ptr()) return AXS6_ERR_DEVICE;
+    axs6::philox_epoch_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(delta, reset);
+    axs6::count_launch();
+    return axs6::check_launch();
 }

@@ -21,6 +21,7 @@ struct FqArgs {
     uint32_t via_bf16;
     uint32_t out_tf32;       // round fp32 results to the nearest TF32 value
     uint64_t seed, offset;
+    const unsigned long long *epoch;   // device counter added to `offset` (stochastic kernels only)
     const float *noise;
 };
 
@@ -90,6 +91,7 @@ __global__ void __launch_bounds__(kThreads) fq_vec_kernel(const FqArgs a)
     __syncthreads();
 
     const int lanes = a.g.block / kChunk;
+    const uint64_t offset = (ROUND == kPhilox) ? a.offset + *a.epoch : 0ull;
     const int64_t step = (int64_t)gridDim.x * kThreads * U;
     for (int64_t base = (int64_t)blockIdx.x * kThreads * U; base < a.g.total_chunks; base += step) {
         uint32_t v[U][8];
@@ -119,7 +121,7 @@ __global__ void __launch_bounds__(kThreads) fq_vec_kernel(const FqArgs a)
 #pragma unroll
         for (int k = 0; k < U; ++k) {
             float u[8], y[8];
-            chunk_uniforms<ROUND>(u, cidx[k], act[k], a.seed, a.offset, a.noise);
+            chunk_uniforms<ROUND>(u, cidx[k], act[k], a.seed, offset, a.noise);
             fq_chunk<GRID, ROUND>(v[k], y, tab, lanes, u);
             if (sizeof(Tout) == 4 && a.out_tf32) {
 #pragma unroll
@@ -139,6 +141,7 @@ __global__ void __launch_bounds__(kThreads) fq_generic_kernel(const FqArgs a)
     __syncthreads();
 
     const int lane = threadIdx.x & 31;
+    const uint64_t offset = (ROUND == kPhilox) ? a.offset + *a.epoch : 0ull;
     const int64_t padded = a.g.cpr * kChunk;
     const int64_t tiles_per_row = (padded + 31) / 32;
     const int64_t tiles = a.g.rows * tiles_per_row;
@@ -150,7 +153,7 @@ __global__ void __launch_bounds__(kThreads) fq_generic_kernel(const FqArgs a)
         const uint32_t v = act ? ChunkIO<Tin>::load1(a.x, row * a.ldx + pc, a.via_bf16 != 0u) : 0u;
         const uint32_t ab = v & 0x7FFFFFFFu;
         const uint32_t amax = group_max(ab, a.g.block);
-        const float u = element_uniform<ROUND>(row * padded + pc, act, a.seed, a.offset, a.noise);
+        const float u = element_uniform<ROUND>(row * padded + pc, act, a.seed, offset, a.noise);
         float y;
         if (GRID == AXS6_GRID_NF5) {
             const Axs6Scale s = axs6_scale_fq(amax);
@@ -258,6 +261,8 @@ static int fq_entry(const void *x, void *y, int in_dtype, int out_dtype, int64_t
     a.via_bf16 = (flags & AXS6_FLAG_INPUT_VIA_BF16) ? 1u : 0u;
     a.out_tf32 = (flags & AXS6_FLAG_OUTPUT_TF32) ? 1u : 0u;
     a.seed = seed; a.offset = offset; a.noise = noise;
+    a.epoch = philox_epoch_ptr();
+    if (round == kPhilox && !a.epoch) return AXS6_ERR_DEVICE;
     const bool vec = aligned16(x) && aligned16(y) && (cols % kChunk == 0) && (ldx % kChunk == 0) &&
                      (ldy % kChunk == 0) && (round != kNoise || aligned16(noise));
     if (in_dtype == AXS6_F32 && out_dtype == AXS6_F32) return dispatch_fq<float, float>(a, grid, round, vec, stream);

@@ -32,6 +32,15 @@ def reset_philox(offset: int = 0) -> None:
     _philox_offset = offset
 
 
+def philox_advance(delta: int = 1 << 40, reset: bool = False, device=None) -> None:
+    """Enqueue ``epoch += delta`` for the device-resident addend of every stochastic kernel's counter
+    (see ``axs6_philox_advance``): call it at the start of a step that is captured in a CUDA graph."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with _on(dev):
+        st = _lib.load().axs6_philox_advance(delta, int(reset), _stream(dev))
+    _lib.check("axs6_philox_advance", st)
+
+
 def _rounding(rounding: str) -> int:
     if rounding == "nearest":
         return ROUND_NEAREST

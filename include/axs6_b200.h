@@ -77,6 +77,14 @@ int64_t axs6_query(int what);
  * value 0 restores the built-in choice. */
 int axs6_tune(int key, int64_t value);
 
+/* Every stochastic kernel adds a per-device, device-resident epoch to its Philox counter offset.
+ * This call enqueues epoch += delta (or epoch = 0 with reset != 0) on `stream`.  It exists for
+ * CUDA-graph replay: the host-side (seed, offset) arguments are frozen into a captured graph, so a
+ * captured training step starts with axs6_philox_advance(large delta) and thereby draws fresh
+ * numbers on every replay.  Without any call the epoch is 0 and nothing changes.  (No
+ * counterpart in the reference, which draws a new seed on the host for every launch.) */
+int axs6_philox_advance(uint64_t delta, int reset, axs6_stream_t stream);
+
 /* Fake-quantise: y = dequantise(quantise(x)) in one pass.
  * Replaces fused_fake_quantize (axs/unified/quantize_unified.py:121-204), the Triton
  * launcher triton_fused_fake_quantize (axs/unified/triton_kernels.py:295-370) and, with
