@@ -376,3 +376,26 @@ def test_planes_to_records_and_back(B):
     assert torch.equal(se2, se) and torch.equal(sg2, sg) and torch.equal(mg2, mg) and sg2.dtype == torch.bool
     back = udist._unpack_gradient(se2, sg2, mg2, shape, B)
     assert_bits_equal(back, oracle.dequantize(ose, osg, omg, 96, oracle.GRID_NF5), "values from planes")
+
+
+def test_philox_epoch_changes_draws_and_reset_restores_them():
+    """`axs6_philox_advance` moves a device-resident addend of the Philox counter: the same host-side
+    (seed, offset) then gives other draws (what a replayed CUDA graph needs); reset brings them back."""
+    x = torch.randn(256, 512, device="cuda")
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+
+    def run():
+        y = torch.empty_like(x)
+        assert lib.axs6_fq(x.data_ptr(), y.data_ptr(), 0, 0, 256, 512, 512, 512, 32, 1, 1, 0, 99, 5, st) == 0
+        return y
+
+    try:
+        a = run()
+        ops.philox_advance(1 << 40)
+        b = run()
+        ops.philox_advance(0, reset=True)
+        c = run()
+    finally:
+        ops.philox_advance(0, reset=True)
+    assert torch.equal(a, c) and not torch.equal(a, b)
