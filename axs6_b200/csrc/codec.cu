@@ -452,10 +452,10 @@ __global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_kernel(const ui
         uint8_t *rec = &stage[buf][threadIdx.x * REC];
         if (b < nblocks) {
             uint32_t w[16];
-            const uint4 *src = reinterpret_cast<const uint4 *>(x + b * 32);
+            const uint16_t *src = x + b * 32;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const uint4 v = src[i];
+                const uint4 v = ld_stream16(src + 8 * i);
                 w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
             }
             uint32_t mx = 0;

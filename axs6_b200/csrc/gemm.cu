@@ -357,7 +357,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 // tcgen05.mma.cta_group::2: each CTA stages ITS 128 rows of A and ITS 128-wide half of B (32 KB per
 // k-block instead of 48 KB), the leader CTA (cluster rank 0) issues M256 N256 K16 instructions
 // that read both CTAs' shared memory and write 128 accumulator rows into each CTA's TMEM.
-// Less shared-memory traffic per flop and a 6-deep ring in the same shared-memory budget.
+// Less shared-memory traffic per flop and a 6-deep ring in the same amount of shared memory.
 //   * every TMA load (no multicast) of either CTA reports its bytes to the LEADER's stage
 //     barrier, which the leader arms with the bytes of both CTAs;
 //   * "stage free" and "accumulator ready" are committed by the leader to its own barrier and,
