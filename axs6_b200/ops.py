@@ -105,6 +105,9 @@ def fake_quantize(x: torch.Tensor, block_size: int = 32, grid: int = GRID_NF5, r
     """One-pass fake-quantise of the last dimension in blocks; returns a new tensor."""
     _check_input(x, who)
     assert block_size in VALID_BLOCK_SIZES, f"block_size must be one of {VALID_BLOCK_SIZES}"
+    if x.dtype not in _DT and x.is_floating_point():       # fp16, fp64: the kernels read fp32 / bf16 only
+        y = fake_quantize(x.float(), block_size, grid, rounding, out_dtype, via_bf16, noise, who)
+        return y if out_dtype is not None else y.to(x.dtype)
     rnd = _rounding(rounding)
     x2, rows, cols, ldx = _as_rows(x)
     odt = out_dtype if out_dtype is not None else (x.dtype if x.dtype in _DT else torch.float32)

@@ -4,11 +4,12 @@ from .quantize_unified import (FUSED_NF5_LUT, NF5_CODEBOOK, REVERSE_NF5_LUT, deq
 from .backend import (accelerated_fake_quantize, accelerated_linear, accelerated_matmul, backend_info, get_backend,
                       set_backend)
 from .functional_unified import axs_linear_unified, axs_matmul_unified, fake_quantize_unified
-from .mixed_precision import AXSLinearMixedPrecision, axs_linear_mixed_precision, convert_to_axs_mixed_precision
+from .mixed_precision import (AXSLinearMixedPrecision, axs_linear_mixed_precision, convert_to_axs_mixed_precision,
+                              estimate_memory_savings)
 from .modules_unified import AXSLinearUnified, convert_to_axs_unified
 
 __all__ = ["fused_fake_quantize", "quantize_unified", "dequantize_unified", "NF5_CODEBOOK", "FUSED_NF5_LUT",
            "REVERSE_NF5_LUT", "accelerated_fake_quantize", "fake_quantize_unified", "get_backend",
            "set_backend", "backend_info", "accelerated_linear", "accelerated_matmul", "axs_linear_unified",
            "axs_matmul_unified", "axs_linear_mixed_precision", "AXSLinearMixedPrecision",
-           "convert_to_axs_mixed_precision", "AXSLinearUnified", "convert_to_axs_unified"]
+           "convert_to_axs_mixed_precision", "estimate_memory_savings", "AXSLinearUnified", "convert_to_axs_unified"]

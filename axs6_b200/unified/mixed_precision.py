@@ -123,28 +123,47 @@ class AXSLinearMixedPrecision(nn.Module):
 def convert_to_axs_mixed_precision(model: nn.Module, block_size: int = DEFAULT_BLOCK_SIZE,
                                    quantize_input: bool = True, quantize_grad: bool = True,
                                    skip_layers: set[str] | None = None, inplace: bool = False) -> nn.Module:
-    """Swap every ``nn.Linear`` for :class:`AXSLinearMixedPrecision`, keeping the parameters
-    (mixed_precision.py:277-349)."""
+    """Replace every ``nn.Linear`` -- and the V1 / unified AXS-6 Linear modules of this package --
+    by :class:`AXSLinearMixedPrecision` with fp32 copies of their parameters; deep copy unless
+    ``inplace`` (mixed_precision.py:277-349)."""
     import copy
+    from ..nn.modules import AXSLinear
+    from .modules_unified import AXSLinearUnified
     if not inplace:
         model = copy.deepcopy(model)
     skip = skip_layers or set()
+    linear_types = (nn.Linear, AXSLinear, AXSLinearUnified)
 
     def swap(parent: nn.Module, prefix: str) -> None:
         for name, child in list(parent.named_children()):
             full = f"{prefix}.{name}" if prefix else name
             if full in skip:
                 continue
-            if isinstance(child, nn.Linear) and not isinstance(child, AXSLinearMixedPrecision):
+            if isinstance(child, linear_types) and not isinstance(child, AXSLinearMixedPrecision):
                 new = AXSLinearMixedPrecision(child.in_features, child.out_features, child.bias is not None,
                                               block_size, quantize_input, quantize_grad)
-                new = new.to(child.weight.device)
-                new.weight = child.weight
+                new.weight.data.copy_(child.weight.data.float())
                 if child.bias is not None:
-                    new.bias = child.bias
-                setattr(parent, name, new)
+                    new.bias.data.copy_(child.bias.data.float())
+                setattr(parent, name, new.to(child.weight.device))
             else:
                 swap(child, full)
 
     swap(model, "")
     return model
+
+
+def estimate_memory_savings(model: nn.Module, batch_size: int = 1, seq_len: int = 1) -> dict[str, float]:
+    """Activation memory kept for backward by the mixed-precision Linears of ``model``: fp32 baseline
+    (quantised input and quantised weight in fp32) against this scheme (quantised input in bf16, weight
+    recomputed), in MiB, and their ratio (mixed_precision.py:357-401)."""
+    fp32_bytes = 0
+    bf16_bytes = 0
+    for m in model.modules():
+        if isinstance(m, AXSLinearMixedPrecision):
+            act = batch_size * seq_len * m.in_features
+            fp32_bytes += (act + m.out_features * m.in_features) * 4
+            bf16_bytes += act * 2
+    fp32_mb, bf16_mb = fp32_bytes / 2 ** 20, bf16_bytes / 2 ** 20
+    return {"fp32_mb": round(fp32_mb, 2), "bf16_recomp_mb": round(bf16_mb, 2),
+            "savings_ratio": round(fp32_mb / bf16_mb, 1) if bf16_mb > 0 else float("inf")}
