@@ -38,6 +38,7 @@ SIGNATURES = {
     "axs6_gemm_bf16": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "axs6_gemm_tf32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "axs6_gemm_status": (_int, []),
+    "axs6_codec_status": (_int, []),
     "axs6_linear_workspace_bytes": (_i64, [_int, _i64, _i64, _i64]),
     "axs6_bias_grad": (_int, [_ptr, _int, _i64, _i64, _i64, _ptr, _ptr, _ptr]),
     "axs6_bias_grad_static": (_int, [_ptr, _int, _i64, _i64, _i64, _ptr, _ptr]),

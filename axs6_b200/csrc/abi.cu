@@ -12,9 +12,9 @@ static std::atomic<long long> g_launches{0};
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
-static std::atomic<long long> g_tune[8];
+static std::atomic<long long> g_tune[16];
 
-int64_t tune_value(int key) { return (key >= 0 && key < 8) ? g_tune[key].load(std::memory_order_relaxed) : 0; }
+int64_t tune_value(int key) { return (key >= 0 && key < 16) ? g_tune[key].load(std::memory_order_relaxed) : 0; }
 
 int cached_occupancy(const void *kernel, int threads)
 {
@@ -105,7 +105,7 @@ AXS6_API int64_t axs6_query(int what)
 
 AXS6_API int axs6_tune(int key, int64_t value)
 {
-    if (key < 0 || key >= 8) return AXS6_ERR_ARG;
+    if (key < 0 || key >= 16) return AXS6_ERR_ARG;
     axs6::g_tune[key].store(value, std::memory_order_relaxed);
     return AXS6_OK;
 }

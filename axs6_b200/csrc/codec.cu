@@ -7,6 +7,7 @@
 // whose records are contiguous in the output.  Threads drop their 6 payload bytes (8 codes)
 // into a shared-memory image of that run, which is then moved with 128-bit accesses (the
 // run's size is a multiple of 16 bytes for every block size and layout).
+#include "async_copy.cuh"
 #include "quant_device.cuh"
 
 namespace axs6 {
@@ -561,6 +562,230 @@ static int launch_pack_fast(const void *x, void *out, int64_t nblocks, int hdr, 
     return check_launch();
 }
 
+// ------------------------------------------------------------------------------------------ bf16 pack, TMA-fed
+// Same arithmetic as pack_bf16_nf5_b32_kernel, different data movement.  That kernel is bound by the
+// SM's load/store data path (its wavefront counter sits at 81 % while DRAM is at 29 %): the per-thread
+// 64-byte rows make every 128-bit global load a 16-wavefront access and the 25 byte-stores per record
+// conflict in shared memory.  Here the TMA unit does both transfers, outside that data path:
+//   in    a ring of 256-block tiles (16 KB each), loaded through a 2-D tensor map {32 values, nblocks}
+//         with the 64-byte swizzle, so that the four 128-bit shared-memory reads of a thread (one
+//         block = one 64-byte row) are free of bank conflicts;
+//   out   the 256 records of an iteration are assembled as whole 32-bit words (funnel shifts; the
+//         word a record shares with its successor is completed with one shuffle) and leave with ONE bulk
+//         shared->global copy, double-buffered.
+// Every mbarrier wait is bounded; a wait that gives up sets g_codec_status (read by axs6_codec_status)
+// and the CTA leaves its loop.
+namespace bulk {
+
+using namespace acp;
+
+constexpr int kStageBytes = kFastBlocks * 64;
+constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr int kCtrlBytes = 1024;                  // mbarriers, in front of the 1024-aligned tiles
+
+__device__ int g_codec_status;
+
+template <int HDR, int kStages>
+constexpr int smem_bytes() { return 1024 + kCtrlBytes + kStages * kStageBytes + 2 * kFastBlocks * (HDR + 24) + kKeyLimit + 16; }
+
+template <int HDR, int kStages, int kMinCtas>
+__global__ void __launch_bounds__(kFastBlocks, kMinCtas) pack_bf16_nf5_b32_bulk_kernel(const __grid_constant__ CUtensorMap xmap,
+                                                                                      uint8_t *__restrict__ out, int64_t nblocks)
+{
+    constexpr int REC = HDR + 24;
+    constexpr int kOut = kFastBlocks * REC;
+    extern __shared__ uint8_t raw[];
+    uint8_t *base = raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u);   // stays a shared-space pointer
+    uint8_t *in0 = base + kCtrlBytes;
+    uint8_t *out0 = in0 + kStages * kStageBytes;
+    uint8_t *table = out0 + 2 * kOut;
+    const uint32_t bar0 = smem_u32(base);
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
+        fence_barrier_init();
+        fence_async_smem();
+    }
+    for (int key = tid; key <= kKeyLimit; key += kFastBlocks) {
+        uint8_t code = 0;
+        if (key < kKeyLimit) {
+            const int j = key >> 7, m = 127 - (key & 127);
+            code = g_reverse[((128 + m) * 1023) >> (8 + j)];
+        }
+        table[key] = code;
+    }
+    __syncthreads();
+
+    const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
+    const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    if (tid == 0) {
+        for (int k = 0; k < kStages && k < nk; ++k) {
+            mbar_expect_tx(bar0 + 8 * k, kStageBytes);
+            tma_load_2d(smem_u32(in0 + k * kStageBytes), &xmap, bar0 + 8 * k, 0,
+                        (int)(((int64_t)blockIdx.x + k * (int64_t)gridDim.x) * kFastBlocks));
+        }
+    }
+    // this thread's block is row `tid` of a tile; 16-byte piece i of a row sits at piece i ^ ((row >> 1) & 3)
+    uint32_t piece[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) piece[i] = (uint32_t)tid * 64u + (uint32_t)((i ^ ((tid >> 1) & 3)) << 4);
+    // its record starts `sh` bytes into word `wb` of the output image
+    const uint32_t wb = (uint32_t)(REC * tid) >> 2, sh = (uint32_t)(REC * tid) & 3u;
+    const uint32_t sft = 8u * (sh + HDR);
+    const bool owns_first = sh == 0u;                                   // else the predecessor writes that word
+    const bool takes_next = ((uint32_t)(REC * (tid + 1)) & 3u) != 0u;    // the successor's head shares my last word
+
+    int s = 0;
+    uint32_t ph = 0;
+    for (int64_t k = 0; k < nk; ++k) {
+        const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
+        const int64_t b = grp * kFastBlocks + tid;
+        uint8_t *ost = out0 + (k & 1) * kOut;
+        const bool ok = mbar_wait_bounded(bar0 + 8 * s, ph, 1, &g_codec_status, kWaitLimit);
+        uint32_t W[7];
+#pragma unroll
+        for (int i = 0; i < 7; ++i) W[i] = 0u;
+        if (ok && b < nblocks) {
+            uint32_t w[16];
+            const uint8_t *tile = in0 + s * kStageBytes;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 v = *reinterpret_cast<const uint4 *>(tile + piece[i]);
+                w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+            }
+            uint32_t mx = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) mx = max_u16x2(mx, w[i] & 0x7FFF7FFFu);
+            const uint32_t amax16 = max(mx & 0xFFFFu, mx >> 16);
+            const uint32_t ef = amax16 >> 7;
+            uint32_t pay[6];
+            uint32_t se;
+            if (amax16 == 0u || (ef >= 11u && ef <= 252u)) {
+                se = amax16 ? ef + 1u : 0u;
+                const uint32_t a1 = amax16 ? ((ef << 7) | 127u) : 0x7FFFu;
+                const uint32_t a2 = a1 | (a1 << 16);
+                const uint32_t lim2 = (uint32_t)kKeyLimit | ((uint32_t)kKeyLimit << 16);
+#pragma unroll
+                for (int gq = 0; gq < 8; ++gq) {                 // 4 values -> one 24-bit group
+                    const uint32_t wa = w[2 * gq], wc = w[2 * gq + 1];
+                    const uint32_t ma = wa & 0x7FFF7FFFu, mb = wc & 0x7FFF7FFFu;
+                    const uint32_t ka = min_u16x2(a2 - ma, lim2), kb = min_u16x2(a2 - mb, lim2);
+                    const uint32_t c0 = table[ka & 0xFFFFu], c1 = table[ka >> 16];
+                    const uint32_t c2 = table[kb & 0xFFFFu], c3 = table[kb >> 16];
+                    uint32_t g = c0 | (c1 << 6) | (c2 << 12) | (c3 << 18);
+                    // sign bits of the non-zero values: bit 15 / 31 of (w & (|w| + 0x7FFF)) per half
+                    const uint32_t ta = wa & (ma + 0x7FFF7FFFu), tb = wc & (mb + 0x7FFF7FFFu);
+                    uint32_t r;
+                    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(ta), "r"(tb), "r"(0xFDB9u));
+                    g |= (r & 0x00020820u) | ((r >> 8) & 0x00800000u);   // sign bits at 5, 11, 17 and 23
+                    if ((gq & 3) == 0) { pay[(gq >> 2) * 3] = g; }
+                    else if ((gq & 3) == 1) { pay[(gq >> 2) * 3] |= g << 24; pay[(gq >> 2) * 3 + 1] = g >> 8; }
+                    else if ((gq & 3) == 2) { pay[(gq >> 2) * 3 + 1] |= g << 16; pay[(gq >> 2) * 3 + 2] = g >> 16; }
+                    else { pay[(gq >> 2) * 3 + 2] |= g << 8; }
+                }
+            } else {
+                // rare block (denormal-range or near-overflow maximum): the general fp32 formulas
+                const Axs6Scale sc = axs6_scale_codes(amax16 << 16);
+                se = (uint32_t)sc.se;
+#pragma unroll
+                for (int i = 0; i < 6; ++i) pay[i] = 0u;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const uint32_t bits = (i & 1) ? (w[i >> 1] & 0xFFFF0000u) : (w[i >> 1] << 16);
+                    const uint32_t ab = bits & 0x7FFFFFFFu;
+                    const int idx = axs6_nf5_index(axs6_normalise(__uint_as_float(ab), sc));
+                    const uint32_t code = (uint32_t)g_reverse[idx] | ((ab != 0u && (bits >> 31)) ? 32u : 0u);
+                    const int word = (6 * i) >> 5, off = (6 * i) & 31;
+                    pay[word] |= code << off;
+                    if (off > 26) pay[word + 1] |= code >> (32 - off);
+                }
+            }
+            // header bytes in front of the payload, the whole record shifted to byte `sh` of its first word
+            uint32_t prev = HDR == 1 ? (se << 24) : (((se << 2) & 0xFFFFu) << 16);
+#pragma unroll
+            for (int i = 0; i < 6; ++i) {
+                W[i] = __funnelshift_lc(prev, pay[i], sft);
+                prev = pay[i];
+            }
+            W[6] = __funnelshift_lc(prev, 0u, sft);
+        }
+        const uint32_t nxt = __shfl_down_sync(0xFFFFFFFFu, W[0], 1);
+        if (takes_next) W[6] |= nxt;
+        uint32_t *o32 = reinterpret_cast<uint32_t *>(ost) + wb;
+        if (owns_first) o32[0] = W[0];
+#pragma unroll
+        for (int i = 1; i < 7; ++i) o32[i] = W[i];
+        fence_async_smem();                    // my words are visible to the TMA unit after the barrier
+        if (tid == 0) bulk_wait_read<0>();     // the previous iteration's store has left the other buffer
+        if (__syncthreads_or(!ok)) break;      // somebody's wait gave up: the whole CTA leaves
+        const int64_t nb = nblocks - grp * kFastBlocks;
+        if (nb >= kFastBlocks) {
+            if (tid == 0) {
+                bulk_store(out + grp * kOut, smem_u32(ost), kOut);
+                bulk_commit();
+            }
+        } else {                               // the ragged last group: plain stores of nb records
+            const int len = (int)nb * REC;
+            uint8_t *dst = out + grp * kOut;
+            const int nvec = len >> 4;
+            for (int i = tid; i < nvec; i += kFastBlocks)
+                st_stream16(dst + 16 * i, reinterpret_cast<const uint4 *>(ost)[i]);
+            for (int i = (nvec << 4) + tid; i < len; i += kFastBlocks) dst[i] = ost[i];
+        }
+        if (tid == 0 && k + kStages < nk) {
+            mbar_expect_tx(bar0 + 8 * s, kStageBytes);
+            tma_load_2d(smem_u32(in0 + s * kStageBytes), &xmap, bar0 + 8 * s, 0,
+                        (int)(((int64_t)blockIdx.x + (k + kStages) * (int64_t)gridDim.x) * kFastBlocks));
+        }
+        if (++s == kStages) { s = 0; ph ^= 1u; }
+    }
+    if (tid == 0) bulk_wait<0>();
+}
+
+// -> status, or 1 when this path does not apply (the caller then uses pack_bf16_nf5_b32_kernel)
+static int launch_pack_bulk(const void *x, void *out, int64_t nblocks, int hdr, cudaStream_t st)
+{
+    if (nblocks >= (1ll << 31) - kFastBlocks) return 1;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return 1;
+    CUtensorMap map;
+    const cuuint64_t gdim[2] = {32, (cuuint64_t)nblocks};
+    const cuuint64_t gstride[1] = {64};
+    const cuuint32_t box[2] = {32, (cuuint32_t)kFastBlocks};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(x), gdim, gstride, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return 1;
+    const DeviceInfo &d = device_info();
+    int64_t ctas = (nblocks + kFastBlocks - 1) / kFastBlocks;
+    const int64_t cap = tune_value(1);
+    const int variant = (int)tune_value(9);          // experiments: 0 = 2 stages, 1 = 3 stages, 2 = 2 stages with up to 64 registers
+    int per_sm = variant == 1 ? 3 : 4;
+    if (cap > 0 && cap < per_sm) per_sm = (int)cap;
+    if (ctas > (int64_t)d.sms * per_sm) ctas = (int64_t)d.sms * per_sm;
+    if (ctas < 1) ctas = 1;
+    uint8_t *o = static_cast<uint8_t *>(out);
+#define AXS6_LAUNCH_BULK(H, S, C)                                                                                         \
+    do {                                                                                                                  \
+        static bool attr_set = false;                                                                                     \
+        if (!attr_set) {                                                                                                  \
+            if (cudaFuncSetAttribute(pack_bf16_nf5_b32_bulk_kernel<H, S, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                     smem_bytes<H, S>()) != cudaSuccess)                                                  \
+                return AXS6_ERR_LAUNCH;                                                                                   \
+            attr_set = true;                                                                                              \
+        }                                                                                                                 \
+        pack_bf16_nf5_b32_bulk_kernel<H, S, C><<<(unsigned)ctas, kFastBlocks, smem_bytes<H, S>(), st>>>(map, o, nblocks); \
+    } while (0)
+    if (hdr == 1) { if (variant == 1) AXS6_LAUNCH_BULK(1, 3, 1); else if (variant == 2) AXS6_LAUNCH_BULK(1, 2, 4); else AXS6_LAUNCH_BULK(1, 2, 1); }
+    else          { if (variant == 1) AXS6_LAUNCH_BULK(2, 3, 1); else if (variant == 2) AXS6_LAUNCH_BULK(2, 2, 4); else AXS6_LAUNCH_BULK(2, 2, 1); }
+#undef AXS6_LAUNCH_BULK
+    count_launch();
+    return check_launch();
+}
+
+}  // namespace bulk
+
 static bool layout_ok(int layout) { return layout == AXS6_LAYOUT_PLANES || layout == AXS6_LAYOUT_WIRE || layout == AXS6_LAYOUT_SPEC; }
 
 }  // namespace axs6
@@ -680,8 +905,14 @@ AXS6_API int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, 
                      (!planes || (aligned16(out1) && aligned16(out2))) && (round != kNoise || aligned16(noise));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (vec && !planes && a.g.flat && in_dtype == AXS6_BF16 && grid == AXS6_GRID_NF5 && round == kNearest && block == 32 &&
-        tune_value(2) != 1)
+        tune_value(2) != 1) {
+        // tune key 2: 1 = general kernel, 2 = per-thread loads (no TMA); default = TMA-fed kernel
+        if (tune_value(2) != 2) {
+            const int r = bulk::launch_pack_bulk(x, out0, rows * (cols / 32), a.hdr, st);
+            if (r != 1) return r;
+        }
         return launch_pack_fast(x, out0, rows * (cols / 32), a.hdr, st);
+    }
     return in_dtype == AXS6_F32 ? dispatch_pack<float>(a, grid, round, planes, vec, st)
                                 : dispatch_pack<__nv_bfloat16>(a, grid, round, planes, vec, st);
 }
@@ -718,4 +949,12 @@ AXS6_API int axs6_unpack(int layout, const void *in0, const void *in1, const voi
     if (grid == AXS6_GRID_NF5) AXS6_CASE(__nv_bfloat16, AXS6_GRID_NF5);
     AXS6_CASE(__nv_bfloat16, AXS6_GRID_UNIFORM);
 #undef AXS6_CASE
+}
+
+AXS6_API int axs6_codec_status(void)
+{
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, axs6::bulk::g_codec_status, sizeof(int)) != cudaSuccess) return AXS6_ERR_DEVICE;
+    if (v != 0) cudaMemcpyToSymbol(axs6::bulk::g_codec_status, &zero, sizeof(int));
+    return v;
 }

@@ -28,6 +28,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include "async_copy.cuh"
 #include "common.cuh"
 
 namespace axs6 {
@@ -61,45 +62,16 @@ struct Params {
 };
 
 // ------------------------------------------------------------------------------------- PTX helpers
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+using acp::smem_u32;
+using acp::mbar_init;
+using acp::mbar_expect_tx;
+using acp::mbar_arrive;
+using acp::tma_load_2d;
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
 // Bounded wait.  Returns false if it gave up (status set) or if another role already failed.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code)
 {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if (mbar_test(bar, parity)) return true;
-        if (i > 64) {
-            __nanosleep(40);
-            if ((i & 255u) == 0u && *(volatile int *)&g_gemm_status != 0) return false;
-        }
-    }
-    atomicCAS(&g_gemm_status, 0, code);
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1)
-{
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+    return acp::mbar_wait_bounded(bar, parity, code, &g_gemm_status, kSpinLimit);
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -553,24 +525,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
 }
 
 // ------------------------------------------------------------------------------------- host
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn()
-{
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
+using acp::EncodeTiledFn;
+using acp::encode_fn;
 
 // 2-D tensor map over rows of `inner` contiguous values (`esize` bytes each, `ld` values apart):
 // box = {128 bytes, box_rows}, 128-byte swizzle, out-of-bounds reads give zeros.

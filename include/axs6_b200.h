@@ -179,6 +179,12 @@ int axs6_transpose_f32(const float *in, float *out, int64_t rows, int64_t cols,
  * Synchronises the device and clears the status. */
 int axs6_gemm_status(void);
 
+/* The same for the pack kernel that is fed by the TMA unit (bf16 input, NF5 grid, nearest rounding,
+ * block 32, byte layouts): 0 = every wait completed; 1 = a wait for a loaded tile gave up and the
+ * records written by that launch are incomplete.  Synchronises the device and clears the status.
+ * No counterpart in the reference. */
+int axs6_codec_status(void);
+
 /* AXS-6 Linear with bf16 tensor-core compute: the graph of _AXSLinearBF16Function
  * (axs/unified/mixed_precision.py:86-155), also reached through accelerated_linear /
  * triton_fused_linear (axs/unified/backend.py:540-618, axs/unified/triton_kernels.py:385-482).
