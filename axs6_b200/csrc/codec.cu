@@ -579,17 +579,18 @@ namespace bulk {
 
 using namespace acp;
 
+constexpr int kStages = 2;                        // with 4 CTAs per SM: 128 KB of loads in flight
 constexpr int kStageBytes = kFastBlocks * 64;
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr int kCtrlBytes = 1024;                  // mbarriers, in front of the 1024-aligned tiles
 
 __device__ int g_codec_status;
 
-template <int HDR, int kStages>
-constexpr int smem_bytes() { return 1024 + kCtrlBytes + kStages * kStageBytes + 2 * kFastBlocks * (HDR + 24) + kKeyLimit + 16; }
+template <int HDR>
+constexpr int smem_bytes() { return 1024 + kCtrlBytes + kStages * kStageBytes + 2 * kFastBlocks * (HDR + 24); }   // dynamic part
 
-template <int HDR, int kStages, int kMinCtas>
-__global__ void __launch_bounds__(kFastBlocks, kMinCtas) pack_bf16_nf5_b32_bulk_kernel(const __grid_constant__ CUtensorMap xmap,
+template <int HDR>
+__global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_bulk_kernel(const __grid_constant__ CUtensorMap xmap,
                                                                                       uint8_t *__restrict__ out, int64_t nblocks)
 {
     constexpr int REC = HDR + 24;
@@ -598,7 +599,7 @@ __global__ void __launch_bounds__(kFastBlocks, kMinCtas) pack_bf16_nf5_b32_bulk_
     uint8_t *base = raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u);   // stays a shared-space pointer
     uint8_t *in0 = base + kCtrlBytes;
     uint8_t *out0 = in0 + kStages * kStageBytes;
-    uint8_t *table = out0 + 2 * kOut;
+    __shared__ __align__(16) uint8_t table[kKeyLimit + 16];   // static: its address is an immediate of every lookup
     const uint32_t bar0 = smem_u32(base);
     const int tid = threadIdx.x;
     if (tid == 0) {
@@ -760,26 +761,23 @@ static int launch_pack_bulk(const void *x, void *out, int64_t nblocks, int hdr, 
     const DeviceInfo &d = device_info();
     int64_t ctas = (nblocks + kFastBlocks - 1) / kFastBlocks;
     const int64_t cap = tune_value(1);
-    const int variant = (int)tune_value(9);          // experiments: 0 = 2 stages, 1 = 3 stages, 2 = 2 stages with up to 64 registers
-    int per_sm = variant == 1 ? 3 : 4;
+    int per_sm = 4;                          // measured 4.9 TB/s; 3 per SM 4.8, 2 per SM 4.5 (3 stages do not help)
     if (cap > 0 && cap < per_sm) per_sm = (int)cap;
     if (ctas > (int64_t)d.sms * per_sm) ctas = (int64_t)d.sms * per_sm;
     if (ctas < 1) ctas = 1;
     uint8_t *o = static_cast<uint8_t *>(out);
-#define AXS6_LAUNCH_BULK(H, S, C)                                                                                         \
-    do {                                                                                                                  \
-        static bool attr_set = false;                                                                                     \
-        if (!attr_set) {                                                                                                  \
-            if (cudaFuncSetAttribute(pack_bf16_nf5_b32_bulk_kernel<H, S, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                     smem_bytes<H, S>()) != cudaSuccess)                                                  \
-                return AXS6_ERR_LAUNCH;                                                                                   \
-            attr_set = true;                                                                                              \
-        }                                                                                                                 \
-        pack_bf16_nf5_b32_bulk_kernel<H, S, C><<<(unsigned)ctas, kFastBlocks, smem_bytes<H, S>(), st>>>(map, o, nblocks); \
-    } while (0)
-    if (hdr == 1) { if (variant == 1) AXS6_LAUNCH_BULK(1, 3, 1); else if (variant == 2) AXS6_LAUNCH_BULK(1, 2, 4); else AXS6_LAUNCH_BULK(1, 2, 1); }
-    else          { if (variant == 1) AXS6_LAUNCH_BULK(2, 3, 1); else if (variant == 2) AXS6_LAUNCH_BULK(2, 2, 4); else AXS6_LAUNCH_BULK(2, 2, 1); }
-#undef AXS6_LAUNCH_BULK
+    static bool attr_done[64] = {};          // the attribute is per device
+    int dev_id = 0;
+    if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= 64) return 1;
+    bool &attr_set = attr_done[dev_id];
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(pack_bf16_nf5_b32_bulk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<1>()) != cudaSuccess ||
+            cudaFuncSetAttribute(pack_bf16_nf5_b32_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<2>()) != cudaSuccess)
+            return AXS6_ERR_LAUNCH;
+        attr_set = true;
+    }
+    if (hdr == 1) pack_bf16_nf5_b32_bulk_kernel<1><<<(unsigned)ctas, kFastBlocks, smem_bytes<1>(), st>>>(map, o, nblocks);
+    else          pack_bf16_nf5_b32_bulk_kernel<2><<<(unsigned)ctas, kFastBlocks, smem_bytes<2>(), st>>>(map, o, nblocks);
     count_launch();
     return check_launch();
 }

@@ -399,3 +399,36 @@ def test_philox_epoch_changes_draws_and_reset_restores_them():
     finally:
         ops.philox_advance(0, reset=True)
     assert torch.equal(a, c) and not torch.equal(a, b)
+
+
+@pytest.mark.parametrize("layout", [ops.LAYOUT_WIRE, ops.LAYOUT_SPEC])
+@pytest.mark.parametrize("shape", [(1, 32), (255, 32), (257, 32), (3, 96), (777, 1056), (2048, 4096)])
+def test_bf16_record_pack_kernels_agree_with_the_oracle(shape, layout):
+    """bf16 input, NF5, nearest, block 32, byte records: the TMA-fed kernel (default), the kernel with
+    per-thread loads (tune key 2 = 2) and the general kernel (tune key 2 = 1) all give the oracle's
+    bytes, for whole and ragged groups of 256 blocks and for blocks that leave the integer fast path
+    (all-zero, negative zeros, denormal-range and near-overflow maxima)."""
+    from axs6_b200 import _lib
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(shape[0] * 131 + shape[1] + layout)
+    x = torch.randn(*shape, generator=g)
+    x[torch.rand(*shape, generator=g) < 0.02] = 0.0
+    x[torch.rand(*shape, generator=g) < 0.01] = -0.0
+    x[torch.rand(*shape, generator=g) < 0.002] *= 1e-30
+    if shape[0] > 2:
+        x[1] *= 1e-38
+        x[2] *= 3e37
+        x[0, :32] = 0.0
+    xb = oracle.f32_to_bf16(x.numpy())
+    se, sg, mg = oracle.quantize(xb, 32, oracle.GRID_NF5)
+    want = oracle.pack_bytes(se, sg, mg, layout)
+    xt = to_cuda(xb)
+    try:
+        for mode in (0, 2, 1):
+            lib.axs6_tune(2, mode)
+            got = ops.pack(xt, 32, ops.GRID_NF5, "nearest", layout)
+            torch.cuda.synchronize()
+            assert_bits_equal(got, want, f"tune(2)={mode} {shape} layout {layout}")
+    finally:
+        lib.axs6_tune(2, 0)
+    assert lib.axs6_codec_status() == 0
