@@ -429,14 +429,62 @@ __device__ __forceinline__ uint32_t min_u16x2(uint32_t a, uint32_t b)
     return r;
 }
 
-template <int HDR>
-__global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_kernel(const uint16_t *__restrict__ x,
-                                                                       uint8_t *__restrict__ out, int64_t nblocks)
+// Codes of one block of 32 bf16 values (16 words of two) as the 192-bit payload and the exponent byte.
+// `table` is the shared-memory key table built by build_key_table.
+__device__ __forceinline__ void bf16_block_payload(const uint32_t (&w)[16], const uint8_t *table, uint32_t (&pay)[6], uint32_t &se)
 {
-    constexpr int REC = HDR + 24;
-    __shared__ __align__(16) uint8_t table[kKeyLimit + 16];
-    __shared__ __align__(16) uint8_t stage[2][kFastBlocks * REC];
-    for (int key = threadIdx.x; key <= kKeyLimit; key += kFastBlocks) {
+    uint32_t mx = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) mx = max_u16x2(mx, w[i] & 0x7FFF7FFFu);
+    const uint32_t amax16 = max(mx & 0xFFFFu, mx >> 16);
+    const uint32_t ef = amax16 >> 7;
+    if (amax16 == 0u || (ef >= 11u && ef <= 252u)) {
+        se = amax16 ? ef + 1u : 0u;
+        const uint32_t a1 = amax16 ? ((ef << 7) | 127u) : 0x7FFFu;
+        const uint32_t a2 = a1 | (a1 << 16);
+        const uint32_t lim2 = (uint32_t)kKeyLimit | ((uint32_t)kKeyLimit << 16);
+#pragma unroll
+        for (int gq = 0; gq < 8; ++gq) {                 // 4 values -> one 24-bit group
+            const uint32_t wa = w[2 * gq], wc = w[2 * gq + 1];
+            const uint32_t ma = wa & 0x7FFF7FFFu, mb = wc & 0x7FFF7FFFu;
+            const uint32_t ka = min_u16x2(a2 - ma, lim2), kb = min_u16x2(a2 - mb, lim2);
+            const uint32_t c0 = table[ka & 0xFFFFu], c1 = table[ka >> 16];
+            const uint32_t c2 = table[kb & 0xFFFFu], c3 = table[kb >> 16];
+            uint32_t g = c0 | (c1 << 6) | (c2 << 12) | (c3 << 18);
+            // sign bits of the non-zero values: bit 15 / 31 of (w & (|w| + 0x7FFF)) per half
+            const uint32_t ta = wa & (ma + 0x7FFF7FFFu), tb = wc & (mb + 0x7FFF7FFFu);
+            // bytes 1, 3 of ta and 1, 3 of tb, each replicated from its top bit: 0x00 or 0xFF per value
+            uint32_t r;
+            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(ta), "r"(tb), "r"(0xFDB9u));
+            g |= (r & 0x00020820u) | ((r >> 8) & 0x00800000u);   // sign bits at 5, 11, 17 and 23
+            // append the 24-bit group to the 192-bit payload
+            if ((gq & 3) == 0) { pay[(gq >> 2) * 3] = g; }
+            else if ((gq & 3) == 1) { pay[(gq >> 2) * 3] |= g << 24; pay[(gq >> 2) * 3 + 1] = g >> 8; }
+            else if ((gq & 3) == 2) { pay[(gq >> 2) * 3 + 1] |= g << 16; pay[(gq >> 2) * 3 + 2] = g >> 16; }
+            else { pay[(gq >> 2) * 3 + 2] |= g << 8; }
+        }
+    } else {
+        // rare block (denormal-range or near-overflow maximum): the general fp32 formulas
+        const Axs6Scale sc = axs6_scale_codes(amax16 << 16);
+        se = (uint32_t)sc.se;
+#pragma unroll
+        for (int i = 0; i < 6; ++i) pay[i] = 0u;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const uint32_t bits = (i & 1) ? (w[i >> 1] & 0xFFFF0000u) : (w[i >> 1] << 16);
+            const uint32_t ab = bits & 0x7FFFFFFFu;
+            const int idx = axs6_nf5_index(axs6_normalise(__uint_as_float(ab), sc));
+            const uint32_t code = (uint32_t)g_reverse[idx] | ((ab != 0u && (bits >> 31)) ? 32u : 0u);
+            const int word = (6 * i) >> 5, off = (6 * i) & 31;
+            pay[word] |= code << off;
+            if (off > 26) pay[word + 1] |= code >> (32 - off);
+        }
+    }
+}
+
+__device__ __forceinline__ void build_key_table(uint8_t *table, int tid, int nthreads)
+{
+    for (int key = tid; key <= kKeyLimit; key += nthreads) {
         uint8_t code = 0;
         if (key < kKeyLimit) {
             const int j = key >> 7, m = 127 - (key & 127);
@@ -444,6 +492,30 @@ __global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_kernel(const ui
         }
         table[key] = code;
     }
+}
+
+// The record of a block as seven 32-bit words of the output image, shifted so that its first byte lands
+// on byte `sh` of the first word: sft = 8 * (sh + HDR).
+template <int HDR>
+__device__ __forceinline__ void record_words(const uint32_t (&pay)[6], uint32_t se, uint32_t sft, uint32_t (&W)[7])
+{
+    uint32_t prev = HDR == 1 ? (se << 24) : (((se << 2) & 0xFFFFu) << 16);
+#pragma unroll
+    for (int i = 0; i < 6; ++i) {
+        W[i] = __funnelshift_lc(prev, pay[i], sft);
+        prev = pay[i];
+    }
+    W[6] = __funnelshift_lc(prev, 0u, sft);
+}
+
+template <int HDR>
+__global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_kernel(const uint16_t *__restrict__ x,
+                                                                       uint8_t *__restrict__ out, int64_t nblocks)
+{
+    constexpr int REC = HDR + 24;
+    __shared__ __align__(16) uint8_t table[kKeyLimit + 16];
+    __shared__ __align__(16) uint8_t stage[2][kFastBlocks * REC];
+    build_key_table(table, threadIdx.x, kFastBlocks);
     __syncthreads();
 
     int buf = 0;
@@ -459,72 +531,21 @@ __global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_kernel(const ui
                 const uint4 v = ld_stream16(src + 8 * i);
                 w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
             }
-            uint32_t mx = 0;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) mx = max_u16x2(mx, w[i] & 0x7FFF7FFFu);
-            const uint32_t amax16 = max(mx & 0xFFFFu, mx >> 16);
-            const uint32_t ef = amax16 >> 7;
-            if (amax16 == 0u || (ef >= 11u && ef <= 252u)) {
-                const uint32_t se = amax16 ? ef + 1u : 0u;
-                const uint32_t a1 = amax16 ? ((ef << 7) | 127u) : 0x7FFFu;
-                const uint32_t a2 = a1 | (a1 << 16);
-                const uint32_t lim2 = (uint32_t)kKeyLimit | ((uint32_t)kKeyLimit << 16);
-                uint32_t pay[6];
-#pragma unroll
-                for (int gq = 0; gq < 8; ++gq) {                 // 4 values -> one 24-bit group
-                    const uint32_t wa = w[2 * gq], wb = w[2 * gq + 1];
-                    const uint32_t ma = wa & 0x7FFF7FFFu, mb = wb & 0x7FFF7FFFu;
-                    const uint32_t ka = min_u16x2(a2 - ma, lim2), kb = min_u16x2(a2 - mb, lim2);
-                    const uint32_t c0 = table[ka & 0xFFFFu], c1 = table[ka >> 16];
-                    const uint32_t c2 = table[kb & 0xFFFFu], c3 = table[kb >> 16];
-                    uint32_t g = c0 | (c1 << 6) | (c2 << 12) | (c3 << 18);
-                    // sign bits of the non-zero values: bit 15 / 31 of (w & (|w| + 0x7FFF)) per half
-                    const uint32_t ta = wa & (ma + 0x7FFF7FFFu), tb = wb & (mb + 0x7FFF7FFFu);
-                    // bytes 1, 3 of ta and 1, 3 of tb, each replicated from its top bit: 0x00 or 0xFF per value
-                    uint32_t r;
-                    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(ta), "r"(tb), "r"(0xFDB9u));
-                    g |= (r & 0x00020820u) | ((r >> 8) & 0x00800000u);   // sign bits at 5, 11, 17 and 23
-                    // append the 24-bit group to the 192-bit payload
-                    if ((gq & 3) == 0) { pay[(gq >> 2) * 3] = g; }
-                    else if ((gq & 3) == 1) { pay[(gq >> 2) * 3] |= g << 24; pay[(gq >> 2) * 3 + 1] = g >> 8; }
-                    else if ((gq & 3) == 2) { pay[(gq >> 2) * 3 + 1] |= g << 16; pay[(gq >> 2) * 3 + 2] = g >> 16; }
-                    else { pay[(gq >> 2) * 3 + 2] |= g << 8; }
-                }
-                if (HDR == 1) {
-                    rec[0] = (uint8_t)se;
-                } else {
-                    rec[0] = (uint8_t)((se << 2) & 0xFFu);
-                    rec[1] = (uint8_t)(se >> 6);
-                }
-#pragma unroll
-                for (int i = 0; i < 6; ++i) {
-                    rec[HDR + 4 * i] = (uint8_t)pay[i];
-                    rec[HDR + 4 * i + 1] = (uint8_t)(pay[i] >> 8);
-                    rec[HDR + 4 * i + 2] = (uint8_t)(pay[i] >> 16);
-                    rec[HDR + 4 * i + 3] = (uint8_t)(pay[i] >> 24);
-                }
+            uint32_t pay[6];
+            uint32_t se;
+            bf16_block_payload(w, table, pay, se);
+            if (HDR == 1) {
+                rec[0] = (uint8_t)se;
             } else {
-                // rare block: the general fp32 formulas, one value at a time, straight into the record
-                const uint32_t amax_bits = amax16 << 16;
-                const Axs6Scale sc = axs6_scale_codes(amax_bits);
-                if (HDR == 1) {
-                    rec[0] = (uint8_t)sc.se;
-                } else {
-                    rec[0] = (uint8_t)((sc.se << 2) & 0xFF);
-                    rec[1] = (uint8_t)(sc.se >> 6);
-                }
-                uint32_t acc = 0;
-                int nb = 0, o = HDR;
-#pragma unroll 1
-                for (int i = 0; i < 32; ++i) {
-                    const uint32_t bits = (uint32_t)x[b * 32 + i] << 16;
-                    const uint32_t ab = bits & 0x7FFFFFFFu;
-                    const int idx = axs6_nf5_index(axs6_normalise(__uint_as_float(ab), sc));
-                    const uint32_t code = (uint32_t)g_reverse[idx] | ((ab != 0u && (bits >> 31)) ? 32u : 0u);
-                    acc |= code << nb;
-                    nb += 6;
-                    while (nb >= 8) { rec[o++] = (uint8_t)acc; acc >>= 8; nb -= 8; }
-                }
+                rec[0] = (uint8_t)((se << 2) & 0xFFu);
+                rec[1] = (uint8_t)(se >> 6);
+            }
+#pragma unroll
+            for (int i = 0; i < 6; ++i) {
+                rec[HDR + 4 * i] = (uint8_t)pay[i];
+                rec[HDR + 4 * i + 1] = (uint8_t)(pay[i] >> 8);
+                rec[HDR + 4 * i + 2] = (uint8_t)(pay[i] >> 16);
+                rec[HDR + 4 * i + 3] = (uint8_t)(pay[i] >> 24);
             }
         }
         __syncthreads();
@@ -607,14 +628,7 @@ __global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_bulk_kernel(con
         fence_barrier_init();
         fence_async_smem();
     }
-    for (int key = tid; key <= kKeyLimit; key += kFastBlocks) {
-        uint8_t code = 0;
-        if (key < kKeyLimit) {
-            const int j = key >> 7, m = 127 - (key & 127);
-            code = g_reverse[((128 + m) * 1023) >> (8 + j)];
-        }
-        table[key] = code;
-    }
+    build_key_table(table, tid, kFastBlocks);
     __syncthreads();
 
     const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
@@ -654,61 +668,10 @@ __global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_bulk_kernel(con
                 const uint4 v = *reinterpret_cast<const uint4 *>(tile + piece[i]);
                 w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
             }
-            uint32_t mx = 0;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) mx = max_u16x2(mx, w[i] & 0x7FFF7FFFu);
-            const uint32_t amax16 = max(mx & 0xFFFFu, mx >> 16);
-            const uint32_t ef = amax16 >> 7;
             uint32_t pay[6];
             uint32_t se;
-            if (amax16 == 0u || (ef >= 11u && ef <= 252u)) {
-                se = amax16 ? ef + 1u : 0u;
-                const uint32_t a1 = amax16 ? ((ef << 7) | 127u) : 0x7FFFu;
-                const uint32_t a2 = a1 | (a1 << 16);
-                const uint32_t lim2 = (uint32_t)kKeyLimit | ((uint32_t)kKeyLimit << 16);
-#pragma unroll
-                for (int gq = 0; gq < 8; ++gq) {                 // 4 values -> one 24-bit group
-                    const uint32_t wa = w[2 * gq], wc = w[2 * gq + 1];
-                    const uint32_t ma = wa & 0x7FFF7FFFu, mb = wc & 0x7FFF7FFFu;
-                    const uint32_t ka = min_u16x2(a2 - ma, lim2), kb = min_u16x2(a2 - mb, lim2);
-                    const uint32_t c0 = table[ka & 0xFFFFu], c1 = table[ka >> 16];
-                    const uint32_t c2 = table[kb & 0xFFFFu], c3 = table[kb >> 16];
-                    uint32_t g = c0 | (c1 << 6) | (c2 << 12) | (c3 << 18);
-                    // sign bits of the non-zero values: bit 15 / 31 of (w & (|w| + 0x7FFF)) per half
-                    const uint32_t ta = wa & (ma + 0x7FFF7FFFu), tb = wc & (mb + 0x7FFF7FFFu);
-                    uint32_t r;
-                    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(ta), "r"(tb), "r"(0xFDB9u));
-                    g |= (r & 0x00020820u) | ((r >> 8) & 0x00800000u);   // sign bits at 5, 11, 17 and 23
-                    if ((gq & 3) == 0) { pay[(gq >> 2) * 3] = g; }
-                    else if ((gq & 3) == 1) { pay[(gq >> 2) * 3] |= g << 24; pay[(gq >> 2) * 3 + 1] = g >> 8; }
-                    else if ((gq & 3) == 2) { pay[(gq >> 2) * 3 + 1] |= g << 16; pay[(gq >> 2) * 3 + 2] = g >> 16; }
-                    else { pay[(gq >> 2) * 3 + 2] |= g << 8; }
-                }
-            } else {
-                // rare block (denormal-range or near-overflow maximum): the general fp32 formulas
-                const Axs6Scale sc = axs6_scale_codes(amax16 << 16);
-                se = (uint32_t)sc.se;
-#pragma unroll
-                for (int i = 0; i < 6; ++i) pay[i] = 0u;
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const uint32_t bits = (i & 1) ? (w[i >> 1] & 0xFFFF0000u) : (w[i >> 1] << 16);
-                    const uint32_t ab = bits & 0x7FFFFFFFu;
-                    const int idx = axs6_nf5_index(axs6_normalise(__uint_as_float(ab), sc));
-                    const uint32_t code = (uint32_t)g_reverse[idx] | ((ab != 0u && (bits >> 31)) ? 32u : 0u);
-                    const int word = (6 * i) >> 5, off = (6 * i) & 31;
-                    pay[word] |= code << off;
-                    if (off > 26) pay[word + 1] |= code >> (32 - off);
-                }
-            }
-            // header bytes in front of the payload, the whole record shifted to byte `sh` of its first word
-            uint32_t prev = HDR == 1 ? (se << 24) : (((se << 2) & 0xFFFFu) << 16);
-#pragma unroll
-            for (int i = 0; i < 6; ++i) {
-                W[i] = __funnelshift_lc(prev, pay[i], sft);
-                prev = pay[i];
-            }
-            W[6] = __funnelshift_lc(prev, 0u, sft);
+            bf16_block_payload(w, table, pay, se);
+            record_words<HDR>(pay, se, sft, W);
         }
         const uint32_t nxt = __shfl_down_sync(0xFFFFFFFFu, W[0], 1);
         if (takes_next) W[6] |= nxt;
@@ -778,6 +741,216 @@ static int launch_pack_bulk(const void *x, void *out, int64_t nblocks, int hdr, 
     }
     if (hdr == 1) pack_bf16_nf5_b32_bulk_kernel<1><<<(unsigned)ctas, kFastBlocks, smem_bytes<1>(), st>>>(map, o, nblocks);
     else          pack_bf16_nf5_b32_bulk_kernel<2><<<(unsigned)ctas, kFastBlocks, smem_bytes<2>(), st>>>(map, o, nblocks);
+    count_launch();
+    return check_launch();
+}
+
+// ------------------------------------------------------------------------------------------ unpack, TMA-fed
+// Records (NF5 grid, block 32, byte layouts) -> bf16 or fp32 values, one thread per block.  The 256
+// records of an iteration arrive with one bulk copy; a thread reads its 25 or 26 bytes as seven words
+// and funnel-shifts them into the exponent byte and the 192-bit payload.  A value is then ONE table
+// lookup and one integer addition: the table holds, for each 6-bit code, the sign and the level's bit
+// pattern with its exponent field lowered by 120, and adding (se - 7) to the exponent field multiplies
+// by 2^(se - 127) exactly (taken for se in [8, 254], where every result is a normal number; other
+// blocks use the fp32 product of the general kernel).  bf16 results are rounded once, in the table:
+// rounding commutes with the power-of-two scale.  The output tile leaves through a tensor map with
+// the swizzle that makes the 128-bit shared-memory stores of a thread conflict-free.
+template <typename Tout>
+struct UnpackOut;
+template <>
+struct UnpackOut<__nv_bfloat16> { static constexpr int kRowBytes = 64, kPieces = 4, kSwzMask = 3, kSwzShift = 1; };
+template <>
+struct UnpackOut<float> { static constexpr int kRowBytes = 128, kPieces = 8, kSwzMask = 7, kSwzShift = 0; };
+
+template <typename Tout, int HDR>
+constexpr int unpack_smem_bytes() { return 1024 + kCtrlBytes + 2 * kFastBlocks * UnpackOut<Tout>::kRowBytes + kStages * kFastBlocks * (HDR + 24); }
+
+template <typename Tout, int HDR>
+__global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const __grid_constant__ CUtensorMap ymap,
+                                                                         const uint8_t *__restrict__ in, int64_t nblocks)
+{
+    constexpr bool kBf16 = sizeof(Tout) == 2;
+    constexpr int REC = HDR + 24;
+    constexpr int kIn = kFastBlocks * REC;
+    constexpr int kTile = kFastBlocks * UnpackOut<Tout>::kRowBytes;
+    constexpr int kPieces = UnpackOut<Tout>::kPieces;
+    extern __shared__ uint8_t raw[];
+    __shared__ __align__(16) uint32_t tlo[64];      // code -> value bits (bf16: in the low half)
+    __shared__ __align__(16) uint32_t thi[64];      // bf16 only: the same in the high half
+    __shared__ float lev[32];
+    uint8_t *base = raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u);
+    uint8_t *tile0 = base + kCtrlBytes;             // 1024-aligned output tiles
+    uint8_t *in0 = tile0 + 2 * kTile;
+    const uint32_t bar0 = smem_u32(base);
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
+        fence_barrier_init();
+        fence_async_smem();
+    }
+    if (tid < 64) {
+        const uint32_t bits = g_codebook_bits[tid & 31];
+        const uint32_t sign = (uint32_t)tid >> 5;
+        if (kBf16) {
+            const uint32_t v = ((uint32_t)axs6_f32_to_bf16_bits(__uint_as_float(bits)) - (120u << 7)) | (sign << 15);
+            tlo[tid] = v;
+            thi[tid] = v << 16;
+        } else {
+            tlo[tid] = (bits - (120u << 23)) | (sign << 31);
+        }
+        if (tid < 32) lev[tid] = __uint_as_float(bits);
+    }
+    __syncthreads();
+
+    const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
+    const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // a group with fewer than 256 records (the last one) is fetched by the threads themselves
+    if (tid == 0) {
+        for (int k = 0; k < kStages && k < nk; ++k) {
+            const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
+            if (nblocks - grp * kFastBlocks >= kFastBlocks) {
+                mbar_expect_tx(bar0 + 8 * k, kIn);
+                bulk_load(smem_u32(in0 + k * kIn), in + grp * kIn, kIn, bar0 + 8 * k);
+            }
+        }
+    }
+    const uint32_t wb = (uint32_t)(REC * tid) >> 2, sh = (uint32_t)(REC * tid) & 3u;
+    const uint32_t sft = 8u * (sh + HDR);
+    uint32_t piece[kPieces];
+#pragma unroll
+    for (int i = 0; i < kPieces; ++i)
+        piece[i] = (uint32_t)tid * UnpackOut<Tout>::kRowBytes +
+                   (uint32_t)((i ^ ((tid >> UnpackOut<Tout>::kSwzShift) & UnpackOut<Tout>::kSwzMask)) << 4);
+
+    int s = 0;
+    uint32_t ph = 0;
+    for (int64_t k = 0; k < nk; ++k) {
+        const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
+        const int64_t b = grp * kFastBlocks + tid;
+        const int64_t nb = nblocks - grp * kFastBlocks;
+        uint8_t *tile = tile0 + (k & 1) * kTile;
+        const uint8_t *stage = in0 + s * kIn;
+        bool ok = true;
+        if (nb >= kFastBlocks) {
+            ok = mbar_wait_bounded(bar0 + 8 * s, ph, 2, &g_codec_status, kWaitLimit);
+        } else {
+            const int len = (int)nb * REC;
+            const uint8_t *src = in + grp * kIn;
+            uint8_t *dst = in0 + s * kIn;
+            for (int i = tid; i < len; i += kFastBlocks) dst[i] = src[i];
+            __syncthreads();
+        }
+        if (ok && b < nblocks) {
+            const uint32_t *r32 = reinterpret_cast<const uint32_t *>(stage) + wb;
+            uint32_t W[7];
+#pragma unroll
+            for (int i = 0; i < 7; ++i) W[i] = r32[i];
+            uint32_t pay[6];
+#pragma unroll
+            for (int i = 0; i < 6; ++i) pay[i] = __funnelshift_rc(W[i], W[i + 1], sft);
+            const uint32_t head = W[0] >> (8u * sh);
+            const uint32_t se = HDR == 1 ? (head & 0xFFu) : ((head >> 2) & 0xFFu);
+            uint32_t o[kBf16 ? 16 : 32];
+            if (se >= 8u && se <= 254u) {
+                const uint32_t kk = kBf16 ? (se - 7u) * 0x00800080u : (se - 7u) << 23;
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    uint32_t a[2];                      // byte offsets (code * 4) of values i and i + 1
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int bit = 6 * (i + e), word = bit >> 5, off = bit & 31;
+                        uint32_t v;
+                        if (off == 0) v = pay[word] << 2;
+                        else if (off == 1) v = pay[word] << 1;
+                        else if (off <= 26) v = pay[word] >> (off - 2);
+                        else v = __funnelshift_r(pay[word], pay[word + 1], off - 2);
+                        a[e] = v & 0xFCu;
+                    }
+                    const uint32_t v0 = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(tlo) + a[0]);
+                    if (kBf16) {
+                        const uint32_t v1 = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(thi) + a[1]);
+                        o[i >> 1] = v0 + v1 + kk;
+                    } else {
+                        const uint32_t v1 = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(tlo) + a[1]);
+                        o[i] = v0 + kk;
+                        o[i + 1] = v1 + kk;
+                    }
+                }
+            } else {
+                // all-zero blocks (se = 0) and blocks at the ends of the exponent range: fp32 product
+                const float scale = axs6_scale_decode(se);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int bit = 6 * i, word = bit >> 5, off = bit & 31;
+                    const uint32_t code = (off <= 26 ? (pay[word] >> off) : __funnelshift_r(pay[word], pay[word + 1], off)) & 63u;
+                    const float y = axs6_decode_value(code >> 5, lev[code & 31u], scale);
+                    if (kBf16) {
+                        const uint32_t h = axs6_f32_to_bf16_bits(y);
+                        if (i & 1) o[i >> 1] |= h << 16; else o[i >> 1] = h;
+                    } else {
+                        o[i] = __float_as_uint(y);
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kPieces; ++i)
+                *reinterpret_cast<uint4 *>(tile + piece[i]) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        }
+        fence_async_smem();
+        if (tid == 0) bulk_wait_read<0>();     // the previous iteration's store has left the other tile
+        if (__syncthreads_or(!ok)) break;
+        if (tid == 0) {
+            tma_store_2d(&ymap, smem_u32(tile), 0, (int)(grp * kFastBlocks));
+            bulk_commit();
+            if (k + kStages < nk) {
+                const int64_t g2 = grp + kStages * (int64_t)gridDim.x;
+                if (nblocks - g2 * kFastBlocks >= kFastBlocks) {
+                    mbar_expect_tx(bar0 + 8 * s, kIn);
+                    bulk_load(smem_u32(in0 + s * kIn), in + g2 * kIn, kIn, bar0 + 8 * s);
+                }
+            }
+        }
+        if (++s == kStages) { s = 0; ph ^= 1u; }
+    }
+    if (tid == 0) bulk_wait<0>();
+}
+
+// -> status, or 1 when this path does not apply (the caller then uses unpack_vec_kernel)
+template <typename Tout>
+static int launch_unpack_bulk(const void *in, void *y, int64_t nblocks, int hdr, cudaStream_t st)
+{
+    if (nblocks >= (1ll << 31) - kFastBlocks) return 1;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return 1;
+    constexpr bool kBf16 = sizeof(Tout) == 2;
+    CUtensorMap map;
+    const cuuint64_t gdim[2] = {32, (cuuint64_t)nblocks};
+    const cuuint64_t gstride[1] = {32 * sizeof(Tout)};
+    const cuuint32_t box[2] = {32, (cuuint32_t)kFastBlocks};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, kBf16 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, y, gdim, gstride, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, kBf16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return 1;
+    const DeviceInfo &d = device_info();
+    int64_t ctas = (nblocks + kFastBlocks - 1) / kFastBlocks;
+    const int64_t cap = tune_value(1);
+    int per_sm = kBf16 ? 4 : 2;
+    if (cap > 0 && cap < per_sm) per_sm = (int)cap;
+    if (ctas > (int64_t)d.sms * per_sm) ctas = (int64_t)d.sms * per_sm;
+    if (ctas < 1) ctas = 1;
+    static bool attr_done[64] = {};
+    int dev_id = 0;
+    if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= 64) return 1;
+    if (!attr_done[dev_id]) {
+        if (cudaFuncSetAttribute(unpack_nf5_b32_bulk_kernel<Tout, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, unpack_smem_bytes<Tout, 1>()) != cudaSuccess ||
+            cudaFuncSetAttribute(unpack_nf5_b32_bulk_kernel<Tout, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, unpack_smem_bytes<Tout, 2>()) != cudaSuccess)
+            return AXS6_ERR_LAUNCH;
+        attr_done[dev_id] = true;
+    }
+    const uint8_t *src = static_cast<const uint8_t *>(in);
+    if (hdr == 1) unpack_nf5_b32_bulk_kernel<Tout, 1><<<(unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 1>(), st>>>(map, src, nblocks);
+    else          unpack_nf5_b32_bulk_kernel<Tout, 2><<<(unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 2>(), st>>>(map, src, nblocks);
     count_launch();
     return check_launch();
 }
@@ -942,6 +1115,12 @@ AXS6_API int axs6_unpack(int layout, const void *in0, const void *in1, const voi
     const bool vec = aligned16(y) && (cols % kChunk == 0) && (ldy % kChunk == 0) && aligned16(in0) &&
                      (!planes || (aligned16(in1) && aligned16(in2)));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // tune key 11: 1 = general kernel only
+    if (vec && !planes && a.g.flat && grid == AXS6_GRID_NF5 && block == 32 && tune_value(11) != 1) {
+        const int r = out_dtype == AXS6_F32 ? bulk::launch_unpack_bulk<float>(in0, y, rows * (cols / 32), a.hdr, st)
+                                            : bulk::launch_unpack_bulk<__nv_bfloat16>(in0, y, rows * (cols / 32), a.hdr, st);
+        if (r != 1) return r;
+    }
 #define AXS6_CASE(T, G) return launch_unpack<T, G>(a, planes, vec, st)
     if (out_dtype == AXS6_F32) { if (grid == AXS6_GRID_NF5) AXS6_CASE(float, AXS6_GRID_NF5); AXS6_CASE(float, AXS6_GRID_UNIFORM); }
     if (grid == AXS6_GRID_NF5) AXS6_CASE(__nv_bfloat16, AXS6_GRID_NF5);

@@ -432,3 +432,39 @@ def test_bf16_record_pack_kernels_agree_with_the_oracle(shape, layout):
     finally:
         lib.axs6_tune(2, 0)
     assert lib.axs6_codec_status() == 0
+
+
+@pytest.mark.parametrize("layout", [ops.LAYOUT_WIRE, ops.LAYOUT_SPEC])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols", [(1, 32), (255, 32), (257, 32), (3, 96), (777, 1056), (1024, 4096)])
+def test_record_unpack_kernels_agree_with_the_oracle(rows, cols, out_dtype, layout):
+    """Byte records -> values (NF5, block 32): the TMA-fed kernel (default) and the general kernel
+    (tune key 11 = 1) both reproduce the oracle bit for bit on RANDOM records, i.e. for every code and
+    every exponent byte, including the blocks outside the integer fast path (se < 8 and se = 255)."""
+    lib = _lib.load()
+    rng = np.random.default_rng(rows * 7 + cols + layout)
+    nblk = cols // 32
+    rec = 24 + (2 if layout == ops.LAYOUT_SPEC else 1)
+    raw = rng.integers(0, 256, size=(rows * nblk, rec), dtype=np.uint8)
+    if layout == ops.LAYOUT_SPEC:
+        raw[:, 0] &= 0xFC                                  # config bits 0 = dense block
+    raw[rng.random(rows * nblk) < 0.05] = 0                # all-zero records
+    if layout == ops.LAYOUT_WIRE:
+        raw[rng.random(rows * nblk) < 0.05, 0] = rng.integers(0, 8)    # tiny exponents
+    se, sg, mg = oracle.unpack_bytes(raw.reshape(-1), rows, nblk, 32, layout)
+    want = oracle.dequantize(se, sg, mg, cols, oracle.GRID_NF5)
+    finite = np.isfinite(want)                            # se = 255 decodes to inf: out of contract
+    if out_dtype == torch.bfloat16:
+        want = oracle.f32_to_bf16(want)
+    buf = torch.from_numpy(raw.reshape(-1).copy()).cuda()
+    try:
+        for mode in (0, 1):
+            lib.axs6_tune(11, mode)
+            got = ops.unpack(layout, buf, rows, cols, 32, ops.GRID_NF5, out_dtype)
+            torch.cuda.synchronize()
+            g = to_bits(got).reshape(-1)[finite.reshape(-1)]
+            w = (want.view(np.uint32) if want.dtype == np.float32 else want).reshape(-1)[finite.reshape(-1)]
+            assert np.array_equal(g, w), f"tune(11)={mode}: {(g != w).sum()} of {g.size} differ"
+    finally:
+        lib.axs6_tune(11, 0)
+    assert lib.axs6_codec_status() == 0
