@@ -745,6 +745,173 @@ static int launch_pack_bulk(const void *x, void *out, int64_t nblocks, int hdr, 
     return check_launch();
 }
 
+// ------------------------------------------------------------------------------------------ fp32 pack, TMA-fed
+// fp32 input, NF5 grid, nearest rounding, block 32, byte records: the data movement of the bf16 kernel
+// above (tiles of 256 blocks x 128 bytes through a tensor map with the 128-byte swizzle, records out
+// with one bulk copy), the arithmetic of the general kernel (axs6_scale_codes and the exact index
+// formulas), one thread per block.
+constexpr int kF32Tile = kFastBlocks * 128;
+
+template <int HDR>
+constexpr int pack_f32_smem_bytes() { return 1024 + kCtrlBytes + kStages * kF32Tile + 2 * kFastBlocks * (HDR + 24); }
+
+template <int HDR>
+__global__ void __launch_bounds__(kFastBlocks) pack_f32_nf5_b32_bulk_kernel(const __grid_constant__ CUtensorMap xmap,
+                                                                           uint8_t *__restrict__ out, int64_t nblocks)
+{
+    constexpr int REC = HDR + 24;
+    constexpr int kOut = kFastBlocks * REC;
+    extern __shared__ uint8_t raw[];
+    __shared__ __align__(16) uint8_t rev[1024];
+    uint8_t *base = raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u);
+    uint8_t *in0 = base + kCtrlBytes;
+    uint8_t *out0 = in0 + kStages * kF32Tile;
+    const uint32_t bar0 = smem_u32(base);
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
+        fence_barrier_init();
+        fence_async_smem();
+    }
+    build_reverse_lut(rev);
+    __syncthreads();
+
+    const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
+    const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    if (tid == 0) {
+        for (int k = 0; k < kStages && k < nk; ++k) {
+            mbar_expect_tx(bar0 + 8 * k, kF32Tile);
+            tma_load_2d(smem_u32(in0 + k * kF32Tile), &xmap, bar0 + 8 * k, 0,
+                        (int)(((int64_t)blockIdx.x + k * (int64_t)gridDim.x) * kFastBlocks));
+        }
+    }
+    uint32_t piece[8];                       // row tid, 16-byte piece i at piece i ^ (row & 7)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) piece[i] = (uint32_t)tid * 128u + (uint32_t)((i ^ (tid & 7)) << 4);
+    const uint32_t wb = (uint32_t)(REC * tid) >> 2, sh = (uint32_t)(REC * tid) & 3u;
+    const uint32_t sft = 8u * (sh + HDR);
+    const bool owns_first = sh == 0u;
+    const bool takes_next = ((uint32_t)(REC * (tid + 1)) & 3u) != 0u;
+
+    int s = 0;
+    uint32_t ph = 0;
+    for (int64_t k = 0; k < nk; ++k) {
+        const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
+        const int64_t b = grp * kFastBlocks + tid;
+        uint8_t *ost = out0 + (k & 1) * kOut;
+        const bool ok = mbar_wait_bounded(bar0 + 8 * s, ph, 3, &g_codec_status, kWaitLimit);
+        uint32_t W[7];
+#pragma unroll
+        for (int i = 0; i < 7; ++i) W[i] = 0u;
+        if (ok && b < nblocks) {
+            uint32_t v[32];
+            const uint8_t *tile = in0 + s * kF32Tile;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint4 q = *reinterpret_cast<const uint4 *>(tile + piece[i]);
+                v[4 * i] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
+            }
+            uint32_t amax = 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) amax = max(amax, v[i] & 0x7FFFFFFFu);
+            const Axs6Scale sc = axs6_scale_codes(amax);
+            uint32_t pay[6];
+#pragma unroll
+            for (int i = 0; i < 6; ++i) pay[i] = 0u;
+            if (sc.fast) {
+                const float c = AXS6_MUL(sc.inv, 1023.0f);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float x = __uint_as_float(v[i]);
+                    const uint32_t code = (uint32_t)rev[axs6_nf5_index_fast(fabsf(x), c)] | (x < 0.0f ? 32u : 0u);
+                    const int word = (6 * i) >> 5, off = (6 * i) & 31;
+                    pay[word] |= code << off;
+                    if (off > 26) pay[word + 1] |= code >> (32 - off);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const uint32_t ab = v[i] & 0x7FFFFFFFu;
+                    const int idx = axs6_nf5_index(axs6_normalise(__uint_as_float(ab), sc));
+                    const uint32_t code = (uint32_t)rev[idx] | ((ab != 0u && (v[i] >> 31)) ? 32u : 0u);
+                    const int word = (6 * i) >> 5, off = (6 * i) & 31;
+                    pay[word] |= code << off;
+                    if (off > 26) pay[word + 1] |= code >> (32 - off);
+                }
+            }
+            record_words<HDR>(pay, (uint32_t)sc.se, sft, W);
+        }
+        const uint32_t nxt = __shfl_down_sync(0xFFFFFFFFu, W[0], 1);
+        if (takes_next) W[6] |= nxt;
+        uint32_t *o32 = reinterpret_cast<uint32_t *>(ost) + wb;
+        if (owns_first) o32[0] = W[0];
+#pragma unroll
+        for (int i = 1; i < 7; ++i) o32[i] = W[i];
+        fence_async_smem();
+        if (tid == 0) bulk_wait_read<0>();
+        if (__syncthreads_or(!ok)) break;
+        const int64_t nb = nblocks - grp * kFastBlocks;
+        if (nb >= kFastBlocks) {
+            if (tid == 0) {
+                bulk_store(out + grp * kOut, smem_u32(ost), kOut);
+                bulk_commit();
+            }
+        } else {
+            const int len = (int)nb * REC;
+            uint8_t *dst = out + grp * kOut;
+            const int nvec = len >> 4;
+            for (int i = tid; i < nvec; i += kFastBlocks)
+                st_stream16(dst + 16 * i, reinterpret_cast<const uint4 *>(ost)[i]);
+            for (int i = (nvec << 4) + tid; i < len; i += kFastBlocks) dst[i] = ost[i];
+        }
+        if (tid == 0 && k + kStages < nk) {
+            mbar_expect_tx(bar0 + 8 * s, kF32Tile);
+            tma_load_2d(smem_u32(in0 + s * kF32Tile), &xmap, bar0 + 8 * s, 0,
+                        (int)(((int64_t)blockIdx.x + (k + kStages) * (int64_t)gridDim.x) * kFastBlocks));
+        }
+        if (++s == kStages) { s = 0; ph ^= 1u; }
+    }
+    if (tid == 0) bulk_wait<0>();
+}
+
+// -> status, or 1 when this path does not apply
+static int launch_pack_f32_bulk(const void *x, void *out, int64_t nblocks, int hdr, cudaStream_t st)
+{
+    if (nblocks >= (1ll << 31) - kFastBlocks) return 1;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return 1;
+    CUtensorMap map;
+    const cuuint64_t gdim[2] = {32, (cuuint64_t)nblocks};
+    const cuuint64_t gstride[1] = {128};
+    const cuuint32_t box[2] = {32, (cuuint32_t)kFastBlocks};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(x), gdim, gstride, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return 1;
+    const DeviceInfo &d = device_info();
+    int64_t ctas = (nblocks + kFastBlocks - 1) / kFastBlocks;
+    const int64_t cap = tune_value(1);
+    int per_sm = 2;
+    if (cap > 0 && cap < per_sm) per_sm = (int)cap;
+    if (ctas > (int64_t)d.sms * per_sm) ctas = (int64_t)d.sms * per_sm;
+    if (ctas < 1) ctas = 1;
+    static bool attr_done[64] = {};
+    int dev_id = 0;
+    if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= 64) return 1;
+    if (!attr_done[dev_id]) {
+        if (cudaFuncSetAttribute(pack_f32_nf5_b32_bulk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, pack_f32_smem_bytes<1>()) != cudaSuccess ||
+            cudaFuncSetAttribute(pack_f32_nf5_b32_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, pack_f32_smem_bytes<2>()) != cudaSuccess)
+            return AXS6_ERR_LAUNCH;
+        attr_done[dev_id] = true;
+    }
+    uint8_t *o = static_cast<uint8_t *>(out);
+    if (hdr == 1) pack_f32_nf5_b32_bulk_kernel<1><<<(unsigned)ctas, kFastBlocks, pack_f32_smem_bytes<1>(), st>>>(map, o, nblocks);
+    else          pack_f32_nf5_b32_bulk_kernel<2><<<(unsigned)ctas, kFastBlocks, pack_f32_smem_bytes<2>(), st>>>(map, o, nblocks);
+    count_launch();
+    return check_launch();
+}
+
 // ------------------------------------------------------------------------------------------ unpack, TMA-fed
 // Records (NF5 grid, block 32, byte layouts) -> bf16 or fp32 values, one thread per block.  The 256
 // records of an iteration arrive with one bulk copy; a thread reads its 25 or 26 bytes as seven words
@@ -1075,6 +1242,11 @@ AXS6_API int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, 
     const bool vec = aligned16(x) && (cols % kChunk == 0) && (ldx % kChunk == 0) && aligned16(out0) &&
                      (!planes || (aligned16(out1) && aligned16(out2))) && (round != kNoise || aligned16(noise));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (vec && !planes && a.g.flat && in_dtype == AXS6_F32 && !a.via_bf16 && grid == AXS6_GRID_NF5 && round == kNearest &&
+        block == 32 && tune_value(2) != 1) {
+        const int r = bulk::launch_pack_f32_bulk(x, out0, rows * (cols / 32), a.hdr, st);
+        if (r != 1) return r;
+    }
     if (vec && !planes && a.g.flat && in_dtype == AXS6_BF16 && grid == AXS6_GRID_NF5 && round == kNearest && block == 32 &&
         tune_value(2) != 1) {
         // tune key 2: 1 = general kernel, 2 = per-thread loads (no TMA); default = TMA-fed kernel

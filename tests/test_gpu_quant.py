@@ -402,12 +402,14 @@ def test_philox_epoch_changes_draws_and_reset_restores_them():
 
 
 @pytest.mark.parametrize("layout", [ops.LAYOUT_WIRE, ops.LAYOUT_SPEC])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
 @pytest.mark.parametrize("shape", [(1, 32), (255, 32), (257, 32), (3, 96), (777, 1056), (2048, 4096)])
-def test_bf16_record_pack_kernels_agree_with_the_oracle(shape, layout):
-    """bf16 input, NF5, nearest, block 32, byte records: the TMA-fed kernel (default), the kernel with
-    per-thread loads (tune key 2 = 2) and the general kernel (tune key 2 = 1) all give the oracle's
-    bytes, for whole and ragged groups of 256 blocks and for blocks that leave the integer fast path
-    (all-zero, negative zeros, denormal-range and near-overflow maxima)."""
+def test_record_pack_kernels_agree_with_the_oracle(shape, dtype, layout):
+    """NF5, nearest, block 32, byte records: the TMA-fed kernels (default; one for bf16 and one for fp32
+    input), the bf16 kernel with per-thread loads (tune key 2 = 2) and the general kernel (tune key
+    2 = 1) all give the oracle's bytes, for whole and ragged groups of 256 blocks and for blocks that
+    leave the fast paths (all-zero, negative zeros, denormal-range and near-overflow maxima, maxima at
+    the top of a binade where the block exponent is bumped)."""
     from axs6_b200 import _lib
     lib = _lib.load()
     g = torch.Generator().manual_seed(shape[0] * 131 + shape[1] + layout)
@@ -419,7 +421,8 @@ def test_bf16_record_pack_kernels_agree_with_the_oracle(shape, layout):
         x[1] *= 1e-38
         x[2] *= 3e37
         x[0, :32] = 0.0
-    xb = oracle.f32_to_bf16(x.numpy())
+    x.view(-1)[::97] = float.fromhex("0x1.fffffep+3")
+    xb = oracle.f32_to_bf16(x.numpy()) if dtype == "bf16" else x.numpy()
     se, sg, mg = oracle.quantize(xb, 32, oracle.GRID_NF5)
     want = oracle.pack_bytes(se, sg, mg, layout)
     xt = to_cuda(xb)
