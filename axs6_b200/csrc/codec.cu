@@ -623,23 +623,21 @@ __global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_bulk_kernel(con
     __shared__ __align__(16) uint8_t table[kKeyLimit + 16];   // static: its address is an immediate of every lookup
     const uint32_t bar0 = smem_u32(base);
     const int tid = threadIdx.x;
+    const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
+    const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
         fence_barrier_init();
         fence_async_smem();
-    }
-    build_key_table(table, tid, kFastBlocks);
-    __syncthreads();
-
-    const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
-    const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    if (tid == 0) {
+        // the first tiles are on their way while the table is being built
         for (int k = 0; k < kStages && k < nk; ++k) {
             mbar_expect_tx(bar0 + 8 * k, kStageBytes);
             tma_load_2d(smem_u32(in0 + k * kStageBytes), &xmap, bar0 + 8 * k, 0,
                         (int)(((int64_t)blockIdx.x + k * (int64_t)gridDim.x) * kFastBlocks));
         }
     }
+    build_key_table(table, tid, kFastBlocks);
+    __syncthreads();
     // this thread's block is row `tid` of a tile; 16-byte piece i of a row sits at piece i ^ ((row >> 1) & 3)
     uint32_t piece[4];
 #pragma unroll
@@ -768,23 +766,20 @@ __global__ void __launch_bounds__(kFastBlocks) pack_f32_nf5_b32_bulk_kernel(cons
     uint8_t *out0 = in0 + kStages * kF32Tile;
     const uint32_t bar0 = smem_u32(base);
     const int tid = threadIdx.x;
+    const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
+    const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
         fence_barrier_init();
         fence_async_smem();
-    }
-    build_reverse_lut(rev);
-    __syncthreads();
-
-    const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
-    const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    if (tid == 0) {
         for (int k = 0; k < kStages && k < nk; ++k) {
             mbar_expect_tx(bar0 + 8 * k, kF32Tile);
             tma_load_2d(smem_u32(in0 + k * kF32Tile), &xmap, bar0 + 8 * k, 0,
                         (int)(((int64_t)blockIdx.x + k * (int64_t)gridDim.x) * kFastBlocks));
         }
     }
+    build_reverse_lut(rev);
+    __syncthreads();
     uint32_t piece[8];                       // row tid, 16-byte piece i at piece i ^ (row & 7)
 #pragma unroll
     for (int i = 0; i < 8; ++i) piece[i] = (uint32_t)tid * 128u + (uint32_t)((i ^ (tid & 7)) << 4);
@@ -950,10 +945,20 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
     uint8_t *in0 = tile0 + 2 * kTile;
     const uint32_t bar0 = smem_u32(base);
     const int tid = threadIdx.x;
+    const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
+    const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
         fence_barrier_init();
         fence_async_smem();
+        // a group with fewer than 256 records (the last one) is fetched by the threads themselves
+        for (int k = 0; k < kStages && k < nk; ++k) {
+            const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
+            if (nblocks - grp * kFastBlocks >= kFastBlocks) {
+                mbar_expect_tx(bar0 + 8 * k, kIn);
+                bulk_load(smem_u32(in0 + k * kIn), in + grp * kIn, kIn, bar0 + 8 * k);
+            }
+        }
     }
     if (tid < 64) {
         const uint32_t bits = g_codebook_bits[tid & 31];
@@ -969,18 +974,6 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
     }
     __syncthreads();
 
-    const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
-    const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    // a group with fewer than 256 records (the last one) is fetched by the threads themselves
-    if (tid == 0) {
-        for (int k = 0; k < kStages && k < nk; ++k) {
-            const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
-            if (nblocks - grp * kFastBlocks >= kFastBlocks) {
-                mbar_expect_tx(bar0 + 8 * k, kIn);
-                bulk_load(smem_u32(in0 + k * kIn), in + grp * kIn, kIn, bar0 + 8 * k);
-            }
-        }
-    }
     const uint32_t wb = (uint32_t)(REC * tid) >> 2, sh = (uint32_t)(REC * tid) & 3u;
     const uint32_t sft = 8u * (sh + HDR);
     uint32_t piece[kPieces];

@@ -1,6 +1,6 @@
 """Runs ONE kernel of the library a few times on a small, larger-than-L2 case, for profilers.
 
-    python -m axs6_b200.profile_case {fq_f32|fq_bf16|fq_bf16_stochastic|pack_wire|unpack_wire|gemm_fwd|gemm_dx|gemm_dw} [launches]
+    python -m axs6_b200.profile_case {fq_f32|fq_bf16|fq_bf16_stochastic|pack_wire|pack_wire_f32|unpack_wire|unpack_wire_bf16|gemm_fwd|gemm_dx|gemm_dw} [launches]
 
 Device footprint stays under 1 GB so that a multi-pass capture finishes quickly.
 """
@@ -33,6 +33,16 @@ def main() -> None:
         x = torch.randn(rows, cols, generator=g, device=dev).to(torch.bfloat16)
         w = torch.empty(rows * cols // 32 * 25, dtype=torch.uint8, device=dev)
         run = lambda: lib.axs6_pack(x.data_ptr(), 1, rows, cols, cols, 32, 1, 0, 0, 0, 0, None, 1, w.data_ptr(), None, None, st)
+    elif what == "pack_wire_f32":
+        x = torch.randn(rows, cols, generator=g, device=dev)
+        w = torch.empty(rows * cols // 32 * 25, dtype=torch.uint8, device=dev)
+        run = lambda: lib.axs6_pack(x.data_ptr(), 0, rows, cols, cols, 32, 1, 0, 0, 0, 0, None, 1, w.data_ptr(), None, None, st)
+    elif what == "unpack_wire_bf16":
+        x = torch.randn(rows, cols, generator=g, device=dev).to(torch.bfloat16)
+        w = torch.empty(rows * cols // 32 * 25, dtype=torch.uint8, device=dev)
+        assert lib.axs6_pack(x.data_ptr(), 1, rows, cols, cols, 32, 1, 0, 0, 0, 0, None, 1, w.data_ptr(), None, None, st) == 0
+        y = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev)
+        run = lambda: lib.axs6_unpack(1, w.data_ptr(), None, None, y.data_ptr(), 1, rows, cols, cols, 32, 1, st)
     elif what == "unpack_wire":
         x = torch.randn(rows, cols, generator=g, device=dev).to(torch.bfloat16)
         w = torch.empty(rows * cols // 32 * 25, dtype=torch.uint8, device=dev)
@@ -58,6 +68,7 @@ def main() -> None:
     torch.cuda.synchronize()
     if what.startswith("gemm"):
         assert lib.axs6_gemm_status() == 0
+    assert lib.axs6_codec_status() == 0
     print(f"{what}: {n} launches ok")
 
 

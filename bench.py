@@ -337,22 +337,31 @@ def bench_codec(torch, lib, udist, dev, pk) -> dict:
         xb = x.to(torch.bfloat16)
         wire = torch.empty(rows * (cols // 32) * 25, dtype=torch.uint8, device=dev)
         out = torch.empty(rows, cols, dtype=torch.float32, device=dev)
-        pool.append((xb, wire, out))
+        pool.append((xb, wire, out, x))
     stream = torch.cuda.current_stream().cuda_stream
 
     def pack(i):
-        xb, wire, _ = pool[i % 4]
+        xb, wire = pool[i % 4][:2]
         assert lib.axs6_pack(xb.data_ptr(), 1, rows, cols, cols, 32, 1, 0, 0, 0, 0, None, 1, wire.data_ptr(), None, None, stream) == 0
 
+    def pack_f32(i):
+        _, wire, _, x = pool[i % 4]
+        assert lib.axs6_pack(x.data_ptr(), 0, rows, cols, cols, 32, 1, 0, 0, 0, 0, None, 1, wire.data_ptr(), None, None, stream) == 0
+
     def unpack(i):
-        _, wire, out = pool[i % 4]
+        _, wire, out = pool[i % 4][:3]
         assert lib.axs6_unpack(1, wire.data_ptr(), None, None, out.data_ptr(), 0, rows, cols, cols, 32, 1, stream) == 0
+
+    def unpack_bf16(i):
+        _, wire, out = pool[i % 4][:3]
+        assert lib.axs6_unpack(1, wire.data_ptr(), None, None, out.data_ptr(), 1, rows, cols, cols, 32, 1, stream) == 0
 
     res = {}
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     n = 40
-    for name, fn, nbytes in (("pack", pack, rows * cols * 2 + rows * cols // 32 * 25),
-                             ("unpack", unpack, rows * cols * 4 + rows * cols // 32 * 25)):
+    rec = rows * cols // 32 * 25
+    for name, fn, nbytes in (("pack_f32", pack_f32, rows * cols * 4 + rec), ("pack", pack, rows * cols * 2 + rec),
+                             ("unpack", unpack, rows * cols * 4 + rec), ("unpack_bf16", unpack_bf16, rows * cols * 2 + rec)):
         for i in range(8):
             fn(i)
         torch.cuda.synchronize()
@@ -364,7 +373,10 @@ def bench_codec(torch, lib, udist, dev, pk) -> dict:
         ms = e0.elapsed_time(e1) / n
         gbs = nbytes / (ms * 1e-3) / 1e9
         res[name] = {"ms": ms, "GBps": gbs, "frac_of_hbm_peak": gbs / pk["hbm_gbs"], "algorithmic_bytes": nbytes}
-    res["workload"] = "bf16 8192x4096 -> 25-byte wire records -> fp32, block 32 (4 rotating buffer sets, 4 x 227 MiB > L2)"
+    res["roundtrip_bf16_GBps"] = 2 * (rows * cols * 2 + rec) / ((res["pack"]["ms"] + res["unpack_bf16"]["ms"]) * 1e-3) / 1e9
+    res["stream_status"] = int(lib.axs6_codec_status())
+    res["workload"] = ("8192x4096, block 32, 25-byte wire records: pack = bf16 -> records, pack_f32 = fp32 -> records, unpack = records "
+                       "-> fp32, unpack_bf16 = records -> bf16 (4 rotating buffer sets, 4 x 355 MiB > L2)")
     return res
 
 
