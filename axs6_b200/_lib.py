@@ -35,6 +35,7 @@ SIGNATURES = {
     "axs6_pack": (_int, [_ptr, _int, _i64, _i64, _i64, _int, _int, _int, _u32, _u64, _u64, _ptr, _int,
                          _ptr, _ptr, _ptr, _ptr]),
     "axs6_unpack": (_int, [_int, _ptr, _ptr, _ptr, _ptr, _int, _i64, _i64, _i64, _int, _int, _ptr]),
+    "axs6_unpack_sum": (_int, [_int, _ptr, _i64, _i64, _ptr, _int, _i64, _i64, _i64, _int, _int, ctypes.c_float, _ptr]),
     "axs6_gemm_bf16": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "axs6_gemm_tf32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "axs6_gemm_status": (_int, []),

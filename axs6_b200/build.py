@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libaxs6_b200.so")
 
-EXACT_SOURCES = ["abi.cu", "fq.cu", "codec.cu", "linear.cu"]      # bit-exact arithmetic: no fma contraction
+EXACT_SOURCES = ["abi.cu", "fq.cu", "codec.cu", "exchange.cu", "linear.cu"]      # bit-exact arithmetic: no fma contraction
 FAST_SOURCES: list[str] = ["gemm.cu"]                          # tensor-core kernels
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

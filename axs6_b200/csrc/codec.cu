@@ -1293,10 +1293,16 @@ AXS6_API int axs6_unpack(int layout, const void *in0, const void *in1, const voi
 #undef AXS6_CASE
 }
 
+namespace axs6 {
+int exchange_status_fetch();     // exchange.cu
+}
+
 AXS6_API int axs6_codec_status(void)
 {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, axs6::bulk::g_codec_status, sizeof(int)) != cudaSuccess) return AXS6_ERR_DEVICE;
     if (v != 0) cudaMemcpyToSymbol(axs6::bulk::g_codec_status, &zero, sizeof(int));
-    return v;
+    const int x = axs6::exchange_status_fetch();
+    if (x < 0) return x;
+    return v != 0 ? v : (x != 0 ? 10 + x : 0);
 }

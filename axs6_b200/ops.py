@@ -130,6 +130,26 @@ def fake_quantize(x: torch.Tensor, block_size: int = 32, grid: int = GRID_NF5, r
     return y.reshape(x.shape)
 
 
+def unpack_sum(layout: int, buf: torch.Tensor, nsrc: int, src_stride: int, rows: int, cols: int, block_size: int = 32,
+               grid: int = GRID_NF5, out_dtype: torch.dtype = torch.float32, divisor: float = 1.0) -> torch.Tensor:
+    """(sum of the ``nsrc`` record buffers' reconstructions) / divisor in one pass; source ``s`` starts at byte
+    ``s * src_stride`` of ``buf``.  Summed in fp32 in source order, like unpacking one by one and adding."""
+    assert block_size in VALID_BLOCK_SIZES, f"block_size must be one of {VALID_BLOCK_SIZES}"
+    _check_input(buf, "unpack_sum")
+    buf = buf.contiguous()
+    nblk = -(-cols // block_size)
+    need = rows * nblk * record_bytes(layout, block_size)
+    if nsrc < 1 or (nsrc > 1 and src_stride < need) or buf.numel() * buf.element_size() < (nsrc - 1) * src_stride + need:
+        raise ValueError(f"buffer of {buf.numel() * buf.element_size()} bytes does not hold {nsrc} sources of {need} bytes "
+                         f"at stride {src_stride}")
+    y = torch.empty((rows, cols), dtype=out_dtype, device=buf.device)
+    with _on(buf.device):
+        st = _lib.load().axs6_unpack_sum(layout, buf.data_ptr(), nsrc, src_stride, y.data_ptr(), _DT[out_dtype], rows, cols,
+                                         cols, block_size, grid, float(divisor), _stream(buf.device))
+    _lib.check("axs6_unpack_sum", st)
+    return y
+
+
 def record_bytes(layout: int, block_size: int) -> int:
     return int(_lib.load().axs6_record_bytes(layout, block_size))
 

@@ -102,6 +102,12 @@ class CudaCodec:
         y = ops.unpack(ops.LAYOUT_WIRE, buf, 1, numel, self.block_size, ops.GRID_NF5, out_dt)
         return y.reshape(-1).to(dtype)
 
+    def unpack_mean(self, gathered: torch.Tensor, world: int, stride: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """Mean of the ``world`` record buffers' reconstructions (buffer r at byte ``r * stride``), one fused pass."""
+        out_dt = dtype if dtype in (torch.float32, torch.bfloat16) else torch.float32
+        y = ops.unpack_sum(ops.LAYOUT_WIRE, gathered, world, stride, 1, numel, self.block_size, ops.GRID_NF5, out_dt, float(world))
+        return y.reshape(-1).to(dtype)
+
     def roundtrip(self, flat: torch.Tensor) -> torch.Tensor:
         """unpack(pack(flat)): what a peer would reconstruct from this rank's records."""
         return self.unpack(self.pack(flat), flat.numel(), flat.dtype)
@@ -148,9 +154,33 @@ def axs6_gradient_hook(state: Any, bucket) -> "torch.futures.Future[torch.Tensor
     return _allreduce_mean(recon, group, world)
 
 
+def _padded16(records: torch.Tensor) -> torch.Tensor:
+    """The records in a buffer whose size is a multiple of 16 bytes, so that every rank's slice of the
+    gathered buffer starts 16-byte aligned (the fused unpack-and-average kernel moves them with bulk copies)."""
+    n = records.numel()
+    n16 = (n + 15) // 16 * 16
+    if n16 == n:
+        return records
+    out = torch.zeros(n16, dtype=records.dtype, device=records.device)
+    out[:n] = records
+    return out
+
+
+def _mean_of_gathered(codec, gathered: torch.Tensor, world: int, stride: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
+    """Mean of the ranks' reconstructions, summed in fp32 in rank order: fused when the codec can."""
+    if hasattr(codec, "unpack_mean"):
+        return codec.unpack_mean(gathered, world, stride, numel, dtype)
+    acc = None
+    for r in range(world):
+        part = codec.unpack(gathered[r * stride:(r + 1) * stride], numel, torch.float32)
+        acc = part if acc is None else acc.add_(part)
+    return acc.div_(world).to(dtype)
+
+
 def axs6_gradient_hook_packed(state: Any, bucket) -> "torch.futures.Future[torch.Tensor]":
     """Compressed exchange: each rank packs its bucket to 25-byte records (6.25 bits per value on
-    the wire), the records are all-gathered, and every rank unpacks all of them and averages.
+    the wire), the records are all-gathered, and every rank decodes all of them and averages in ONE fused pass
+    (``axs6_unpack_sum``: every record read once, the mean written once).
 
     Same name and registration as the reference's packed hook (distributed.py:308-367) but not
     its arithmetic: the reference all-reduces the bit-packed bytes as integers and averages
@@ -160,16 +190,12 @@ def axs6_gradient_hook_packed(state: Any, bucket) -> "torch.futures.Future[torch
     world = dist.get_world_size(group)
     grad = bucket.buffer()
     numel, dtype = grad.numel(), grad.dtype
-    mine = codec.pack(grad.reshape(-1))
+    mine = _padded16(codec.pack(grad.reshape(-1)))
     gathered = torch.empty(world * mine.numel(), dtype=mine.dtype, device=mine.device)
     fut = dist.all_gather_into_tensor(gathered, mine, group=group, async_op=True).get_future()
 
     def done(f):
-        acc = None
-        for r in range(world):
-            part = codec.unpack(gathered[r * mine.numel():(r + 1) * mine.numel()], numel, torch.float32)
-            acc = part if acc is None else acc.add_(part)
-        return acc.div_(world).to(dtype)
+        return _mean_of_gathered(codec, gathered, world, mine.numel(), numel, dtype)
 
     return fut.then(done)
 
@@ -195,11 +221,7 @@ class AXS6GradCompressor:
             recon = codec.roundtrip(flat).to(grad.dtype)
             dist.all_reduce(recon, op=dist.ReduceOp.SUM, group=group)
             return recon.div_(world).reshape(grad.shape)
-        mine = codec.pack(flat)
+        mine = _padded16(codec.pack(flat))
         gathered = torch.empty(world * mine.numel(), dtype=mine.dtype, device=mine.device)
         dist.all_gather_into_tensor(gathered, mine, group=group)
-        acc = None
-        for r in range(world):
-            part = codec.unpack(gathered[r * mine.numel():(r + 1) * mine.numel()], flat.numel(), torch.float32)
-            acc = part if acc is None else acc.add_(part)
-        return acc.div_(world).to(grad.dtype).reshape(grad.shape)
+        return _mean_of_gathered(codec, gathered, world, mine.numel(), flat.numel(), grad.dtype).reshape(grad.shape)

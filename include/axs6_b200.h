@@ -179,11 +179,23 @@ int axs6_transpose_f32(const float *in, float *out, int64_t rows, int64_t cols,
  * Synchronises the device and clears the status. */
 int axs6_gemm_status(void);
 
-/* The same for the pack kernel that is fed by the TMA unit (bf16 input, NF5 grid, nearest rounding,
- * block 32, byte layouts): 0 = every wait completed; 1 = a wait for a loaded tile gave up and the
- * records written by that launch are incomplete.  Synchronises the device and clears the status.
- * No counterpart in the reference. */
+/* The same for the pack / unpack kernels that are fed by the TMA unit (NF5 grid, nearest rounding,
+ * block 32, byte layouts) and for axs6_unpack_sum: 0 = every wait completed; 1..3 = a pack (1 bf16,
+ * 3 fp32) or unpack (2) kernel gave up waiting for a loaded tile, 11 / 12 = a consumer / the producer
+ * of axs6_unpack_sum gave up; the output of that launch is incomplete.  Synchronises the device and
+ * clears the status.  No counterpart in the reference. */
 int axs6_codec_status(void);
+
+/* y = (unpack(records) + unpack(records + src_stride) + ... nsrc terms) / divisor, summed in fp32 in
+ * source order; every source holds the byte records (AXS6_LAYOUT_WIRE or AXS6_LAYOUT_SPEC) of the same
+ * rows x cols tensor.  The receiving side of the compressed gradient exchange in ONE pass: it replaces
+ * the loop "unpack each rank's buffer, add, divide by the world size" that follows the all-gather
+ * (axs/unified/distributed.py:308-367 is the reference's packed hook; its arithmetic on the packed
+ * bytes is not reproduced, the result here is the mean of the ranks' reconstructions).
+ * src_stride in bytes (a multiple of 16 for the fast kernel); divisor != 0. */
+int axs6_unpack_sum(int layout, const void *records, int64_t nsrc, int64_t src_stride, void *y,
+                    int out_dtype, int64_t rows, int64_t cols, int64_t ldy, int block, int grid,
+                    float divisor, axs6_stream_t stream);
 
 /* AXS-6 Linear with bf16 tensor-core compute: the graph of _AXSLinearBF16Function
  * (axs/unified/mixed_precision.py:86-155), also reached through accelerated_linear /

@@ -471,3 +471,48 @@ def test_record_unpack_kernels_agree_with_the_oracle(rows, cols, out_dtype, layo
     finally:
         lib.axs6_tune(11, 0)
     assert lib.axs6_codec_status() == 0
+
+
+@pytest.mark.parametrize("layout", [ops.LAYOUT_WIRE, ops.LAYOUT_SPEC])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nsrc,rows,cols", [(1, 255, 32), (2, 257, 32), (3, 1, 32), (3, 777, 1056), (8, 512, 4096), (5, 100, 96)])
+def test_fused_unpack_and_average_matches_the_oracle(nsrc, rows, cols, out_dtype, layout):
+    """axs6_unpack_sum (the receiving side of the packed gradient exchange) on RANDOM records of nsrc
+    sources: bit-identical to summing the oracle's reconstructions in fp32 in source order and dividing by
+    nsrc, for the producer/consumer TMA kernel (default) and the one-thread-per-value kernel (tune key 11)."""
+    lib = _lib.load()
+    rng = np.random.default_rng(nsrc * 1000 + rows + cols + layout)
+    nblk = cols // 32
+    rec = 24 + (2 if layout == ops.LAYOUT_SPEC else 1)
+    per = rows * nblk * rec
+    stride = (per + 15) // 16 * 16 + 16 * (nsrc % 2)          # padded, and not always the minimum
+    raw = np.zeros(nsrc * stride, dtype=np.uint8)
+    acc = None
+    for s in range(nsrc):
+        r = rng.integers(0, 256, size=(rows * nblk, rec), dtype=np.uint8)
+        se_in = rng.integers(0, 250, size=rows * nblk).astype(np.uint32)      # sums of up to 8 sources stay finite
+        se_in[rng.random(rows * nblk) < 0.05] = rng.integers(0, 8)           # blocks outside the integer fast path
+        if layout == ops.LAYOUT_SPEC:
+            r[:, 0] = (se_in << 2) & 0xFF
+            r[:, 1] = se_in >> 6
+        else:
+            r[:, 0] = se_in
+        r[rng.random(rows * nblk) < 0.05] = 0
+        raw[s * stride:s * stride + per] = r.reshape(-1)
+        se, sg, mg = oracle.unpack_bytes(r.reshape(-1), rows, nblk, 32, layout)
+        part = oracle.dequantize(se, sg, mg, cols, oracle.GRID_NF5)
+        acc = part if acc is None else (acc + part).astype(np.float32)
+    assert np.isfinite(acc).all()
+    want = (acc / np.float32(nsrc)).astype(np.float32)
+    if out_dtype == torch.bfloat16:
+        want = oracle.f32_to_bf16(want)
+    buf = torch.from_numpy(raw).cuda()
+    try:
+        for mode in (0, 1):
+            lib.axs6_tune(11, mode)
+            got = ops.unpack_sum(layout, buf, nsrc, stride, rows, cols, 32, ops.GRID_NF5, out_dtype, float(nsrc))
+            torch.cuda.synchronize()
+            assert_bits_equal(got, want, f"tune(11)={mode} nsrc={nsrc} {rows}x{cols}")
+    finally:
+        lib.axs6_tune(11, 0)
+    assert lib.axs6_codec_status() == 0
