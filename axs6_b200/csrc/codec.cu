@@ -1295,6 +1295,7 @@ AXS6_API int axs6_unpack(int layout, const void *in0, const void *in1, const voi
 
 namespace axs6 {
 int exchange_status_fetch();     // exchange.cu
+int fq_status_fetch();           // fq.cu
 }
 
 AXS6_API int axs6_codec_status(void)
@@ -1304,5 +1305,7 @@ AXS6_API int axs6_codec_status(void)
     if (v != 0) cudaMemcpyToSymbol(axs6::bulk::g_codec_status, &zero, sizeof(int));
     const int x = axs6::exchange_status_fetch();
     if (x < 0) return x;
-    return v != 0 ? v : (x != 0 ? 10 + x : 0);
+    const int q = axs6::fq_status_fetch();
+    if (q < 0) return q;
+    return v != 0 ? v : (x != 0 ? 10 + x : (q != 0 ? 20 + q : 0));
 }

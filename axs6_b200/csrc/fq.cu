@@ -9,6 +9,7 @@
 //                      occupancy of the instantiation, U independent chunks per thread in flight.
 //   fq_generic_kernel  any pointer alignment / extent: one lane per value, coalesced scalar
 //                      accesses, amax over B lanes.
+#include "async_copy.cuh"
 #include "quant_device.cuh"
 
 namespace axs6 {
@@ -240,6 +241,204 @@ ChunkGeom make_geom(int64_t rows, int64_t cols, int block)
     return g;
 }
 
+// ------------------------------------------------------------------------------------------ bf16 -> bf16, TMA-fed
+// bf16 in, bf16 out, NF5 grid, nearest rounding, block 32, contiguous and 16-byte aligned: one thread per
+// block, tiles of 256 blocks moved by the TMA unit in both directions and quantised IN PLACE in shared
+// memory (a 3-slot ring: one slot being loaded, one computed, one stored).  The arithmetic is integer
+// arithmetic on the bf16 bit patterns.  With E the exponent field of the block maximum the scale is
+// S = 2^(E - 126) (the top-of-binade exponent bump of the fp32 path cannot occur: the low 16 mantissa
+// bits are zero) and for a value (128 + m) * 2^(e - 134)
+//     idx = trunc(|x| / S * 1023) = ((128 + m) * 1023) >> (8 + j),   j = E - e,   exactly,
+// so the reconstruction level depends on key = ((E << 7) | 127) - |x|_bits only.  The table holds, per key,
+// the level rounded to bf16 (rounding commutes with the power-of-two scale) with its exponent field lowered
+// by 120; adding (E - 6) to the exponent field multiplies by S.  Taken for E in [11, 252] and for all-zero
+// blocks; other blocks (denormal-range or near-overflow maxima) use the fp32 formulas of the general kernel.
+namespace fqb {
+
+using namespace acp;
+
+constexpr int kBlocksB = 256;
+constexpr int kSlots = 3;
+constexpr int kSlotBytes = kBlocksB * 64;
+constexpr int kKeyLim = 1280;
+constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr int kSmemBytes = 1024 + 1024 + kSlots * kSlotBytes;
+
+__device__ int g_fq_status;
+
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    asm("max.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t min_u16x2(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    asm("min.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+__global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __grid_constant__ CUtensorMap xmap,
+                                                                       const __grid_constant__ CUtensorMap ymap, int64_t nblocks)
+{
+    extern __shared__ uint8_t raw[];
+    __shared__ __align__(16) uint16_t table[kKeyLim + 8];      // key -> level bits (bf16), exponent field - 120
+    uint8_t *base = raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u);
+    uint8_t *slot0 = base + 1024;
+    const uint32_t bar0 = smem_u32(base);
+    const int tid = threadIdx.x;
+    const int64_t groups = (nblocks + kBlocksB - 1) / kBlocksB;
+    const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    if (tid == 0) {
+        for (int s = 0; s < kSlots; ++s) mbar_init(bar0 + 8 * s, 1);
+        fence_barrier_init();
+        fence_async_smem();
+        for (int k = 0; k < 2 && k < nk; ++k) {                // two tiles ahead; the third slot is the one being stored
+            mbar_expect_tx(bar0 + 8 * k, kSlotBytes);
+            tma_load_2d(smem_u32(slot0 + k * kSlotBytes), &xmap, bar0 + 8 * k, 0,
+                        (int)(((int64_t)blockIdx.x + k * (int64_t)gridDim.x) * kBlocksB));
+        }
+    }
+    for (int key = tid; key <= kKeyLim; key += kBlocksB) {
+        uint32_t code = 0;
+        if (key < kKeyLim) {
+            const int j = key >> 7, m = 127 - (key & 127);
+            code = g_reverse[((128 + m) * 1023) >> (8 + j)];
+        }
+        table[key] = (uint16_t)(axs6_f32_to_bf16_bits(__uint_as_float(g_codebook_bits[code])) - (120u << 7));
+    }
+    __syncthreads();
+
+    uint32_t piece[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) piece[i] = (uint32_t)tid * 64u + (uint32_t)((i ^ ((tid >> 1) & 3)) << 4);
+
+    int s = 0;
+    uint32_t ph = 0;
+    for (int64_t k = 0; k < nk; ++k) {
+        const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
+        const int64_t b = grp * kBlocksB + tid;
+        uint8_t *slot = slot0 + s * kSlotBytes;
+        const bool ok = mbar_wait_bounded(bar0 + 8 * s, ph, 1, &g_fq_status, kWaitLimit);
+        if (ok && b < nblocks) {
+            uint32_t w[16];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 v = *reinterpret_cast<const uint4 *>(slot + piece[i]);
+                w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+            }
+            uint32_t mx = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) mx = max_u16x2(mx, w[i] & 0x7FFF7FFFu);
+            const uint32_t amax16 = max(mx & 0xFFFFu, mx >> 16);
+            const uint32_t ef = amax16 >> 7;
+            if (amax16 == 0u || (ef >= 11u && ef <= 252u)) {
+                const uint32_t a1 = amax16 ? ((ef << 7) | 127u) : 0x7FFFu;
+                const uint32_t a2 = a1 | (a1 << 16);
+                const uint32_t lim2 = (uint32_t)kKeyLim | ((uint32_t)kKeyLim << 16);
+                const uint32_t kk = amax16 ? (ef - 6u) * 0x00800080u : 0u;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const uint32_t wi = w[i];
+                    const uint32_t ma = wi & 0x7FFF7FFFu;
+                    const uint32_t k2 = min_u16x2(a2 - ma, lim2) << 1;            // byte offsets of the two table entries
+                    const uint32_t lo = *reinterpret_cast<const uint16_t *>(reinterpret_cast<const uint8_t *>(table) + (k2 & 0xFFFFu));
+                    const uint32_t hi = *reinterpret_cast<const uint16_t *>(reinterpret_cast<const uint8_t *>(table) + (k2 >> 16));
+                    const uint32_t val = (hi * 65536u + lo) + kk;
+                    // halves that hold +-0 become +0: bit 15 / 31 of t says "non-zero", spread over its half
+                    const uint32_t t = ma + 0x7FFF7FFFu;
+                    uint32_t nz;
+                    asm("prmt.b32 %0, %1, %1, %2;" : "=r"(nz) : "r"(t), "r"(0xBB99u));
+                    w[i] = (val | (wi & 0x80008000u)) & nz;
+                }
+            } else {
+                const Axs6Scale sc = axs6_scale_fq(amax16 << 16);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    uint32_t o = 0;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t bits = h ? (w[i] & 0xFFFF0000u) : (w[i] << 16);
+                        const float n = axs6_normalise(__uint_as_float(bits & 0x7FFFFFFFu), sc);
+                        const int idx = axs6_nf5_index(n);
+                        const float y = axs6_fq_value(bits, __uint_as_float(g_codebook_bits[g_reverse[idx]]), sc.scale);
+                        o |= (uint32_t)axs6_f32_to_bf16_bits(y) << (16 * h);
+                    }
+                    w[i] = o;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                *reinterpret_cast<uint4 *>(slot + piece[i]) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
+        fence_async_smem();
+        if (__syncthreads_or(!ok)) break;
+        if (tid == 0) {
+            tma_store_2d(&ymap, smem_u32(slot), 0, (int)(grp * kBlocksB));
+            bulk_commit();
+            if (k + 2 < nk) {
+                // the slot of the previous iteration: its store has finished reading once at most one store
+                // (the one just committed) is pending
+                bulk_wait_read<1>();
+                const int s2 = s == 0 ? kSlots - 1 : s - 1;
+                mbar_expect_tx(bar0 + 8 * s2, kSlotBytes);
+                tma_load_2d(smem_u32(slot0 + s2 * kSlotBytes), &xmap, bar0 + 8 * s2, 0,
+                            (int)(((int64_t)blockIdx.x + (k + 2) * (int64_t)gridDim.x) * kBlocksB));
+            }
+        }
+        if (++s == kSlots) { s = 0; ph ^= 1u; }
+    }
+    if (tid == 0) bulk_wait<0>();
+}
+
+// -> status, or 1 when this path does not apply
+static int launch(const void *x, void *y, int64_t nblocks, cudaStream_t st)
+{
+    if (nblocks >= (1ll << 31) - kBlocksB) return 1;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return 1;
+    CUtensorMap xm, ym;
+    const cuuint64_t gdim[2] = {32, (cuuint64_t)nblocks};
+    const cuuint64_t gstride[1] = {64};
+    const cuuint32_t box[2] = {32, (cuuint32_t)kBlocksB};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&xm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(x), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
+        enc(&ym, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, y, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return 1;
+    const DeviceInfo &d = device_info();
+    int64_t ctas = (nblocks + kBlocksB - 1) / kBlocksB;
+    const int64_t cap = tune_value(0);
+    int per_sm = 3;                          // 32768 x 8192: 6.47 TB/s with 3 CTAs per SM, 5.96 with 4, 5.79 with 2
+    if (cap > 0 && cap < per_sm) per_sm = (int)cap;
+    if (ctas > (int64_t)d.sms * per_sm) ctas = (int64_t)d.sms * per_sm;
+    if (ctas < 1) ctas = 1;
+    static bool attr_done[64] = {};
+    int dev_id = 0;
+    if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= 64) return 1;
+    if (!attr_done[dev_id]) {
+        if (cudaFuncSetAttribute(fq_bf16_nf5_b32_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+            return AXS6_ERR_LAUNCH;
+        attr_done[dev_id] = true;
+    }
+    fq_bf16_nf5_b32_bulk_kernel<<<(unsigned)ctas, kBlocksB, kSmemBytes, st>>>(xm, ym, nblocks);
+    count_launch();
+    return check_launch();
+}
+
+}  // namespace fqb
+
+// Status word of the TMA-fed fake-quantise kernel, cleared when non-zero (read by axs6_codec_status).
+int fq_status_fetch()
+{
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, fqb::g_fq_status, sizeof(int)) != cudaSuccess) return AXS6_ERR_DEVICE;
+    if (v != 0) cudaMemcpyToSymbol(fqb::g_fq_status, &zero, sizeof(int));
+    return v;
+}
+
 static int fq_entry(const void *x, void *y, int in_dtype, int out_dtype, int64_t rows, int64_t cols,
                     int64_t ldx, int64_t ldy, int block, int grid, int round, uint32_t flags,
                     uint64_t seed, uint64_t offset, const float *noise, cudaStream_t stream)
@@ -265,6 +464,12 @@ static int fq_entry(const void *x, void *y, int in_dtype, int out_dtype, int64_t
     if (round == kPhilox && !a.epoch) return AXS6_ERR_DEVICE;
     const bool vec = aligned16(x) && aligned16(y) && (cols % kChunk == 0) && (ldx % kChunk == 0) &&
                      (ldy % kChunk == 0) && (round != kNoise || aligned16(noise));
+    // tune key 12: 1 = general kernel only
+    if (vec && a.g.flat && in_dtype == AXS6_BF16 && out_dtype == AXS6_BF16 && grid == AXS6_GRID_NF5 && round == kNearest &&
+        block == 32 && tune_value(12) != 1) {
+        const int r = fqb::launch(x, y, rows * (cols / 32), stream);
+        if (r != 1) return r;
+    }
     if (in_dtype == AXS6_F32 && out_dtype == AXS6_F32) return dispatch_fq<float, float>(a, grid, round, vec, stream);
     if (in_dtype == AXS6_F32 && out_dtype == AXS6_BF16) return dispatch_fq<float, __nv_bfloat16>(a, grid, round, vec, stream);
     if (in_dtype == AXS6_BF16 && out_dtype == AXS6_F32) return dispatch_fq<__nv_bfloat16, float>(a, grid, round, vec, stream);

@@ -265,6 +265,16 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         if rank == 0:
             extra["linear"] = {"error": repr(e)}
 
+    if world > 1:
+        try:
+            from axs6_b200 import exchange_bench
+            ex = exchange_bench.run(rank, world, dev)
+            if rank == 0:
+                extra["grad_exchange"] = ex
+        except Exception as e:
+            if rank == 0:
+                extra["grad_exchange"] = {"error": repr(e)}
+
     try:
         from axs6_b200 import minigpt_bench
         mg = minigpt_bench.run(args, rank, world, dev)

@@ -182,7 +182,8 @@ int axs6_gemm_status(void);
 /* The same for the pack / unpack kernels that are fed by the TMA unit (NF5 grid, nearest rounding,
  * block 32, byte layouts) and for axs6_unpack_sum: 0 = every wait completed; 1..3 = a pack (1 bf16,
  * 3 fp32) or unpack (2) kernel gave up waiting for a loaded tile, 11 / 12 = a consumer / the producer
- * of axs6_unpack_sum gave up; the output of that launch is incomplete.  Synchronises the device and
+ * of axs6_unpack_sum gave up, 21 = the TMA-fed bf16 fake-quantise kernel gave up; the output of that
+ * launch is incomplete.  Synchronises the device and
  * clears the status.  No counterpart in the reference. */
 int axs6_codec_status(void);
 

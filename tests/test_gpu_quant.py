@@ -516,3 +516,33 @@ def test_fused_unpack_and_average_matches_the_oracle(nsrc, rows, cols, out_dtype
     finally:
         lib.axs6_tune(11, 0)
     assert lib.axs6_codec_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(1, 32), (255, 32), (257, 32), (513, 32), (3, 96), (777, 1056), (2048, 4096)])
+def test_bf16_fake_quantise_kernels_agree_with_the_oracle(shape):
+    """bf16 -> bf16, NF5, nearest, block 32: the TMA-fed in-place kernel (default) and the general kernel
+    (tune key 12 = 1) both give the oracle's bits, including +-0 values, all-zero blocks and blocks whose
+    maximum lies in the denormal range or next to overflow."""
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(shape[0] * 17 + shape[1])
+    x = torch.randn(*shape, generator=g)
+    x[torch.rand(*shape, generator=g) < 0.02] = 0.0
+    x[torch.rand(*shape, generator=g) < 0.02] = -0.0
+    x[torch.rand(*shape, generator=g) < 0.002] *= 1e-30
+    if shape[0] > 2:
+        x[1] *= 1e-38
+        x[2] *= 3e37
+        x[0, :32] = 0.0
+    xb = oracle.f32_to_bf16(x.numpy())
+    want = oracle.fused_fake_quantize(xb, 32)
+    xt = to_cuda(xb)
+    try:
+        for mode in (0, 1):
+            lib.axs6_tune(12, mode)
+            got = qu.fused_fake_quantize(xt, 32)
+            torch.cuda.synchronize()
+            assert got.dtype == torch.bfloat16
+            assert_bits_equal(got, want, f"tune(12)={mode} {shape}")
+    finally:
+        lib.axs6_tune(12, 0)
+    assert lib.axs6_codec_status() == 0
