@@ -27,6 +27,11 @@ def next_philox(n_draws: int) -> tuple[int, int]:
     return torch.initial_seed() & 0xFFFFFFFFFFFFFFFF, off
 
 
+def philox_offset() -> int:
+    """The host-side Philox counter (what the next stochastic call starts from)."""
+    return _philox_offset
+
+
 def reset_philox(offset: int = 0) -> None:
     global _philox_offset
     _philox_offset = offset

@@ -6,10 +6,14 @@ from .backend import (accelerated_fake_quantize, accelerated_linear, accelerated
 from .functional_unified import axs_linear_unified, axs_matmul_unified, fake_quantize_unified
 from .mixed_precision import (AXSLinearMixedPrecision, axs_linear_mixed_precision, convert_to_axs_mixed_precision,
                               estimate_memory_savings)
-from .modules_unified import AXSLinearUnified, convert_to_axs_unified
+from .modules_unified import (AXSEmbeddingUnified, AXSLayerNormUnified, AXSLinearUnified, AXSMultiheadAttentionUnified,
+                              convert_to_axs_unified)
+from .training_unified import AmaxEMA, AXSTrainingPipelineUnified
 
 __all__ = ["fused_fake_quantize", "quantize_unified", "dequantize_unified", "NF5_CODEBOOK", "FUSED_NF5_LUT",
            "REVERSE_NF5_LUT", "accelerated_fake_quantize", "fake_quantize_unified", "get_backend",
            "set_backend", "backend_info", "accelerated_linear", "accelerated_matmul", "axs_linear_unified",
            "axs_matmul_unified", "axs_linear_mixed_precision", "AXSLinearMixedPrecision",
-           "convert_to_axs_mixed_precision", "estimate_memory_savings", "AXSLinearUnified", "convert_to_axs_unified"]
+           "convert_to_axs_mixed_precision", "estimate_memory_savings", "AXSLinearUnified", "convert_to_axs_unified",
+           "AXSLayerNormUnified", "AXSEmbeddingUnified", "AXSMultiheadAttentionUnified", "AmaxEMA",
+           "AXSTrainingPipelineUnified"]

@@ -1,0 +1,128 @@
+"""Callers of the fake-quantise kernels besides the Linear layers: embedding, attention, model conversion
+and the training pipeline (axs/unified/modules_unified.py:120-368, training_unified.py:115-410)."""
+import importlib
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+import oracle
+from gpu_util import assert_bits_equal
+
+pytestmark = pytest.mark.gpu
+
+from axs6_b200 import ops  # noqa: E402
+
+um = importlib.import_module("axs6_b200.unified.modules_unified")
+mp = importlib.import_module("axs6_b200.unified.mixed_precision")
+tu = importlib.import_module("axs6_b200.unified.training_unified")
+
+
+def test_embedding_quantises_only_the_looked_up_rows():
+    torch.manual_seed(0)
+    emb = um.AXSEmbeddingUnified(1000, 96, padding_idx=0).cuda()
+    assert float(emb.weight.detach()[0].abs().sum()) == 0.0
+    idx = torch.randint(0, 1000, (4, 17), device="cuda")
+    out = emb(idx)
+    rows = emb.weight.detach()[idx.reshape(-1)].cpu().numpy()
+    assert_bits_equal(out, oracle.fused_fake_quantize(rows, 32).reshape(4, 17, 96), "embedding rows")
+    out.sum().backward()                                   # straight-through: a count of occurrences per row
+    counts = torch.bincount(idx.reshape(-1), minlength=1000).float()
+    counts[0] = 0.0                                        # padding row receives no gradient
+    torch.testing.assert_close(emb.weight.grad[:, 0], counts)
+    emb._warmup_active = True
+    assert torch.equal(emb(idx), emb.weight.detach()[idx])
+
+
+def test_layer_norm_is_plain():
+    ln = um.AXSLayerNormUnified(64).cuda()
+    x = torch.randn(5, 64, device="cuda")
+    torch.testing.assert_close(ln(x), torch.nn.functional.layer_norm(x, [64]))
+
+
+def test_attention_shapes_gradients_and_quantised_weights():
+    torch.manual_seed(1)
+    att = um.AXSMultiheadAttentionUnified(64, 4).cuda()
+    x = torch.randn(2, 48, 64, device="cuda", requires_grad=True)
+    mask = torch.full((48, 48), float("-inf"), device="cuda").triu(1)
+    y = att(x, x, x, attn_mask=mask)
+    assert y.shape == (2, 48, 64) and bool(torch.isfinite(y).all())
+    y.square().mean().backward()
+    for p in list(att.parameters()) + [x]:
+        assert p.grad is not None and bool(torch.isfinite(p.grad).all())
+    # against the same attention in full precision: close, not equal
+    with torch.no_grad():
+        q, k, v = (torch.nn.functional.linear(x, m.weight, m.bias).reshape(2, 48, 4, 16).transpose(1, 2)
+                   for m in (att.q_proj, att.k_proj, att.v_proj))
+        w = torch.softmax(q @ k.transpose(-2, -1) * 0.25 + mask, dim=-1)
+        ref = torch.nn.functional.linear((w @ v).transpose(1, 2).reshape(2, 48, 64), att.out_proj.weight, att.out_proj.bias)
+    rel = float((y.detach() - ref).norm() / ref.norm())
+    assert 0.0 < rel < 0.15, rel
+
+
+def test_convert_to_axs_unified_swaps_linear_norm_and_embedding():
+    class Tiny(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = nn.Embedding(50, 32)
+            self.norm = nn.LayerNorm(32)
+            self.fc = nn.Linear(32, 8)
+            self.keep = nn.Linear(8, 8)
+
+        def forward(self, t):
+            return self.keep(self.fc(self.norm(self.emb(t))))
+
+    src = Tiny().cuda()
+    conv = um.convert_to_axs_unified(src, skip_layers={"keep"})
+    assert isinstance(conv.emb, um.AXSEmbeddingUnified) and isinstance(conv.norm, um.AXSLayerNormUnified)
+    assert isinstance(conv.fc, um.AXSLinearUnified) and type(conv.keep) is nn.Linear
+    assert type(src.fc) is nn.Linear                                        # the source model is untouched
+    for a, b in ((conv.emb.weight, src.emb.weight), (conv.fc.weight, src.fc.weight), (conv.norm.bias, src.norm.bias)):
+        assert torch.equal(a, b) and a.data_ptr() != b.data_ptr()
+    out = conv(torch.randint(0, 50, (3, 5), device="cuda"))
+    assert out.shape == (3, 5, 8) and bool(torch.isfinite(out).all())
+    again = um.convert_to_axs_unified(conv, inplace=True)
+    assert again is conv and isinstance(again.fc, um.AXSLinearUnified)
+
+
+def _mixed_model():
+    torch.manual_seed(3)
+    return nn.Sequential(mp.AXSLinearMixedPrecision(32, 64), nn.ReLU(), mp.AXSLinearMixedPrecision(64, 1)).cuda()
+
+
+def _mse(out, x):
+    return torch.nn.functional.mse_loss(out.float(), x[:, :4].sum(dim=1, keepdim=True) * 0.5)
+
+
+def test_pipeline_trains_mixed_precision_layers_and_resumes_bit_identically(tmp_path):
+    torch.manual_seed(11)
+    ops.reset_philox(0)
+    model = _mixed_model()
+    pipe = tu.AXSTrainingPipelineUnified(model, torch.optim.AdamW(model.parameters(), lr=1e-2), warmup_steps=3,
+                                         loss_scale_init=1024.0, max_grad_norm=5.0)
+    x = torch.randn(256, 32, device="cuda")
+    log = [pipe.training_step(x, _mse) for _ in range(40)]
+    assert [r["warmup"] for r in log[:4]] == [True, True, True, False]
+    assert all(m._warmup_active is False for m in model.modules() if isinstance(m, mp.AXSLinearMixedPrecision))
+    assert not any(r["overflow"] for r in log) and log[-1]["loss"] < 0.6 * log[0]["loss"]
+    path = pipe.save_checkpoint(tmp_path / "ck.pt")
+    want = [pipe.training_step(x, _mse)["loss"] for _ in range(5)]
+
+    other_model = _mixed_model()
+    other = tu.AXSTrainingPipelineUnified(other_model, torch.optim.AdamW(other_model.parameters(), lr=1e-2), warmup_steps=3,
+                                          loss_scale_init=1024.0, max_grad_norm=5.0)
+    ops.reset_philox(12345)                                                  # must be overwritten by the checkpoint
+    other.load_checkpoint(path, map_location="cuda")
+    got = [other.training_step(x, _mse)["loss"] for _ in range(5)]
+    assert got == want                                                       # same stochastic-rounding stream too
+
+
+def test_pipeline_overflow_on_the_gpu_uses_one_fused_check():
+    model = _mixed_model()
+    pipe = tu.AXSTrainingPipelineUnified(model, torch.optim.SGD(model.parameters(), lr=0.1), loss_scale_init=8.0)
+    x = torch.randn(64, 32, device="cuda")
+    res = pipe.training_step(x, lambda out, inp: out.float().sum() * float("inf"))
+    assert res["overflow"] is True and pipe.loss_scale == 4.0
+    res = pipe.training_step(x, _mse)
+    assert res["overflow"] is False and res["step"] == 1 and res["grad_norm"] > 0
