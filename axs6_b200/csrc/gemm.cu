@@ -57,7 +57,8 @@ struct Params {
     int tiles_m, tiles_n;
     uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;   // descriptor strides (bytes)
     int bk;                   // values per k-block: 64 (bf16) or 32 (tf32)
-    int splits;               // split-K factor of the 2-CTA kernel (1 or 2); 2 = fp32 output accumulated with red.add
+    int splits;               // split-K factor (>= 2: fp32 output accumulated with red.add into a zero-filled C)
+    int tail_begin;           // 2-CTA kernel: tiles from this one on are computed as two K halves (0 = none)
     uint32_t mn_box_bytes;    // bytes of one MN-major TMA box: 128 B x bk rows
 };
 
@@ -404,11 +405,21 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     const uint32_t rank = cluster_ctarank();            // 0 = leader
     const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
     const int tiles_m = (p.M + 255) / 256, tiles_n = (p.N + TN - 1) / TN;
+    // Work units.  With splits == 1 and no tail (p.tail_begin == 0) every tile is one unit.  Tiles from tail_begin on (the
+    // ones that would otherwise form a last, partly filled wave) are two units each, one per half of the
+    // contraction, accumulated into the zero-filled output with red.add; with two addends the sum does not
+    // depend on their order.  p.splits > 1 splits every tile instead.
     const int splits = p.splits;
-    const int num_tiles = tiles_m * tiles_n * splits;     // work units: (tile, K range)
     const int total_kb = (p.K + BK - 1) / BK;
-    auto kb_begin = [&](int t) { return (int)(((long long)(t % splits) * total_kb) / splits); };
-    auto kb_end = [&](int t) { return (int)(((long long)(t % splits + 1) * total_kb) / splits); };
+    const int all_tiles = tiles_m * tiles_n;
+    const int tail_begin = splits > 1 ? 0 : ((p.tail_begin <= 0 || p.tail_begin > all_tiles) ? all_tiles : p.tail_begin);
+    const int tail_parts = splits > 1 ? splits : 2;
+    const int num_tiles = tail_begin + (all_tiles - tail_begin) * tail_parts;
+    auto unit_tile = [&](int t) { return t < tail_begin ? t : tail_begin + (t - tail_begin) / tail_parts; };
+    auto unit_part = [&](int t) { return t < tail_begin ? 0 : (t - tail_begin) % tail_parts; };
+    auto unit_split = [&](int t) { return t >= tail_begin; };
+    auto kb_begin = [&](int t) { return unit_split(t) ? (int)(((long long)unit_part(t) * total_kb) / tail_parts) : 0; };
+    auto kb_end = [&](int t) { return unit_split(t) ? (int)(((long long)(unit_part(t) + 1) * total_kb) / tail_parts) : total_kb; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages2; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -434,7 +445,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             uint32_t ph = 0;
             bool ok = true;
             for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-                const int tile = t / splits;
+                const int tile = unit_tile(t);
                 const int m0 = (tile / tiles_n) * 256 + (int)rank * 128;
                 const int n0 = (tile % tiles_n) * TN + (int)rank * (TN / 2);
                 for (int kb = kb_begin(t); kb < kb_end(t); ++kb) {
@@ -500,13 +511,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         bool ok = true;
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) && (p.ldc % 8 == 0);
         for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-            const int tile = t / splits;
+            const int tile = unit_tile(t);
             const int m0 = (tile / tiles_n) * 256 + (int)rank * 128, n0 = (tile % tiles_n) * TN;
             if (!mbar_wait(tfull_bar(acc), aph, 4)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TN);
-            epilogue_tile<TN>(p, taddr, row, n0, vec_ok, splits > 1, (t % splits) == 0);
+            epilogue_tile<TN>(p, taddr, row, n0, vec_ok, unit_split(t), unit_part(t) == 0);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
@@ -565,7 +576,20 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     // (tune key 7: 1 forces the single-CTA kernel, 2 forces pairs)
     int64_t pair_tiles = ((M + 255) / 256) * ((N + BN - 1) / BN);
     const int64_t mode = tune_value(7);
-    const bool pairs = !kTf32 && mode != 1 && (mode == 2 || mode == 3 || pair_tiles >= d.sms / 2);
+    // Fewer pair tiles than clusters: pairs still win over the single-CTA kernel when at least a quarter of the
+    // clusters get a tile (a pair reads a third of the bytes per flop from L2, and the single-CTA kernel on
+    // 4096 x 1024 x 8192 was bound by that feed: 140 us), or when the output is fp32 and the contraction can be
+    // split so that most clusters get a unit (weight gradients of small layers).  More than two partials are
+    // added in no fixed order, so the last bits can differ between runs; tune key 3 = 1 forbids splits.
+    int64_t pair_splits = 1;
+    if (!kTf32 && c_dtype == AXS6_F32 && tune_value(3) == 0 && pair_tiles < d.sms / 2) {
+        const int64_t total_kb = (K + BK - 1) / BK;
+        pair_splits = (d.sms / 2) / pair_tiles;
+        if (pair_splits > total_kb / 16) pair_splits = total_kb / 16;
+        if (pair_splits > 8) pair_splits = 8;
+        if (pair_splits < 1) pair_splits = 1;
+    }
+    const bool pairs = !kTf32 && mode != 1 && (mode == 2 || mode == 3 || pair_tiles * pair_splits >= d.sms / 4);
     // 128-wide tiles: only through tune key 7 = 3.  Measured on the 4096 x 4096 x 16384 weight-gradient
     // product they fill the waves better (6.92 of 7 instead of 3.46 of 4) but run at 806 instead of
     // 1246 TFLOP/s: the per-k-block costs of the single producer and issuer threads no longer hide.
@@ -602,6 +626,8 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     // slower than not splitting (452 vs 436 us: the zero-fill and the red.add traffic cost more than
     // the better-filled last wave gains), so it is never chosen automatically.
     p.splits = (pairs && c_dtype == AXS6_F32 && tune_value(3) == 2 && K >= 16 * BK) ? 2 : 1;
+    if (pairs && pair_splits > 1 && mode != 3) p.splits = (int)pair_splits;
+    p.tail_begin = 0;
     // Few output tiles but a long contraction (the weight gradient of a small layer: 1024 x 1024 from
     // 8192 rows is 32 tiles for 148 SMs): split K so that about one work unit per SM exists; the
     // partial products are added into the zero-filled fp32 output with red.add.  The order of more than
@@ -645,6 +671,21 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
         // tune key 8: SMs to leave to other work (a collective running on another stream)
         const int64_t usable = d.sms - (tune_value(8) > 0 && tune_value(8) < d.sms - 2 ? tune_value(8) : 0);
         int clusters = (int)(units < usable / 2 ? units : usable / 2);
+        // Tail split (fp32 output, long contraction; tune key 3 = 1 turns it off): when the last wave would be
+        // at most half full, its tiles are computed as two K halves each, so that wave takes half the time.
+        // Weight gradient 4096 x 4096 x 16384: 256 tiles on 74 clusters, 3 full waves + 34 tiles -> 68 half
+        // units: 3.5 waves instead of 4.  The rows that hold those tiles are zero-filled first.
+        if (!narrow && p.splits == 1 && c_dtype == AXS6_F32 && tune_value(3) != 1 && K >= 32 * BK && pair_tiles > clusters) {
+            const int64_t rem = pair_tiles % clusters;
+            if (rem > 0 && 2 * rem <= clusters) {
+                p.tail_begin = (int)(pair_tiles - rem);
+                const int64_t tiles_n2 = (N + 255) / 256;
+                const int64_t row0 = (p.tail_begin / tiles_n2) * 256;
+                if (cudaMemset2DAsync(static_cast<float *>(c) + row0 * ldc, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)(M - row0),
+                                      stream) != cudaSuccess)
+                    return AXS6_ERR_LAUNCH;
+            }
+        }
         if (p.splits > 1 &&
             cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess)
             return AXS6_ERR_LAUNCH;
