@@ -161,9 +161,10 @@ def record_bytes(layout: int, block_size: int) -> int:
 
 def pack(x: torch.Tensor, block_size: int = 32, grid: int = GRID_NF5, rounding: str = "nearest",
          layout: int = LAYOUT_PLANES, via_bf16: bool = False, noise: torch.Tensor | None = None,
-         who: str = "pack"):
+         who: str = "pack", out: torch.Tensor | None = None):
     """Quantise to codes.  PLANES -> (exponents u8 (rows, nblk), signs bool (rows, nblk, B),
-    magnitudes u8 (rows, nblk, B)); WIRE / SPEC -> flat uint8 tensor of block records."""
+    magnitudes u8 (rows, nblk, B)); WIRE / SPEC -> flat uint8 tensor of block records (written into
+    ``out`` when given: a contiguous uint8 tensor on the same device with room for the records)."""
     _check_input(x, who)
     assert block_size in VALID_BLOCK_SIZES, f"block_size must be one of {VALID_BLOCK_SIZES}"
     rnd = _rounding(rounding)
@@ -178,7 +179,13 @@ def pack(x: torch.Tensor, block_size: int = 32, grid: int = GRID_NF5, rounding: 
         outs = (se, sg, mg)
         ptrs = (se.data_ptr(), sg.data_ptr(), mg.data_ptr())
     else:
-        buf = torch.empty(rows * nblk * record_bytes(layout, block_size), dtype=torch.uint8, device=dev)
+        need = rows * nblk * record_bytes(layout, block_size)
+        if out is not None:
+            if out.dtype != torch.uint8 or out.device != dev or not out.is_contiguous() or out.numel() < need:
+                raise ValueError(f"out must be a contiguous uint8 tensor on {dev} with at least {need} bytes")
+            buf = out
+        else:
+            buf = torch.empty(need, dtype=torch.uint8, device=dev)
         outs = buf
         ptrs = (buf.data_ptr(), None, None)
     nz = None

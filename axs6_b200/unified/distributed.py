@@ -97,6 +97,14 @@ class CudaCodec:
         """1-D tensor -> uint8 wire records of its zero-padded blocks."""
         return ops.pack(flat.reshape(1, -1), self.block_size, ops.GRID_NF5, "nearest", ops.LAYOUT_WIRE, who="pack")
 
+    def pack_padded16(self, flat: torch.Tensor) -> torch.Tensor:
+        """The same records at the front of a buffer whose size is rounded up to a multiple of 16 bytes."""
+        nblk = -(-flat.numel() // self.block_size)
+        n = nblk * ops.record_bytes(ops.LAYOUT_WIRE, self.block_size)
+        buf = torch.empty((n + 15) // 16 * 16, dtype=torch.uint8, device=flat.device)
+        ops.pack(flat.reshape(1, -1), self.block_size, ops.GRID_NF5, "nearest", ops.LAYOUT_WIRE, who="pack", out=buf)
+        return buf
+
     def unpack(self, buf: torch.Tensor, numel: int, dtype: torch.dtype) -> torch.Tensor:
         out_dt = dtype if dtype in (torch.float32, torch.bfloat16) else torch.float32
         y = ops.unpack(ops.LAYOUT_WIRE, buf, 1, numel, self.block_size, ops.GRID_NF5, out_dt)
@@ -154,6 +162,10 @@ def axs6_gradient_hook(state: Any, bucket) -> "torch.futures.Future[torch.Tensor
     return _allreduce_mean(recon, group, world)
 
 
+def _packed16(codec, flat: torch.Tensor) -> torch.Tensor:
+    return codec.pack_padded16(flat) if hasattr(codec, "pack_padded16") else _padded16(codec.pack(flat))
+
+
 def _padded16(records: torch.Tensor) -> torch.Tensor:
     """The records in a buffer whose size is a multiple of 16 bytes, so that every rank's slice of the
     gathered buffer starts 16-byte aligned (the fused unpack-and-average kernel moves them with bulk copies)."""
@@ -190,7 +202,7 @@ def axs6_gradient_hook_packed(state: Any, bucket) -> "torch.futures.Future[torch
     world = dist.get_world_size(group)
     grad = bucket.buffer()
     numel, dtype = grad.numel(), grad.dtype
-    mine = _padded16(codec.pack(grad.reshape(-1)))
+    mine = _packed16(codec, grad.reshape(-1))
     gathered = torch.empty(world * mine.numel(), dtype=mine.dtype, device=mine.device)
     fut = dist.all_gather_into_tensor(gathered, mine, group=group, async_op=True).get_future()
 
@@ -221,7 +233,7 @@ class AXS6GradCompressor:
             recon = codec.roundtrip(flat).to(grad.dtype)
             dist.all_reduce(recon, op=dist.ReduceOp.SUM, group=group)
             return recon.div_(world).reshape(grad.shape)
-        mine = _padded16(codec.pack(flat))
+        mine = _packed16(codec, flat)
         gathered = torch.empty(world * mine.numel(), dtype=mine.dtype, device=mine.device)
         dist.all_gather_into_tensor(gathered, mine, group=group)
         return _mean_of_gathered(codec, gathered, world, mine.numel(), flat.numel(), grad.dtype).reshape(grad.shape)
