@@ -136,9 +136,11 @@ def fake_quantize(x: torch.Tensor, block_size: int = 32, grid: int = GRID_NF5, r
 
 
 def unpack_sum(layout: int, buf: torch.Tensor, nsrc: int, src_stride: int, rows: int, cols: int, block_size: int = 32,
-               grid: int = GRID_NF5, out_dtype: torch.dtype = torch.float32, divisor: float = 1.0) -> torch.Tensor:
+               grid: int = GRID_NF5, out_dtype: torch.dtype = torch.float32, divisor: float = 1.0,
+               out: torch.Tensor | None = None) -> torch.Tensor:
     """(sum of the ``nsrc`` record buffers' reconstructions) / divisor in one pass; source ``s`` starts at byte
-    ``s * src_stride`` of ``buf``.  Summed in fp32 in source order, like unpacking one by one and adding."""
+    ``s * src_stride`` of ``buf``.  Summed in fp32 in source order, like unpacking one by one and adding.
+    ``out``: a contiguous fp32 / bf16 tensor of rows * cols values to write into instead of a new one."""
     assert block_size in VALID_BLOCK_SIZES, f"block_size must be one of {VALID_BLOCK_SIZES}"
     _check_input(buf, "unpack_sum")
     buf = buf.contiguous()
@@ -147,7 +149,12 @@ def unpack_sum(layout: int, buf: torch.Tensor, nsrc: int, src_stride: int, rows:
     if nsrc < 1 or (nsrc > 1 and src_stride < need) or buf.numel() * buf.element_size() < (nsrc - 1) * src_stride + need:
         raise ValueError(f"buffer of {buf.numel() * buf.element_size()} bytes does not hold {nsrc} sources of {need} bytes "
                          f"at stride {src_stride}")
-    y = torch.empty((rows, cols), dtype=out_dtype, device=buf.device)
+    if out is not None:
+        if out.dtype not in _DT or out.device != buf.device or not out.is_contiguous() or out.numel() != rows * cols:
+            raise ValueError("out must be a contiguous fp32 or bf16 tensor of rows * cols values on the records' device")
+        y, out_dtype = out.view(rows, cols), out.dtype
+    else:
+        y = torch.empty((rows, cols), dtype=out_dtype, device=buf.device)
     with _on(buf.device):
         st = _lib.load().axs6_unpack_sum(layout, buf.data_ptr(), nsrc, src_stride, y.data_ptr(), _DT[out_dtype], rows, cols,
                                          cols, block_size, grid, float(divisor), _stream(buf.device))

@@ -110,8 +110,14 @@ class CudaCodec:
         y = ops.unpack(ops.LAYOUT_WIRE, buf, 1, numel, self.block_size, ops.GRID_NF5, out_dt)
         return y.reshape(-1).to(dtype)
 
-    def unpack_mean(self, gathered: torch.Tensor, world: int, stride: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
-        """Mean of the ``world`` record buffers' reconstructions (buffer r at byte ``r * stride``), one fused pass."""
+    def unpack_mean(self, gathered: torch.Tensor, world: int, stride: int, numel: int, dtype: torch.dtype,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+        """Mean of the ``world`` record buffers' reconstructions (buffer r at byte ``r * stride``), one fused pass;
+        written into ``out`` (fp32 or bf16, contiguous, ``numel`` values) when given."""
+        if out is not None and out.dtype in (torch.float32, torch.bfloat16) and out.is_contiguous():
+            ops.unpack_sum(ops.LAYOUT_WIRE, gathered, world, stride, 1, numel, self.block_size, ops.GRID_NF5,
+                           divisor=float(world), out=out)
+            return out
         out_dt = dtype if dtype in (torch.float32, torch.bfloat16) else torch.float32
         y = ops.unpack_sum(ops.LAYOUT_WIRE, gathered, world, stride, 1, numel, self.block_size, ops.GRID_NF5, out_dt, float(world))
         return y.reshape(-1).to(dtype)
@@ -178,10 +184,12 @@ def _padded16(records: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def _mean_of_gathered(codec, gathered: torch.Tensor, world: int, stride: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
-    """Mean of the ranks' reconstructions, summed in fp32 in rank order: fused when the codec can."""
+def _mean_of_gathered(codec, gathered: torch.Tensor, world: int, stride: int, numel: int, dtype: torch.dtype,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+    """Mean of the ranks' reconstructions, summed in fp32 in rank order: fused when the codec can, and then
+    written straight into ``out`` (the gradient bucket itself) so that nothing is allocated after the gather."""
     if hasattr(codec, "unpack_mean"):
-        return codec.unpack_mean(gathered, world, stride, numel, dtype)
+        return codec.unpack_mean(gathered, world, stride, numel, dtype, out)
     acc = None
     for r in range(world):
         part = codec.unpack(gathered[r * stride:(r + 1) * stride], numel, torch.float32)
@@ -206,8 +214,11 @@ def axs6_gradient_hook_packed(state: Any, bucket) -> "torch.futures.Future[torch
     gathered = torch.empty(world * mine.numel(), dtype=mine.dtype, device=mine.device)
     fut = dist.all_gather_into_tensor(gathered, mine, group=group, async_op=True).get_future()
 
+    flat = grad.reshape(-1)
+
     def done(f):
-        return _mean_of_gathered(codec, gathered, world, mine.numel(), numel, dtype)
+        # the records were read before the gather; the bucket can take the result
+        return _mean_of_gathered(codec, gathered, world, mine.numel(), numel, dtype, out=flat).reshape(grad.shape)
 
     return fut.then(done)
 
