@@ -162,6 +162,98 @@ def unpack_sum(layout: int, buf: torch.Tensor, nsrc: int, src_stride: int, rows:
     return y
 
 
+# ---------------------------------------------------------------------------------- host buffers
+# Fake-quantise of a tensor that lives in pinned HOST memory: rows are cut into chunks (blocks never cross a
+# row) that flow through a ring of device buffers on three streams -- host->device copy, kernel, device->host
+# copy -- so that the two PCIe directions run at the same time and the kernel hides under the copies.
+_HOST_RING: dict = {}
+
+
+def _host_ring(dev: torch.device, in_dtype: torch.dtype, out_dtype: torch.dtype, chunk_elems: int, depth: int):
+    key = (dev.index, in_dtype, out_dtype, depth)
+    ring = _HOST_RING.get(key)
+    if ring is None or ring["elems"] < chunk_elems:
+        ring = {"elems": chunk_elems,
+                "x": [torch.empty(chunk_elems, dtype=in_dtype, device=dev) for _ in range(depth)],
+                "y": [torch.empty(chunk_elems, dtype=out_dtype, device=dev) for _ in range(depth)],
+                "s_in": torch.cuda.Stream(dev), "s_k": torch.cuda.Stream(dev), "s_out": torch.cuda.Stream(dev)}
+        _HOST_RING[key] = ring
+    return ring
+
+
+def fake_quantize_host(src: torch.Tensor, dst: torch.Tensor | None = None, block_size: int = 32, grid: int = GRID_NF5,
+                       rounding: str = "nearest", device=None, chunk_bytes: int = 32 << 20, depth: int = 3) -> torch.Tensor:
+    """``dst = fake_quantize(src)`` for PINNED host tensors (fp32 or bf16, same shape; ``dst`` is allocated pinned
+    when omitted), computed on the GPU in chunks of about ``chunk_bytes`` with the copies in both directions and
+    the kernel overlapped.  Returns ``dst`` after the last copy has been enqueued; the current stream of
+    ``device`` waits for it, so ``torch.cuda.current_stream().synchronize()`` (or any later work on that
+    stream) sees the finished result."""
+    if not isinstance(src, torch.Tensor) or src.is_cuda:
+        raise TypeError("fake_quantize_host expects a host tensor; use fake_quantize for device tensors")
+    if src.dtype not in _DT:
+        raise TypeError("fake_quantize_host takes fp32 or bf16 tensors")
+    if dst is None:
+        dst = torch.empty(src.shape, dtype=src.dtype, pin_memory=True)
+    if dst.is_cuda or dst.shape != src.shape or dst.dtype not in _DT:
+        raise ValueError("dst must be a host tensor of the same shape, fp32 or bf16")
+    if not (src.is_pinned() and dst.is_pinned() and src.is_contiguous() and dst.is_contiguous()):
+        raise ValueError("fake_quantize_host needs contiguous pinned host tensors (tensor.pin_memory())")
+    assert block_size in VALID_BLOCK_SIZES, f"block_size must be one of {VALID_BLOCK_SIZES}"
+    rnd = _rounding(rounding)
+    if src.dim() == 0:
+        raise ValueError("fake_quantize_host needs at least one dimension")
+    if src.numel() == 0:
+        return dst
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    cols = src.shape[-1]
+    rows = src.numel() // cols
+    s2, d2 = src.view(rows, cols), dst.view(rows, cols)
+    rows_per_chunk = max(1, min(rows, chunk_bytes // max(1, cols * src.element_size())))
+    ring = _host_ring(dev, src.dtype, dst.dtype, rows_per_chunk * cols, depth)
+    lib = _lib.load()
+    main = torch.cuda.current_stream(dev)
+    s_in, s_k, s_out = ring["s_in"], ring["s_k"], ring["s_out"]
+    start = torch.cuda.Event()
+    start.record(main)
+    for st in (s_in, s_k, s_out):
+        st.wait_event(start)                              # whatever produced src / last used the ring is done
+    x_free = [None] * depth                               # kernel that last read x[b]
+    y_free = [None] * depth                               # copy that last read y[b]
+    nblk = -(-cols // block_size)
+    with _on(dev):
+        for i, r0 in enumerate(range(0, rows, rows_per_chunk)):
+            b = i % depth
+            r1 = min(rows, r0 + rows_per_chunk)
+            n = (r1 - r0) * cols
+            xb, yb = ring["x"][b][:n], ring["y"][b][:n]
+            if x_free[b] is not None:
+                s_in.wait_event(x_free[b])
+            with torch.cuda.stream(s_in):
+                xb.copy_(s2[r0:r1].reshape(-1), non_blocking=True)
+                ev_in = torch.cuda.Event()
+                ev_in.record(s_in)
+            s_k.wait_event(ev_in)
+            if y_free[b] is not None:
+                s_k.wait_event(y_free[b])
+            seed, off = (0, 0)
+            if rnd == ROUND_STOCHASTIC:
+                seed, off = next_philox((r1 - r0) * nblk * block_size)
+            st_code = lib.axs6_fq(xb.data_ptr(), yb.data_ptr(), _DT[src.dtype], _DT[dst.dtype], r1 - r0, cols, cols, cols,
+                                  block_size, grid, rnd, 0, seed, off, s_k.cuda_stream)
+            _lib.check("axs6_fq", st_code)
+            ev_k = torch.cuda.Event()
+            ev_k.record(s_k)
+            x_free[b] = ev_k
+            s_out.wait_event(ev_k)
+            with torch.cuda.stream(s_out):
+                d2[r0:r1].reshape(-1).copy_(yb, non_blocking=True)
+                ev_out = torch.cuda.Event()
+                ev_out.record(s_out)
+            y_free[b] = ev_out
+    main.wait_stream(s_out)
+    return dst
+
+
 def record_bytes(layout: int, block_size: int) -> int:
     return int(_lib.load().axs6_record_bytes(layout, block_size))
 

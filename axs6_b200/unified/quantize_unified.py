@@ -40,6 +40,14 @@ def fused_fake_quantize(tensor: torch.Tensor, block_size: int = DEFAULT_BLOCK_SI
     return ops.fake_quantize(tensor, block_size, ops.GRID_NF5, rounding, who="fused_fake_quantize")
 
 
+def fused_fake_quantize_host(tensor: torch.Tensor, out: torch.Tensor | None = None, block_size: int = DEFAULT_BLOCK_SIZE,
+                             rounding: Literal["nearest", "stochastic"] = "nearest") -> torch.Tensor:
+    """:func:`fused_fake_quantize` for a tensor in pinned host memory: computed on the GPU with the host-to-device
+    copy, the kernel and the device-to-host copy pipelined over chunks of rows (``ops.fake_quantize_host``).  The
+    reference's call on a CPU tensor runs its eager CPU path; here the work still happens on the device."""
+    return ops.fake_quantize_host(tensor, out, block_size, ops.GRID_NF5, rounding)
+
+
 def quantize_unified(tensor: torch.Tensor, block_size: int = DEFAULT_BLOCK_SIZE,
                      rounding: Literal["nearest", "stochastic"] = "nearest") -> AXSTensor:
     """NF5 codes as an ``AXSTensor`` (reference: quantize_unified.py:211-282)."""

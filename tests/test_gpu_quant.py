@@ -546,3 +546,26 @@ def test_bf16_fake_quantise_kernels_agree_with_the_oracle(shape):
     finally:
         lib.axs6_tune(12, 0)
     assert lib.axs6_codec_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_host_buffer_fake_quantise_is_the_device_result(dtype):
+    """fused_fake_quantize_host: pinned host tensors through a ring of device buffers (more chunks than ring
+    slots, a ragged last chunk, a second call that reuses the ring) gives the bits of the device operator."""
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(1000, 416, generator=g) * torch.logspace(-3, 1, 1000).unsqueeze(1)).to(dtype)
+    hx = x.pin_memory()
+    want = qu.fused_fake_quantize(x.cuda(), 32).cpu()
+    got = ops.fake_quantize_host(hx, None, 32, chunk_bytes=64 * 416 * x.element_size(), depth=3)     # 16 chunks, last one short
+    torch.cuda.synchronize()
+    assert got.is_pinned() and got.dtype == dtype and got.shape == x.shape
+    assert torch.equal(got.view(torch.int32 if dtype == torch.float32 else torch.int16),
+                       want.view(torch.int32 if dtype == torch.float32 else torch.int16))
+    hy = torch.empty_like(hx).pin_memory()
+    out = qu.fused_fake_quantize_host(hx.view(10, 100, 416), hy.view(10, 100, 416), 32)
+    torch.cuda.current_stream().synchronize()
+    assert out.data_ptr() == hy.data_ptr() and torch.equal(hy.view(-1).view(torch.uint8), want.reshape(-1).view(torch.uint8))
+    with pytest.raises(ValueError):
+        ops.fake_quantize_host(x)                       # not pinned
+    with pytest.raises(TypeError):
+        ops.fake_quantize_host(x.cuda())
