@@ -569,3 +569,43 @@ def test_host_buffer_fake_quantise_is_the_device_result(dtype):
         ops.fake_quantize_host(x)                       # not pinned
     with pytest.raises(TypeError):
         ops.fake_quantize_host(x.cuda())
+
+
+def test_bf16_integer_paths_on_every_exponent_and_mantissa():
+    """The TMA-fed bf16 kernels replace the fp32 formulas by integer arithmetic on the bit patterns.  Sweep:
+    block maxima with every exponent field 1..253 (maxima of 2^127 and above make the scale overflow: outside the
+    contract) and four mantissas; under each maximum, values with every
+    mantissa at 14 exponent distances, both signs, plus +-0 and bf16 denormals.  Fake-quantise output and packed
+    records must equal the oracle's bit for bit."""
+    mant = np.arange(128, dtype=np.uint32)
+    blocks = []
+    for E in range(1, 254):
+        for ma in (0, 1, 63, 127):
+            amax = (E << 7) | ma
+            vals = [np.array([0x0000, 0x8000, 0x0001, 0x8001, 0x007F, 0x807F], dtype=np.uint32)]
+            for j in range(14):
+                e = E - j
+                if e < 1:
+                    break
+                v = (e << 7) | mant
+                v = v[v <= amax]
+                vals.append(v)
+                vals.append(v | 0x8000)
+            v = np.concatenate(vals)
+            pad = (-len(v)) % 31
+            v = np.concatenate([v, np.zeros(pad, dtype=np.uint32)]).reshape(-1, 31)
+            sign = 0x8000 if (E + ma) % 2 else 0
+            blk = np.concatenate([np.full((v.shape[0], 1), amax | sign, dtype=np.uint32), v], axis=1)
+            blocks.append(blk)
+    x = np.concatenate(blocks).astype(np.uint16)                          # (nblocks, 32)
+    assert x.shape[0] > 100000
+    xt = to_cuda(x)
+    fq = qu.fused_fake_quantize(xt, 32)
+    assert_bits_equal(fq, oracle.fused_fake_quantize(x, 32), "fake-quantise bf16, all exponents")
+    se, sg, mg = oracle.quantize(x, 32, oracle.GRID_NF5)
+    for layout in (ops.LAYOUT_WIRE, ops.LAYOUT_SPEC):
+        rec = ops.pack(xt, 32, ops.GRID_NF5, "nearest", layout)
+        assert_bits_equal(rec, oracle.pack_bytes(se, sg, mg, layout), f"pack bf16 layout {layout}, all exponents")
+        back = ops.unpack(layout, rec, x.shape[0], 32, 32, ops.GRID_NF5, torch.bfloat16)
+        assert_bits_equal(back, oracle.f32_to_bf16(oracle.dequantize(se, sg, mg, 32, oracle.GRID_NF5)), "unpack to bf16")
+    assert _lib.load().axs6_codec_status() == 0
