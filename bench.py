@@ -250,22 +250,25 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
 
     extra = {}
     cpu = None
+    sections = {t for t in args.sections.split(",") if t}
     if rank == 0:
-        extra["codec"] = bench_codec(torch, lib, udist, dev, pk)
-        extra["fq_sweep"] = bench_sweep(torch, lib, dev, pk, x)
+        if "codec" in sections:
+            extra["codec"] = bench_codec(torch, lib, udist, dev, pk)
+        if "fq_sweep" in sections:
+            extra["fq_sweep"] = bench_sweep(torch, lib, dev, pk, x)
         if world == 1:
             cpu = cpu_baseline(x)
     del x, y
     torch.cuda.empty_cache()
     try:
-        extra_linear = bench_linear(args, rank, world, dev, pk)
+        extra_linear = bench_linear(args, rank, world, dev, pk) if "linear" in sections else None
         if extra_linear is not None and rank == 0:
             extra["linear"] = extra_linear
     except Exception as e:          # the linear metric is reported separately; never hide the headline
         if rank == 0:
             extra["linear"] = {"error": repr(e)}
 
-    if world > 1:
+    if world > 1 and "grad_exchange" in sections:
         try:
             from axs6_b200 import exchange_bench
             ex = exchange_bench.run(rank, world, dev)
@@ -275,14 +278,15 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             if rank == 0:
                 extra["grad_exchange"] = {"error": repr(e)}
 
-    try:
-        from axs6_b200 import minigpt_bench
-        mg = minigpt_bench.run(args, rank, world, dev)
-        if rank == 0:
-            extra["minigpt"] = mg
-    except Exception as e:
-        if rank == 0:
-            extra["minigpt"] = {"error": repr(e)}
+    if "minigpt" in sections:
+        try:
+            from axs6_b200 import minigpt_bench
+            mg = minigpt_bench.run(args, rank, world, dev)
+            if rank == 0:
+                extra["minigpt"] = mg
+        except Exception as e:
+            if rank == 0:
+                extra["minigpt"] = {"error": repr(e)}
 
     if rank == 0:
         line = {
@@ -444,6 +448,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--sections", default="codec,fq_sweep,linear,grad_exchange,minigpt",
+                    help="extra sections of the JSON line to measure after the headline (comma list; empty = none)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
