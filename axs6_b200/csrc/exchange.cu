@@ -44,8 +44,8 @@ __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %
 
 // One record (seven words starting at the word that holds its first byte, `sft` = 8 * (byte offset in
 // that word + header bytes)) added to, or for the first source stored into, the 32 accumulators.
-template <int HDR>
-__device__ __forceinline__ void accumulate_record(const uint32_t (&W)[7], uint32_t head, uint32_t sft, bool first,
+template <int HDR, bool kFirst>
+__device__ __forceinline__ void accumulate_record(const uint32_t (&W)[7], uint32_t head, uint32_t sft,
                                                   const uint32_t *table, const float *lev, float (&acc)[32])
 {
     uint32_t pay[6];
@@ -62,7 +62,7 @@ __device__ __forceinline__ void accumulate_record(const uint32_t (&W)[7], uint32
             else if (off <= 26) v = pay[word] >> (off - 2);
             else v = __funnelshift_r(pay[word], pay[word + 1], off - 2);
             const float val = __uint_as_float(*reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(table) + (v & 0xFCu)) + kk);
-            acc[i] = first ? val : AXS6_ADD(acc[i], val);
+            acc[i] = kFirst ? val : AXS6_ADD(acc[i], val);
         }
     } else {
         const float scale = axs6_scale_decode(se);
@@ -71,7 +71,7 @@ __device__ __forceinline__ void accumulate_record(const uint32_t (&W)[7], uint32
             const int bit = 6 * i, word = bit >> 5, off = bit & 31;
             const uint32_t code = (off <= 26 ? (pay[word] >> off) : __funnelshift_r(pay[word], pay[word + 1], off)) & 63u;
             const float val = axs6_decode_value(code >> 5, lev[code & 31u], scale);
-            acc[i] = first ? val : AXS6_ADD(acc[i], val);
+            acc[i] = kFirst ? val : AXS6_ADD(acc[i], val);
         }
     }
 }
@@ -171,7 +171,10 @@ __global__ void __launch_bounds__(kThreadsX) unpack_sum_bulk_kernel(const __grid
                 sft_r = 8u * HDR;
                 head_shift = 0u;
             }
-            if (ok && b < nblocks) accumulate_record<HDR>(W, W[0] >> head_shift, sft_r, r == 0, table, lev, acc);
+            if (ok && b < nblocks) {
+                if (r == 0) accumulate_record<HDR, true>(W, W[0] >> head_shift, sft_r, table, lev, acc);
+                else        accumulate_record<HDR, false>(W, W[0] >> head_shift, sft_r, table, lev, acc);
+            }
         }
         if (ok && b < nblocks) {
             uint32_t o[kBf16 ? 16 : 32];

@@ -1,6 +1,6 @@
 """Runs ONE kernel of the library a few times on a small, larger-than-L2 case, for profilers.
 
-    python -m axs6_b200.profile_case {fq_f32|fq_bf16|fq_bf16_stochastic|pack_wire|pack_wire_f32|unpack_wire|unpack_wire_bf16|gemm_fwd|gemm_dx|gemm_dw} [launches]
+    python -m axs6_b200.profile_case {fq_f32|fq_bf16|fq_bf16_stochastic|pack_wire|pack_wire_f32|unpack_wire|unpack_wire_bf16|unpack_sum4|gemm_fwd|gemm_dx|gemm_dw} [launches]
 
 Device footprint stays under 1 GB so that a multi-pass capture finishes quickly.
 """
@@ -43,6 +43,16 @@ def main() -> None:
         assert lib.axs6_pack(x.data_ptr(), 1, rows, cols, cols, 32, 1, 0, 0, 0, 0, None, 1, w.data_ptr(), None, None, st) == 0
         y = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev)
         run = lambda: lib.axs6_unpack(1, w.data_ptr(), None, None, y.data_ptr(), 1, rows, cols, cols, 32, 1, st)
+    elif what == "unpack_sum4":
+        from . import ops
+        per = rows * cols // 32 * 25
+        w = torch.empty(4 * per, dtype=torch.uint8, device=dev)
+        for s_ in range(4):
+            xs = torch.randn(rows, cols, generator=g, device=dev)
+            w[s_ * per:(s_ + 1) * per] = ops.pack(xs, 32, 1, "nearest", 1)
+            del xs
+        y = torch.empty(rows, cols, device=dev)
+        run = lambda: lib.axs6_unpack_sum(1, w.data_ptr(), 4, per, y.data_ptr(), 0, rows, cols, cols, 32, 1, 4.0, st)
     elif what == "unpack_wire":
         x = torch.randn(rows, cols, generator=g, device=dev).to(torch.bfloat16)
         w = torch.empty(rows * cols // 32 * 25, dtype=torch.uint8, device=dev)
