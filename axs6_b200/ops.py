@@ -216,7 +216,10 @@ def fake_quantize_host(src: torch.Tensor, dst: torch.Tensor | None = None, block
     start = torch.cuda.Event()
     start.record(main)
     for st in (s_in, s_k, s_out):
-        st.wait_event(start)                              # whatever produced src / last used the ring is done
+        st.wait_event(start)                              # whatever produced src on the caller's stream is done
+    s_in.wait_stream(s_k)                                 # and so is an earlier call that used the ring from
+    s_in.wait_stream(s_out)                               # another stream of the caller
+    s_k.wait_stream(s_out)
     x_free = [None] * depth                               # kernel that last read x[b]
     y_free = [None] * depth                               # copy that last read y[b]
     nblk = -(-cols // block_size)

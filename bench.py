@@ -351,7 +351,9 @@ def bench_codec(torch, lib, udist, dev, pk) -> dict:
         xb = x.to(torch.bfloat16)
         wire = torch.empty(rows * (cols // 32) * 25, dtype=torch.uint8, device=dev)
         out = torch.empty(rows, cols, dtype=torch.float32, device=dev)
-        pool.append((xb, wire, out, x))
+        planes = (torch.empty(rows * cols // 32, dtype=torch.uint8, device=dev), torch.empty(rows * cols, dtype=torch.uint8, device=dev),
+                  torch.empty(rows * cols, dtype=torch.uint8, device=dev)) if i < 2 else None
+        pool.append((xb, wire, out, x, planes))
     stream = torch.cuda.current_stream().cuda_stream
 
     def pack(i):
@@ -359,8 +361,17 @@ def bench_codec(torch, lib, udist, dev, pk) -> dict:
         assert lib.axs6_pack(xb.data_ptr(), 1, rows, cols, cols, 32, 1, 0, 0, 0, 0, None, 1, wire.data_ptr(), None, None, stream) == 0
 
     def pack_f32(i):
-        _, wire, _, x = pool[i % 4]
+        _, wire, _, x = pool[i % 4][:4]
         assert lib.axs6_pack(x.data_ptr(), 0, rows, cols, cols, 32, 1, 0, 0, 0, 0, None, 1, wire.data_ptr(), None, None, stream) == 0
+
+    def pack_planes(i):
+        x, pl = pool[i % 2][3], pool[i % 2][4]
+        assert lib.axs6_pack(x.data_ptr(), 0, rows, cols, cols, 32, 1, 0, 0, 0, 0, None, 0, pl[0].data_ptr(), pl[1].data_ptr(),
+                             pl[2].data_ptr(), stream) == 0
+
+    def unpack_planes(i):
+        out, pl = pool[i % 2][2], pool[i % 2][4]
+        assert lib.axs6_unpack(0, pl[0].data_ptr(), pl[1].data_ptr(), pl[2].data_ptr(), out.data_ptr(), 0, rows, cols, cols, 32, 1, stream) == 0
 
     def unpack(i):
         _, wire, out = pool[i % 4][:3]
@@ -375,7 +386,9 @@ def bench_codec(torch, lib, udist, dev, pk) -> dict:
     n = 40
     rec = rows * cols // 32 * 25
     for name, fn, nbytes in (("pack_f32", pack_f32, rows * cols * 4 + rec), ("pack", pack, rows * cols * 2 + rec),
-                             ("unpack", unpack, rows * cols * 4 + rec), ("unpack_bf16", unpack_bf16, rows * cols * 2 + rec)):
+                             ("unpack", unpack, rows * cols * 4 + rec), ("unpack_bf16", unpack_bf16, rows * cols * 2 + rec),
+                             ("pack_planes", pack_planes, rows * cols * 6 + rows * cols // 32),
+                             ("unpack_planes", unpack_planes, rows * cols * 6 + rows * cols // 32)):
         for i in range(8):
             fn(i)
         torch.cuda.synchronize()
@@ -390,7 +403,8 @@ def bench_codec(torch, lib, udist, dev, pk) -> dict:
     res["roundtrip_bf16_GBps"] = 2 * (rows * cols * 2 + rec) / ((res["pack"]["ms"] + res["unpack_bf16"]["ms"]) * 1e-3) / 1e9
     res["stream_status"] = int(lib.axs6_codec_status())
     res["workload"] = ("8192x4096, block 32, 25-byte wire records: pack = bf16 -> records, pack_f32 = fp32 -> records, unpack = records "
-                       "-> fp32, unpack_bf16 = records -> bf16 (4 rotating buffer sets, 4 x 355 MiB > L2)")
+                       "-> fp32, unpack_bf16 = records -> bf16 (4 rotating buffer sets, 4 x 355 MiB > L2); pack_planes / unpack_planes = fp32 <-> "
+                       "AXSTensor planes (exponent, sign and magnitude bytes: quantize_unified / dequantize_unified), 2 buffer sets")
     return res
 
 
