@@ -242,7 +242,8 @@ ChunkGeom make_geom(int64_t rows, int64_t cols, int block)
 }
 
 // ------------------------------------------------------------------------------------------ bf16 -> bf16, TMA-fed
-// bf16 in, bf16 out, NF5 grid, nearest rounding, block 32, contiguous and 16-byte aligned: one thread per
+// bf16 in, bf16 out, NF5 grid, block 32, contiguous and 16-byte aligned, nearest rounding or stochastic
+// rounding with the library's own draws (the noise-supplied form stays with the general kernel): one thread per
 // block, tiles of 256 blocks moved by the TMA unit in both directions and quantised IN PLACE in shared
 // memory (a 3-slot ring: one slot being loaded, one computed, one stored).  The arithmetic is integer
 // arithmetic on the bf16 bit patterns.  With E the exponent field of the block maximum the scale is
@@ -279,11 +280,39 @@ __device__ __forceinline__ uint32_t min_u16x2(uint32_t a, uint32_t b)
     return r;
 }
 
+// The ten round keys of Philox4x32-10 for one seed, computed on the host and passed by value: in the kernel
+// they are constant-bank operands of the xors instead of twenty additions per block of draws.
+struct PhiloxKeys { uint32_t k0[10], k1[10]; };
+
+__device__ __forceinline__ Axs6Philox philox_with_keys(uint64_t counter, const PhiloxKeys &ks)
+{
+    uint32_t c0 = (uint32_t)counter, c1 = (uint32_t)(counter >> 32), c2 = 0u, c3 = 0u;
+#pragma unroll
+    for (int i = 0; i < 10; ++i) {
+        const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
+        const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
+        const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ ks.k0[i];
+        const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ ks.k1[i];
+        c1 = (uint32_t)p1; c3 = (uint32_t)p0; c0 = n0; c2 = n2;
+    }
+    Axs6Philox o;
+    o.r[0] = c0; o.r[1] = c1; o.r[2] = c2; o.r[3] = c3;
+    return o;
+}
+
+// ROUND = kNearest: the integer path described above.  ROUND = kPhilox (stochastic rounding with the
+// library's own draws): the arithmetic of fq_vec_kernel, value by value -- same Philox block per 8 values,
+// same fused multiply-add for the dithered index, same products -- so both kernels give the same bits.
+template <int ROUND>
 __global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __grid_constant__ CUtensorMap xmap,
-                                                                       const __grid_constant__ CUtensorMap ymap, int64_t nblocks)
+                                                                       const __grid_constant__ CUtensorMap ymap, int64_t nblocks,
+                                                                       uint64_t seed, uint64_t offset0,
+                                                                       const unsigned long long *epoch,
+                                                                       const __grid_constant__ PhiloxKeys keys)
 {
     extern __shared__ uint8_t raw[];
-    __shared__ __align__(16) uint16_t table[kKeyLim + 8];      // key -> level bits (bf16), exponent field - 120
+    __shared__ __align__(16) uint16_t table[ROUND == kNearest ? kKeyLim + 8 : 8];   // key -> level bits (bf16), exponent field - 120
+    __shared__ __align__(16) uint16_t lvl[ROUND == kNearest ? 8 : 1024];   // LUT index -> the same
     uint8_t *base = raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u);
     uint8_t *slot0 = base + 1024;
     const uint32_t bar0 = smem_u32(base);
@@ -300,15 +329,21 @@ __global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __
                         (int)(((int64_t)blockIdx.x + k * (int64_t)gridDim.x) * kBlocksB));
         }
     }
-    for (int key = tid; key <= kKeyLim; key += kBlocksB) {
-        uint32_t code = 0;
-        if (key < kKeyLim) {
-            const int j = key >> 7, m = 127 - (key & 127);
-            code = g_reverse[((128 + m) * 1023) >> (8 + j)];
+    if (ROUND == kNearest) {
+        for (int key = tid; key <= kKeyLim; key += kBlocksB) {
+            uint32_t code = 0;
+            if (key < kKeyLim) {
+                const int j = key >> 7, m = 127 - (key & 127);
+                code = g_reverse[((128 + m) * 1023) >> (8 + j)];
+            }
+            table[key] = (uint16_t)(axs6_f32_to_bf16_bits(__uint_as_float(g_codebook_bits[code])) - (120u << 7));
         }
-        table[key] = (uint16_t)(axs6_f32_to_bf16_bits(__uint_as_float(g_codebook_bits[code])) - (120u << 7));
+    } else {
+        for (int i = tid; i < 1024; i += kBlocksB)
+            lvl[i] = (uint16_t)(axs6_f32_to_bf16_bits(__uint_as_float(g_codebook_bits[g_reverse[i]])) - (120u << 7));
     }
     __syncthreads();
+    const uint64_t offset = ROUND == kPhilox ? offset0 + *epoch : 0ull;
 
     uint32_t piece[4];
 #pragma unroll
@@ -333,7 +368,58 @@ __global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __
             for (int i = 0; i < 16; ++i) mx = max_u16x2(mx, w[i] & 0x7FFF7FFFu);
             const uint32_t amax16 = max(mx & 0xFFFFu, mx >> 16);
             const uint32_t ef = amax16 >> 7;
-            if (amax16 == 0u || (ef >= 11u && ef <= 252u)) {
+            if (ROUND == kPhilox && amax16 != 0u && ef >= 11u && ef <= 252u) {
+                // the dithered index exactly as fq_vec_kernel forms it, trunc(fma(|x|, 1023 / S, u - 0.5)) with
+                // u - 0.5 = fma(h, 2^-16, 2^-17 - 0.5) (exact); the value through the bf16 level table
+                const float c = AXS6_MUL(__uint_as_float((253u - ef) << 23), 1023.0f);
+                const uint32_t kk = (ef - 6u) * 0x00800080u;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {                      // chunks of 8 values: one Philox block each
+                    const Axs6Philox rnd = philox_with_keys(offset + (uint64_t)(b * 4 + q), keys);
+#pragma unroll
+                    for (int pi = 0; pi < 4; ++pi) {
+                        const uint32_t wi = w[4 * q + pi];
+                        const float d0 = __fmaf_rn((float)(rnd.r[pi] & 0xFFFFu), 1.52587890625e-5f, -0.49999237060546875f);
+                        const float d1 = __fmaf_rn((float)(rnd.r[pi] >> 16), 1.52587890625e-5f, -0.49999237060546875f);
+                        const int i0 = __float2int_rz(__fmaf_rn(fabsf(__uint_as_float(wi << 16)), c, d0));
+                        const int i1 = __float2int_rz(__fmaf_rn(fabsf(__uint_as_float(wi & 0xFFFF0000u)), c, d1));
+                        const uint32_t val = ((uint32_t)lvl[i1] * 65536u + (uint32_t)lvl[i0]) + kk;
+                        const uint32_t t = (wi & 0x7FFF7FFFu) + 0x7FFF7FFFu;
+                        uint32_t nz;
+                        asm("prmt.b32 %0, %1, %1, %2;" : "=r"(nz) : "r"(t), "r"(0xBB99u));
+                        w[4 * q + pi] = (val | (wi & 0x80008000u)) & nz;
+                    }
+                }
+            } else if (ROUND == kPhilox && amax16 != 0u) {
+                // rare block: the fp32 formulas of the general kernel
+                const Axs6Scale sc = axs6_scale_fq(amax16 << 16);
+                const float c = AXS6_MUL(sc.inv, 1023.0f);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float u[8];
+                    chunk_uniforms<kPhilox>(u, b * 4 + q, true, seed, offset, nullptr);
+#pragma unroll
+                    for (int pi = 0; pi < 4; ++pi) {
+                        uint32_t o = 0;
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const uint32_t wi = w[4 * q + pi];
+                            const uint32_t bits = h ? (wi & 0xFFFF0000u) : (wi << 16);
+                            const float x = __uint_as_float(bits);
+                            float y;
+                            if (sc.fast) {
+                                const float level = __uint_as_float(g_codebook_bits[g_reverse[axs6_nf5_index_dithered_fast(fabsf(x), c, u[2 * pi + h])]]);
+                                y = axs6_fq_value_fast(x, level, sc.scale);
+                            } else {
+                                const float n = axs6_normalise(__uint_as_float(bits & 0x7FFFFFFFu), sc);
+                                y = axs6_fq_value(bits, __uint_as_float(g_codebook_bits[g_reverse[axs6_nf5_index_dithered(n, u[2 * pi + h])]]), sc.scale);
+                            }
+                            o |= (uint32_t)axs6_f32_to_bf16_bits(y) << (16 * h);
+                        }
+                        w[4 * q + pi] = o;
+                    }
+                }
+            } else if (amax16 == 0u || (ef >= 11u && ef <= 252u)) {
                 const uint32_t a1 = amax16 ? ((ef << 7) | 127u) : 0x7FFFu;
                 const uint32_t a2 = a1 | (a1 << 16);
                 const uint32_t lim2 = (uint32_t)kKeyLim | ((uint32_t)kKeyLim << 16);
@@ -393,7 +479,8 @@ __global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __
 }
 
 // -> status, or 1 when this path does not apply
-static int launch(const void *x, void *y, int64_t nblocks, cudaStream_t st)
+static int launch(const void *x, void *y, int64_t nblocks, int round, uint64_t seed, uint64_t offset,
+                  const unsigned long long *epoch, cudaStream_t st)
 {
     if (nblocks >= (1ll << 31) - kBlocksB) return 1;
     EncodeTiledFn enc = encode_fn();
@@ -419,11 +506,18 @@ static int launch(const void *x, void *y, int64_t nblocks, cudaStream_t st)
     int dev_id = 0;
     if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= 64) return 1;
     if (!attr_done[dev_id]) {
-        if (cudaFuncSetAttribute(fq_bf16_nf5_b32_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+        if (cudaFuncSetAttribute(fq_bf16_nf5_b32_bulk_kernel<kNearest>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
+            cudaFuncSetAttribute(fq_bf16_nf5_b32_bulk_kernel<kPhilox>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
             return AXS6_ERR_LAUNCH;
         attr_done[dev_id] = true;
     }
-    fq_bf16_nf5_b32_bulk_kernel<<<(unsigned)ctas, kBlocksB, kSmemBytes, st>>>(xm, ym, nblocks);
+    PhiloxKeys keys;
+    for (int i = 0; i < 10; ++i) {
+        keys.k0[i] = (uint32_t)seed + (uint32_t)i * 0x9E3779B9u;
+        keys.k1[i] = (uint32_t)(seed >> 32) + (uint32_t)i * 0xBB67AE85u;
+    }
+    if (round == kNearest) fq_bf16_nf5_b32_bulk_kernel<kNearest><<<(unsigned)ctas, kBlocksB, kSmemBytes, st>>>(xm, ym, nblocks, 0, 0, nullptr, keys);
+    else                   fq_bf16_nf5_b32_bulk_kernel<kPhilox><<<(unsigned)ctas, kBlocksB, kSmemBytes, st>>>(xm, ym, nblocks, seed, offset, epoch, keys);
     count_launch();
     return check_launch();
 }
@@ -465,9 +559,9 @@ static int fq_entry(const void *x, void *y, int in_dtype, int out_dtype, int64_t
     const bool vec = aligned16(x) && aligned16(y) && (cols % kChunk == 0) && (ldx % kChunk == 0) &&
                      (ldy % kChunk == 0) && (round != kNoise || aligned16(noise));
     // tune key 12: 1 = general kernel only
-    if (vec && a.g.flat && in_dtype == AXS6_BF16 && out_dtype == AXS6_BF16 && grid == AXS6_GRID_NF5 && round == kNearest &&
-        block == 32 && tune_value(12) != 1) {
-        const int r = fqb::launch(x, y, rows * (cols / 32), stream);
+    if (vec && a.g.flat && in_dtype == AXS6_BF16 && out_dtype == AXS6_BF16 && grid == AXS6_GRID_NF5 &&
+        (round == kNearest || round == kPhilox) && block == 32 && tune_value(12) != 1) {
+        const int r = fqb::launch(x, y, rows * (cols / 32), round, seed, offset, a.epoch, stream);
         if (r != 1) return r;
     }
     if (in_dtype == AXS6_F32 && out_dtype == AXS6_F32) return dispatch_fq<float, float>(a, grid, round, vec, stream);

@@ -609,3 +609,35 @@ def test_bf16_integer_paths_on_every_exponent_and_mantissa():
         back = ops.unpack(layout, rec, x.shape[0], 32, 32, ops.GRID_NF5, torch.bfloat16)
         assert_bits_equal(back, oracle.f32_to_bf16(oracle.dequantize(se, sg, mg, 32, oracle.GRID_NF5)), "unpack to bf16")
     assert _lib.load().axs6_codec_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(255, 32), (257, 32), (3, 96), (777, 1056), (2048, 4096)])
+def test_stochastic_bf16_kernels_give_the_same_bits(shape):
+    """Stochastic rounding with the library's draws, bf16 -> bf16: the TMA-fed kernel (default) forms the
+    dithered index and the value exactly as the general kernel (tune key 12 = 1) does, so for one seed and
+    offset both give the same bits -- including +-0 values, all-zero blocks and blocks outside the fast range."""
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(shape[0] + shape[1])
+    x = torch.randn(*shape, generator=g)
+    x[torch.rand(*shape, generator=g) < 0.02] = 0.0
+    x[torch.rand(*shape, generator=g) < 0.02] = -0.0
+    if shape[0] > 2:
+        x[1] *= 1e-38
+        x[2] *= 3e37
+        x[0, :32] = 0.0
+    xt = x.to(torch.bfloat16).cuda()
+    outs = []
+    try:
+        for mode in (0, 1):
+            lib.axs6_tune(12, mode)
+            torch.manual_seed(5)
+            ops.reset_philox(1000)
+            outs.append(qu.fused_fake_quantize(xt, 32, "stochastic"))
+    finally:
+        lib.axs6_tune(12, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    nearest = qu.fused_fake_quantize(xt, 32)
+    frac = float((outs[0] != nearest).float().mean())
+    assert 0.0 < frac < 0.05                              # the dither moves about 1 % of the values
+    assert lib.axs6_codec_status() == 0
