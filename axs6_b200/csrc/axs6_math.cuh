@@ -306,5 +306,37 @@ AXS6_HD Axs6Philox axs6_philox(uint64_t counter, uint64_t key)
     return o;
 }
 
+// The ten round keys for one 64-bit key, and the same generator taking them ready-made: kernels receive the
+// struct by value, so the keys are constant-bank operands of the xors instead of twenty additions per block.
+struct Axs6PhiloxKeys { uint32_t k0[10], k1[10]; };
+
+AXS6_HD Axs6PhiloxKeys axs6_philox_keys(uint64_t key)
+{
+    Axs6PhiloxKeys ks;
+    for (int i = 0; i < 10; ++i) {
+        ks.k0[i] = (uint32_t)key + (uint32_t)i * 0x9E3779B9u;
+        ks.k1[i] = (uint32_t)(key >> 32) + (uint32_t)i * 0xBB67AE85u;
+    }
+    return ks;
+}
+
+AXS6_HD Axs6Philox axs6_philox_keyed(uint64_t counter, const Axs6PhiloxKeys &ks)
+{
+    uint32_t c0 = (uint32_t)counter, c1 = (uint32_t)(counter >> 32), c2 = 0u, c3 = 0u;
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+    for (int i = 0; i < 10; ++i) {
+        const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
+        const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
+        const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ ks.k0[i];
+        const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ ks.k1[i];
+        c1 = (uint32_t)p1; c3 = (uint32_t)p0; c0 = n0; c2 = n2;
+    }
+    Axs6Philox o;
+    o.r[0] = c0; o.r[1] = c1; o.r[2] = c2; o.r[3] = c3;
+    return o;
+}
+
 // 16 random bits -> the midpoints (h + 0.5) / 65536 of a 2^-16 grid on (0, 1): mean exactly 1/2.
 AXS6_HD float axs6_u01_16(uint32_t h) { return ((float)h + 0.5f) * 1.52587890625e-5f; }

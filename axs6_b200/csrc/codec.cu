@@ -21,6 +21,7 @@ struct CodecArgs {
     ChunkGeom g;
     uint32_t via_bf16;
     uint64_t seed, offset;
+    Axs6PhiloxKeys keys;               // round keys of `seed`
     const unsigned long long *epoch;   // device counter added to `offset` (stochastic kernels only)
     const float *noise;
     uint8_t *p0, *p1, *p2;   // planes (exp, sign, mag) or p0 = records
@@ -118,7 +119,7 @@ __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
             float u[8];
             uint32_t code[8];
             int se;
-            chunk_uniforms<ROUND>(u, c, act[k], a.seed, offset, a.noise);
+            chunk_uniforms<ROUND>(u, c, act[k], a.keys, offset, a.noise);
             chunk_codes<GRID, ROUND>(v[k], code, se, rev, lanes, u);
             if (LAYOUT == kPlanes) {
                 if (act[k]) {
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(kThreads) pack_generic_kernel(const CodecArgs 
         const uint32_t amax = group_max(ab, B);
         const Axs6Scale s = axs6_scale_codes(amax);
         const float n = axs6_normalise(__uint_as_float(ab), s);
-        const float u = element_uniform<ROUND>(row * padded + pc, in_pad, a.seed, offset, a.noise);
+        const float u = element_uniform<ROUND>(row * padded + pc, in_pad, a.keys, offset, a.noise);
         int m;
         if (GRID == AXS6_GRID_NF5) {
             const int idx = (ROUND == kNearest) ? axs6_nf5_index(n)
@@ -1226,6 +1227,7 @@ AXS6_API int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, 
     a.g.flat = (cols % block == 0 && ldx == cols) ? 1 : 0;
     a.via_bf16 = (flags & AXS6_FLAG_INPUT_VIA_BF16) ? 1u : 0u;
     a.seed = seed; a.offset = offset; a.noise = noise;
+    a.keys = axs6_philox_keys(seed);
     a.epoch = philox_epoch_ptr();
     if (round == kPhilox && !a.epoch) return AXS6_ERR_DEVICE;
     a.p0 = static_cast<uint8_t *>(out0); a.p1 = static_cast<uint8_t *>(out1); a.p2 = static_cast<uint8_t *>(out2);
@@ -1271,6 +1273,7 @@ AXS6_API int axs6_unpack(int layout, const void *in0, const void *in1, const voi
     a.g = make_geom(rows, cols, block);
     a.g.flat = (cols % block == 0 && ldy == cols) ? 1 : 0;
     a.via_bf16 = 0; a.seed = 0; a.offset = 0; a.noise = nullptr; a.epoch = nullptr;
+    a.keys = axs6_philox_keys(0);
     a.p0 = const_cast<uint8_t *>(static_cast<const uint8_t *>(in0));
     a.p1 = const_cast<uint8_t *>(static_cast<const uint8_t *>(in1));
     a.p2 = const_cast<uint8_t *>(static_cast<const uint8_t *>(in2));

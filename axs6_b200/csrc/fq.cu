@@ -22,6 +22,7 @@ struct FqArgs {
     uint32_t via_bf16;
     uint32_t out_tf32;       // round fp32 results to the nearest TF32 value
     uint64_t seed, offset;
+    Axs6PhiloxKeys keys;               // round keys of `seed`
     const unsigned long long *epoch;   // device counter added to `offset` (stochastic kernels only)
     const float *noise;
 };
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(kThreads) fq_vec_kernel(const FqArgs a)
 #pragma unroll
         for (int k = 0; k < U; ++k) {
             float u[8], y[8];
-            chunk_uniforms<ROUND>(u, cidx[k], act[k], a.seed, offset, a.noise);
+            chunk_uniforms<ROUND>(u, cidx[k], act[k], a.keys, offset, a.noise);
             fq_chunk<GRID, ROUND>(v[k], y, tab, lanes, u);
             if (sizeof(Tout) == 4 && a.out_tf32) {
 #pragma unroll
@@ -154,7 +155,7 @@ __global__ void __launch_bounds__(kThreads) fq_generic_kernel(const FqArgs a)
         const uint32_t v = act ? ChunkIO<Tin>::load1(a.x, row * a.ldx + pc, a.via_bf16 != 0u) : 0u;
         const uint32_t ab = v & 0x7FFFFFFFu;
         const uint32_t amax = group_max(ab, a.g.block);
-        const float u = element_uniform<ROUND>(row * padded + pc, act, a.seed, offset, a.noise);
+        const float u = element_uniform<ROUND>(row * padded + pc, act, a.keys, offset, a.noise);
         float y;
         if (GRID == AXS6_GRID_NF5) {
             const Axs6Scale s = axs6_scale_fq(amax);
@@ -280,35 +281,15 @@ __device__ __forceinline__ uint32_t min_u16x2(uint32_t a, uint32_t b)
     return r;
 }
 
-// The ten round keys of Philox4x32-10 for one seed, computed on the host and passed by value: in the kernel
-// they are constant-bank operands of the xors instead of twenty additions per block of draws.
-struct PhiloxKeys { uint32_t k0[10], k1[10]; };
-
-__device__ __forceinline__ Axs6Philox philox_with_keys(uint64_t counter, const PhiloxKeys &ks)
-{
-    uint32_t c0 = (uint32_t)counter, c1 = (uint32_t)(counter >> 32), c2 = 0u, c3 = 0u;
-#pragma unroll
-    for (int i = 0; i < 10; ++i) {
-        const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
-        const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
-        const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ ks.k0[i];
-        const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ ks.k1[i];
-        c1 = (uint32_t)p1; c3 = (uint32_t)p0; c0 = n0; c2 = n2;
-    }
-    Axs6Philox o;
-    o.r[0] = c0; o.r[1] = c1; o.r[2] = c2; o.r[3] = c3;
-    return o;
-}
-
 // ROUND = kNearest: the integer path described above.  ROUND = kPhilox (stochastic rounding with the
-// library's own draws): the arithmetic of fq_vec_kernel, value by value -- same Philox block per 8 values,
+// library's own draws; the round keys arrive as a kernel constant): the arithmetic of fq_vec_kernel, value by value -- same Philox block per 8 values,
 // same fused multiply-add for the dithered index, same products -- so both kernels give the same bits.
 template <int ROUND>
 __global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __grid_constant__ CUtensorMap xmap,
                                                                        const __grid_constant__ CUtensorMap ymap, int64_t nblocks,
                                                                        uint64_t seed, uint64_t offset0,
                                                                        const unsigned long long *epoch,
-                                                                       const __grid_constant__ PhiloxKeys keys)
+                                                                       const __grid_constant__ Axs6PhiloxKeys keys)
 {
     extern __shared__ uint8_t raw[];
     __shared__ __align__(16) uint16_t table[ROUND == kNearest ? kKeyLim + 8 : 8];   // key -> level bits (bf16), exponent field - 120
@@ -375,7 +356,7 @@ __global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __
                 const uint32_t kk = (ef - 6u) * 0x00800080u;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {                      // chunks of 8 values: one Philox block each
-                    const Axs6Philox rnd = philox_with_keys(offset + (uint64_t)(b * 4 + q), keys);
+                    const Axs6Philox rnd = axs6_philox_keyed(offset + (uint64_t)(b * 4 + q), keys);
 #pragma unroll
                     for (int pi = 0; pi < 4; ++pi) {
                         const uint32_t wi = w[4 * q + pi];
@@ -397,7 +378,7 @@ __global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     float u[8];
-                    chunk_uniforms<kPhilox>(u, b * 4 + q, true, seed, offset, nullptr);
+                    chunk_uniforms<kPhilox>(u, b * 4 + q, true, keys, offset, nullptr);
 #pragma unroll
                     for (int pi = 0; pi < 4; ++pi) {
                         uint32_t o = 0;
@@ -511,11 +492,7 @@ static int launch(const void *x, void *y, int64_t nblocks, int round, uint64_t s
             return AXS6_ERR_LAUNCH;
         attr_done[dev_id] = true;
     }
-    PhiloxKeys keys;
-    for (int i = 0; i < 10; ++i) {
-        keys.k0[i] = (uint32_t)seed + (uint32_t)i * 0x9E3779B9u;
-        keys.k1[i] = (uint32_t)(seed >> 32) + (uint32_t)i * 0xBB67AE85u;
-    }
+    const Axs6PhiloxKeys keys = axs6_philox_keys(seed);
     if (round == kNearest) fq_bf16_nf5_b32_bulk_kernel<kNearest><<<(unsigned)ctas, kBlocksB, kSmemBytes, st>>>(xm, ym, nblocks, 0, 0, nullptr, keys);
     else                   fq_bf16_nf5_b32_bulk_kernel<kPhilox><<<(unsigned)ctas, kBlocksB, kSmemBytes, st>>>(xm, ym, nblocks, seed, offset, epoch, keys);
     count_launch();
@@ -554,6 +531,7 @@ static int fq_entry(const void *x, void *y, int in_dtype, int out_dtype, int64_t
     a.via_bf16 = (flags & AXS6_FLAG_INPUT_VIA_BF16) ? 1u : 0u;
     a.out_tf32 = (flags & AXS6_FLAG_OUTPUT_TF32) ? 1u : 0u;
     a.seed = seed; a.offset = offset; a.noise = noise;
+    a.keys = axs6_philox_keys(seed);
     a.epoch = philox_epoch_ptr();
     if (round == kPhilox && !a.epoch) return AXS6_ERR_DEVICE;
     const bool vec = aligned16(x) && aligned16(y) && (cols % kChunk == 0) && (ldx % kChunk == 0) &&

@@ -135,11 +135,11 @@ __device__ __forceinline__ uint32_t group_max(uint32_t m, int lanes)
 // ---- uniform draws for one chunk ---------------------------------------------------------------
 template <int ROUND>
 __device__ __forceinline__ void chunk_uniforms(float (&u)[8], int64_t chunk, bool active,
-                                               uint64_t seed, uint64_t offset, const float *noise)
+                                               const Axs6PhiloxKeys &keys, uint64_t offset, const float *noise)
 {
     if (ROUND == kPhilox) {
         // one Philox4x32-10 block per chunk: eight 16-bit draws
-        const Axs6Philox a = axs6_philox(offset + (uint64_t)chunk, seed);
+        const Axs6Philox a = axs6_philox_keyed(offset + (uint64_t)chunk, keys);
 #pragma unroll
         for (int i = 0; i < 4; ++i) { u[2 * i] = axs6_u01_16(a.r[i] & 0xFFFFu); u[2 * i + 1] = axs6_u01_16(a.r[i] >> 16); }
     } else if (ROUND == kNoise) {
@@ -157,10 +157,10 @@ __device__ __forceinline__ void chunk_uniforms(float (&u)[8], int64_t chunk, boo
 // Uniform draw for one padded element index (generic kernels).
 template <int ROUND>
 __device__ __forceinline__ float element_uniform(int64_t padded_index, bool active,
-                                                 uint64_t seed, uint64_t offset, const float *noise)
+                                                 const Axs6PhiloxKeys &keys, uint64_t offset, const float *noise)
 {
     if (ROUND == kPhilox) {
-        const Axs6Philox a = axs6_philox(offset + (uint64_t)(padded_index >> 3), seed);
+        const Axs6Philox a = axs6_philox_keyed(offset + (uint64_t)(padded_index >> 3), keys);
         const uint32_t w = a.r[(padded_index & 7) >> 1];
         return axs6_u01_16((padded_index & 1) ? (w >> 16) : (w & 0xFFFFu));
     }
