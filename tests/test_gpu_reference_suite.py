@@ -259,3 +259,38 @@ def test_conversion_variants_and_memory_estimate():
 
 def test_no_bounded_wait_gave_up_in_this_file():
     assert _lib.load().axs6_gemm_status() == 0
+
+
+# ---------------------------------------------------------------- first-generation launchers (axs/triton_kernels)
+def test_first_generation_launchers():
+    """triton_quantize / triton_dequantize / triton_fake_quantize / triton_axs_matmul (uniform grid, 2-D input,
+    row length a multiple of the block size): codes, reconstruction and fake-quantise bit for bit against the
+    oracle's uniform-grid path, the product within 1e-3 of the product of the oracle-quantised operands."""
+    lk = importlib.import_module("axs6_b200.triton_kernels")
+    torch.manual_seed(21)
+    x = torch.randn(96, 160) * torch.logspace(-2, 2, 96).unsqueeze(1)
+    for B in (8, 16, 32):
+        se, sg, mg = lk.triton_quantize(x.cuda(), B)
+        ose, osg, omg = oracle.quantize(x.numpy(), B, oracle.GRID_UNIFORM)
+        assert se.shape == (96, 160 // B) and sg.shape == (96, 160) and sg.dtype == torch.bool and mg.dtype == torch.uint8
+        assert_bits_equal(se, ose, "exponents")
+        assert_bits_equal(sg, osg.reshape(96, 160), "signs")
+        assert_bits_equal(mg, omg.reshape(96, 160), "magnitudes")
+        back = lk.triton_dequantize(se, sg, mg, B)
+        assert back.dtype == torch.float32
+        assert_bits_equal(back, oracle.dequantize(ose, osg, omg, 160, oracle.GRID_UNIFORM), "dequantize")
+        assert_bits_equal(lk.triton_fake_quantize(x.cuda(), B), oracle.fake_quantize_uniform(x.numpy(), B), "fake quantize")
+    sq = lk.triton_fake_quantize(x.cuda(), 32, stochastic=True)
+    assert sq.shape == x.shape and bool(torch.isfinite(sq).all())
+    with pytest.raises(AssertionError):
+        lk.triton_fake_quantize(torch.randn(4, 33, device="cuda"))
+    with pytest.raises(AssertionError):
+        lk.triton_quantize(torch.randn(2, 4, 32, device="cuda"))
+    a, b = torch.randn(130, 256), torch.randn(256, 72)
+    c = lk.triton_axs_matmul(a.cuda(), b.cuda())
+    aq = oracle.fake_quantize_uniform(a.numpy(), 32).astype(np.float64)
+    bq = oracle.fake_quantize_uniform(np.ascontiguousarray(b.numpy().T), 32).astype(np.float64).T
+    ref = torch.from_numpy(aq @ bq)
+    assert c.shape == (130, 72) and c.dtype == torch.float32
+    _close(c, ref)
+    _close(lk.triton_axs_matmul(a.cuda(), b.cuda(), quantize_a=False, quantize_b=False), (a.double() @ b.double()))
