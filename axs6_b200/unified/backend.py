@@ -74,6 +74,16 @@ def accelerated_matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return out.reshape(*a.shape[:-1], b.shape[-1])
 
 
+def detect_best_backend() -> BackendType:
+    """The reference probes for Triton / int8 / compiled paths (backend.py:88-125); here the answer is fixed."""
+    return BackendType.CUDA_SM100
+
+
+def clear_int8_weight_cache() -> None:
+    """The reference caches int8 re-quantised weights (backend.py:261-280); this package has no such cache.
+    Kept so that training loops written for the reference can keep calling it after ``optimizer.step()``."""
+
+
 def backend_info() -> dict[str, object]:
     """Diagnostics in the spirit of backend.py:678-691."""
     cuda = torch.cuda.is_available()

@@ -13,6 +13,16 @@ from .. import ops
 from ..core import DEFAULT_BLOCK_SIZE, VALID_BLOCK_SIZES
 
 
+def has_triton() -> bool:
+    """The reference asks whether Triton can be imported (triton_kernels.py:50-53).  These launchers do not
+    need it; the answer says whether they can run: a CUDA device and the library are present."""
+    try:
+        from .. import _lib
+        return bool(torch.cuda.is_available() and _lib.load().axs6_query(0))
+    except Exception:
+        return False
+
+
 def triton_fused_fake_quantize(tensor: torch.Tensor, block_size: int = DEFAULT_BLOCK_SIZE,
                                rounding: Literal["nearest", "stochastic"] = "nearest", *,
                                n_blocks: int = 32) -> torch.Tensor:

@@ -66,3 +66,23 @@ def test_product_never_imports_the_oracle():
                 text = open(os.path.join(root, f)).read()
                 assert not re.search(r"^\s*(import|from)\s+oracle\b", text, flags=re.M), f
                 assert "liboracle" not in text, f
+
+
+def test_unified_package_exports_the_reference_names():
+    """Every public name of the reference's ``axs.unified`` (its ``__all__``, axs/unified/__init__.py:80-127)
+    exists in ``axs6_b200.unified``, so `import axs6_b200.unified as unified` needs no further edits."""
+    import axs6_b200.unified as u
+    names = ["fused_fake_quantize", "quantize_unified", "dequantize_unified", "quantization_error_unified",
+             "FUSED_NF5_LUT", "NF5_CODEBOOK", "REVERSE_NF5_LUT", "fake_quantize_unified", "axs_linear_unified",
+             "axs_matmul_unified", "AXSLinearUnified", "AXSLayerNormUnified", "AXSEmbeddingUnified",
+             "AXSMultiheadAttentionUnified", "convert_to_axs_unified", "AXSTrainingPipelineUnified", "AmaxEMA",
+             "BackendType", "accelerated_fake_quantize", "accelerated_linear", "accelerated_matmul", "backend_info",
+             "clear_int8_weight_cache", "detect_best_backend", "get_backend", "set_backend", "has_triton",
+             "triton_fused_fake_quantize", "triton_fused_linear", "AXSLinearMixedPrecision",
+             "axs_linear_mixed_precision", "convert_to_axs_mixed_precision", "estimate_memory_savings",
+             "AXS6GradCompressor", "axs6_gradient_hook", "axs6_gradient_hook_packed"]
+    missing = [n for n in names if not hasattr(u, n)]
+    assert not missing, missing
+    assert set(names) <= set(u.__all__)
+    u.clear_int8_weight_cache()
+    assert u.detect_best_backend() == u.get_backend()
