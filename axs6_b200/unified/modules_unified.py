@@ -122,7 +122,7 @@ def convert_to_axs_unified(model: nn.Module, block_size: int = DEFAULT_BLOCK_SIZ
     """Swap ``nn.Linear`` (and the V1 ``AXSLinear``) for :class:`AXSLinearUnified`, ``nn.LayerNorm`` for
     :class:`AXSLayerNormUnified` and ``nn.Embedding`` for :class:`AXSEmbeddingUnified`; the new modules take
     over the old modules' parameters.  RMSNorm and other norms are left alone.  Deep copy unless ``inplace``."""
-    from ..nn.modules import AXSLinear
+    from ..nn.modules import AXSEmbedding, AXSLayerNorm, AXSLinear
     if not inplace:
         model = copy.deepcopy(model)
     skip = skip_layers or set()
@@ -140,11 +140,12 @@ def convert_to_axs_unified(model: nn.Module, block_size: int = DEFAULT_BLOCK_SIZ
                 if child.bias is not None:
                     new.bias = child.bias
                 setattr(parent, name, new)
-            elif isinstance(child, nn.LayerNorm) and child.elementwise_affine and child.bias is not None:
+            elif isinstance(child, AXSLayerNorm) or (isinstance(child, nn.LayerNorm) and child.elementwise_affine
+                                                     and child.bias is not None):
                 new = AXSLayerNormUnified(list(child.normalized_shape), eps=child.eps).to(child.weight.device)
                 new.weight, new.bias = child.weight, child.bias
                 setattr(parent, name, new)
-            elif isinstance(child, nn.Embedding):
+            elif isinstance(child, (nn.Embedding, AXSEmbedding)):
                 new = AXSEmbeddingUnified(child.num_embeddings, child.embedding_dim, child.padding_idx, block_size)
                 new = new.to(child.weight.device)
                 new.weight = child.weight

@@ -126,3 +126,36 @@ def test_pipeline_overflow_on_the_gpu_uses_one_fused_check():
     assert res["overflow"] is True and pipe.loss_scale == 4.0
     res = pipe.training_step(x, _mse)
     assert res["overflow"] is False and res["step"] == 1 and res["grad_norm"] > 0
+
+
+def test_v1_modules_and_conversion():
+    """axs/nn/modules.py: AXSLayerNorm quantises its output, AXSEmbedding its rows (both on the uniform grid),
+    AXSMultiheadAttention runs on AXSLinear projections, convert_to_axs swaps Linear / LayerNorm / Embedding and
+    convert_to_axs_unified accepts the V1 modules in turn."""
+    nnm = importlib.import_module("axs6_b200.nn.modules")
+    torch.manual_seed(2)
+    ln = nnm.AXSLayerNorm(96).cuda()
+    x = torch.randn(7, 96, device="cuda")
+    want = oracle.fake_quantize_uniform(torch.nn.functional.layer_norm(x, [96]).cpu().numpy(), 32)
+    assert_bits_equal(ln(x), want, "layer norm output")
+    emb = nnm.AXSEmbedding(100, 64, padding_idx=3).cuda()
+    idx = torch.randint(0, 100, (5, 9), device="cuda")
+    rows = emb.weight.detach()[idx.reshape(-1)].cpu().numpy()
+    assert_bits_equal(emb(idx), oracle.fake_quantize_uniform(rows, 32).reshape(5, 9, 64), "embedding rows")
+    att = nnm.AXSMultiheadAttention(64, 4).cuda()
+    q = torch.randn(2, 16, 64, device="cuda", requires_grad=True)
+    y = att(q, q, q)
+    y.sum().backward()
+    assert y.shape == (2, 16, 64) and q.grad is not None and bool(torch.isfinite(q.grad).all())
+
+    model = nn.Sequential(nn.Embedding(50, 32), nn.LayerNorm(32), nn.Linear(32, 8)).cuda()
+    v1 = nnm.convert_to_axs(model, skip_layers={"2"})
+    assert isinstance(v1[0], nnm.AXSEmbedding) and isinstance(v1[1], nnm.AXSLayerNorm) and type(v1[2]) is nn.Linear
+    assert torch.equal(v1[0].weight, model[0].weight) and type(model[1]) is nn.LayerNorm
+    v1 = nnm.convert_to_axs(model)
+    assert isinstance(v1[2], nnm.AXSLinear)
+    out = v1(torch.randint(0, 50, (4, 6), device="cuda"))
+    assert out.shape == (4, 6, 8) and bool(torch.isfinite(out).all())
+    uni = um.convert_to_axs_unified(v1)
+    assert isinstance(uni[0], um.AXSEmbeddingUnified) and isinstance(uni[1], um.AXSLayerNormUnified)
+    assert isinstance(uni[2], um.AXSLinearUnified) and torch.equal(uni[2].weight, model[2].weight)
