@@ -344,11 +344,13 @@ __global__ void __launch_bounds__(kThreads) unpack_generic_kernel(const CodecArg
 
 // ------------------------------------------------------------------------------------------ host
 template <typename K>
-static int launch_codec(K kernel, const CodecArgs &a, int64_t items_per_cta, int64_t items, cudaStream_t stream)
+static int launch_codec(K kernel, const CodecArgs &a, int64_t items_per_cta, int64_t items, cudaStream_t stream,
+                        int max_per_sm = 0)
 {
     const DeviceInfo &d = device_info();
     int per_sm = cached_occupancy(reinterpret_cast<const void *>(kernel), kThreads);
     if (per_sm < 1) return AXS6_ERR_LAUNCH;
+    if (max_per_sm > 0 && per_sm > max_per_sm) per_sm = max_per_sm;
     int64_t ctas = (items + items_per_cta - 1) / items_per_cta;
     const int64_t cap = tune_value(1);
     if (cap > 0 && per_sm > cap) per_sm = (int)cap;
@@ -391,7 +393,10 @@ template <typename Tout, int GRID>
 static int launch_unpack(const CodecArgs &a, bool planes, bool vec, cudaStream_t st)
 {
     if (vec) {
-        if (planes) return launch_codec(unpack_vec_kernel<Tout, GRID, kPlanes>, a, (int64_t)kThreads * kU, a.g.total_chunks, st);
+        // planes -> fp32: 6.0 TB/s with 5 or 6 resident CTAs per SM, 4.5 with the 8 that fit (too many stores in
+        // flight); planes -> bf16 is fastest with all 8
+        if (planes) return launch_codec(unpack_vec_kernel<Tout, GRID, kPlanes>, a, (int64_t)kThreads * kU, a.g.total_chunks, st,
+                                        sizeof(Tout) == 4 ? 6 : 0);
         return launch_codec(unpack_vec_kernel<Tout, GRID, kBytes>, a, (int64_t)kThreads * kU, a.g.total_chunks, st);
     }
     const int64_t total = a.g.rows * a.g.cols;
