@@ -488,16 +488,10 @@ __device__ __forceinline__ void bf16_block_payload(const uint32_t (&w)[16], cons
     }
 }
 
-__device__ __forceinline__ void build_key_table(uint8_t *table, int tid, int nthreads)
+__device__ __forceinline__ void build_key_table(uint8_t *table /*kKeyLimit + 16, 16-byte aligned*/, int tid, int nthreads)
 {
-    for (int key = tid; key <= kKeyLimit; key += nthreads) {
-        uint8_t code = 0;
-        if (key < kKeyLimit) {
-            const int j = key >> 7, m = 127 - (key & 127);
-            code = g_reverse[((128 + m) * 1023) >> (8 + j)];
-        }
-        table[key] = code;
-    }
+    for (int i = tid; i < (kKeyLimit + 16) / 16; i += nthreads)
+        reinterpret_cast<uint4 *>(table)[i] = reinterpret_cast<const uint4 *>(g_key_code)[i];
 }
 
 // The record of a block as seven 32-bit words of the output image, shifted so that its first byte lands

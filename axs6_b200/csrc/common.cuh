@@ -45,5 +45,10 @@ inline bool valid_dtype(int d) { return d == AXS6_F32 || d == AXS6_BF16; }
 // Codebook levels (fp32 bits) and LUT-index -> code table, baked into each module image.
 static __device__ __align__(16) const uint32_t g_codebook_bits[32] = AXS6_CODEBOOK_BITS_INIT;
 static __device__ __align__(16) const uint8_t g_reverse[1024] = AXS6_REVERSE_INIT;
+// derived tables (see gen_tables.py): kernels copy them into shared memory with 16-byte loads
+static __device__ __align__(16) const uint32_t g_value_lut_bits[1024] = AXS6_VALUE_LUT_BITS_INIT;
+static __device__ __align__(16) const uint8_t g_key_code[1296] = AXS6_KEY_CODE_INIT;
+static __device__ __align__(16) const uint16_t g_key_level_bf16[1288] = AXS6_KEY_LEVEL_BF16_INIT;
+static __device__ __align__(16) const uint16_t g_lut_level_bf16[1024] = AXS6_LUT_LEVEL_BF16_INIT;
 
 }  // namespace axs6

@@ -88,7 +88,7 @@ __device__ __forceinline__ void fq_chunk(const uint32_t (&v)[8], float (&y)[8], 
 template <typename Tin, typename Tout, int GRID, int ROUND, int U>
 __global__ void __launch_bounds__(kThreads) fq_vec_kernel(const FqArgs a)
 {
-    __shared__ float tab[GRID == AXS6_GRID_NF5 ? 1024 : 32];
+    __shared__ __align__(16) float tab[GRID == AXS6_GRID_NF5 ? 1024 : 32];
     if (GRID == AXS6_GRID_NF5) build_value_lut(tab); else build_levels<GRID>(tab);
     __syncthreads();
 
@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(kThreads) fq_vec_kernel(const FqArgs a)
 template <typename Tin, typename Tout, int GRID, int ROUND>
 __global__ void __launch_bounds__(kThreads) fq_generic_kernel(const FqArgs a)
 {
-    __shared__ float tab[GRID == AXS6_GRID_NF5 ? 1024 : 32];
+    __shared__ __align__(16) float tab[GRID == AXS6_GRID_NF5 ? 1024 : 32];
     if (GRID == AXS6_GRID_NF5) build_value_lut(tab); else build_levels<GRID>(tab);
     __syncthreads();
 
@@ -311,17 +311,11 @@ __global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __
         }
     }
     if (ROUND == kNearest) {
-        for (int key = tid; key <= kKeyLim; key += kBlocksB) {
-            uint32_t code = 0;
-            if (key < kKeyLim) {
-                const int j = key >> 7, m = 127 - (key & 127);
-                code = g_reverse[((128 + m) * 1023) >> (8 + j)];
-            }
-            table[key] = (uint16_t)(axs6_f32_to_bf16_bits(__uint_as_float(g_codebook_bits[code])) - (120u << 7));
-        }
+        for (int i = tid; i < (kKeyLim + 8) / 8; i += kBlocksB)
+            reinterpret_cast<uint4 *>(table)[i] = reinterpret_cast<const uint4 *>(g_key_level_bf16)[i];
     } else {
-        for (int i = tid; i < 1024; i += kBlocksB)
-            lvl[i] = (uint16_t)(axs6_f32_to_bf16_bits(__uint_as_float(g_codebook_bits[g_reverse[i]])) - (120u << 7));
+        for (int i = tid; i < 1024 / 8; i += kBlocksB)
+            reinterpret_cast<uint4 *>(lvl)[i] = reinterpret_cast<const uint4 *>(g_lut_level_bf16)[i];
     }
     __syncthreads();
     const uint64_t offset = ROUND == kPhilox ? offset0 + *epoch : 0ull;

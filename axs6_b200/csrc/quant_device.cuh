@@ -171,10 +171,10 @@ __device__ __forceinline__ float element_uniform(int64_t padded_index, bool acti
 // ---- shared-memory tables ----------------------------------------------------------------------
 // NF5: the 1024-entry value LUT, rebuilt as codebook[reverse[i]] (bit-identical to the
 // reference's FUSED_NF5_LUT).  One gather per element instead of two.
-__device__ __forceinline__ void build_value_lut(float *lut /*1024*/)
+__device__ __forceinline__ void build_value_lut(float *lut /*1024, 16-byte aligned*/)
 {
-    for (int i = threadIdx.x; i < 1024; i += blockDim.x)
-        lut[i] = __uint_as_float(g_codebook_bits[g_reverse[i]]);
+    for (int i = threadIdx.x; i < 256; i += blockDim.x)
+        reinterpret_cast<uint4 *>(lut)[i] = reinterpret_cast<const uint4 *>(g_value_lut_bits)[i];
 }
 __device__ __forceinline__ void build_reverse_lut(uint8_t *rev /*1024*/)
 {
