@@ -69,12 +69,19 @@ const char *axs6_strerror(int status);
  * 2 = ABI version, 3 = number of kernels launched by this process so far. */
 int64_t axs6_query(int what);
 
-/* Performance knobs for experiments (process-wide, not needed for correct results):
- * key 0 = cap on resident CTAs per SM of the fake-quantise kernels, key 1 = the same for the
- * pack / unpack kernels, key 2 = 1 disables the specialised bf16 pack kernel, key 3 = 2 turns on split-K (two partials, fp32 output) in the bf16 GEMM, keys 4-6 = overrides
- * of the GEMM's shared-memory descriptor strides, key 7 = GEMM kernel (1 single-CTA, 2 CTA pairs, 3 CTA pairs with 128-wide tiles), key 8 = SMs the GEMM leaves free (for a collective
- * on another stream);
- * value 0 restores the built-in choice. */
+/* Performance knobs for experiments and tests (process-wide, never needed for correct results;
+ * value 0 restores the built-in choice):
+ *   key 0   cap on resident CTAs per SM of the fake-quantise kernels
+ *   key 1   the same for the pack / unpack kernels
+ *   key 2   record pack of bf16 / fp32 input: 1 = general kernel only, 2 = bf16 kernel with per-thread
+ *           loads instead of the TMA-fed one
+ *   key 3   GEMM K splits: 1 = never split (bit-reproducible fp32 outputs), 2 = two-way split of every
+ *           tile in the CTA-pair kernel
+ *   keys 4-6  overrides of the GEMM's shared-memory descriptor strides (LBO, SBO, K step)
+ *   key 7   GEMM kernel: 1 single-CTA, 2 CTA pairs, 3 CTA pairs with 128-wide tiles
+ *   key 8   SMs the GEMM leaves free (for a collective on another stream)
+ *   key 11  1 = general unpack / unpack-and-sum kernels only (no TMA-fed kernel)
+ *   key 12  1 = general fake-quantise kernel only (no TMA-fed bf16 kernel) */
 int axs6_tune(int key, int64_t value);
 
 /* Every stochastic kernel adds a per-device, device-resident epoch to its Philox counter offset.
