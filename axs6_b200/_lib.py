@@ -14,11 +14,13 @@ LIB_PATH = os.path.join(HERE, "libaxs6_b200.so")
 F32, BF16 = 0, 1
 GRID_UNIFORM, GRID_NF5 = 0, 1
 ROUND_NEAREST, ROUND_STOCHASTIC = 0, 1
-LAYOUT_PLANES, LAYOUT_WIRE, LAYOUT_SPEC = 0, 1, 2
+LAYOUT_PLANES, LAYOUT_WIRE, LAYOUT_SPEC, LAYOUT_SPLIT = 0, 1, 2, 3
 FLAG_INPUT_VIA_BF16 = 1
 FLAG_OUTPUT_TF32 = 2
 LINEAR_QUANTIZE_INPUT, LINEAR_QUANTIZE_GRAD, LINEAR_COMPUTE_TF32, LINEAR_BIAS_FROM_QUANTIZED = 1, 2, 4, 8
 LINEAR_BIAS_VIA_BF16 = 16
+LINEAR_REUSE_WQ, LINEAR_REUSE_GQ = 32, 64
+LINEAR_OPERANDS_PACKED = 128
 
 _i64, _int, _u32, _u64, _ptr = ctypes.c_int64, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p
 
@@ -37,6 +39,7 @@ SIGNATURES = {
     "axs6_unpack": (_int, [_int, _ptr, _ptr, _ptr, _ptr, _int, _i64, _i64, _i64, _int, _int, _ptr]),
     "axs6_unpack_sum": (_int, [_int, _ptr, _i64, _i64, _ptr, _int, _i64, _i64, _i64, _int, _int, ctypes.c_float, _ptr]),
     "axs6_gemm_bf16": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
+    "axs6_gemm_packed": (_int, [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _ptr, _ptr, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "axs6_gemm_tf32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "axs6_gemm_status": (_int, []),
     "axs6_codec_status": (_int, []),

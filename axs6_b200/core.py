@@ -9,8 +9,10 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass
+from enum import IntEnum
 from typing import Literal
 
+import numpy as np
 import torch
 
 from . import ops
@@ -25,6 +27,94 @@ AXS6_MAX_MAGNITUDE: int = 31
 AXS6_EXPONENT_BIAS: int = 127
 DEFAULT_BLOCK_SIZE: int = 32
 VALID_BLOCK_SIZES: tuple[int, ...] = (8, 16, 32)
+
+
+class BlockConfig(IntEnum):
+    """2-bit mode field of a block header (core.py:44-50); only DENSE is produced."""
+
+    DENSE = 0b00
+    SPARSE = 0b01
+    HIGH_PREC = 0b10
+    RESERVED = 0b11
+
+
+@dataclass
+class AXSBlock:
+    """One encoded block, field for field the reference's host-side container (core.py:59-152): the biased
+    8-bit ``shared_exponent`` (scale = 2^(shared_exponent - 127)), the 2-bit ``config``, ``signs`` (bool, True =
+    negative) and ``magnitudes`` (uint8 in [0, 31]), both of shape ``(block_size,)``.
+
+    This is a format utility on numpy arrays for single blocks (the reference's is a Python loop);
+    whole tensors go through :func:`tensor_to_bytes` / :func:`tensor_from_bytes`, which run on the GPU
+    and produce the same bytes."""
+
+    shared_exponent: int
+    config: BlockConfig
+    signs: np.ndarray
+    magnitudes: np.ndarray
+    block_size: int = DEFAULT_BLOCK_SIZE
+
+    @property
+    def scale(self) -> float:
+        return math.ldexp(1.0, self.shared_exponent - AXS6_EXPONENT_BIAS)
+
+    @property
+    def total_bits(self) -> int:
+        return AXS6_HEADER_BITS + self.block_size * AXS6_VALUE_BITS
+
+    @property
+    def bits_per_value(self) -> float:
+        return self.total_bits / self.block_size
+
+    def to_bytes(self) -> bytes:
+        """u16 little-endian header ``(exponent << 2) | config``, then the codes ``(sign << 5) | magnitude`` as a
+        little-endian stream of 6-bit fields (core.py:97-118): 2 + ceil(6 B / 8) bytes."""
+        header = ((int(self.shared_exponent) << 2) | int(self.config)) & 0xFFFF
+        codes = (np.asarray(self.signs, dtype=bool).astype(np.uint8) << 5) | (np.asarray(self.magnitudes, dtype=np.uint8) & 31)
+        codes = codes[: self.block_size]
+        field_bits = (codes[:, None] >> np.arange(6, dtype=np.uint8)) & 1            # (B, 6), least significant first
+        payload = np.packbits(field_bits.reshape(-1).astype(np.uint8), bitorder="little")
+        return header.to_bytes(2, "little") + payload.tobytes()
+
+    @classmethod
+    def from_bytes(cls, data: bytes, block_size: int = DEFAULT_BLOCK_SIZE) -> "AXSBlock":
+        """Inverse of :meth:`to_bytes` (core.py:120-152)."""
+        header = int.from_bytes(data[:2], "little")
+        nbytes = (6 * block_size + 7) // 8
+        stream = np.unpackbits(np.frombuffer(data[2:2 + nbytes], dtype=np.uint8), bitorder="little")[: 6 * block_size]
+        codes = (stream.reshape(block_size, 6).astype(np.uint8) << np.arange(6, dtype=np.uint8)).sum(axis=1).astype(np.uint8)
+        return cls(shared_exponent=header >> 2, config=BlockConfig(header & 3), signs=(codes >> 5).astype(bool),
+                   magnitudes=(codes & 31).astype(np.uint8), block_size=block_size)
+
+
+def axs_encode_block(values: np.ndarray, rounding: Literal["nearest", "stochastic"] = "nearest") -> AXSBlock:
+    """Encode one block given as a 1-D array of 8, 16 or 32 values, in double precision on the host, following
+    the reference's per-block encoder (core.py:214-270): exponent = floor(log2(max |v|)) + 1 + 127 clamped to
+    [0, 255] (0 for an all-zero block), magnitude = round-half-even(|v| / scale * 31) clamped to [0, 31], or
+    floor + Bernoulli(fraction) with ``np.random.uniform`` draws for ``"stochastic"``."""
+    v = np.asarray(values, dtype=np.float64).reshape(-1)
+    n = v.shape[0]
+    assert n in VALID_BLOCK_SIZES, f"Block size must be one of {VALID_BLOCK_SIZES}"
+    mag_abs = np.abs(v)
+    top = float(mag_abs.max())
+    if top == 0.0:
+        return AXSBlock(0, BlockConfig.DENSE, np.zeros(n, dtype=bool), np.zeros(n, dtype=np.uint8), n)
+    se = min(255, max(0, math.floor(math.log2(top)) + 1 + AXS6_EXPONENT_BIAS))
+    steps = mag_abs / math.ldexp(1.0, se - AXS6_EXPONENT_BIAS) * AXS6_MAX_MAGNITUDE
+    if rounding == "stochastic":
+        low = np.floor(steps)
+        draws = np.random.uniform(0, 1, size=n)
+        q = low + (draws < (steps - low))
+    else:
+        q = np.round(steps)
+    q = np.clip(q, 0, AXS6_MAX_MAGNITUDE).astype(np.uint8)
+    return AXSBlock(se, BlockConfig.DENSE, v < 0, q, n)
+
+
+def axs_decode_block(block: AXSBlock) -> np.ndarray:
+    """float64 values of one block: magnitude / 31 * scale, negated where the sign is set (core.py:273-286)."""
+    out = block.magnitudes.astype(np.float64) / AXS6_MAX_MAGNITUDE * block.scale
+    return np.where(np.asarray(block.signs, dtype=bool), -out, out)
 
 
 @dataclass
@@ -87,6 +177,18 @@ def quantize(tensor: torch.Tensor, block_size: int = DEFAULT_BLOCK_SIZE,
 def dequantize(axs_tensor: AXSTensor) -> torch.Tensor:
     """Back to fp32 with the original shape (reference: core.py:372-403)."""
     return _dequantize_planes(axs_tensor, ops.GRID_UNIFORM)
+
+
+def quantization_error(original: torch.Tensor, block_size: int = DEFAULT_BLOCK_SIZE,
+                       rounding: Literal["nearest", "stochastic"] = "nearest") -> dict[str, float]:
+    """Error statistics of quantise -> dequantise on ``original`` (core.py:411-440): ``mse``, ``rmse``,
+    ``max_abs_error``, ``mean_abs_error``, ``signal_to_noise_db``."""
+    back = dequantize(quantize(original, block_size=block_size, rounding=rounding))
+    err = (original - back).float()
+    mse = err.pow(2).mean().item()
+    power = original.float().pow(2).mean().item()
+    return {"mse": mse, "rmse": math.sqrt(mse), "max_abs_error": err.abs().max().item(),
+            "mean_abs_error": err.abs().mean().item(), "signal_to_noise_db": 10 * math.log10(power / max(mse, 1e-45))}
 
 
 def tensor_to_bytes(tensor: torch.Tensor, block_size: int = DEFAULT_BLOCK_SIZE,

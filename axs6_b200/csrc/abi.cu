@@ -31,6 +31,20 @@ int cached_occupancy(const void *kernel, int threads)
     return per_sm;
 }
 
+bool ensure_dynamic_smem(const void *kernel, int bytes)
+{
+    static std::map<std::pair<const void *, int>, int> done;
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = done.find({kernel, dev});
+    if (it != done.end() && it->second >= bytes) return true;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+    done[{kernel, dev}] = bytes;
+    return true;
+}
+
 // ---- Philox epoch: a device-resident addend to the counter offset of every stochastic kernel -------
 __device__ unsigned long long g_philox_epoch;
 

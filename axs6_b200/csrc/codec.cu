@@ -141,9 +141,11 @@ __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
                 if (j == 0) {
                     if (a.hdr == 1) {
                         s[0] = (uint8_t)se;
-                    } else {
+                    } else if (a.hdr == 2) {
                         s[0] = (uint8_t)((se << 2) & 0xFF);
                         s[1] = (uint8_t)(se >> 6);
+                    } else if (act[k]) {
+                        a.p1[c >> lg] = (uint8_t)se;            // split layout: exponents in a plane of their own
                     }
                 }
                 s += a.hdr + 6 * j;
@@ -218,9 +220,11 @@ __global__ void __launch_bounds__(kThreads) pack_generic_kernel(const CodecArgs 
             if (i == 0) {
                 if (a.hdr == 1) {
                     r[0] = (uint8_t)s.se;
-                } else {
+                } else if (a.hdr == 2) {
                     r[0] = (uint8_t)((s.se << 2) & 0xFF);
                     r[1] = (uint8_t)(s.se >> 6);
+                } else {
+                    a.p1[blk] = (uint8_t)s.se;
                 }
             }
             const int q = i & 3;
@@ -285,7 +289,8 @@ __global__ void __launch_bounds__(kThreads) unpack_vec_kernel(const CodecArgs a)
             } else {
                 const int lb = k * blocks_per_group + lb_thread;
                 const uint8_t *s = stage + lb * a.rec;
-                se = (a.hdr == 1) ? (uint32_t)s[0] : (((uint32_t)s[0] | ((uint32_t)s[1] << 8)) >> 2) & 0xFFu;
+                se = (a.hdr == 1) ? (uint32_t)s[0] : (a.hdr == 2) ? (((uint32_t)s[0] | ((uint32_t)s[1] << 8)) >> 2) & 0xFFu
+                                                                  : (uint32_t)a.p1[c >> lg];
                 s += a.hdr + 6 * j;
                 const uint32_t lo = (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
                 const uint32_t hi = (uint32_t)s[4] | ((uint32_t)s[5] << 8);
@@ -330,7 +335,8 @@ __global__ void __launch_bounds__(kThreads) unpack_generic_kernel(const CodecArg
             mag = a.p2[row * padded + pc] & 31u;
         } else {
             const uint8_t *r = a.p0 + blk * a.rec;
-            se = (a.hdr == 1) ? (uint32_t)r[0] : (((uint32_t)r[0] | ((uint32_t)r[1] << 8)) >> 2) & 0xFFu;
+            se = (a.hdr == 1) ? (uint32_t)r[0] : (a.hdr == 2) ? (((uint32_t)r[0] | ((uint32_t)r[1] << 8)) >> 2) & 0xFFu
+                                                              : (uint32_t)a.p1[blk];
             const int bit = 6 * i, k = bit >> 3, sh = bit & 7;
             uint32_t w = r[a.hdr + k];
             if (sh > 2) w |= (uint32_t)r[a.hdr + k + 1] << 8;
@@ -727,16 +733,9 @@ static int launch_pack_bulk(const void *x, void *out, int64_t nblocks, int hdr, 
     if (ctas > (int64_t)d.sms * per_sm) ctas = (int64_t)d.sms * per_sm;
     if (ctas < 1) ctas = 1;
     uint8_t *o = static_cast<uint8_t *>(out);
-    static bool attr_done[64] = {};          // the attribute is per device
-    int dev_id = 0;
-    if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= 64) return 1;
-    bool &attr_set = attr_done[dev_id];
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(pack_bf16_nf5_b32_bulk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<1>()) != cudaSuccess ||
-            cudaFuncSetAttribute(pack_bf16_nf5_b32_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<2>()) != cudaSuccess)
-            return AXS6_ERR_LAUNCH;
-        attr_set = true;
-    }
+    if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&pack_bf16_nf5_b32_bulk_kernel<1>), smem_bytes<1>()) ||
+        !ensure_dynamic_smem(reinterpret_cast<const void *>(&pack_bf16_nf5_b32_bulk_kernel<2>), smem_bytes<2>()))
+        return AXS6_ERR_LAUNCH;
     if (hdr == 1) pack_bf16_nf5_b32_bulk_kernel<1><<<(unsigned)ctas, kFastBlocks, smem_bytes<1>(), st>>>(map, o, nblocks);
     else          pack_bf16_nf5_b32_bulk_kernel<2><<<(unsigned)ctas, kFastBlocks, smem_bytes<2>(), st>>>(map, o, nblocks);
     count_launch();
@@ -891,15 +890,9 @@ static int launch_pack_f32_bulk(const void *x, void *out, int64_t nblocks, int h
     if (cap > 0 && cap < per_sm) per_sm = (int)cap;
     if (ctas > (int64_t)d.sms * per_sm) ctas = (int64_t)d.sms * per_sm;
     if (ctas < 1) ctas = 1;
-    static bool attr_done[64] = {};
-    int dev_id = 0;
-    if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= 64) return 1;
-    if (!attr_done[dev_id]) {
-        if (cudaFuncSetAttribute(pack_f32_nf5_b32_bulk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, pack_f32_smem_bytes<1>()) != cudaSuccess ||
-            cudaFuncSetAttribute(pack_f32_nf5_b32_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, pack_f32_smem_bytes<2>()) != cudaSuccess)
-            return AXS6_ERR_LAUNCH;
-        attr_done[dev_id] = true;
-    }
+    if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&pack_f32_nf5_b32_bulk_kernel<1>), pack_f32_smem_bytes<1>()) ||
+        !ensure_dynamic_smem(reinterpret_cast<const void *>(&pack_f32_nf5_b32_bulk_kernel<2>), pack_f32_smem_bytes<2>()))
+        return AXS6_ERR_LAUNCH;
     uint8_t *o = static_cast<uint8_t *>(out);
     if (hdr == 1) pack_f32_nf5_b32_bulk_kernel<1><<<(unsigned)ctas, kFastBlocks, pack_f32_smem_bytes<1>(), st>>>(map, o, nblocks);
     else          pack_f32_nf5_b32_bulk_kernel<2><<<(unsigned)ctas, kFastBlocks, pack_f32_smem_bytes<2>(), st>>>(map, o, nblocks);
@@ -1099,15 +1092,9 @@ static int launch_unpack_bulk(const void *in, void *y, int64_t nblocks, int hdr,
     if (cap > 0 && cap < per_sm) per_sm = (int)cap;
     if (ctas > (int64_t)d.sms * per_sm) ctas = (int64_t)d.sms * per_sm;
     if (ctas < 1) ctas = 1;
-    static bool attr_done[64] = {};
-    int dev_id = 0;
-    if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= 64) return 1;
-    if (!attr_done[dev_id]) {
-        if (cudaFuncSetAttribute(unpack_nf5_b32_bulk_kernel<Tout, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, unpack_smem_bytes<Tout, 1>()) != cudaSuccess ||
-            cudaFuncSetAttribute(unpack_nf5_b32_bulk_kernel<Tout, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, unpack_smem_bytes<Tout, 2>()) != cudaSuccess)
-            return AXS6_ERR_LAUNCH;
-        attr_done[dev_id] = true;
-    }
+    if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&unpack_nf5_b32_bulk_kernel<Tout, 1>), unpack_smem_bytes<Tout, 1>()) ||
+        !ensure_dynamic_smem(reinterpret_cast<const void *>(&unpack_nf5_b32_bulk_kernel<Tout, 2>), unpack_smem_bytes<Tout, 2>()))
+        return AXS6_ERR_LAUNCH;
     const uint8_t *src = static_cast<const uint8_t *>(in);
     if (hdr == 1) unpack_nf5_b32_bulk_kernel<Tout, 1><<<(unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 1>(), st>>>(map, src, nblocks);
     else          unpack_nf5_b32_bulk_kernel<Tout, 2><<<(unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 2>(), st>>>(map, src, nblocks);
@@ -1117,7 +1104,10 @@ static int launch_unpack_bulk(const void *in, void *y, int64_t nblocks, int hdr,
 
 }  // namespace bulk
 
-static bool layout_ok(int layout) { return layout == AXS6_LAYOUT_PLANES || layout == AXS6_LAYOUT_WIRE || layout == AXS6_LAYOUT_SPEC; }
+static bool layout_ok(int layout)
+{
+    return layout == AXS6_LAYOUT_PLANES || layout == AXS6_LAYOUT_WIRE || layout == AXS6_LAYOUT_SPEC || layout == AXS6_LAYOUT_SPLIT;
+}
 
 }  // namespace axs6
 
@@ -1200,6 +1190,7 @@ AXS6_API int64_t axs6_record_bytes(int layout, int block)
     if (!axs6::valid_block(block)) return 0;
     if (layout == AXS6_LAYOUT_WIRE) return 1 + block * 3 / 4;
     if (layout == AXS6_LAYOUT_SPEC) return 2 + block * 3 / 4;
+    if (layout == AXS6_LAYOUT_SPLIT) return block * 3 / 4;          // payload only; the exponent lives in its own plane
     return 0;
 }
 
@@ -1215,7 +1206,8 @@ AXS6_API int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, 
     if (flags & ~AXS6_FLAG_INPUT_VIA_BF16) return AXS6_ERR_ARG;
     if (rows == 0 || cols == 0) return AXS6_OK;
     const bool planes = layout == AXS6_LAYOUT_PLANES;
-    if (!x || !out0 || (planes && (!out1 || !out2))) return AXS6_ERR_ARG;
+    const bool split = layout == AXS6_LAYOUT_SPLIT;
+    if (!x || !out0 || (planes && (!out1 || !out2)) || (split && !out1)) return AXS6_ERR_ARG;
     const DeviceInfo &d = device_info();
     if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
 
@@ -1231,11 +1223,14 @@ AXS6_API int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, 
     if (round == kPhilox && !a.epoch) return AXS6_ERR_DEVICE;
     a.p0 = static_cast<uint8_t *>(out0); a.p1 = static_cast<uint8_t *>(out1); a.p2 = static_cast<uint8_t *>(out2);
     a.rec = (int)axs6_record_bytes(layout, block);
-    a.hdr = layout == AXS6_LAYOUT_SPEC ? 2 : 1;
+    a.hdr = layout == AXS6_LAYOUT_SPEC ? 2 : (split ? 0 : 1);
     a.lanes_log2 = block == 32 ? 2 : (block == 16 ? 1 : 0);
     const bool vec = aligned16(x) && (cols % kChunk == 0) && (ldx % kChunk == 0) && aligned16(out0) &&
                      (!planes || (aligned16(out1) && aligned16(out2))) && (round != kNoise || aligned16(noise));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (split)          // general kernels only
+        return in_dtype == AXS6_F32 ? dispatch_pack<float>(a, grid, round, planes, vec, st)
+                                    : dispatch_pack<__nv_bfloat16>(a, grid, round, planes, vec, st);
     if (vec && !planes && a.g.flat && in_dtype == AXS6_F32 && !a.via_bf16 && grid == AXS6_GRID_NF5 && round == kNearest &&
         block == 32 && tune_value(2) != 1) {
         const int r = bulk::launch_pack_f32_bulk(x, out0, rows * (cols / 32), a.hdr, st);
@@ -1263,7 +1258,8 @@ AXS6_API int axs6_unpack(int layout, const void *in0, const void *in1, const voi
     if (rows < 0 || cols < 0 || ldy < cols) return AXS6_ERR_ARG;
     if (rows == 0 || cols == 0) return AXS6_OK;
     const bool planes = layout == AXS6_LAYOUT_PLANES;
-    if (!y || !in0 || (planes && (!in1 || !in2))) return AXS6_ERR_ARG;
+    const bool split = layout == AXS6_LAYOUT_SPLIT;
+    if (!y || !in0 || (planes && (!in1 || !in2)) || (split && !in1)) return AXS6_ERR_ARG;
     const DeviceInfo &d = device_info();
     if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
 
@@ -1277,13 +1273,13 @@ AXS6_API int axs6_unpack(int layout, const void *in0, const void *in1, const voi
     a.p1 = const_cast<uint8_t *>(static_cast<const uint8_t *>(in1));
     a.p2 = const_cast<uint8_t *>(static_cast<const uint8_t *>(in2));
     a.rec = (int)axs6_record_bytes(layout, block);
-    a.hdr = layout == AXS6_LAYOUT_SPEC ? 2 : 1;
+    a.hdr = layout == AXS6_LAYOUT_SPEC ? 2 : (split ? 0 : 1);
     a.lanes_log2 = block == 32 ? 2 : (block == 16 ? 1 : 0);
     const bool vec = aligned16(y) && (cols % kChunk == 0) && (ldy % kChunk == 0) && aligned16(in0) &&
                      (!planes || (aligned16(in1) && aligned16(in2)));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // tune key 11: 1 = general kernel only
-    if (vec && !planes && a.g.flat && grid == AXS6_GRID_NF5 && block == 32 && tune_value(11) != 1) {
+    if (vec && !planes && !split && a.g.flat && grid == AXS6_GRID_NF5 && block == 32 && tune_value(11) != 1) {
         const int r = out_dtype == AXS6_F32 ? bulk::launch_unpack_bulk<float>(in0, y, rows * (cols / 32), a.hdr, st)
                                             : bulk::launch_unpack_bulk<__nv_bfloat16>(in0, y, rows * (cols / 32), a.hdr, st);
         if (r != 1) return r;
@@ -1304,10 +1300,14 @@ AXS6_API int axs6_codec_status(void)
 {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, axs6::bulk::g_codec_status, sizeof(int)) != cudaSuccess) return AXS6_ERR_DEVICE;
-    if (v != 0) cudaMemcpyToSymbol(axs6::bulk::g_codec_status, &zero, sizeof(int));
+    // Only the word that is reported is cleared: a second failure recorded in another word stays for the next call.
+    if (v != 0) {
+        cudaMemcpyToSymbol(axs6::bulk::g_codec_status, &zero, sizeof(int));
+        return v;
+    }
     const int x = axs6::exchange_status_fetch();
-    if (x < 0) return x;
+    if (x != 0) return x < 0 ? x : 10 + x;
     const int q = axs6::fq_status_fetch();
-    if (q < 0) return q;
-    return v != 0 ? v : (x != 0 ? 10 + x : (q != 0 ? 20 + q : 0));
+    if (q != 0) return q < 0 ? q : 20 + q;
+    return 0;
 }

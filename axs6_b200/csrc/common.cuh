@@ -24,6 +24,9 @@ void count_launch(int n = 1);         // bookkeeping behind axs6_query(3)
 int64_t tune_value(int key);          // axs6_tune() knobs (0 = default)
 // cudaOccupancyMaxActiveBlocksPerMultiprocessor, remembered per (kernel, device); 0 on error
 int cached_occupancy(const void *kernel, int threads);
+// cudaFuncSetAttribute(kernel, max dynamic shared memory, bytes), done once per (kernel, device) under a
+// lock, so concurrent first calls from several host threads are safe.  false on error.
+bool ensure_dynamic_smem(const void *kernel, int bytes);
 // Device address of this device's Philox epoch counter (added to every stochastic kernel's offset; see
 // axs6_philox_advance).  nullptr on error.
 const unsigned long long *philox_epoch_ptr();
@@ -31,6 +34,10 @@ const unsigned long long *philox_epoch_ptr();
 int gemm_launch(bool tf32, const void *a, const void *b, void *c, const float *bias, int64_t M, int64_t N, int64_t K,
                 int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn, int c_dtype, int bias_via_bf16,
                 cudaStream_t stream);
+
+int gemm_packed_launch(const void *a, const void *a_exps, int64_t lda, const void *b, const void *b_exps, int64_t ldb, void *c,
+                       const float *bias, int64_t M, int64_t N, int64_t K, int64_t ldc, int a_mn, int b_mn, int c_dtype,
+                       int bias_via_bf16, cudaStream_t stream);
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -260,15 +260,9 @@ static int launch_bulk(const uint8_t *in, int64_t nsrc, int64_t src_stride, void
     if (cap > 0 && cap < per_sm) per_sm = (int)cap;
     if (ctas > (int64_t)d.sms * per_sm) ctas = (int64_t)d.sms * per_sm;
     if (ctas < 1) ctas = 1;
-    static bool attr_done[64] = {};
-    int dev_id = 0;
-    if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= 64) return 1;
-    if (!attr_done[dev_id]) {
-        if (cudaFuncSetAttribute(unpack_sum_bulk_kernel<Tout, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<Tout, 1>()) != cudaSuccess ||
-            cudaFuncSetAttribute(unpack_sum_bulk_kernel<Tout, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<Tout, 2>()) != cudaSuccess)
-            return AXS6_ERR_LAUNCH;
-        attr_done[dev_id] = true;
-    }
+    if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&unpack_sum_bulk_kernel<Tout, 1>), smem_bytes<Tout, 1>()) ||
+        !ensure_dynamic_smem(reinterpret_cast<const void *>(&unpack_sum_bulk_kernel<Tout, 2>), smem_bytes<Tout, 2>()))
+        return AXS6_ERR_LAUNCH;
     if (hdr == 1) unpack_sum_bulk_kernel<Tout, 1><<<(unsigned)ctas, kThreadsX, smem_bytes<Tout, 1>(), st>>>(map, in, nsrc, src_stride, nblocks, divisor);
     else          unpack_sum_bulk_kernel<Tout, 2><<<(unsigned)ctas, kThreadsX, smem_bytes<Tout, 2>(), st>>>(map, in, nsrc, src_stride, nblocks, divisor);
     count_launch();

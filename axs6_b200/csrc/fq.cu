@@ -477,15 +477,9 @@ static int launch(const void *x, void *y, int64_t nblocks, int round, uint64_t s
     if (cap > 0 && cap < per_sm) per_sm = (int)cap;
     if (ctas > (int64_t)d.sms * per_sm) ctas = (int64_t)d.sms * per_sm;
     if (ctas < 1) ctas = 1;
-    static bool attr_done[64] = {};
-    int dev_id = 0;
-    if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= 64) return 1;
-    if (!attr_done[dev_id]) {
-        if (cudaFuncSetAttribute(fq_bf16_nf5_b32_bulk_kernel<kNearest>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
-            cudaFuncSetAttribute(fq_bf16_nf5_b32_bulk_kernel<kPhilox>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-            return AXS6_ERR_LAUNCH;
-        attr_done[dev_id] = true;
-    }
+    if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&fq_bf16_nf5_b32_bulk_kernel<kNearest>), kSmemBytes) ||
+        !ensure_dynamic_smem(reinterpret_cast<const void *>(&fq_bf16_nf5_b32_bulk_kernel<kPhilox>), kSmemBytes))
+        return AXS6_ERR_LAUNCH;
     const Axs6PhiloxKeys keys = axs6_philox_keys(seed);
     if (round == kNearest) fq_bf16_nf5_b32_bulk_kernel<kNearest><<<(unsigned)ctas, kBlocksB, kSmemBytes, st>>>(xm, ym, nblocks, 0, 0, nullptr, keys);
     else                   fq_bf16_nf5_b32_bulk_kernel<kPhilox><<<(unsigned)ctas, kBlocksB, kSmemBytes, st>>>(xm, ym, nblocks, seed, offset, epoch, keys);

@@ -126,12 +126,11 @@ __device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn, uint32_t fmt)
 
 // Drains one 128 x 256 fp32 accumulator: this thread owns TMEM lane (= output row) `row` and walks
 // the 256 columns in chunks of 32 (tcgen05.ld 32x32b.x32), adds the bias, converts and stores.
-template <int TN = BN>
 __device__ __forceinline__ void epilogue_tile(const Params &p, uint32_t taddr, int row, int n0, bool vec_ok,
                                               bool accumulate = false, bool add_bias = true)
 {
 #pragma unroll 1
-    for (int c = 0; c < TN / 32; ++c) {
+    for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         AXS6_TMEM_LD32(taddr + (uint32_t)(c * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -337,11 +336,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 //     with a second tcgen05.commit, to the peer's barrier at the same offset;
 //   * "accumulator drained" arrives on the leader's barrier from the epilogue warps of both CTAs.
 // All waits are bounded as in the 1-CTA kernel.
-// Tile width TN is 256, or 128 for problems whose 256-wide tiles fill the last wave of clusters badly
-// (e.g. a 4096 x 4096 weight gradient: 256 tile pairs on 74 clusters = 3.46 waves; 512 narrower
-// pairs = 6.92 waves).
-template <int TN> struct Pair {
-    static constexpr int kStages = TN == 256 ? 6 : 8;
+struct Pair {
+    static constexpr int TN = 256;                             // tile width
+    static constexpr int kStages = 6;
     static constexpr int kABytes = 128 * BK * 2;               // this CTA's 128 rows of A
     static constexpr int kBBytes = (TN / 2) * BK * 2;          // this CTA's half of the TN output columns of B
     static constexpr int kStageBytes = kABytes + kBBytes;
@@ -385,11 +382,11 @@ __device__ __forceinline__ void tc_mma2(uint32_t tmem_d, uint64_t adesc, uint64_
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-template <int TN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsGemm, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p)
 {
-    constexpr int kStages2 = Pair<TN>::kStages, kA2Bytes = Pair<TN>::kABytes, kStage2Bytes = Pair<TN>::kStageBytes;
+    constexpr int TN = Pair::TN;
+    constexpr int kStages2 = Pair::kStages, kA2Bytes = Pair::kABytes, kStage2Bytes = Pair::kStageBytes;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar0 = base + kStages2 * kStage2Bytes;
@@ -517,7 +514,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TN);
-            epilogue_tile<TN>(p, taddr, row, n0, vec_ok, unit_split(t), unit_part(t) == 0);
+            epilogue_tile(p, taddr, row, n0, vec_ok, unit_split(t), unit_part(t) == 0);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
@@ -534,6 +531,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
+
+#include "gemm_packed_kernel.cuh"
 
 // ------------------------------------------------------------------------------------- host
 using acp::EncodeTiledFn;
@@ -556,6 +555,97 @@ static bool make_map(CUtensorMap *map, const void *ptr, int esize, uint64_t inne
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+
+
+// SMs the GEMM may use: all of them, minus the reserve of tune key 8 (left to a collective on another stream).
+static int64_t usable_sms(const DeviceInfo &d)
+{
+    const int64_t r = tune_value(8);
+    return d.sms - (r > 0 && r < d.sms - 2 ? r : 0);
+}
+
+// 2-D tensor map over a plane of payload bytes: rows of `pitch` bytes, box = {box_bytes, box_rows}, no swizzle,
+// bytes outside the plane read as zero.
+static bool make_byte_map(CUtensorMap *map, const void *ptr, uint64_t pitch, uint64_t rows, uint32_t box_bytes, uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t gdim[2] = {pitch, rows};
+    const cuuint64_t gstride[1] = {pitch};
+    const cuuint32_t box[2] = {box_bytes, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), gdim, gstride, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// C = op(A) op(B) where an operand with a non-null exponent plane is held as AXS-6 codes in the split layout
+// (blocks of 32 along its contiguous dimension) and decoded to bf16 inside the kernel.
+static int launch_gemm_packed(const void *a, const void *a_exps, int64_t lda, const void *b, const void *b_exps, int64_t ldb,
+                              void *c, const float *bias, int64_t M, int64_t N, int64_t K, int64_t ldc, int a_mn, int b_mn,
+                              int c_dtype, int bias_via_bf16, cudaStream_t stream)
+{
+    if (M < 0 || N < 0 || K < 0 || (a_mn & ~1) || (b_mn & ~1) || !valid_dtype(c_dtype)) return AXS6_ERR_ARG;
+    if (M == 0 || N == 0) return AXS6_OK;
+    if (!a || !b || !c || K == 0 || ldc < N) return AXS6_ERR_ARG;
+    if (!a_exps && !b_exps) return AXS6_ERR_ARG;                 // nothing packed: axs6_gemm_bf16 is the entry point
+    if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return AXS6_ERR_UNSUPPORTED;
+    if (!aligned16(a) || !aligned16(b)) return AXS6_ERR_ALIGN;
+    const DeviceInfo &d = device_info();
+    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+    // stored shape of each operand: (rows, cols) with cols contiguous
+    const int64_t a_rows = a_mn ? K : M, a_cols = a_mn ? M : K;
+    const int64_t b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;
+    CUtensorMap ma, mb;
+    PackedParams q;
+    q.a_exps = static_cast<const uint8_t *>(a_exps); q.b_exps = static_cast<const uint8_t *>(b_exps);
+    q.a_nblk = (int)(a_cols / 32); q.b_nblk = (int)(b_cols / 32);
+    q.a_rows = (int)a_rows; q.b_rows = (int)b_rows;
+    bool ok = true;
+    if (a_exps) {
+        if (a_cols % 64) return AXS6_ERR_UNSUPPORTED;            // payload rows must be 16-byte multiples
+        ok = ok && make_byte_map(&ma, a, (uint64_t)a_cols * 3 / 4, (uint64_t)a_rows, a_mn ? 96 : 48, a_mn ? 64 : 128);
+    } else {
+        if (lda < a_cols) return AXS6_ERR_ARG;
+        if ((lda * 2) % 16) return AXS6_ERR_ALIGN;
+        ok = ok && (a_mn ? make_map(&ma, a, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BK)
+                         : make_map(&ma, a, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 128));
+    }
+    if (b_exps) {
+        if (b_cols % 64) return AXS6_ERR_UNSUPPORTED;
+        ok = ok && make_byte_map(&mb, b, (uint64_t)b_cols * 3 / 4, (uint64_t)b_rows, b_mn ? 96 : 48, b_mn ? 64 : 128);
+    } else {
+        if (ldb < b_cols) return AXS6_ERR_ARG;
+        if ((ldb * 2) % 16) return AXS6_ERR_ALIGN;
+        ok = ok && (b_mn ? make_map(&mb, b, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BK)
+                         : make_map(&mb, b, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 128));
+    }
+    if (!ok) return AXS6_ERR_DEVICE;
+
+    Params p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.a_mn = a_mn; p.b_mn = b_mn;
+    p.c = c; p.ldc = ldc; p.c_bf16 = (c_dtype == AXS6_BF16) ? 1 : 0;
+    p.bias = bias; p.bias_bf16 = bias_via_bf16;
+    p.tiles_m = (int)((M + BM - 1) / BM); p.tiles_n = (int)((N + BN - 1) / BN);
+    p.bk = BK; p.mn_box_bytes = 128u * BK; p.splits = 1; p.tail_begin = 0;
+    p.a_lbo = a_mn ? p.mn_box_bytes : 0u; p.a_sbo = 1024u; p.a_kstep = a_mn ? 16u * 128u : 32u;
+    p.b_lbo = b_mn ? p.mn_box_bytes : 0u; p.b_sbo = 1024u; p.b_kstep = b_mn ? 16u * 128u : 32u;
+
+    const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    const int64_t usable = usable_sms(d);
+    const int clusters = (int)(pair_tiles < usable / 2 ? pair_tiles : usable / 2);
+    const void *kern = a_exps && b_exps ? reinterpret_cast<const void *>(&gemm2q_kernel<true, true>)
+                       : a_exps        ? reinterpret_cast<const void *>(&gemm2q_kernel<true, false>)
+                                       : reinterpret_cast<const void *>(&gemm2q_kernel<false, true>);
+    if (!ensure_dynamic_smem(kern, PairQ::kSmemBytes)) return AXS6_ERR_LAUNCH;
+    if (a_exps && b_exps) gemm2q_kernel<true, true><<<2 * clusters, kThreadsPacked, PairQ::kSmemBytes, stream>>>(ma, mb, p, q);
+    else if (a_exps)      gemm2q_kernel<true, false><<<2 * clusters, kThreadsPacked, PairQ::kSmemBytes, stream>>>(ma, mb, p, q);
+    else                  gemm2q_kernel<false, true><<<2 * clusters, kThreadsPacked, PairQ::kSmemBytes, stream>>>(ma, mb, p, q);
+    count_launch();
+    return check_launch();
+}
+
 template <bool kTf32>
 static int launch_gemm(const void *a, const void *b, void *c, const float *bias, int64_t M, int64_t N, int64_t K,
                        int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn, int c_dtype, int bias_via_bf16,
@@ -572,43 +662,37 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     const DeviceInfo &d = device_info();
     if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
 
-    // bf16: CTA pairs on 256 x 256 tiles when there are enough of them to fill the GPU
-    // (tune key 7: 1 forces the single-CTA kernel, 2 forces pairs)
-    int64_t pair_tiles = ((M + 255) / 256) * ((N + BN - 1) / BN);
-    const int64_t mode = tune_value(7);
+    // Split policy (fp32 output only; partial products are added into the zero-filled output with red.add).
+    // Built-in: at most TWO partials per output element, whose sum does not depend on their order, so every
+    // result is bit-reproducible.  Tune key 3: 1 = never split, 2 = two-way split of every tile of the CTA-pair
+    // kernel, 3 = allow up to 8 (pairs) / 16 (single CTA) partials, added in no fixed order (last bits can
+    // differ from run to run).
+    const int64_t split_mode = tune_value(3);
+    const int64_t max_pair_splits = split_mode == 3 ? 8 : 2, max_cta_splits = split_mode == 3 ? 16 : 2;
+    const bool may_split = c_dtype == AXS6_F32 && split_mode != 1;
+
+    // bf16: CTA pairs on 256 x 256 tiles (tune key 7: 1 forces the single-CTA kernel, 2 forces pairs).
     // Fewer pair tiles than clusters: pairs still win over the single-CTA kernel when at least a quarter of the
-    // clusters get a tile (a pair reads a third of the bytes per flop from L2, and the single-CTA kernel on
-    // 4096 x 1024 x 8192 was bound by that feed: 140 us), or when the output is fp32 and the contraction can be
-    // split so that most clusters get a unit (weight gradients of small layers).  More than two partials are
-    // added in no fixed order, so the last bits can differ between runs; tune key 3 = 1 forbids splits.
+    // clusters get a tile (a pair reads a third fewer bytes per flop from L2, and the single-CTA kernel on
+    // 4096 x 1024 x 8192 was bound by that feed), or when the contraction can be split so that more clusters
+    // get a unit (weight gradients of small layers).
+    const int64_t pair_tiles = ((M + 255) / 256) * ((N + Pair::TN - 1) / Pair::TN);
+    const int64_t mode = tune_value(7);
     int64_t pair_splits = 1;
-    if (!kTf32 && c_dtype == AXS6_F32 && tune_value(3) == 0 && pair_tiles < d.sms / 2) {
+    if (!kTf32 && may_split && pair_tiles < d.sms / 2) {
         const int64_t total_kb = (K + BK - 1) / BK;
         pair_splits = (d.sms / 2) / pair_tiles;
         if (pair_splits > total_kb / 16) pair_splits = total_kb / 16;
-        if (pair_splits > 8) pair_splits = 8;
+        if (pair_splits > max_pair_splits) pair_splits = max_pair_splits;
         if (pair_splits < 1) pair_splits = 1;
     }
-    const bool pairs = !kTf32 && mode != 1 && (mode == 2 || mode == 3 || pair_tiles * pair_splits >= d.sms / 4);
-    // 128-wide tiles: only through tune key 7 = 3.  Measured on the 4096 x 4096 x 16384 weight-gradient
-    // product they fill the waves better (6.92 of 7 instead of 3.46 of 4) but run at 806 instead of
-    // 1246 TFLOP/s: the per-k-block costs of the single producer and issuer threads no longer hide.
-    bool narrow = false;
-    if (pairs) {
-        const int64_t clusters = d.sms / 2;
-        const int64_t narrow_tiles = ((M + 255) / 256) * ((N + 127) / 128);
-        const double eff_wide = (double)pair_tiles / (double)(((pair_tiles + clusters - 1) / clusters) * clusters);
-        const double eff_narrow = (double)narrow_tiles / (double)(((narrow_tiles + clusters - 1) / clusters) * clusters);
-        narrow = mode == 3;
-        (void)eff_wide; (void)eff_narrow;
-        if (narrow) pair_tiles = narrow_tiles;
-    }
+    const bool pairs = !kTf32 && mode != 1 && (mode == 2 || pair_tiles * pair_splits >= d.sms / 4);
 
     CUtensorMap ma, mb;
     const bool oka = a_mn ? make_map(&ma, a, esize, (uint64_t)M, (uint64_t)K, (uint64_t)lda, bk)
                           : make_map(&ma, a, esize, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM);
     const bool okb = b_mn ? make_map(&mb, b, esize, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, bk)
-                          : make_map(&mb, b, esize, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, pairs ? (narrow ? 64 : 128) : BN);
+                          : make_map(&mb, b, esize, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, pairs ? Pair::TN / 2 : BN);
     if (!oka || !okb) return AXS6_ERR_DEVICE;
 
     Params p;
@@ -621,65 +705,31 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     p.tiles_n = (int)((N + BN - 1) / BN);
     p.bk = bk;
     p.mn_box_bytes = 128u * bk;
-    // Split K in two (fp32 output only): available through tune key 3 = 2.  Measured on the
-    // 4096 x 4096 x 16384 weight-gradient product (256 tile pairs on 74 clusters = 3.46 waves) it is
-    // slower than not splitting (452 vs 436 us: the zero-fill and the red.add traffic cost more than
-    // the better-filled last wave gains), so it is never chosen automatically.
-    p.splits = (pairs && c_dtype == AXS6_F32 && tune_value(3) == 2 && K >= 16 * BK) ? 2 : 1;
-    if (pairs && pair_splits > 1 && mode != 3) p.splits = (int)pair_splits;
+    p.splits = 1;
     p.tail_begin = 0;
-    // Few output tiles but a long contraction (the weight gradient of a small layer: 1024 x 1024 from
-    // 8192 rows is 32 tiles for 148 SMs): split K so that about one work unit per SM exists; the
-    // partial products are added into the zero-filled fp32 output with red.add.  The order of more than
-    // two partials is not fixed, so results can differ in the last bits between runs; tune key 3 = 1
-    // turns this off.
-    if (!pairs && c_dtype == AXS6_F32 && tune_value(3) != 1) {
-        const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
-        int64_t want = d.sms / tiles;
-        const int64_t max_by_k = K / (8 * bk);
-        if (want > max_by_k) want = max_by_k;
-        if (want > 16) want = 16;
-        if (want >= 2) p.splits = (int)want;
-    }
     // K-major, 128-byte swizzle: 8-row groups are 1024 B apart, one MMA K step is 32 B.
     // MN-major: 128-byte chunks of the output index are one TMA box (bk k-rows x 128 B) apart,
     // groups of 8 k-rows 1024 B apart, one MMA K step (32 B / esize rows) is that many rows x 128 B.
     const uint32_t mn_kstep = (32u / esize) * 128u;
     p.a_lbo = a_mn ? p.mn_box_bytes : 0u; p.a_sbo = 1024u; p.a_kstep = a_mn ? mn_kstep : 32u;
     p.b_lbo = b_mn ? p.mn_box_bytes : 0u; p.b_sbo = 1024u; p.b_kstep = b_mn ? mn_kstep : 32u;
-    if (tune_value(4)) p.a_lbo = p.b_lbo = (uint32_t)tune_value(4);
-    if (tune_value(5)) p.a_sbo = p.b_sbo = (uint32_t)tune_value(5);
-    if (tune_value(6)) { if (a_mn) p.a_kstep = (uint32_t)tune_value(6); if (b_mn) p.b_kstep = (uint32_t)tune_value(6); }
 
-    static bool attr_set[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(gemm_kernel<kTf32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-            return AXS6_ERR_LAUNCH;
-        attr_set[dev] = true;
-    }
     if (pairs) {
-        static bool attr2_set[64];
-        if (dev >= 0 && dev < 64 && !attr2_set[dev]) {
-            if (cudaFuncSetAttribute(gemm2_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, Pair<256>::kSmemBytes) != cudaSuccess ||
-                cudaFuncSetAttribute(gemm2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Pair<128>::kSmemBytes) != cudaSuccess)
-                return AXS6_ERR_LAUNCH;
-            attr2_set[dev] = true;
-        }
+        if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm2_kernel), Pair::kSmemBytes)) return AXS6_ERR_LAUNCH;
+        if (may_split && split_mode == 2 && K >= 16 * BK) p.splits = 2;
+        if (pair_splits > 1) p.splits = (int)pair_splits;
         const int64_t units = pair_tiles * p.splits;
-        // tune key 8: SMs to leave to other work (a collective running on another stream)
-        const int64_t usable = d.sms - (tune_value(8) > 0 && tune_value(8) < d.sms - 2 ? tune_value(8) : 0);
-        int clusters = (int)(units < usable / 2 ? units : usable / 2);
-        // Tail split (fp32 output, long contraction; tune key 3 = 1 turns it off): when the last wave would be
-        // at most half full, its tiles are computed as two K halves each, so that wave takes half the time.
-        // Weight gradient 4096 x 4096 x 16384: 256 tiles on 74 clusters, 3 full waves + 34 tiles -> 68 half
-        // units: 3.5 waves instead of 4.  The rows that hold those tiles are zero-filled first.
-        if (!narrow && p.splits == 1 && c_dtype == AXS6_F32 && tune_value(3) != 1 && K >= 32 * BK && pair_tiles > clusters) {
+        const int64_t usable = usable_sms(d);
+        const int clusters = (int)(units < usable / 2 ? units : usable / 2);
+        // Tail split (long contraction): when the last wave of tiles would be at most half full, its tiles are
+        // computed as two K halves each, so that wave takes half the time.  Weight gradient 4096 x 4096 x 16384:
+        // 256 tiles on 74 clusters, 3 full waves + 34 tiles -> 68 half units: 3.5 waves instead of 4.  The rows
+        // that hold those tiles are zero-filled first.
+        if (p.splits == 1 && may_split && K >= 32 * BK && pair_tiles > clusters) {
             const int64_t rem = pair_tiles % clusters;
             if (rem > 0 && 2 * rem <= clusters) {
                 p.tail_begin = (int)(pair_tiles - rem);
-                const int64_t tiles_n2 = (N + 255) / 256;
+                const int64_t tiles_n2 = (N + Pair::TN - 1) / Pair::TN;
                 const int64_t row0 = (p.tail_begin / tiles_n2) * 256;
                 if (cudaMemset2DAsync(static_cast<float *>(c) + row0 * ldc, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)(M - row0),
                                       stream) != cudaSuccess)
@@ -689,18 +739,24 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
         if (p.splits > 1 &&
             cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess)
             return AXS6_ERR_LAUNCH;
-        if (narrow)
-            gemm2_kernel<128><<<2 * clusters, kThreadsGemm, Pair<128>::kSmemBytes, stream>>>(ma, mb, p);
-        else
-            gemm2_kernel<256><<<2 * clusters, kThreadsGemm, Pair<256>::kSmemBytes, stream>>>(ma, mb, p);
+        gemm2_kernel<<<2 * clusters, kThreadsGemm, Pair::kSmemBytes, stream>>>(ma, mb, p);
         count_launch();
         return check_launch();
     }
-    int ctas = p.tiles_m * p.tiles_n * p.splits;
-    {
-        const int64_t usable = d.sms - (tune_value(8) > 0 && tune_value(8) < d.sms - 2 ? tune_value(8) : 0);
-        if (ctas > usable) ctas = (int)usable;
+
+    if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm_kernel<kTf32>), kSmemBytes)) return AXS6_ERR_LAUNCH;
+    // Few output tiles but a long contraction (the weight gradient of a small layer): split K so that more SMs
+    // get a work unit.
+    if (may_split) {
+        const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+        int64_t want = d.sms / tiles;
+        const int64_t max_by_k = K / (8 * bk);
+        if (want > max_by_k) want = max_by_k;
+        if (want > max_cta_splits) want = max_cta_splits;
+        if (want >= 2) p.splits = (int)want;
     }
+    int ctas = p.tiles_m * p.tiles_n * p.splits;
+    if (ctas > usable_sms(d)) ctas = (int)usable_sms(d);
     if (p.splits > 1 &&
         cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess)
         return AXS6_ERR_LAUNCH;
@@ -722,7 +778,22 @@ int gemm_launch(bool tf32, const void *a, const void *b, void *c, const float *b
     return gemm::launch_gemm<false>(a, b, c, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, c_dtype, bias_via_bf16, stream);
 }
 
+int gemm_packed_launch(const void *a, const void *a_exps, int64_t lda, const void *b, const void *b_exps, int64_t ldb, void *c,
+                       const float *bias, int64_t M, int64_t N, int64_t K, int64_t ldc, int a_mn, int b_mn, int c_dtype,
+                       int bias_via_bf16, cudaStream_t stream)
+{
+    return gemm::launch_gemm_packed(a, a_exps, lda, b, b_exps, ldb, c, bias, M, N, K, ldc, a_mn, b_mn, c_dtype, bias_via_bf16, stream);
+}
+
 }  // namespace axs6
+
+AXS6_API int axs6_gemm_packed(const void *a, const void *a_exps, int64_t lda, const void *b, const void *b_exps, int64_t ldb,
+                              void *c, const float *bias, int64_t M, int64_t N, int64_t K, int64_t ldc, int a_mn, int b_mn,
+                              int c_dtype, axs6_stream_t stream)
+{
+    return axs6::gemm::launch_gemm_packed(a, a_exps, lda, b, b_exps, ldb, c, bias, M, N, K, ldc, a_mn, b_mn, c_dtype, 0,
+                                          static_cast<cudaStream_t>(stream));
+}
 
 // C[M,N] (+ bias[N]) = op(A) * op(B) with bf16 operands and fp32 accumulation.
 //   a_mn = 0: A is (M, K) row-major with leading dimension lda;  a_mn = 1: A is (K, M) row-major.

@@ -2,8 +2,8 @@
 // fake-quantise the operands to bf16 (one HBM pass each), then the tcgen05 GEMMs.
 //
 //   forward   xq = FQ(bf16(x))  wq = FQ(bf16(w))  y = xq wq^T + bias
-//   backward  wq = FQ(bf16(w))  gq = FQ_stochastic(bf16(g))  dx = gq wq  dw = gq^T xq (fp32)
-//             db = column sums of the un-quantised g (fp32)
+//   backward  gq = FQ_stochastic(bf16(g))  dw = gq^T xq (fp32)  wq = FQ(bf16(w)) (or the forward's, reused)
+//             dx = gq wq  db = column sums of the un-quantised g (fp32)
 // This is the graph of _AXSLinearBF16Function (axs/unified/mixed_precision.py:86-155).  xq is
 // materialised because backward needs it (the reference saves input_q); gq is materialised
 // because dx and dw must see the same stochastic rounding (the reference quantises once).
@@ -228,6 +228,20 @@ static int column_sums(const void *g, int dtype, float *out, float *partial, int
 }
 
 static int64_t round_up8(int64_t v) { return (v + 7) / 8 * 8; }
+// A (rows, cols) operand held as codes: the payload plane (rows * cols/32 * 24 bytes, rounded up to 256) followed by
+// the exponent plane (rows * cols/32 bytes).
+static int64_t packed_exps_offset(int64_t rows, int64_t cols) { return (rows * ((cols + 31) / 32) * 24 + 255) / 256 * 256; }
+static int64_t packed_bytes(int64_t rows, int64_t cols) { return packed_exps_offset(rows, cols) + rows * ((cols + 31) / 32); }
+static int pack_operand(const void *x, int dtype, int64_t rows, int64_t cols, int64_t ld, int rounding, uint64_t seed,
+                        uint64_t offset, const float *noise, void *ws, axs6_stream_t stream)
+{
+    return axs6_pack(x, dtype, rows, cols, ld, 32, AXS6_GRID_NF5, rounding, AXS6_FLAG_INPUT_VIA_BF16, seed, offset, noise,
+                     AXS6_LAYOUT_SPLIT, ws, static_cast<uint8_t *>(ws) + packed_exps_offset(rows, cols), nullptr, stream);
+}
+static const void *exps_of(const void *ws, int64_t rows, int64_t cols)
+{
+    return static_cast<const uint8_t *>(ws) + packed_exps_offset(rows, cols);
+}
 static int64_t round_up4(int64_t v) { return (v + 3) / 4 * 4; }
 
 }  // namespace axs6
@@ -258,6 +272,9 @@ AXS6_API int64_t axs6_linear_workspace_bytes(int what, int64_t M, int64_t N, int
     case 5: return N * round_up4(K) * 4;            // wq, TF32 path
     case 6: return M * round_up4(N) * 4;            // gq, TF32 path
     case 7: return (K * round_up4(N) + N * round_up4(M) + K * round_up4(M)) * 4;   // transposes, TF32 backward
+    case 8: return packed_bytes(M, K);              // xq as codes (AXS6_LINEAR_OPERANDS_PACKED)
+    case 9: return packed_bytes(N, K);              // wq as codes
+    case 10: return packed_bytes(M, N);             // gq as codes
     default: return -1;
     }
 }
@@ -270,11 +287,25 @@ AXS6_API int axs6_linear_fwd(const void *x, int x_dtype, int64_t ldx, const void
     if (!valid_dtype(x_dtype) || !valid_dtype(w_dtype) || !valid_dtype(y_dtype) || !valid_block(block)) return AXS6_ERR_ARG;
     if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
     if (M < 0 || N < 0 || K < 0 || ldx < K || ldw < K || ldy < N) return AXS6_ERR_ARG;
-    if (flags & ~(AXS6_LINEAR_QUANTIZE_INPUT | AXS6_LINEAR_COMPUTE_TF32 | AXS6_LINEAR_BIAS_VIA_BF16)) return AXS6_ERR_ARG;
+    if (flags & ~(AXS6_LINEAR_QUANTIZE_INPUT | AXS6_LINEAR_COMPUTE_TF32 | AXS6_LINEAR_BIAS_VIA_BF16 | AXS6_LINEAR_OPERANDS_PACKED))
+        return AXS6_ERR_ARG;
     if (M == 0 || N == 0) return AXS6_OK;
     if (!x || !w || !y || !xq || !wq || K == 0) return AXS6_ERR_ARG;
     if (!aligned16(xq) || !aligned16(wq)) return AXS6_ERR_ALIGN;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (flags & AXS6_LINEAR_OPERANDS_PACKED) {
+        // quantise on load: both operands go to HBM as 6-bit codes (0.78 bytes per value) and are decoded to bf16
+        // inside the GEMM; xq (codes) is what backward keeps
+        if ((flags & AXS6_LINEAR_COMPUTE_TF32) || !(flags & AXS6_LINEAR_QUANTIZE_INPUT) || block != 32 || grid != AXS6_GRID_NF5 ||
+            K % 64 || N % 64)
+            return AXS6_ERR_UNSUPPORTED;
+        int rcp = pack_operand(w, w_dtype, N, K, ldw, AXS6_ROUND_NEAREST, 0, 0, nullptr, wq, stream);
+        if (rcp) return rcp;
+        rcp = pack_operand(x, x_dtype, M, K, ldx, AXS6_ROUND_NEAREST, 0, 0, nullptr, xq, stream);
+        if (rcp) return rcp;
+        return gemm_packed_launch(xq, exps_of(xq, M, K), 0, wq, exps_of(wq, N, K), 0, y, bias, M, N, K, ldy, 0, 0, y_dtype,
+                                  (flags & AXS6_LINEAR_BIAS_VIA_BF16) ? 1 : 0, st);
+    }
     if (flags & AXS6_LINEAR_COMPUTE_TF32) {
         // fp32 graph (axs/unified/functional_unified.py:107-131, axs/nn/functional.py:101-129): operands
         // fake-quantised in fp32, rounded to TF32, product on the TF32 tensor cores
@@ -314,10 +345,14 @@ AXS6_API int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void
     if (!valid_dtype(g_dtype) || !valid_dtype(w_dtype) || !valid_block(block)) return AXS6_ERR_ARG;
     if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
     if (M < 0 || N < 0 || K < 0 || ldg < N) return AXS6_ERR_ARG;
-    if (flags & ~(AXS6_LINEAR_QUANTIZE_GRAD | AXS6_LINEAR_COMPUTE_TF32 | AXS6_LINEAR_BIAS_FROM_QUANTIZED)) return AXS6_ERR_ARG;
+    if (flags & ~(AXS6_LINEAR_QUANTIZE_GRAD | AXS6_LINEAR_COMPUTE_TF32 | AXS6_LINEAR_BIAS_FROM_QUANTIZED |
+                  AXS6_LINEAR_REUSE_WQ | AXS6_LINEAR_REUSE_GQ | AXS6_LINEAR_OPERANDS_PACKED))
+        return AXS6_ERR_ARG;
+    if ((flags & AXS6_LINEAR_COMPUTE_TF32) && (flags & (AXS6_LINEAR_REUSE_WQ | AXS6_LINEAR_REUSE_GQ))) return AXS6_ERR_UNSUPPORTED;
     if (M == 0 || N == 0 || K == 0) return AXS6_OK;
     if (!g || !gq) return AXS6_ERR_ARG;
-    if (dx && (!w || !wq || !valid_dtype(dx_dtype) || lddx < K || ldw < K)) return AXS6_ERR_ARG;
+    if (dx && (!wq || !valid_dtype(dx_dtype) || lddx < K)) return AXS6_ERR_ARG;
+    if (dx && !(flags & AXS6_LINEAR_REUSE_WQ) && (!w || ldw < K)) return AXS6_ERR_ARG;
     if (dw && (!xq || lddw < K)) return AXS6_ERR_ARG;
     if (db && !db_partial) return AXS6_ERR_WORKSPACE;
     if (!aligned16(gq) || (wq && !aligned16(wq)) || (xq && !aligned16(xq))) return AXS6_ERR_ALIGN;
@@ -366,8 +401,38 @@ AXS6_API int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void
         }
         return AXS6_OK;
     }
+    if (flags & AXS6_LINEAR_OPERANDS_PACKED) {
+        if ((flags & (AXS6_LINEAR_COMPUTE_TF32 | AXS6_LINEAR_BIAS_FROM_QUANTIZED)) || !(flags & AXS6_LINEAR_QUANTIZE_GRAD) ||
+            block != 32 || grid != AXS6_GRID_NF5 || K % 64 || N % 64)
+            return AXS6_ERR_UNSUPPORTED;
+        if (!(flags & AXS6_LINEAR_REUSE_GQ)) {
+            rc = pack_operand(g, g_dtype, M, N, ldg, AXS6_ROUND_STOCHASTIC, seed, offset, noise, gq, stream);
+            if (rc) return rc;
+        }
+        if (dw) {       // dw (N, K) = gq^T xq: both operands stored (contraction, output), blocks along the output index
+            rc = gemm_packed_launch(gq, exps_of(gq, M, N), 0, xq, exps_of(xq, M, K), 0, dw, nullptr, N, K, M, lddw, 1, 1,
+                                    AXS6_F32, 0, st);
+            if (rc) return rc;
+        }
+        if (dx) {
+            if (!(flags & AXS6_LINEAR_REUSE_WQ)) {
+                rc = pack_operand(w, w_dtype, N, K, ldw, AXS6_ROUND_NEAREST, 0, 0, nullptr, wq, stream);
+                if (rc) return rc;
+            }
+            rc = gemm_packed_launch(gq, exps_of(gq, M, N), 0, wq, exps_of(wq, N, K), 0, dx, nullptr, M, K, N, lddx, 0, 1,
+                                    dx_dtype, 0, st);
+            if (rc) return rc;
+        }
+        if (db) {
+            rc = axs6_bias_grad(g, g_dtype, ldg, M, N, db, db_partial, stream);
+            if (rc) return rc;
+        }
+        return AXS6_OK;
+    }
     const int64_t ldq = round_up8(K), ldgq = round_up8(N);
-    if (flags & AXS6_LINEAR_QUANTIZE_GRAD) {
+    if (flags & AXS6_LINEAR_REUSE_GQ) {
+        rc = AXS6_OK;            // gq holds the quantised gradient of an earlier call on the same g
+    } else if (flags & AXS6_LINEAR_QUANTIZE_GRAD) {
         rc = noise ? axs6_fq_with_noise(g, gq, g_dtype, AXS6_BF16, M, N, ldg, ldgq, block, grid,
                                         AXS6_FLAG_INPUT_VIA_BF16, noise, stream)
                    : axs6_fq(g, gq, g_dtype, AXS6_BF16, M, N, ldg, ldgq, block, grid, AXS6_ROUND_STOCHASTIC,
@@ -376,17 +441,22 @@ AXS6_API int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void
         rc = cast_to_bf16(g, g_dtype, gq, M, N, ldg, ldgq, st);
     }
     if (rc) return rc;
-    if (dx) {
-        rc = axs6_fq(w, wq, w_dtype, AXS6_BF16, N, K, ldw, ldq, block, grid, AXS6_ROUND_NEAREST,
-                     AXS6_FLAG_INPUT_VIA_BF16, 0, 0, stream);
-        if (rc) return rc;
-        // dx (M, K) = gq (M, N) * wq (N, K): contraction over N; wq is (contraction, output) row-major
-        rc = axs6_gemm_bf16(gq, wq, dx, nullptr, M, K, N, ldgq, ldq, lddx, 0, 1, dx_dtype, stream);
-        if (rc) return rc;
-    }
+    // The weight gradient comes first: it is the product a data-parallel caller hands to its all-reduce, which
+    // can then run under the input-gradient product (call once with dw only, start the collective, call again
+    // with dx / db and AXS6_LINEAR_REUSE_GQ).
     if (dw) {
         // dw (N, K) = gq^T (N, M) * xq (M, K): contraction over M; both operands (contraction, output) row-major
         rc = axs6_gemm_bf16(gq, xq, dw, nullptr, N, K, M, ldgq, ldq, lddw, 1, 1, AXS6_F32, stream);
+        if (rc) return rc;
+    }
+    if (dx) {
+        if (!(flags & AXS6_LINEAR_REUSE_WQ)) {
+            rc = axs6_fq(w, wq, w_dtype, AXS6_BF16, N, K, ldw, ldq, block, grid, AXS6_ROUND_NEAREST,
+                         AXS6_FLAG_INPUT_VIA_BF16, 0, 0, stream);
+            if (rc) return rc;
+        }
+        // dx (M, K) = gq (M, N) * wq (N, K): contraction over N; wq is (contraction, output) row-major
+        rc = axs6_gemm_bf16(gq, wq, dx, nullptr, M, K, N, ldgq, ldq, lddx, 0, 1, dx_dtype, stream);
         if (rc) return rc;
     }
     if (db) {

@@ -367,17 +367,100 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None
     with _on(a.device):
         st = fn(a.data_ptr(), b.data_ptr(), c.data_ptr(),
                 bias_f.data_ptr() if bias_f is not None else None, M, N, K,
-                a.stride(0) if a.shape[0] > 1 else max(a.shape[1], 8),
-                b.stride(0) if b.shape[0] > 1 else max(b.shape[1], 8), N,
+                _row_pitch(a), _row_pitch(b), N,
                 int(a_mn), int(b_mn), _DT[out_dtype], _stream(a.device))
     _lib.check("axs6_gemm", st)
     return c
 
 
+class PackedOperand:
+    """A matrix held as AXS-6 codes in the split layout: ``codes`` uint8 (rows, cols // 32, 24), ``exps`` uint8
+    (rows, cols // 32); NF5 grid, blocks of 32 along the columns."""
+
+    def __init__(self, codes: torch.Tensor, exps: torch.Tensor, rows: int, cols: int):
+        self.codes, self.exps, self.rows, self.cols = codes, exps, rows, cols
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+
+def pack_split(x: torch.Tensor, rounding: str = "nearest", via_bf16: bool = False, noise: torch.Tensor | None = None) -> PackedOperand:
+    """Quantise a 2-D tensor (NF5, block 32 along the last dimension) into the split layout that
+    ``gemm_packed`` reads; the last dimension must be a multiple of 64."""
+    _check_input(x, "pack_split")
+    assert x.dim() == 2 and x.shape[1] % 64 == 0, "pack_split takes a 2-D tensor whose last dimension is a multiple of 64"
+    rows, cols = x.shape
+    codes = torch.empty((rows, cols // 32, 24), dtype=torch.uint8, device=x.device)
+    exps = torch.empty((rows, cols // 32), dtype=torch.uint8, device=x.device)
+    x2, _, _, ldx = _as_rows(x)
+    rnd = _rounding(rounding)
+    seed, off, nz = 0, 0, None
+    if rnd == ROUND_STOCHASTIC:
+        if noise is not None:
+            nz = noise.to(device=x.device, dtype=torch.float32).contiguous()
+        else:
+            seed, off = next_philox(rows * cols)
+    flags = FLAG_INPUT_VIA_BF16 if (via_bf16 and x2.dtype == torch.float32) else 0
+    with _on(x.device):
+        st = _lib.load().axs6_pack(x2.data_ptr(), _DT[x2.dtype], rows, cols, ldx, 32, GRID_NF5, rnd, flags, seed, off,
+                                   nz.data_ptr() if nz is not None else None, _lib.LAYOUT_SPLIT, codes.data_ptr(),
+                                   exps.data_ptr(), None, _stream(x.device))
+    _lib.check("axs6_pack", st)
+    return PackedOperand(codes, exps, rows, cols)
+
+
+def unpack_split(pk: PackedOperand, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Values of a :class:`PackedOperand`, (rows, cols)."""
+    y = torch.empty((pk.rows, pk.cols), dtype=out_dtype, device=pk.codes.device)
+    with _on(y.device):
+        st = _lib.load().axs6_unpack(_lib.LAYOUT_SPLIT, pk.codes.data_ptr(), pk.exps.data_ptr(), None, y.data_ptr(), _DT[out_dtype],
+                                     pk.rows, pk.cols, pk.cols, 32, GRID_NF5, _stream(y.device))
+    _lib.check("axs6_unpack", st)
+    return y
+
+
+def gemm_packed(a, b, bias: torch.Tensor | None = None, a_mn: bool = False, b_mn: bool = False,
+                out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """C = op(A) op(B) with one or both operands given as :class:`PackedOperand` (decoded to bf16 inside the
+    kernel); the other, if any, a 2-D bf16 tensor with 16-byte aligned rows.  Shapes as in ``gemm_bf16``."""
+    pa, pb = isinstance(a, PackedOperand), isinstance(b, PackedOperand)
+    assert pa or pb, "gemm_packed needs at least one PackedOperand"
+    M, K = (a.shape[1], a.shape[0]) if a_mn else a.shape
+    N, K2 = (b.shape[1], b.shape[0]) if b_mn else b.shape
+    assert K == K2, "contraction lengths differ"
+    dev = (a.codes if pa else a).device
+    c = torch.empty((M, N), dtype=out_dtype, device=dev)
+    bias_f = bias.to(device=dev, dtype=torch.float32).contiguous() if bias is not None else None
+
+    def args(t, packed):
+        if packed:
+            return t.codes.data_ptr(), t.exps.data_ptr(), 0
+        assert t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1
+        return t.data_ptr(), None, _row_pitch(t)
+    ap, ae, lda = args(a, pa)
+    bp, be, ldb = args(b, pb)
+    with _on(dev):
+        st = _lib.load().axs6_gemm_packed(ap, ae, lda, bp, be, ldb, c.data_ptr(), bias_f.data_ptr() if bias_f is not None else None,
+                                          M, N, K, N, int(a_mn), int(b_mn), _DT[out_dtype], _stream(dev))
+    _lib.check("axs6_gemm_packed", st)
+    return c
+
+
+def _row_pitch(t: torch.Tensor) -> int:
+    """Leading dimension handed to the library: the row stride, or for a one-row operand (whose stride means
+    nothing) the row length rounded up to a 16-byte multiple."""
+    if t.shape[0] > 1:
+        return t.stride(0)
+    per16 = 16 // t.element_size()
+    return max((t.shape[1] + per16 - 1) // per16 * per16, per16)
+
+
 def _padded_copy(t: torch.Tensor) -> torch.Tensor:
     """Copy into a buffer whose rows start 16-byte aligned (row length rounded up to 8 elements)."""
     rows, cols = t.shape
-    ld = (cols + 7) // 8 * 8
+    per16 = 16 // t.element_size()
+    ld = (cols + per16 - 1) // per16 * per16
     buf = torch.zeros((rows, ld), dtype=t.dtype, device=t.device)
     buf[:, :cols].copy_(t)
     return buf[:, :cols]
@@ -401,6 +484,10 @@ def _ws_bytes(what: int, M: int, N: int, K: int) -> int:
     if what == 5: return N * _r4(K) * 4
     if what == 6: return M * _r4(N) * 4
     if what == 7: return (K * _r4(N) + N * _r4(M) + K * _r4(M)) * 4
+    if what in (8, 9, 10):
+        rows, cols = {8: (M, K), 9: (N, K), 10: (M, N)}[what]
+        nblk = (cols + 31) // 32
+        return (rows * nblk * 24 + 255) // 256 * 256 + rows * nblk
     raise ValueError(what)
 
 
@@ -420,17 +507,21 @@ def _carve(dev, sizes: list[int]) -> list[int]:
 
 
 def linear_fwd(x2: torch.Tensor, w: torch.Tensor, bias_f32: torch.Tensor | None, block_size: int, grid: int,
-               quantize_input: bool, out_dtype: torch.dtype, tf32: bool = False, bias_via_bf16: bool = False):
-    """-> (y (M, N), xq workspace holding the quantised activations that backward needs).
-    ``tf32``: the fp32 graph (operands fake-quantised in fp32, TF32 tensor cores) instead of bf16."""
+               quantize_input: bool, out_dtype: torch.dtype, tf32: bool = False, bias_via_bf16: bool = False,
+               return_wq: bool = False, packed: bool = False):
+    """-> (y (M, N), xq workspace holding the quantised activations that backward needs); with
+    ``return_wq`` also the workspace that holds the quantised weight (backward can reuse it while the
+    weight is unchanged).  ``tf32``: the fp32 graph (operands fake-quantised in fp32, TF32 tensor cores)
+    instead of bf16.  ``packed``: the workspaces hold 6-bit codes and the GEMM decodes them on load
+    (``linear_packed_ok`` says whether the shapes allow it)."""
     M, K = x2.shape
     N = w.shape[0]
     dev = x2.device
-    xq = torch.empty(max(_ws_bytes(4 if tf32 else 0, M, N, K), 16), dtype=torch.uint8, device=dev)
-    wq = torch.empty(max(_ws_bytes(5 if tf32 else 1, M, N, K), 16), dtype=torch.uint8, device=dev)
+    xq = torch.empty(max(_ws_bytes(8 if packed else (4 if tf32 else 0), M, N, K), 16), dtype=torch.uint8, device=dev)
+    wq = torch.empty(max(_ws_bytes(9 if packed else (5 if tf32 else 1), M, N, K), 16), dtype=torch.uint8, device=dev)
     y = torch.empty((M, N), dtype=out_dtype, device=dev)
     flags = (_lib.LINEAR_QUANTIZE_INPUT if quantize_input else 0) | (_lib.LINEAR_COMPUTE_TF32 if tf32 else 0) | \
-            (_lib.LINEAR_BIAS_VIA_BF16 if bias_via_bf16 else 0)
+            (_lib.LINEAR_BIAS_VIA_BF16 if bias_via_bf16 else 0) | (_lib.LINEAR_OPERANDS_PACKED if packed else 0)
     with _on(dev):
         st = _lib.load().axs6_linear_fwd(x2.data_ptr(), _DT[x2.dtype], x2.stride(0) if M > 1 else K,
                                          w.data_ptr(), _DT[w.dtype], w.stride(0) if N > 1 else K,
@@ -438,21 +529,26 @@ def linear_fwd(x2: torch.Tensor, w: torch.Tensor, bias_f32: torch.Tensor | None,
                                          y.data_ptr(), _DT[out_dtype], N, M, N, K, block_size, grid, flags,
                                          xq.data_ptr(), wq.data_ptr(), _stream(dev))
     _lib.check("axs6_linear_fwd", st)
+    if return_wq:
+        return y, xq, wq
     return y, xq
 
 
 def linear_bwd(g2: torch.Tensor, xq: torch.Tensor, w: torch.Tensor, M: int, N: int, K: int, block_size: int,
                grid: int, quantize_grad: bool, need_dx: bool, need_dw: bool, need_db: bool,
                dx_dtype: torch.dtype = torch.bfloat16, noise: torch.Tensor | None = None, tf32: bool = False,
-               bias_from_quantized: bool = False):
-    """-> (dx (M, K) or None, dw fp32 (N, K) or None, db fp32 (N,) or None)."""
+               bias_from_quantized: bool = False, wq: torch.Tensor | None = None, packed: bool = False):
+    """-> (dx (M, K) or None, dw fp32 (N, K) or None, db fp32 (N,) or None).  ``wq``: the quantised-weight
+    workspace of the forward call, valid only while the weight has not changed (bf16 graph); without it the
+    quantised weight is recomputed."""
     dev = g2.device
+    reuse_wq = wq is not None and need_dx and not tf32
     dx = torch.empty((M, K), dtype=dx_dtype, device=dev) if need_dx else None
     dw = torch.empty((N, K), dtype=torch.float32, device=dev) if need_dw else None
     db = torch.empty((N,), dtype=torch.float32, device=dev) if need_db else None
     keep, (p_gq, p_wq, p_part, p_tscr) = _carve(dev, [
-        _ws_bytes(6 if tf32 else 2, M, N, K),
-        _ws_bytes(5 if tf32 else 1, M, N, K) if need_dx else 0,
+        _ws_bytes(10 if packed else (6 if tf32 else 2), M, N, K),
+        _ws_bytes(9 if packed else (5 if tf32 else 1), M, N, K) if (need_dx and not reuse_wq) else 0,
         _ws_bytes(3, M, N, K) if need_db else 0,
         _ws_bytes(7, M, N, K) if (tf32 and (need_dx or need_dw)) else 0])
     seed, off = (0, 0)
@@ -463,7 +559,10 @@ def linear_bwd(g2: torch.Tensor, xq: torch.Tensor, w: torch.Tensor, M: int, N: i
         else:
             seed, off = next_philox(M * (-(-N // block_size)) * block_size)
     flags = (_lib.LINEAR_QUANTIZE_GRAD if quantize_grad else 0) | (_lib.LINEAR_COMPUTE_TF32 if tf32 else 0) | \
-            (_lib.LINEAR_BIAS_FROM_QUANTIZED if bias_from_quantized else 0)
+            (_lib.LINEAR_BIAS_FROM_QUANTIZED if bias_from_quantized else 0) | (_lib.LINEAR_REUSE_WQ if reuse_wq else 0) | \
+            (_lib.LINEAR_OPERANDS_PACKED if packed else 0)
+    if reuse_wq:
+        p_wq = wq.data_ptr()
     with _on(dev):
         st = _lib.load().axs6_linear_bwd(
             g2.data_ptr(), _DT[g2.dtype], g2.stride(0) if M > 1 else N, xq.data_ptr() if need_dw else None,
@@ -475,6 +574,11 @@ def linear_bwd(g2: torch.Tensor, xq: torch.Tensor, w: torch.Tensor, M: int, N: i
     _lib.check("axs6_linear_bwd", st)
     del keep
     return dx, dw, db
+
+
+def linear_packed_ok(N: int, K: int, block_size: int, quantize_input: bool, quantize_grad: bool) -> bool:
+    """Whether the quantise-on-load Linear (operands as codes) can serve this layer."""
+    return block_size == 32 and quantize_input and quantize_grad and K % 64 == 0 and N % 64 == 0
 
 
 def bias_grad(g: torch.Tensor) -> torch.Tensor:

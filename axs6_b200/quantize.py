@@ -1,8 +1,9 @@
 """Rounding-strategy wrappers over :func:`axs6_b200.core.quantize`.
 
-Mirrors ``axs/quantize.py`` for the strategies on the hot path: ``quantize_nearest``
-(quantize.py:120-129), ``quantize_stochastic`` (:132-146), error feedback (:149-200, a host
-composition of quantise / dequantise kernels) and the dispatcher ``quantize_adaptive`` (:315-352).
+Mirrors ``axs/quantize.py``: ``quantize_nearest`` (quantize.py:120-129), ``quantize_stochastic``
+(:132-146), error feedback (:149-200, a host composition of quantise / dequantise kernels),
+gradient-aware stochastic rounding (:203-307, the stochastic kernel fed with transformed draws) and
+the dispatcher ``quantize_adaptive`` (:315-352).
 """
 from __future__ import annotations
 
@@ -10,7 +11,8 @@ from enum import Enum
 
 import torch
 
-from .core import DEFAULT_BLOCK_SIZE, AXSTensor, dequantize, quantize
+from . import ops
+from .core import DEFAULT_BLOCK_SIZE, VALID_BLOCK_SIZES, AXSTensor, _quantize_planes, dequantize, quantize
 
 
 class RoundingMode(Enum):
@@ -63,6 +65,33 @@ def quantize_with_error_feedback(tensor: torch.Tensor, block_size: int = DEFAULT
     return q
 
 
+def quantize_gasr(tensor: torch.Tensor, gradient: torch.Tensor, block_size: int = DEFAULT_BLOCK_SIZE,
+                  temperature: float = 1.0, noise: torch.Tensor | None = None) -> AXSTensor:
+    """Gradient-aware stochastic rounding (quantize.py:203-307): a value between two levels goes up with
+    probability ``frac ** (2 - w)``, ``w = sigmoid(temperature * |g| / mean_block(|g|))``, so values with large
+    gradients round closer to nearest.
+
+    ``rand < frac ** e`` holds exactly when ``rand ** (1 / e) < frac`` (e >= 1, both sides in [0, 1]), so the
+    rule is the stochastic uniform-grid kernel fed with the transformed draws ``rand ** (1 / (2 - w))``: the
+    weights and the transformed draws are elementwise torch ops on the device, exponent, magnitudes and signs
+    come from the pack kernel.  ``noise``: the U[0,1) draws ``rand`` in the zero-padded (rows, nblk, block)
+    layout (default: ``torch.rand``), which makes the result reproducible."""
+    assert tensor.shape == gradient.shape, "Tensor and gradient must have same shape"
+    assert block_size in VALID_BLOCK_SIZES
+    if not tensor.is_cuda:
+        raise RuntimeError("quantize_gasr requires a CUDA tensor")
+    last = tensor.shape[-1]
+    g = gradient.reshape(-1, last).float().abs()
+    pad = (-last) % block_size
+    if pad:
+        g = torch.nn.functional.pad(g, (0, pad))
+    gb = g.view(g.shape[0], -1, block_size)
+    weight = torch.sigmoid(temperature * gb / gb.mean(dim=-1, keepdim=True).clamp(min=1e-45))
+    rand = torch.rand_like(weight) if noise is None else noise.to(device=tensor.device, dtype=torch.float32).reshape(weight.shape)
+    draws = rand.pow(1.0 / (2.0 - weight))
+    return _quantize_planes(tensor, block_size, "stochastic", ops.GRID_UNIFORM, "quantize_gasr", noise=draws)
+
+
 def quantize_adaptive(tensor: torch.Tensor, mode: RoundingMode = RoundingMode.NEAREST,
                       block_size: int = DEFAULT_BLOCK_SIZE, gradient: torch.Tensor | None = None,
                       param_name: str = "default", ef_state: ErrorFeedbackState | None = None,
@@ -74,5 +103,7 @@ def quantize_adaptive(tensor: torch.Tensor, mode: RoundingMode = RoundingMode.NE
     if mode == RoundingMode.ERROR_FEEDBACK:
         return quantize_with_error_feedback(tensor, block_size, "nearest", param_name, ef_state)
     if mode == RoundingMode.GASR:
-        raise NotImplementedError("gradient-aware stochastic rounding is outside the accelerated path")
+        if gradient is None:
+            raise ValueError("GASR mode requires a gradient tensor")
+        return quantize_gasr(tensor, gradient, block_size, gasr_temperature)
     raise ValueError(f"Unknown rounding mode: {mode}")

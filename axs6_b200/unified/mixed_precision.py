@@ -16,6 +16,15 @@ import torch.nn.functional as F
 from .. import ops
 from ..core import DEFAULT_BLOCK_SIZE, VALID_BLOCK_SIZES
 
+# Keep the forward's quantised weight (bf16, N x K) alive until backward instead of recomputing it there:
+# one fake-quantise pass less per layer and step, for 2 bytes per weight of extra memory between the two.
+KEEP_QUANTIZED_WEIGHT = True
+
+# Quantise-on-load variant: activations, weight and gradient go to HBM as 6-bit codes (0.78 bytes per value instead
+# of 2) and the GEMMs decode them in shared memory; the activation saved for backward shrinks by 2.56x.  Off by
+# default: the two-pass path is the one that reproduces the reference at exact zeros (codes have no zero).
+PACKED_OPERANDS = False
+
 # Test hook: when set to a tensor, the next backward uses these U[0,1) draws for the gradient's
 # stochastic rounding (padded (M, nblk, block) layout) instead of the Philox stream.
 _noise_for_next_backward: torch.Tensor | None = None
@@ -47,9 +56,16 @@ class _AXSLinearBF16Function(torch.autograd.Function):
         b32 = None
         if bias is not None:                      # F.linear sees bf16(bias): rounded inside the GEMM epilogue
             b32 = bias if (bias.dtype == torch.float32 and bias.is_contiguous()) else bias.float().contiguous()
-        y, xq = ops.linear_fwd(x2, w, b32, block_size, ops.GRID_NF5, bool(quantize_input), torch.bfloat16,
-                               bias_via_bf16=True)
+        packed = PACKED_OPERANDS and ops.linear_packed_ok(weight.shape[0], weight.shape[1], block_size, bool(quantize_input),
+                                                          bool(quantize_grad))
+        y, xq, wq = ops.linear_fwd(x2, w, b32, block_size, ops.GRID_NF5, bool(quantize_input), torch.bfloat16,
+                                   bias_via_bf16=True, return_wq=True, packed=packed)
+        ctx.packed = packed
         ctx.save_for_backward(xq, weight, bias)
+        # The quantised weight is kept for backward and used there if the weight is still the same version
+        # (the reference recomputes it, mixed_precision.py:130, to save memory; the bits are the same).
+        ctx.wq = wq if KEEP_QUANTIZED_WEIGHT else None
+        ctx.w_version = weight._version
         ctx.block_size = block_size
         ctx.quantize_grad = bool(quantize_grad)
         ctx.in_shape = input.shape
@@ -67,7 +83,9 @@ class _AXSLinearBF16Function(torch.autograd.Function):
         noise, _noise_for_next_backward = _noise_for_next_backward, None
         dx, dw, db = ops.linear_bwd(g2, xq, w, M, N, K, ctx.block_size, ops.GRID_NF5, ctx.quantize_grad,
                                     ctx.needs_input_grad[0], ctx.needs_input_grad[1],
-                                    bias is not None and ctx.needs_input_grad[2], torch.bfloat16, noise)
+                                    bias is not None and ctx.needs_input_grad[2], torch.bfloat16, noise,
+                                    wq=ctx.wq if weight._version == ctx.w_version else None, packed=ctx.packed)
+        ctx.wq = None
         if dx is not None:
             dx = dx.reshape(ctx.in_shape)
         return dx, dw, db, None, None, None

@@ -1,14 +1,16 @@
 #!/usr/bin/env python
 """Benchmark of the AXS-6 hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--scaling weak|strong]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--scaling strong|weak]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --case NAME [--launches n]        # one kernel on a small case, for profilers
 
 Headline workload (one "step" = one pass of the NF5 fake-quantise kernel over the rank's shard):
 the largest tensor of the fake-quantise sweep, 32768 x 8192 fp32, per-row sigma log-uniform in
-[1e-4, 10], block 32, nearest rounding.  With `--scaling weak` (default) every rank owns a
-32768 x 8192 shard of a (N*32768) x 8192 tensor; with `--scaling strong` the one 32768 x 8192
-tensor is split by rows over the ranks.  No collective is involved: blocks never cross rows.
+[1e-4, 10], block 32, nearest rounding.  With N ranks the default (`--scaling strong`) splits that
+ONE tensor by rows, 32768 / N rows per rank; `--scaling weak` gives every rank a 32768 x 8192 tensor
+of its own.  The reading that is not the headline is measured too and reported under
+`other_scaling`.  No collective is involved: blocks never cross rows.
 
 Prints ONE JSON line on rank 0:
   value      fake-quant GB/s (algorithmic bytes = numel * (4 + 4)), inputs resident in HBM,
@@ -17,12 +19,14 @@ Prints ONE JSON line on rank 0:
              pinned HOST buffers: H2D copy + kernel + D2H copy of every step inside the timed region
              (the operator pipelines them over chunks of rows, so both PCIe directions run at once)
   roofline   achieved / measured HBM peak for the dominant kernel
-  cpu_baseline  the CPU oracle (a port of the reference's eager algorithm, C + OpenMP) on a
-             bounded row sample of the same tensor, on this box's host cores
+  cpu_baseline  the reference's CPU implementation of the same pass on a bounded row sample of the same
+             tensor, on this box's host cores, thread count set explicitly and reported: kind
+             "reference" = the reference's own eager function from baseline/_ref, "port" = the C
+             restatement under oracle/ when that copy is absent
   codec, linear   the two other metrics of the path (pack->unpack GB/s, fused-linear TFLOP/s)
   fq_sweep, minigpt   the fake-quantise sweep (fp32 + bf16) and the MiniGPT-style training step
-`--impl reference` times the CPU oracle alone (the reference is pure Python/torch and does not
-travel to the GPU box; the oracle is its pinned C restatement) and prints the same line shape.
+`--impl reference` times that CPU arm alone, on the first 4096 rows of the same seeded tensor, and
+prints the same line shape (rank 0 only under torchrun).
 """
 from __future__ import annotations
 
@@ -126,43 +130,127 @@ def make_input(rows: int, cols: int, seed: int, device):
     return torch.randn(rows, cols, generator=g, device=device) * sig
 
 
-# --------------------------------------------------------------------------------------- reference arm
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+# --------------------------------------------------------------------------------------- CPU arm
+class CpuReference:
+    """The reference's CPU implementation of the headline path, with every host thread it can use.
+
+    kind "reference": the reference's own eager ``fused_fake_quantize`` (axs/unified/quantize_unified.py:121-204),
+    imported unmodified from ``baseline/_ref`` (put there by baseline/install_reference.py; it travels with the
+    repository snapshot but is not part of its history).  kind "port": the C + OpenMP restatement under
+    ``oracle/`` when that copy is absent.  Thread counts are set explicitly (a launcher such as torchrun exports
+    OMP_NUM_THREADS=1) and the count in effect is what ``cores`` reports."""
+
+    def __init__(self):
+        import torch
+        self.torch = torch
+        want = host_cores()
+        ref_dir = os.path.join(ROOT, "baseline", "_ref")
+        self.kind = "port"
+        if os.path.isdir(os.path.join(ref_dir, "axs")):
+            try:
+                if ref_dir not in sys.path:
+                    sys.path.insert(0, ref_dir)
+                import importlib
+                self.ref_fq = importlib.import_module("axs.unified.quantize_unified").fused_fake_quantize
+                torch.set_num_threads(want)
+                self.cores = int(torch.get_num_threads())
+                self.kind = "reference"
+            except Exception:
+                self.kind = "port"
+        if self.kind == "port":
+            import oracle
+            oracle.build()
+            self.oracle = oracle
+            self.cores = oracle.set_threads(want)
+
+    def run(self, x_cpu) -> None:
+        """One pass over a CPU fp32 tensor."""
+        if self.kind == "reference":
+            with self.torch.no_grad():
+                self.ref_fq(x_cpu, BLOCK, "nearest")
+        else:
+            self.oracle.fused_fake_quantize(x_cpu.numpy(), BLOCK)
+
+    def describe(self) -> str:
+        return ("reference eager fused_fake_quantize (torch CPU ops, unmodified copy under baseline/_ref)" if self.kind == "reference"
+                else "C + OpenMP port of the reference's eager algorithm (oracle/)")
+
+
+def reference_sample(sample_rows: int):
+    """The first `sample_rows` rows of the 32768 x 8192 workload tensor: the rows rank 0 of the GPU arm holds."""
+    import torch
+    if torch.cuda.is_available():
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        x = make_input(ROWS, COLS, 1000, dev)[:sample_rows].cpu()
+        torch.cuda.empty_cache()
+        return x, True
+    return make_input(sample_rows, COLS, 1000, torch.device("cpu")), False
+
+
 def run_reference(args, rank: int, world: int) -> None:
-    """CPU arm: the oracle (C + OpenMP port of the reference's eager algorithm) on host cores."""
+    """CPU arm: the reference's own implementation of the path on the box's host cores (rank 0 only)."""
     if rank != 0:
         return
-    import numpy as np
-    import oracle
-    oracle.build()
-    cores = os.cpu_count() or 1
-    sample_rows = 2048
-    rng = np.random.default_rng(0)
-    sig = (10.0 ** (rng.random((sample_rows, 1)) * 5 - 4)).astype(np.float32)
-    x = rng.standard_normal((sample_rows, COLS), dtype=np.float32) * sig
+    sample_rows = 4096
+    x, same = reference_sample(sample_rows)
+    cpu = CpuReference()
     for _ in range(max(1, min(args.warmup, 3))):
-        oracle.fused_fake_quantize(x, BLOCK)
+        cpu.run(x)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        oracle.fused_fake_quantize(x, BLOCK)
+        cpu.run(x)
     dt = (time.perf_counter() - t0) / args.steps
-    gbs = x.size * 8 / dt / 1e9
-    sample = f"{sample_rows}x{COLS} fp32 rows of the {ROWS}x{COLS} workload per step"
+    gbs = x.numel() * 8 / dt / 1e9
+    sample = (f"first {sample_rows} rows ({sample_rows}x{COLS} fp32) of the {ROWS}x{COLS} workload tensor per step"
+              + ("" if same else " (generated on the CPU: no CUDA device for the GPU arm's generator)"))
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": args.scaling,
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"NF5 fake-quantize {ROWS}x{COLS} fp32, block {BLOCK}, nearest (fake-quantize sweep, largest size)",
-                   "sample": sample, "l2": "n/a (CPU)"},
-        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": WORKLOAD, "sample": sample, "l2": "n/a (CPU)", "what": cpu.describe()},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cpu.cores, "kind": cpu.kind, "sample": sample},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
+def cpu_baseline(x) -> dict:
+    """The CPU arm on a bounded row sample of the same tensor (about 10 s), all host threads."""
+    sample_rows = 4096
+    xs = x[:sample_rows].cpu()
+    cpu = CpuReference()
+    cpu.run(xs[:256])
+    reps = 0
+    t0 = time.perf_counter()
+    while True:
+        cpu.run(xs)
+        reps += 1
+        if time.perf_counter() - t0 > 10 or reps >= 20:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": xs.numel() * 8 / dt / 1e9, "unit": UNIT, "cores": cpu.cores, "kind": cpu.kind,
+            "sample": f"first {sample_rows} rows ({sample_rows}x{COLS} fp32) of the workload, {reps} reps", "what": cpu.describe()}
+
+
 # --------------------------------------------------------------------------------------- our arm
+WORKLOAD = f"NF5 fake-quantize {ROWS}x{COLS} fp32, block {BLOCK}, nearest (fake-quantize sweep, largest size)"
+
+# DRAM bytes (read + write) of ONE launch of the headline kernel, from an ncu capture of this workload's launch
+# (profiles/fq_vec_kernel_f32_32768x8192.md); None where no capture of that shard size exists.
+TRAFFIC_BYTES_PER_LAUNCH: dict[int, float] = {}
+TRAFFIC_CAPTURED = {"rows": 8192, "cols": 8192, "dram_bytes": 486.1e6, "algorithmic_bytes": 8192 * 8192 * 8,
+                    "source": "profiles/fq_vec_kernel_f32_8192x8192.md"}
+
+
 def run_ours(args, rank: int, local_rank: int, world: int) -> None:
-    import numpy as np
     import torch
     import torch.distributed as dist
 
@@ -179,72 +267,111 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     if lib.axs6_query(0) != 1:
         raise RuntimeError("bench.py needs a compute-capability 10.x device; there is no fallback path")
     pk = peaks()
-
-    rows = ROWS if args.scaling == "weak" else ROWS // world
-    x = make_input(rows, COLS, 1000 + rank, dev)
-    y = torch.empty_like(x)
-    numel = x.numel()
-    bytes_per_step = numel * 8
     stream = torch.cuda.current_stream().cuda_stream
-
-    def step():
-        st = lib.axs6_fq(x.data_ptr(), y.data_ptr(), 0, 0, rows, COLS, COLS, COLS, BLOCK, 1, 0, 0, 0, 0, stream)
-        if st != 0:
-            raise RuntimeError(f"axs6_fq -> {st}")
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
+    def max_over_ranks(v: float) -> float:
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def shard(scaling: str):
+        """This rank's rows: strong = its contiguous row range of THE 32768 x 8192 tensor (seed 1000);
+        weak = a 32768 x 8192 tensor of its own (seed 1000 + rank)."""
+        if scaling == "weak" or world == 1:
+            return make_input(ROWS, COLS, 1000 + rank, dev)
+        per = ROWS // world
+        full = make_input(ROWS, COLS, 1000, dev)
+        part = full[rank * per:(rank + 1) * per].clone()
+        del full
+        torch.cuda.empty_cache()
+        return part
+
+    def time_fq(x, steps: int, warmup: int):
+        """CUDA-event time of `steps` back-to-back launches over this rank's shard.  A shard whose input +
+        output are below 1 GiB rotates through several output buffers and input copies so that every launch
+        reads data that is not in L2."""
+        rows = x.shape[0]
+        nbytes = x.numel() * 8
+        sets = max(1, min(8, -(-(1 << 30) // nbytes)))
+        xs = [x] + [x.clone() for _ in range(sets - 1)]
+        ys = [torch.empty_like(x) for _ in range(sets)]
+
+        def step(i):
+            xi, yi = xs[i % sets], ys[i % sets]
+            st = lib.axs6_fq(xi.data_ptr(), yi.data_ptr(), 0, 0, rows, COLS, COLS, COLS, BLOCK, 1, 0, 0, 0, 0, stream)
+            if st != 0:
+                raise RuntimeError(f"axs6_fq -> {st}")
+
+        for i in range(max(warmup, 3)):
+            step(i)
+        barrier()
+        l0 = _lib.launches()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(steps):
+            step(i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        return ms, _lib.launches() - l0, step, sets
+
+    primary = args.scaling if world > 1 else "weak"          # one GPU: the two readings coincide
+    x = shard(primary)
+    rows = x.shape[0]
+    numel = x.numel()
+    bytes_per_step = numel * 8
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
-    l0 = _lib.launches()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    launches = _lib.launches() - l0
+    ms, launches, step, sets = time_fq(x, args.steps, args.warmup)
     # keep the sampler running over a few more launches if the timed region was very short
     t_end = time.perf_counter() + 0.6
+    i = 0
     while time.perf_counter() < t_end and len(sampler.samples) < 6:
-        step()
+        step(i)
+        i += 1
         torch.cuda.synchronize()
     clocks = sampler.finish()
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
-    ms_per_step = ms_max / args.steps
+    ms_per_step = max_over_ranks(ms) / args.steps
     value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
     achieved = bytes_per_step / (ms / args.steps * 1e-3) / 1e9          # this rank's kernel
+
+    # ---------------- the other reading of "N GPUs" (more than one rank only)
+    other = None
+    if world > 1:
+        other_name = "weak" if primary == "strong" else "strong"
+        xo = shard(other_name)
+        ms_o, _, _, sets_o = time_fq(xo, args.steps, args.warmup)
+        ms_o = max_over_ranks(ms_o) / args.steps
+        other = {"scaling": other_name, "per_gpu_shard": f"{xo.shape[0]}x{COLS}", "ms_per_step": ms_o,
+                 "value": world * xo.numel() * 8 / (ms_o * 1e-3) / 1e9, "unit": UNIT, "rotating_buffer_sets": sets_o}
+        del xo
+        torch.cuda.empty_cache()
 
     # ---------------- end to end: host buffers through the Python operator
     e2e_steps = max(1, min(args.steps, 3))
     hx = torch.empty((rows, COLS), dtype=torch.float32, pin_memory=True)
     hy = torch.empty((rows, COLS), dtype=torch.float32, pin_memory=True)
     hx.copy_(x)
+
     def e2e_step():
         # host buffers in, host buffers out: chunks of rows pipelined over H2D copy, kernel and D2H copy
         qu.fused_fake_quantize_host(hx, hy, BLOCK)
     e2e_step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
     for _ in range(e2e_steps):
         e2e_step()
     e1.record()
     barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / e2e_steps
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
     e2e_val = world * bytes_per_step / (e2e_ms * 1e-3) / 1e9
     del hx, hy
 
@@ -254,14 +381,15 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     if rank == 0:
         if "codec" in sections:
             extra["codec"] = bench_codec(torch, lib, udist, dev, pk)
-        if "fq_sweep" in sections:
-            extra["fq_sweep"] = bench_sweep(torch, lib, dev, pk, x)
         if world == 1:
             cpu = cpu_baseline(x)
-    del x, y
+    del x
+    torch.cuda.empty_cache()
+    if rank == 0 and "fq_sweep" in sections:
+        extra["fq_sweep"] = bench_sweep(torch, lib, dev, pk)
     torch.cuda.empty_cache()
     try:
-        extra_linear = bench_linear(args, rank, world, dev, pk) if "linear" in sections else None
+        extra_linear = linear_section(args, rank, world, dev, pk) if "linear" in sections else None
         if extra_linear is not None and rank == 0:
             extra["linear"] = extra_linear
     except Exception as e:          # the linear metric is reported separately; never hide the headline
@@ -270,8 +398,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
 
     if world > 1 and "grad_exchange" in sections:
         try:
-            from axs6_b200 import exchange_bench
-            ex = exchange_bench.run(rank, world, dev)
+            import bench_exchange
+            ex = bench_exchange.run(rank, world, dev)
             if rank == 0:
                 extra["grad_exchange"] = ex
         except Exception as e:
@@ -280,8 +408,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
 
     if "minigpt" in sections:
         try:
-            from axs6_b200 import minigpt_bench
-            mg = minigpt_bench.run(args, rank, world, dev)
+            import bench_minigpt
+            mg = bench_minigpt.run(args, rank, world, dev)
             if rank == 0:
                 extra["minigpt"] = mg
         except Exception as e:
@@ -292,12 +420,15 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"NF5 fake-quantize {ROWS}x{COLS} fp32, block {BLOCK}, nearest (fake-quantize sweep, largest size)",
-                       "per_gpu_shard": f"{rows}x{COLS}", "parallelism": f"rows sharded over {world} GPU(s), no collective",
-                       "l2": f"input {numel * 4 / 2**20:.0f} MiB + output {numel * 4 / 2**20:.0f} MiB per launch, larger than the 126 MB L2"},
+            "scaling": primary, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "per_gpu_shard": f"{rows}x{COLS}",
+                       "parallelism": (f"the {ROWS}x{COLS} tensor split by rows over {world} GPU(s), no collective" if primary == "strong" or world == 1
+                                       else f"one {ROWS}x{COLS} tensor per GPU ({world} GPU(s)), no collective"),
+                       "l2": f"input {numel * 4 / 2**20:.0f} MiB + output {numel * 4 / 2**20:.0f} MiB per launch, "
+                             f"{sets} rotating buffer set(s): every launch streams data larger than the 126 MB L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / pk["hbm_gbs"], "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(rows),
+                         "traffic_captured": TRAFFIC_CAPTURED,
                          "peak_source": pk["source"], "kernel": "fq_vec_kernel<float,float,NF5,nearest>",
                          "algorithmic_bytes_per_launch": bytes_per_step},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": numel * 4 * world,
@@ -305,6 +436,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        if other is not None:
+            line["other_scaling"] = other
         if cpu is not None:
             line["cpu_baseline"] = cpu
         line.update(extra)
@@ -312,30 +445,6 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-
-
-# DRAM bytes (read + write) of one launch of the headline kernel from the ncu capture summarised
-# under profiles/ (captured on a 4096 x 8192 case and scaled by rows; traffic grows with rows).
-TRAFFIC_BYTES_PER_LAUNCH: dict[int, float] = {32768: 4 * 486.1e6, 16384: 2 * 486.1e6, 8192: 486.1e6, 4096: 243.05e6}
-
-
-def cpu_baseline(x) -> dict:
-    """CPU oracle on a bounded row sample of the same tensor, all host threads."""
-    import oracle
-    oracle.build()
-    sample_rows = 4096
-    xs = x[:sample_rows].cpu().numpy()
-    oracle.fused_fake_quantize(xs[:256], BLOCK)
-    reps = 0
-    t0 = time.perf_counter()
-    while True:
-        oracle.fused_fake_quantize(xs, BLOCK)
-        reps += 1
-        if time.perf_counter() - t0 > 10 or reps >= 20:
-            break
-    dt = (time.perf_counter() - t0) / reps
-    return {"value": xs.size * 8 / dt / 1e9, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
-            "sample": f"first {sample_rows} rows ({sample_rows}x{COLS} fp32) of the workload, {reps} reps"}
 
 
 def bench_codec(torch, lib, udist, dev, pk) -> dict:
@@ -400,7 +509,15 @@ def bench_codec(torch, lib, udist, dev, pk) -> dict:
         ms = e0.elapsed_time(e1) / n
         gbs = nbytes / (ms * 1e-3) / 1e9
         res[name] = {"ms": ms, "GBps": gbs, "frac_of_hbm_peak": gbs / pk["hbm_gbs"], "algorithmic_bytes": nbytes}
-    res["roundtrip_bf16_GBps"] = 2 * (rows * cols * 2 + rec) / ((res["pack"]["ms"] + res["unpack_bf16"]["ms"]) * 1e-3) / 1e9
+    rt_bytes = 2 * (rows * cols * 2 + rec)
+    rt_ms = res["pack"]["ms"] + res["unpack_bf16"]["ms"]
+    res["roundtrip_bf16_GBps"] = rt_bytes / (rt_ms * 1e-3) / 1e9
+    res["roofline"] = {"bound": "hbm", "achieved": res["roundtrip_bf16_GBps"], "peak": pk["hbm_gbs"], "unit": "GB/s",
+                       "frac": res["roundtrip_bf16_GBps"] / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                       "kernel": "pack_bf16_nf5_b32_bulk_kernel + unpack_nf5_b32_bulk_kernel<bf16>",
+                       "algorithmic_bytes_per_roundtrip": rt_bytes,
+                       "note": "encode + decode round trip of the bf16 8192x4096 tensor: (values + 25-byte records) read or written "
+                               "by each of the two launches, over the sum of their CUDA-event times"}
     res["stream_status"] = int(lib.axs6_codec_status())
     res["workload"] = ("8192x4096, block 32, 25-byte wire records: pack = bf16 -> records, pack_f32 = fp32 -> records, unpack = records "
                        "-> fp32, unpack_bf16 = records -> bf16 (4 rotating buffer sets, 4 x 355 MiB > L2); pack_planes / unpack_planes = fp32 <-> "
@@ -408,26 +525,31 @@ def bench_codec(torch, lib, udist, dev, pk) -> dict:
     return res
 
 
-def bench_sweep(torch, lib, dev, pk, x_big) -> list:
-    """Fake-quantise sweep (fp32 and bf16; 256^2, 4096^2, 8192x4096, 32768x8192).  Shapes smaller
-    than L2 rotate through slices of the 1 GiB tensor so that every launch reads cold data."""
+def bench_sweep(torch, lib, dev, pk) -> list:
+    """Fake-quantise sweep: fp32 and bf16 at 1024^2 (the reference's CPU-runnable case), 256^2, 4096^2,
+    8192x4096 and 32768x8192, per-row sigma log-uniform in [1e-4, 10] (N(0, 0.02) for 1024^2).  Shapes that
+    fit L2 rotate through slots of a 512 Mi-value tensor so that every launch reads cold data."""
     stream = torch.cuda.current_stream().cuda_stream
     out = []
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for dt_name, dt_code, esz in (("f32", 0, 4), ("bf16", 1, 2)):
-        src = x_big if dt_code == 0 else x_big.view(-1)[: x_big.numel() // 2].to(torch.bfloat16)
-        flat = src.view(-1)
-        dst = torch.empty_like(flat)
-        for rows, cols in ((256, 256), (4096, 4096), (8192, 4096), (32768, 8192)):
+    total = ROWS * COLS
+    for dt_name, dt_code, esz, tdt in (("f32", 0, 4, torch.float32), ("bf16", 1, 2, torch.bfloat16)):
+        src = torch.empty(total, dtype=tdt, device=dev)
+        quarter = total // 4
+        for q in range(4):                                   # filled in quarters: no 2 GiB fp32 temporary for bf16
+            src[q * quarter:(q + 1) * quarter].copy_(make_input(ROWS // 4, COLS, 2000 + q, dev).view(-1))
+        dst = torch.empty_like(src)
+        for rows, cols in ((1024, 1024), (256, 256), (4096, 4096), (8192, 4096), (32768, 8192)):
             n = rows * cols
-            if n > flat.numel():
-                continue
-            slots = max(1, min(flat.numel() // n, 64))
+            slots = max(1, min(total // n, 64))
             iters = 30 if n >= (1 << 24) else 200
+            if (rows, cols) == (1024, 1024):                 # values ~ N(0, 0.02) in every slot used
+                g = torch.Generator(device=dev).manual_seed(0)
+                src[:slots * n].copy_((torch.randn(slots * n, generator=g, device=dev) * 0.02).to(tdt))
 
             def run(i):
                 off = (i % slots) * n * esz
-                st = lib.axs6_fq(flat.data_ptr() + off, dst.data_ptr() + off, dt_code, dt_code, rows, cols, cols, cols,
+                st = lib.axs6_fq(src.data_ptr() + off, dst.data_ptr() + off, dt_code, dt_code, rows, cols, cols, cols,
                                  BLOCK, 1, 0, 0, 0, 0, stream)
                 assert st == 0
             for i in range(5):
@@ -441,18 +563,19 @@ def bench_sweep(torch, lib, dev, pk, x_big) -> list:
             ms = e0.elapsed_time(e1) / iters
             gbs = n * esz * 2 / (ms * 1e-3) / 1e9
             out.append({"shape": f"{rows}x{cols}", "dtype": dt_name, "us": ms * 1e3, "GBps": gbs,
-                        "frac_of_hbm_peak": gbs / pk["hbm_gbs"], "rotating_slots": slots})
-        del dst
+                        "frac_of_hbm_peak": gbs / pk["hbm_gbs"], "rotating_slots": slots,
+                        "algorithmic_bytes": n * esz * 2})
+            if (rows, cols) == (1024, 1024):                 # restore the sweep distribution in the slots just overwritten
+                src[:quarter].copy_(make_input(ROWS // 4, COLS, 2000, dev).view(-1))
+        del src, dst
+        torch.cuda.empty_cache()
     return out
 
 
-def bench_linear(args, rank, world, dev, pk):
-    """AXS-6 Linear forward + backward (M=16384, K=N=4096); filled in by the linear module."""
-    try:
-        from axs6_b200 import linear_bench
-    except Exception:
-        return None
-    return linear_bench.run(args, rank, world, dev, pk)
+def linear_section(args, rank, world, dev, pk):
+    """AXS-6 Linear forward + backward (M=16384, K=N=4096); see bench_linear.py."""
+    import bench_linear
+    return bench_linear.run(args, rank, world, dev, pk)
 
 
 def main() -> None:
@@ -461,10 +584,19 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
+                    help="what N GPUs means for the headline: strong = the one 32768x8192 tensor split by rows (default), "
+                         "weak = one such tensor per GPU; the other reading is reported under `other_scaling`")
     ap.add_argument("--sections", default="codec,fq_sweep,linear,grad_exchange,minigpt",
                     help="extra sections of the JSON line to measure after the headline (comma list; empty = none)")
+    ap.add_argument("--case", default=None,
+                    help="run ONE kernel a few times on a small larger-than-L2 case and exit (for profilers); see bench_cases.py")
+    ap.add_argument("--launches", type=int, default=3, help="launches of --case")
     args = ap.parse_args()
+    if args.case:
+        import bench_cases
+        bench_cases.run_case(args.case, args.launches)
+        return
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -481,7 +613,7 @@ def main() -> None:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29541"),
                os.path.abspath(__file__), "--gpus", str(args.gpus), "--steps", str(args.steps),
-               "--warmup", str(args.warmup), "--scaling", args.scaling]
+               "--warmup", str(args.warmup), "--scaling", args.scaling, "--sections", args.sections]
         sys.exit(subprocess.call(cmd))
     run_ours(args, rank, local_rank, world)
 

@@ -1,8 +1,10 @@
 """Runs ONE kernel of the library a few times on a small, larger-than-L2 case, for profilers.
 
-    python -m axs6_b200.profile_case {fq_f32|fq_bf16|fq_bf16_stochastic|pack_wire|pack_wire_f32|unpack_wire|unpack_wire_bf16|unpack_sum4|gemm_fwd|gemm_dx|gemm_dw} [launches]
+    python bench.py --case {fq_f32|fq_bf16|fq_bf16_stochastic|pack_wire|pack_wire_f32|unpack_wire|unpack_wire_bf16|
+                            unpack_sum4|gemm_fwd|gemm_dx|gemm_dw|fq_f32_full} [--launches n]
 
-Device footprint stays under 1 GB so that a multi-pass capture finishes quickly.
+Device footprint stays under 1 GB so that a multi-pass capture finishes quickly (fq_f32_full is the
+benchmark's own 32768 x 8192 launch, 2 GiB, meant for single-pass metrics only).
 """
 from __future__ import annotations
 
@@ -10,18 +12,21 @@ import sys
 
 import torch
 
-from . import _lib
+from axs6_b200 import _lib
 
 
-def main() -> None:
-    what = sys.argv[1] if len(sys.argv) > 1 else "fq_f32"
-    n = int(sys.argv[2]) if len(sys.argv) > 2 else 3
+def run_case(what: str = "fq_f32", n: int = 3) -> None:
     lib = _lib.load()
     dev = torch.device("cuda", 0)
     rows, cols = 8192, 8192                       # 256 MiB fp32 / 128 MiB bf16: larger than the 126 MB L2
     g = torch.Generator(device=dev).manual_seed(0)
     st = torch.cuda.current_stream().cuda_stream
-    if what == "fq_f32":
+    if what == "fq_f32_full":
+        rows, cols = 32768, 8192
+        x = torch.randn(rows, cols, generator=g, device=dev)
+        y = torch.empty_like(x)
+        run = lambda: lib.axs6_fq(x.data_ptr(), y.data_ptr(), 0, 0, rows, cols, cols, cols, 32, 1, 0, 0, 0, 0, st)
+    elif what == "fq_f32":
         x = torch.randn(rows, cols, generator=g, device=dev)
         y = torch.empty_like(x)
         run = lambda: lib.axs6_fq(x.data_ptr(), y.data_ptr(), 0, 0, rows, cols, cols, cols, 32, 1, 0, 0, 0, 0, st)
@@ -44,7 +49,7 @@ def main() -> None:
         y = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev)
         run = lambda: lib.axs6_unpack(1, w.data_ptr(), None, None, y.data_ptr(), 1, rows, cols, cols, 32, 1, st)
     elif what == "unpack_sum4":
-        from . import ops
+        from axs6_b200 import ops
         per = rows * cols // 32 * 25
         w = torch.empty(4 * per, dtype=torch.uint8, device=dev)
         for s_ in range(4):
@@ -83,4 +88,4 @@ def main() -> None:
 
 
 if __name__ == "__main__":
-    main()
+    run_case(sys.argv[1] if len(sys.argv) > 1 else "fq_f32", int(sys.argv[2]) if len(sys.argv) > 2 else 3)

@@ -29,7 +29,7 @@ class _Bucket:
 
 def run(rank: int, world: int, dev, steps: int = 10) -> dict:
     import torch.distributed as dist
-    from .unified import distributed as udist
+    from axs6_b200.unified import distributed as udist
     g = torch.Generator(device=dev).manual_seed(900 + rank)
     grad = torch.randn(NUMEL, generator=g, device=dev) * 1e-3
     state = udist.HookState()

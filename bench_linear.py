@@ -1,0 +1,319 @@
+"""Timing of the AXS-6 Linear forward + backward (bf16 activations (M, K), fp32 master weights
+(N, K), block 32 along K) for ``bench.py``: K = N = 4096.
+
+One step = ``axs6_linear_fwd`` + ``axs6_linear_bwd`` through the C ABI with caller-owned buffers:
+fake-quantise passes for activations, weight and (stochastic) gradient, three tcgen05 GEMMs, the
+bias-gradient column sums.  The backward reuses the forward's quantised weight.
+
+More than one rank = data parallel over the batch: X, Y, dX sharded by rows, W replicated, the fp32
+weight gradient summed with an NCCL all-reduce.  The backward is issued as two calls: the first
+produces dW, whose all-reduce starts at once on NCCL's stream; the second produces dX and db under
+it, with a few SMs left free for the collective's CTAs (``axs6_tune(8, n)``).  Both readings of
+"N GPUs" are timed: ``weak`` = 16384 rows per GPU, ``strong`` = 16384 rows in total, and for the
+strong case also the compute alone (all-reduce off).
+"""
+from __future__ import annotations
+
+import torch
+
+from axs6_b200 import _lib
+
+M_ROWS, K, N, BLOCK = 16384, 4096, 4096, 32
+FLAG_QGRAD, FLAG_REUSE_WQ, FLAG_REUSE_GQ, FLAG_PACKED = 2, 32, 64, 128
+
+
+class _Case:
+    """Buffers and launch closures of one Linear of M rows on this rank."""
+
+    def __init__(self, lib, dev, M: int, seed: int, packed: bool = False):
+        self.lib, self.M = lib, M
+        self.pk = FLAG_PACKED if packed else 0
+        g = torch.Generator(device=dev).manual_seed(seed)
+        self.x = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+        self.w = torch.randn(N, K, generator=g, device=dev) * 0.02
+        self.bias = torch.zeros(N, device=dev)
+        self.go = torch.randn(M, N, generator=g, device=dev).to(torch.bfloat16)
+        self.y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        self.dx = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+        self.dws = [torch.empty(N, K, dtype=torch.float32, device=dev) for _ in range(2)]
+        self.db = torch.empty(N, dtype=torch.float32, device=dev)
+        codes = (8, 9, 10, 3) if packed else (0, 1, 2, 3)
+        ws = [torch.empty(int(lib.axs6_linear_workspace_bytes(i, M, N, K)), dtype=torch.uint8, device=dev) for i in codes]
+        self.xq, self.wq, self.gq, self.part = ws
+        self.stream = torch.cuda.current_stream().cuda_stream
+
+    def fwd(self):
+        st = self.lib.axs6_linear_fwd(self.x.data_ptr(), 1, K, self.w.data_ptr(), 0, K, self.bias.data_ptr(), self.y.data_ptr(),
+                                      1, N, self.M, N, K, BLOCK, 1, 1 | self.pk, self.xq.data_ptr(), self.wq.data_ptr(), self.stream)
+        assert st == 0, st
+
+    def _bwd(self, i, dx, dw, db, flags):
+        M = self.M
+        st = self.lib.axs6_linear_bwd(self.go.data_ptr(), 1, N, self.xq.data_ptr(), self.w.data_ptr(), 0, K, dx, 1, K, dw, K, db,
+                                      M, N, K, BLOCK, 1, flags | self.pk, 1234, i * (M * N // 8), None, self.gq.data_ptr(),
+                                      self.wq.data_ptr(), self.part.data_ptr(), None, self.stream)
+        assert st == 0, st
+
+    def bwd_dw(self, i):
+        self._bwd(i, None, self.dws[i % 2].data_ptr(), None, FLAG_QGRAD)
+
+    def bwd_dx(self, i):
+        self._bwd(i, self.dx.data_ptr(), None, self.db.data_ptr(), FLAG_QGRAD | FLAG_REUSE_WQ | FLAG_REUSE_GQ)
+
+    def bwd_all(self, i):
+        self._bwd(i, self.dx.data_ptr(), self.dws[i % 2].data_ptr(), self.db.data_ptr(), FLAG_QGRAD | FLAG_REUSE_WQ)
+
+
+def _rel(a, b) -> float:
+    a, b = a.double(), b.double()
+    return float((a - b).norm() / b.norm())
+
+
+def _parity(case: _Case) -> dict:
+    """One forward + backward, then 64 sampled rows of y, dX and dW against fp32 products (cuBLAS, TF32 off) of the
+    quantised operands the step itself produced.  Tolerances: bf16 outputs 4e-3, fp32 dW 1e-3 (relative Frobenius)."""
+    M = case.M
+    case.fwd()
+    case.bwd_all(0)
+    torch.cuda.synchronize()
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        xq = case.xq.view(torch.bfloat16).view(M, K)
+        wq = case.wq.view(torch.bfloat16).view(N, K)
+        gq = case.gq.view(torch.bfloat16).view(M, N)
+        g = torch.Generator(device="cpu").manual_seed(5)
+        ri = torch.randperm(M, generator=g)[:64].to(xq.device)
+        ni = torch.randperm(N, generator=g)[:64].to(xq.device)
+        ey = _rel(case.y[ri].float(), xq[ri].float() @ wq.float().t() + case.bias.to(torch.bfloat16).float())
+        edx = _rel(case.dx[ri].float(), gq[ri].float() @ wq.float())
+        edw = _rel(case.dws[0][ni], gq[:, ni].float().t() @ xq.float())
+        edb = _rel(case.db, case.go.float().sum(0))
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    ok = ey < 4e-3 and edx < 4e-3 and edw < 1e-3 and edb < 1e-4
+    return {"parity_checked": bool(ok), "rel_err": {"y": ey, "dx": edx, "dw": edw, "db": edb},
+            "against": "fp32 matmul (TF32 off) of the step's own quantised operands, 64 sampled rows per product"}
+
+
+def _time_steps(case: _Case, steps: int, world: int, dist, group, allreduce: bool, reserve: int, lib, dev):
+    """CUDA-event time per step, max over ranks; kernel launches of this library per step."""
+    pending = [None, None]
+
+    def step(i):
+        case.fwd()
+        if pending[i % 2] is not None:
+            pending[i % 2].wait()
+            pending[i % 2] = None
+        if allreduce and world > 1:
+            case.bwd_dw(i)
+            pending[i % 2] = dist.all_reduce(case.dws[i % 2], group=group, async_op=True)
+            if reserve:
+                lib.axs6_tune(8, reserve)
+            case.bwd_dx(i)
+            if reserve:
+                lib.axs6_tune(8, 0)
+        else:
+            case.bwd_all(i)
+
+    def drain():
+        for j in range(2):
+            if pending[j] is not None:
+                pending[j].wait()
+                pending[j] = None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(3):
+        step(i)
+    drain()
+    barrier()
+    l0 = _lib.launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(i)
+    drain()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item()) / steps, (_lib.launches() - l0) / steps
+
+
+def _packed_variant(lib, dev, steps: int, t_of) -> dict:
+    """The same step with AXS6_LINEAR_OPERANDS_PACKED, and its kernels alone (M = 16384, one GPU)."""
+    M = M_ROWS
+    c = _Case(lib, dev, M, 4000, packed=True)
+    st = c.stream
+
+    def step(i=[0]):
+        c.fwd()
+        c.bwd_all(i[0])
+        i[0] += 1
+    step()
+    torch.cuda.synchronize()
+    ms = t_of(step, max(5, steps // 2))
+    off = lambda rows, cols: (rows * (cols // 32) * 24 + 255) // 256 * 256
+    xq, wq, gq = c.xq.data_ptr(), c.wq.data_ptr(), c.gq.data_ptr()
+    xe, we, ge = xq + off(M, K), wq + off(N, K), gq + off(M, N)
+    fl = 2.0 * M * N * K
+    out = {"ms_per_step": ms, "TFLOPs": 3 * fl / (ms * 1e-3) / 1e12, "parts": {}}
+    gf = lambda: lib.axs6_gemm_packed(xq, xe, 0, wq, we, 0, c.y.data_ptr(), None, M, N, K, N, 0, 0, 1, st)
+    gdx = lambda: lib.axs6_gemm_packed(gq, ge, 0, wq, we, 0, c.dx.data_ptr(), None, M, K, N, K, 0, 1, 1, st)
+    gdw = lambda: lib.axs6_gemm_packed(gq, ge, 0, xq, xe, 0, c.dws[0].data_ptr(), None, N, K, M, K, 1, 1, 0, st)
+    for name, fn in (("gemm_fwd", gf), ("gemm_dx", gdx), ("gemm_dw", gdw)):
+        assert fn() == 0
+        m = t_of(fn)
+        out["parts"][name] = {"ms": m, "TFLOPs": fl / (m * 1e-3) / 1e12}
+    px = lambda: lib.axs6_pack(c.x.data_ptr(), 1, M, K, K, 32, 1, 0, 1, 0, 0, None, 3, xq, xe, None, st)
+    pw = lambda: lib.axs6_pack(c.w.data_ptr(), 0, N, K, K, 32, 1, 0, 1, 0, 0, None, 3, wq, we, None, st)
+    pg = lambda: lib.axs6_pack(c.go.data_ptr(), 1, M, N, N, 32, 1, 1, 1, 7, 0, None, 3, gq, ge, None, st)
+    for name, fn, nb in (("pack_x", px, M * K * 2.78125), ("pack_w", pw, N * K * 4.78125), ("pack_g_stochastic", pg, M * N * 2.78125)):
+        assert fn() == 0
+        m = t_of(fn)
+        out["parts"][name] = {"ms": m, "GBps": nb / (m * 1e-3) / 1e9}
+    # only W as codes (activations and gradient stay bf16 tiles fed by TMA)
+    bx = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+    gw = lambda: lib.axs6_gemm_packed(bx.data_ptr(), None, K, wq, we, 0, c.y.data_ptr(), None, M, N, K, N, 0, 0, 1, st)
+    assert gw() == 0
+    m = t_of(gw)
+    out["parts"]["gemm_fwd_only_w_packed"] = {"ms": m, "TFLOPs": fl / (m * 1e-3) / 1e12}
+    out["gemm_status"] = int(lib.axs6_gemm_status())
+    out["note"] = ("activations, weight and gradient written to HBM as 6-bit codes (0.78 bytes per value) by axs6_pack and decoded "
+                   "to bf16 by the decode warps of axs6_gemm_packed; compare with `parts` (bf16 workspaces + plain GEMM)")
+    return out
+
+
+def run(args, rank: int, world: int, dev, pk: dict, steps: int | None = None) -> dict:
+    import torch.distributed as dist
+    lib = _lib.load()
+    steps = steps or max(5, min(args.steps, 20))
+    weak = _Case(lib, dev, M_ROWS, 4000 + rank)
+    parity = _parity(weak) if rank == 0 else {}
+    flops_weak = 6.0 * M_ROWS * N * K
+
+    # a process group of its own whose collective kernels use few CTAs, so that they fit beside the GEMM
+    group, nccl_ctas = None, None
+    if world > 1:
+        try:
+            opts = dist.ProcessGroupNCCL.Options()
+            opts.config.max_ctas = 16
+            opts.config.min_ctas = 1
+            group = dist.new_group(ranks=list(range(world)), pg_options=opts)
+            nccl_ctas = 16
+        except Exception:
+            group = None
+
+    res = {}
+    ms, launches = _time_steps(weak, steps, world, dist, group, True, 16 if world > 1 else 0, lib, dev)
+    res_weak = {"ms_per_step": ms, "TFLOPs": world * flops_weak / (ms * 1e-3) / 1e12, "rows_per_gpu": M_ROWS}
+    reserve_sweep = {}
+    if world > 1:
+        for n in (0, 8, 24):
+            m_n, _ = _time_steps(weak, max(5, steps // 2), world, dist, group, True, n, lib, dev)
+            reserve_sweep[str(n)] = m_n
+        reserve_sweep["16"] = ms
+        m_off, _ = _time_steps(weak, max(5, steps // 2), world, dist, group, False, 0, lib, dev)
+        res_weak["ms_per_step_allreduce_off"] = m_off
+        res_weak["ms_per_step_by_reserved_sms"] = reserve_sweep
+    status = int(lib.axs6_gemm_status())
+
+    # the three GEMMs and the fake-quantise passes alone, and the library GEMM (cuBLAS through torch.matmul) on the
+    # same quantised bf16 operands in the same process
+    parts = {}
+    if rank == 0:
+        c, M = weak, M_ROWS
+        stream = c.stream
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+        def t_of(fn, n=10):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n
+        xq, wq, gq = c.xq, c.wq, c.gq
+        gf = lambda: lib.axs6_gemm_bf16(xq.data_ptr(), wq.data_ptr(), c.y.data_ptr(), None, M, N, K, K, K, N, 0, 0, 1, stream)
+        gdx = lambda: lib.axs6_gemm_bf16(gq.data_ptr(), wq.data_ptr(), c.dx.data_ptr(), None, M, K, N, N, K, K, 0, 1, 1, stream)
+        gdw = lambda: lib.axs6_gemm_bf16(gq.data_ptr(), xq.data_ptr(), c.dws[0].data_ptr(), None, N, K, M, N, K, K, 1, 1, 0, stream)
+        fqx = lambda: lib.axs6_fq(c.x.data_ptr(), xq.data_ptr(), 1, 1, M, K, K, K, BLOCK, 1, 0, 1, 0, 0, stream)
+        fqw = lambda: lib.axs6_fq(c.w.data_ptr(), wq.data_ptr(), 0, 1, N, K, K, K, BLOCK, 1, 0, 1, 0, 0, stream)
+        fqg = lambda: lib.axs6_fq(c.go.data_ptr(), gq.data_ptr(), 1, 1, M, N, N, N, BLOCK, 1, 1, 1, 7, 0, stream)
+        dbs = lambda: lib.axs6_bias_grad(c.go.data_ptr(), 1, N, M, N, c.db.data_ptr(), c.part.data_ptr(), stream)
+        txq, twq, tgq = (t.view(torch.bfloat16) for t in (xq, wq, gq))
+        txq, twq, tgq = txq.view(M, K), twq.view(N, K), tgq.view(M, N)
+        ty, tdx, tdw = torch.empty_like(c.y), torch.empty_like(c.dx), torch.empty(N, K, dtype=torch.bfloat16, device=dev)
+        lib_f = lambda: torch.matmul(txq, twq.t(), out=ty)
+        lib_dx = lambda: torch.matmul(tgq, twq, out=tdx)
+        lib_dw = lambda: torch.matmul(tgq.t(), txq, out=tdw)
+        fl = 2.0 * M * N * K
+        for name, fn, lfn in (("gemm_fwd", gf, lib_f), ("gemm_dx", gdx, lib_dx), ("gemm_dw", gdw, lib_dw)):
+            m = t_of(fn)
+            ml = t_of(lfn)
+            parts[name] = {"ms": m, "TFLOPs": fl / (m * 1e-3) / 1e12,
+                           "library_ms": ml, "library_TFLOPs": fl / (ml * 1e-3) / 1e12, "vs_library": ml / m}
+        for name, fn, nb in (("fq_x", fqx, M * K * 4), ("fq_w", fqw, N * K * 6), ("fq_g_stochastic", fqg, M * N * 4),
+                             ("bias_grad", dbs, M * N * 2)):
+            m = t_of(fn)
+            parts[name] = {"ms": m, "GBps": nb / (m * 1e-3) / 1e9}
+        parts["library"] = "torch.matmul (cuBLAS) on the same quantised bf16 operands, bf16 output, same process"
+        del ty, tdx, tdw
+    best = max((v["TFLOPs"] for k, v in parts.items() if k.startswith("gemm")), default=0.0)
+    del weak
+    torch.cuda.empty_cache()
+
+    # the quantise-on-load variant: operands in HBM as 6-bit codes, decoded to bf16 inside the GEMMs
+    packed = None
+    if rank == 0:
+        try:
+            packed = _packed_variant(lib, dev, steps, t_of)
+        except Exception as e:
+            packed = {"error": repr(e)}
+        torch.cuda.empty_cache()
+
+    strong = None
+    if world > 1:
+        Ms = M_ROWS // world
+        sc = _Case(lib, dev, Ms, 4100 + rank)
+        flops_strong = 6.0 * M_ROWS * N * K                 # whole job
+        m_s, _ = _time_steps(sc, steps, world, dist, group, True, 16, lib, dev)
+        m_c, _ = _time_steps(sc, steps, world, dist, group, False, 0, lib, dev)
+        strong = {"rows_per_gpu": Ms, "ms_per_step": m_s, "TFLOPs": flops_strong / (m_s * 1e-3) / 1e12,
+                  "compute_only": {"ms_per_step": m_c, "TFLOPs": flops_strong / (m_c * 1e-3) / 1e12,
+                                   "note": "the same sharded step with the dW all-reduce switched off"}}
+        del sc
+        torch.cuda.empty_cache()
+
+    tflops = res_weak["TFLOPs"]
+    out = {
+        "metric": "axs6_linear_fwd_bwd_TFLOPs", "value": tflops, "unit": "TFLOP/s", "ms_per_step": res_weak["ms_per_step"],
+        "steps": steps, "n_gpus": world, "scaling": "weak", "gpu_launches": launches * steps, "gemm_status": status,
+        "workload": (f"AXS-6 Linear fwd+bwd, M={M_ROWS} rows per GPU, K={K}, N={N}, bf16 activations, fp32 master weights, "
+                     f"block {BLOCK} along K, stochastic gradient rounding" +
+                     (", dW all-reduced over NCCL under the dX product" if world > 1 else "")),
+        "algorithmic_flops_per_step": flops_weak,
+        "roofline": {"bound": "tensor", "achieved": tflops / world, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": tflops / world / pk["bf16_tflops_sustained"], "peak_burst": pk["bf16_tflops"],
+                     "frac_of_burst": tflops / world / pk["bf16_tflops"], "peak_source": pk["source"],
+                     "note": "whole step (fake-quantise passes + 3 GEMMs + column sums) over 6*M*N*K flops, against the "
+                             "sustained cuBLAS bf16 figure; per-kernel figures in `parts`"},
+        "best_gemm_TFLOPs": best,
+        "parts": parts,
+        "weak": res_weak,
+    }
+    out.update(parity)
+    if packed is not None:
+        out["operands_packed"] = packed
+    if strong is not None:
+        out["strong"] = strong
+        out["nccl_max_ctas"] = nccl_ctas
+    return out

@@ -16,7 +16,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .unified.mixed_precision import AXSLinearMixedPrecision
+from axs6_b200.unified.mixed_precision import AXSLinearMixedPrecision
 
 LAYERS, D_MODEL, HEADS, FFN, SEQ, VOCAB, BATCH = 12, 1024, 16, 4096, 1024, 32000, 8
 
@@ -83,7 +83,7 @@ def _graphed_step(dev, steps: int) -> dict:
     AdamW) and replayed, which removes the host launch cost of about 1300 kernels per step (measured: the
     step is GPU-bound either way, 29 ms replayed against 31 ms eager).  The captured step starts with `philox_advance`, so every replay rounds the
     gradients with fresh draws although the host-side offsets are frozen in the graph."""
-    from . import _lib, ops
+    from axs6_b200 import _lib, ops
     torch.manual_seed(1234)
     model = MiniGPT(lambda i, o, bias=True: AXSLinearMixedPrecision(i, o, bias=bias)).to(dev)
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True, capturable=True)
@@ -135,7 +135,7 @@ def _graphed_step(dev, steps: int) -> dict:
 
 def run(args, rank: int, world: int, dev, steps: int = 8) -> dict:
     import torch.distributed as dist
-    from . import _lib
+    from axs6_b200 import _lib
     out = {}
     for name, linear in (("axs6", lambda i, o, bias=True: AXSLinearMixedPrecision(i, o, bias=bias)),
                          ("bf16_nn_linear", lambda i, o, bias=True: _Bf16Linear(i, o, bias=bias))):

@@ -33,8 +33,13 @@ enum { AXS6_LAYOUT_PLANES = 0, /* AXSTensor planes: u8 exponent (rows,nblk), u8 
                                   magnitude (rows,nblk,block)      (axs/core.py:160-182)      */
        AXS6_LAYOUT_WIRE = 1,   /* per block: 1 exponent byte + 6-bit codes, 25 B for block 32
                                   (axs/unified/distributed.py:147-198)                        */
-       AXS6_LAYOUT_SPEC = 2 }; /* per block: u16 LE (exponent<<2 | config 0) + 6-bit codes,
+       AXS6_LAYOUT_SPEC = 2,   /* per block: u16 LE (exponent<<2 | config 0) + 6-bit codes,
                                   26 B for block 32 (axs/core.py:97-118, FORMAT_SPEC.md:29-48) */
+       AXS6_LAYOUT_SPLIT = 3 };/* the bytes of a WIRE record in two planes: payloads (rows, nblk, 3*block/4)
+                                  and exponents u8 (rows, nblk).  Rows of the payload plane start 16-byte
+                                  aligned when cols is a multiple of 64, which is what lets the TMA unit
+                                  fetch operand tiles of packed codes for axs6_gemm_packed.  (No
+                                  counterpart in the reference; same 25 bytes per block of 32.)          */
 
 /* flags */
 #define AXS6_FLAG_INPUT_VIA_BF16 1u /* round an fp32 input to bf16 before quantising: the
@@ -53,6 +58,22 @@ enum { AXS6_LAYOUT_PLANES = 0, /* AXSTensor planes: u8 exponent (rows,nblk), u8 
                                          `bias.to(bfloat16)` (mixed_precision.py:108)                 */
 #define AXS6_LINEAR_BIAS_FROM_QUANTIZED 8u /* db sums the QUANTISED gradient, as the fp32 reference
                                          functions do (functional_unified.py:151, :161-165)      */
+
+#define AXS6_LINEAR_REUSE_WQ 32u       /* backward: `wq` already holds FQ(bf16(w)) -- the buffer the forward call of the
+                                         same step filled, with the weight unchanged since -- so it is not
+                                         recomputed (bit-identical by construction; the reference recomputes only
+                                         to save memory, mixed_precision.py:130); `w` may then be NULL      */
+#define AXS6_LINEAR_REUSE_GQ 64u       /* backward: `gq` already holds the quantised gradient, written by an earlier
+                                         axs6_linear_bwd call on the same g (lets a caller ask for dw first, start
+                                         its all-reduce, and then ask for dx / db without a second rounding pass) */
+
+#define AXS6_LINEAR_OPERANDS_PACKED 128u /* quantise on load: xq / wq / gq hold 6-bit codes (payload plane, then the exponent
+                                         plane at the next 256-byte boundary; workspace codes 8, 9, 10) instead of bf16,
+                                         and the GEMMs decode them in shared memory (axs6_gemm_packed).  Needs
+                                         AXS6_LINEAR_QUANTIZE_INPUT / _GRAD, NF5, block 32, K and N multiples of 64
+                                         (AXS6_ERR_UNSUPPORTED otherwise).  The saved activation shrinks from 2 to
+                                         0.78 bytes per value.  Equal to the bf16 path except where an operand holds
+                                         an exact zero, which codes cannot express (see axs6_gemm_packed)        */
 
 #define AXS6_OK 0
 #define AXS6_ERR_ARG (-1)         /* null pointer, negative size, bad enum, bad block size  */
@@ -75,10 +96,12 @@ int64_t axs6_query(int what);
  *   key 1   the same for the pack / unpack kernels
  *   key 2   record pack of bf16 / fp32 input: 1 = general kernel only, 2 = bf16 kernel with per-thread
  *           loads instead of the TMA-fed one
- *   key 3   GEMM K splits: 1 = never split (bit-reproducible fp32 outputs), 2 = two-way split of every
- *           tile in the CTA-pair kernel
- *   keys 4-6  overrides of the GEMM's shared-memory descriptor strides (LBO, SBO, K step)
- *   key 7   GEMM kernel: 1 single-CTA, 2 CTA pairs, 3 CTA pairs with 128-wide tiles
+ *   key 3   GEMM K splits of fp32 outputs.  Built-in (0): at most two partial products per output element,
+ *           whose sum does not depend on their order, so every result is bit-reproducible.  1 = never
+ *           split, 2 = two-way split of every tile in the CTA-pair kernel, 3 = allow up to 8 / 16 partials
+ *           for problems with few tiles: faster weight gradients of small layers, but the partials are added
+ *           in no fixed order and the last bits can differ from run to run
+ *   key 7   GEMM kernel: 1 single-CTA, 2 CTA pairs
  *   key 8   SMs the GEMM leaves free (for a collective on another stream)
  *   key 11  1 = general unpack / unpack-and-sum kernels only (no TMA-fed kernel)
  *   key 12  1 = general fake-quantise kernel only (no TMA-fed bf16 kernel) */
@@ -121,6 +144,7 @@ int axs6_fq_with_noise(const void *x, void *y, int in_dtype, int out_dtype,
  * layout PLANES: out0 = exponents u8 (rows*nblk), out1 = signs u8 (rows*nblk*block),
  *                out2 = magnitudes u8 (rows*nblk*block).
  * layout WIRE/SPEC: out0 = rows*nblk records of (1|2) + block*3/4 bytes; out1/out2 unused.
+ * layout SPLIT: out0 = rows*nblk payloads of block*3/4 bytes, out1 = rows*nblk exponent bytes.
  * `noise` (may be NULL) as in axs6_fq_with_noise; if NULL and rounding is stochastic the
  * Philox stream (seed, offset) is used. */
 int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, int64_t ldx,
@@ -161,6 +185,21 @@ int axs6_gemm_bf16(const void *a, const void *b, void *c, const float *bias,
                    int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                    int a_mn, int b_mn, int c_dtype, axs6_stream_t stream);
 
+/* The same product with one or both operands held as AXS-6 codes and decoded to bf16 inside the kernel
+ * ("quantise on load"): the data flow of the reference's fused linear kernel, which produces the quantised
+ * tile inside its K loop (axs/unified/triton_kernels.py:151-282), so that no quantised operand is written to
+ * HBM as bf16.  An operand with a non-null exponent plane (`a_exps` / `b_exps`) is packed: its pointer is the
+ * payload plane of AXS6_LAYOUT_SPLIT (NF5 grid, block 32, blocks along the operand's contiguous dimension,
+ * as written by axs6_pack for the stored matrix: (M,K) or (K,M) for A, (N,K) or (K,N) for B) and its
+ * leading dimension is ignored; its contiguous extent must be a multiple of 64 (AXS6_ERR_UNSUPPORTED
+ * otherwise).  An operand with a null exponent plane is bf16 as in axs6_gemm_bf16.  At least one operand
+ * must be packed.  The decoded values are bit-identical to axs6_unpack(..., AXS6_BF16) of the same codes;
+ * note that codes cannot express an exact zero (axs/unified/quantize_unified.py:273, :300-302: a zero
+ * input packs to the smallest level), which is where this differs from fake-quantising the operand. */
+int axs6_gemm_packed(const void *a, const void *a_exps, int64_t lda, const void *b, const void *b_exps, int64_t ldb,
+                     void *c, const float *bias, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                     int a_mn, int b_mn, int c_dtype, axs6_stream_t stream);
+
 /* Same product with fp32 operands that the tensor cores consume as TF32 (kind::tf32): 10 mantissa
  * bits of every operand value are used, the rest is ignored.  For the fp32 Linear paths
  * (axs/unified/functional_unified.py:123, :155-160; axs/nn/functional.py:121, :144-145;
@@ -182,7 +221,9 @@ int axs6_transpose_f32(const float *in, float *out, int64_t rows, int64_t cols,
 /* Device-side status of the GEMM kernels since the last call of this function: 0 = every
  * wait inside the kernels completed; n > 0 = a bounded wait gave up (1 TMA producer waiting
  * for a free stage, 2 MMA issuer waiting for a free accumulator, 3 MMA issuer waiting for a
- * loaded stage, 4 epilogue waiting for a finished accumulator) and the result is invalid.
+ * loaded stage, 4 epilogue waiting for a finished accumulator; axs6_gemm_packed also 5 decode warps waiting
+ * for a payload tile, 6 decode warps waiting for a free stage, 7 producer waiting for a free payload stage)
+ * and the result is invalid.
  * Synchronises the device and clears the status. */
 int axs6_gemm_status(void);
 
@@ -222,10 +263,10 @@ int axs6_linear_fwd(const void *x, int x_dtype, int64_t ldx, const void *w, int 
                     int64_t M, int64_t N, int64_t K, int block, int grid, uint32_t flags,
                     void *xq, void *wq, axs6_stream_t stream);
 
-/* Backward:  wq = FQ(bf16(w)) (recomputed, mixed_precision.py:130), gq = FQ_stochastic(bf16(g))
- *            (or bf16(g) without AXS6_LINEAR_QUANTIZE_GRAD, :133-136), dx (M,K) = gq wq stored as
- *            dx_dtype (:139), dw (N,K) = gq^T xq in fp32 (:145), db (N) = column sums of the
- *            un-quantised g in fp32 (:150).  Any of dx, dw, db may be NULL (not needed).
+/* Backward:  gq = FQ_stochastic(bf16(g)) (or bf16(g) without AXS6_LINEAR_QUANTIZE_GRAD,
+ *            mixed_precision.py:133-136), dw (N,K) = gq^T xq in fp32 (:145), wq = FQ(bf16(w)) (recomputed, :130,
+ *            unless AXS6_LINEAR_REUSE_WQ), dx (M,K) = gq wq stored as dx_dtype (:139), db (N) = column sums of
+ *            the un-quantised g in fp32 (:150), enqueued in this order.  Any of dx, dw, db may be NULL (not needed).
  * `noise` (may be NULL): U[0,1) draws for the gradient in the padded (M, nblk, block) layout,
  * instead of the Philox stream (seed, offset).  Workspaces: gq = what 2, wq = what 1,
  * db_partial = what 3 of axs6_linear_workspace_bytes (db_partial only if db is given);
@@ -266,7 +307,8 @@ int axs6_bias_grad_static(const void *g, int g_dtype, int64_t ldg, int64_t rows,
                           float *db, axs6_stream_t stream);
 
 /* Bytes of a caller-owned work buffer: what 0 = xq, 1 = wq, 2 = gq (bf16 compute), 3 = db_partial,
- * 4 = xq, 5 = wq, 6 = gq of the AXS6_LINEAR_COMPUTE_TF32 graph (fp32), 7 = its tf32_scratch. */
+ * 4 = xq, 5 = wq, 6 = gq of the AXS6_LINEAR_COMPUTE_TF32 graph (fp32), 7 = its tf32_scratch,
+ * 8 = xq, 9 = wq, 10 = gq of AXS6_LINEAR_OPERANDS_PACKED (codes). */
 int64_t axs6_linear_workspace_bytes(int what, int64_t M, int64_t N, int64_t K);
 
 #ifdef __cplusplus

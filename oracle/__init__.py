@@ -213,6 +213,11 @@ def gemm_nt(a: np.ndarray, b: np.ndarray) -> np.ndarray:
     return c
 
 
+def set_threads(n: int = 0) -> int:
+    """Set (n > 0) and return the number of OpenMP threads the oracle's loops use."""
+    return int(lib().orc_set_threads(int(n)))
+
+
 def log2_bump_scan(cap: int = 1 << 16) -> np.ndarray:
     out = np.zeros(cap, dtype=np.uint32)
     n = lib().orc_log2_bump_scan(_p(out), _i64(cap))

@@ -19,8 +19,25 @@
 #include <math.h>
 #include <stdint.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 typedef int64_t i64;
+
+/* Threads the parallel loops below use: n > 0 sets the count (a launcher may have exported
+ * OMP_NUM_THREADS=1), the return value is the count in effect.  Used by the timed CPU baseline,
+ * which states the number of cores it ran on. */
+int orc_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
 
 /* floor(log2(a)) as torch's fp32 CPU log2 returns it: the fp32 result of log2
  * behaves as the correctly rounded value, so an amax a few ulps below a power of

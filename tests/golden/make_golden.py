@@ -14,6 +14,8 @@ Files written:
   fq_cases.npz       fake-quantise / quantise / byte-layout cases (nearest and stochastic)
   linear_cases.npz   small Linear forward/backward cases of the three autograd Functions
   manifest.json      case list, torch version, sha256 of the large-config outputs
+  block_cases.npz    per-block host utilities of axs/core.py (axs_encode_block / axs_decode_block /
+                     AXSBlock.to_bytes) and quantization_error; written alone with --only blocks
 """
 from __future__ import annotations
 
@@ -153,9 +155,68 @@ def grid_boundary_blocks() -> torch.Tensor:
     return torch.from_numpy(np.concatenate([blocks, blocks * np.float32(2.0 ** -9)], axis=0))
 
 
+def block_cases(ref_core) -> None:
+    """Inputs and the reference's outputs for the per-block encoder / decoder (numpy, double precision) and for
+    quantization_error (torch, CPU)."""
+    gen = np.random.default_rng(77)
+    store = {}
+    n = 0
+    for B in (8, 16, 32):
+        blocks = [gen.standard_normal(B) * s for s in (1.0, 1e-3, 37.5, 2.0 ** -130, 1e30)]
+        blocks.append(np.zeros(B))
+        blocks.append(np.full(B, 0.5))                                   # maximum exactly a power of two
+        tie = (np.arange(B) % 32 + 0.5) / 31.0 * 0.999                   # values near half-way points of the grid
+        blocks.append(tie)
+        blocks.append(np.float64(np.float32(gen.standard_normal(B))))    # fp32-representable values
+        neg = gen.standard_normal(B)
+        neg[::3] = -0.0
+        blocks.append(neg)
+        for v in blocks:
+            for rounding in ("nearest", "stochastic"):
+                name = f"blk{n}"
+                np.random.seed(1000 + n)
+                draws = np.random.uniform(0, 1, size=B)
+                np.random.seed(1000 + n)
+                blk = ref_core.axs_encode_block(v, rounding)
+                store[f"{name}.values"] = np.asarray(v, dtype=np.float64)
+                store[f"{name}.rounding"] = np.array([rounding == "stochastic"])
+                store[f"{name}.seed"] = np.array([1000 + n])
+                store[f"{name}.draws"] = draws
+                store[f"{name}.exponent"] = np.array([blk.shared_exponent])
+                store[f"{name}.signs"] = np.asarray(blk.signs, dtype=bool)
+                store[f"{name}.magnitudes"] = np.asarray(blk.magnitudes, dtype=np.uint8)
+                store[f"{name}.bytes"] = np.frombuffer(blk.to_bytes(), dtype=np.uint8)
+                store[f"{name}.decoded"] = ref_core.axs_decode_block(blk)
+                store[f"{name}.props"] = np.array([blk.scale, blk.total_bits, blk.bits_per_value])
+                n += 1
+    store["count"] = np.array([n])
+    tg = torch.Generator().manual_seed(5)
+    x = torch.randn(64, 256, generator=tg)
+    for B in (8, 16, 32):
+        e = ref_core.quantization_error(x, B, "nearest")
+        store[f"qerr.b{B}"] = np.array([e["mse"], e["rmse"], e["max_abs_error"], e["mean_abs_error"], e["signal_to_noise_db"]])
+    store["qerr.x"] = bits(x)
+    # gradient-aware stochastic rounding (axs/quantize.py:203-307) with recorded draws
+    ref_q = __import__("importlib").import_module("axs.quantize")
+    for B, shape in ((32, (48, 96)), (16, (20, 50)), (8, (7, 24))):
+        xg = torch.randn(*shape, generator=tg) * 0.3
+        gg = torch.randn(*shape, generator=tg) * torch.rand(shape[0], 1, generator=tg) * 4
+        nblk = -(-shape[1] // B)
+        noise = rand24(gen, shape[0] * nblk * B).reshape(shape[0], nblk, B)
+        for temp in (1.0, 3.0):
+            with fixed_noise(noise):
+                q = ref_q.quantize_gasr(xg, gg, B, temp)
+            key = f"gasr.b{B}.t{int(temp)}"
+            store[f"{key}.x"] = bits(xg); store[f"{key}.g"] = bits(gg); store[f"{key}.noise"] = noise.numpy()
+            store[f"{key}.se"] = q.shared_exponents.numpy(); store[f"{key}.sign"] = q.signs.numpy(); store[f"{key}.mag"] = q.magnitudes.numpy()
+    np.savez_compressed(os.path.join(HERE, "block_cases.npz"), **store)
+    print(f"wrote {n} block cases")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
+    ap.add_argument("--only", default="", help="'blocks' = write block_cases.npz only")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
@@ -171,6 +232,10 @@ def main() -> None:
     ref_fu = importlib.import_module("axs.unified.functional_unified")
     ref_mp = importlib.import_module("axs.unified.mixed_precision")
     ref_qu = importlib.import_module("axs.unified.quantize_unified")
+
+    block_cases(ref_core)
+    if args.only == "blocks":
+        return
 
     manifest: dict = {"torch": torch.__version__, "cases": {}, "hashes": {}}
 

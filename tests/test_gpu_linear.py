@@ -63,6 +63,18 @@ def test_gemm_ragged_operands_and_bias_and_bf16_out():
     assert torch.equal(Cb.cpu(), C.cpu().to(torch.bfloat16))      # same accumulator, rounded once
 
 
+def test_gemm_single_row_operand_with_ragged_length():
+    """M = 1 with a contraction length that is not a 16-byte multiple (bf16 K = 100, fp32 K = 50)."""
+    g = torch.Generator().manual_seed(3)
+    for dtype, K in ((torch.bfloat16, 100), (torch.float32, 50)):
+        A = torch.randn(1, K, generator=g).to(dtype)
+        B = torch.randn(24, K, generator=g).to(dtype)
+        C = ops.gemm_bf16(A.cuda(), B.cuda())
+        gemm_status_ok()
+        assert C.shape == (1, 24)
+        assert rel(C.cpu(), A.double() @ B.double().t()) < (1e-5 if dtype == torch.bfloat16 else TOL)
+
+
 def test_gemm_rejects_misaligned_operands():
     lib = _lib.load()
     a = torch.zeros(64, 72, dtype=torch.bfloat16, device="cuda")
@@ -139,6 +151,49 @@ def test_linear_fp32_accumulator_meets_1e_minus_3():
     assert rel(y.cpu(), torch.from_numpy(ry)) < 1e-5
     assert rel(dx.cpu(), torch.from_numpy(rdx)) < 1e-5
     assert rel(dw.cpu(), torch.from_numpy(rdw)) < 1e-5
+
+
+def test_backward_reusing_the_forward_quantised_weight_is_bit_identical():
+    """dX from the forward's quantised weight equals dX from the recomputed one (mixed_precision.py:130), also when
+    backward is split into a dW call and a dX call that reuses the rounded gradient; a weight changed in place
+    between forward and backward is re-quantised."""
+    g = torch.Generator().manual_seed(17)
+    M, K, N = 192, 256, 160
+    x = torch.randn(M, K, generator=g).cuda()
+    w0 = (torch.randn(N, K, generator=g) * 0.05).cuda()
+    go = torch.randn(M, N, generator=g).cuda().to(torch.bfloat16)
+    noise = torch.rand(M * N, generator=g).cuda()
+    grads = {}
+    try:
+        for keep in (True, False):
+            mp.KEEP_QUANTIZED_WEIGHT = keep
+            xt, wt = x.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+            y = mp.axs_linear_mixed_precision(xt, wt, None, 32, True, True)
+            mp._noise_for_next_backward = noise
+            y.backward(go)
+            grads[keep] = (xt.grad.clone(), wt.grad.clone())
+    finally:
+        mp.KEEP_QUANTIZED_WEIGHT = True
+    assert torch.equal(grads[True][0], grads[False][0]) and torch.equal(grads[True][1], grads[False][1])
+    # two calls through the C ABI: dW first, then dX / db reusing the rounded gradient and the forward's weight
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    xb = x.to(torch.bfloat16)
+    ws = [torch.empty(int(lib.axs6_linear_workspace_bytes(i, M, N, K)), dtype=torch.uint8, device="cuda") for i in range(4)]
+    yb = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    assert lib.axs6_linear_fwd(xb.data_ptr(), 1, K, w0.data_ptr(), 0, K, None, yb.data_ptr(), 1, N, M, N, K, 32, 1, 1,
+                               ws[0].data_ptr(), ws[1].data_ptr(), st) == 0
+    dx = torch.empty(M, K, dtype=torch.bfloat16, device="cuda")
+    dw = torch.empty(N, K, device="cuda")
+    db = torch.empty(N, device="cuda")
+    args = lambda dxp, dwp, dbp, flags: (go.data_ptr(), 1, N, ws[0].data_ptr(), w0.data_ptr(), 0, K, dxp, 1, K, dwp, K, dbp,
+                                         M, N, K, 32, 1, flags, 0, 0, noise.data_ptr(), ws[2].data_ptr(), ws[1].data_ptr(),
+                                         ws[3].data_ptr(), None, st)
+    assert lib.axs6_linear_bwd(*args(None, dw.data_ptr(), None, 2)) == 0
+    assert lib.axs6_linear_bwd(*args(dx.data_ptr(), None, db.data_ptr(), 2 | 32 | 64)) == 0
+    gemm_status_ok()
+    assert torch.equal(dx.float(), grads[True][0]) and torch.equal(dw, grads[True][1])
+    assert torch.allclose(db, go.float().sum(0), rtol=1e-5, atol=1e-4)
 
 
 def test_linear_golden_from_reference(linear_cases, manifest):
@@ -363,17 +418,38 @@ def test_split_k_weight_gradient_product_is_deterministic_and_accurate():
     assert rel(outs[0].cpu(), ref) < 1e-5 and rel(outs[2].cpu(), ref) < 1e-5
 
 
+class _DecoderBlock(torch.nn.Module):
+    """Pre-norm decoder block (d_model 256, 4 heads, FFN 1024) with every Linear supplied by `linear`."""
+    D, HEADS, FFN = 256, 4, 1024
+
+    def __init__(self, linear):
+        super().__init__()
+        D = self.D
+        self.ln1, self.ln2 = torch.nn.LayerNorm(D), torch.nn.LayerNorm(D)
+        self.q, self.k, self.v, self.o = (linear(D, D) for _ in range(4))
+        self.fc1, self.fc2 = linear(D, self.FFN), linear(self.FFN, D)
+
+    def forward(self, x):
+        B, T, D = x.shape
+        F = torch.nn.functional
+        h = self.ln1(x.float()).to(torch.bfloat16)
+        q, k, v = (m(h).view(B, T, self.HEADS, -1).transpose(1, 2) for m in (self.q, self.k, self.v))
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, T, D)
+        x = x + self.o(a)
+        h = self.ln2(x.float()).to(torch.bfloat16)
+        return x + self.fc2(F.gelu(self.fc1(h)))
+
+
 def test_minigpt_block_trains_with_axs6_linears():
     """A decoder block built on AXSLinearMixedPrecision: forward/backward run, gradients reach every
     parameter, a few AdamW steps reduce the loss (convergence smoke test in the spirit of
     tests/test_mixed_precision.py:286-348 of the reference)."""
-    mg = importlib.import_module("axs6_b200.minigpt_bench")
     torch.manual_seed(0)
-    blk = mg.Block(lambda i, o, bias=True: mp.AXSLinearMixedPrecision(i, o, bias=bias)).cuda()
-    head = mp.AXSLinearMixedPrecision(mg.D_MODEL, 64).cuda()
+    blk = _DecoderBlock(lambda i, o, bias=True: mp.AXSLinearMixedPrecision(i, o, bias=bias)).cuda()
+    head = mp.AXSLinearMixedPrecision(_DecoderBlock.D, 64).cuda()
     params = list(blk.parameters()) + list(head.parameters())
     opt = torch.optim.AdamW(params, lr=1e-3)
-    x = torch.randn(2, 128, mg.D_MODEL, device="cuda").to(torch.bfloat16)
+    x = torch.randn(2, 128, _DecoderBlock.D, device="cuda").to(torch.bfloat16)
     y = torch.randint(0, 64, (2 * 128,), device="cuda")
     losses = []
     for _ in range(12):
