@@ -21,6 +21,8 @@ LINEAR_QUANTIZE_INPUT, LINEAR_QUANTIZE_GRAD, LINEAR_COMPUTE_TF32, LINEAR_BIAS_FR
 LINEAR_BIAS_VIA_BF16 = 16
 LINEAR_REUSE_WQ, LINEAR_REUSE_GQ = 32, 64
 LINEAR_OPERANDS_PACKED = 128
+LINEAR_SPLITK_WORKSPACE = 256
+LINEAR_FP32_ACCURACY = 512
 
 _i64, _int, _u32, _u64, _ptr = ctypes.c_int64, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p
 
@@ -39,6 +41,8 @@ SIGNATURES = {
     "axs6_unpack": (_int, [_int, _ptr, _ptr, _ptr, _ptr, _int, _i64, _i64, _i64, _int, _int, _ptr]),
     "axs6_unpack_sum": (_int, [_int, _ptr, _i64, _i64, _ptr, _int, _i64, _i64, _i64, _int, _int, ctypes.c_float, _ptr]),
     "axs6_gemm_bf16": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
+    "axs6_gemm_bf16_ws": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr, _i64, _ptr]),
+    "axs6_gemm_workspace_bytes": (_i64, [_i64, _i64, _i64, _int]),
     "axs6_gemm_packed": (_int, [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _ptr, _ptr, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "axs6_gemm_tf32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "axs6_gemm_status": (_int, []),

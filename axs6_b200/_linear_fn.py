@@ -39,7 +39,7 @@ class AXSLinearFP32Function(torch.autograd.Function):
         tf32 = not all_bf16
         out_dtype = torch.bfloat16 if all_bf16 else torch.float32
         b32 = bias.float().contiguous() if bias is not None else None
-        y, xq = ops.linear_fwd(x2, w, b32, block_size, grid, bool(quantize_input), out_dtype, tf32=tf32)
+        y, xq = ops.linear_fwd(x2, w, b32, block_size, grid, bool(quantize_input), out_dtype, tf32=tf32, fp32_accuracy=tf32)
         ctx.save_for_backward(xq, weight, bias)
         ctx.cfg = (block_size, bool(quantize_grad), grid, tf32, out_dtype, input.shape)
         return y.reshape(*input.shape[:-1], weight.shape[0])

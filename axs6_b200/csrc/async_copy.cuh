@@ -49,6 +49,29 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     return false;
 }
 
+// Poll `bar` for `parity` at most `limit` times, whatever the status word says.  Used on the way out of a kernel
+// that gave up: the thread that issued asynchronous loads waits for the ones still in flight, so that none can
+// land after the CTA has released its shared memory.
+__device__ __forceinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity, uint32_t limit)
+{
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if (i > 64) __nanosleep(40);
+    }
+    return false;
+}
+// The same for `ahead` consecutive stages of a ring of `stages` barriers (8 bytes apart from `bar0`) starting at
+// position (s, ph).
+__device__ __forceinline__ void drain_ring(uint32_t bar0, int stages, int s, uint32_t ph, int ahead, uint32_t limit)
+{
+    for (int j = 0; j < ahead; ++j) {
+        int sj = s + j;
+        uint32_t pj = ph;
+        if (sj >= stages) { sj -= stages; pj ^= 1u; }
+        mbar_wait_quiet(bar0 + 8u * (uint32_t)sj, pj, limit);
+    }
+}
+
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // Orders this thread's ordinary shared-memory accesses before later accesses by the TMA unit.
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

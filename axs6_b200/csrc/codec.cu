@@ -81,8 +81,10 @@ __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
 {
     __shared__ __align__(16) uint8_t rev[GRID == AXS6_GRID_NF5 ? 1024 : 16];
     __shared__ __align__(16) uint8_t stage[LAYOUT == kBytes ? kStageBytes : 16];
+    pdl_launch_dependents();
     if (GRID == AXS6_GRID_NF5) build_reverse_lut(rev);
     __syncthreads();
+    pdl_wait();                    // nothing of the caller's memory is touched before this point
 
     const int lg = a.lanes_log2, lanes = 1 << lg;
     const uint64_t offset = (ROUND == kPhilox) ? a.offset + *a.epoch : 0ull;
@@ -174,8 +176,10 @@ template <typename Tin, int GRID, int ROUND, int LAYOUT>
 __global__ void __launch_bounds__(kThreads) pack_generic_kernel(const CodecArgs a)
 {
     __shared__ __align__(16) uint8_t rev[GRID == AXS6_GRID_NF5 ? 1024 : 16];
+    pdl_launch_dependents();
     if (GRID == AXS6_GRID_NF5) build_reverse_lut(rev);
     __syncthreads();
+    pdl_wait();                    // nothing of the caller's memory is touched before this point
 
     const int lane = threadIdx.x & 31;
     const uint64_t offset = (ROUND == kPhilox) ? a.offset + *a.epoch : 0ull;
@@ -243,8 +247,10 @@ __global__ void __launch_bounds__(kThreads) unpack_vec_kernel(const CodecArgs a)
 {
     __shared__ float lev[32];
     __shared__ __align__(16) uint8_t stage[LAYOUT == kBytes ? kStageBytes : 16];
+    pdl_launch_dependents();
     build_levels<GRID>(lev);
     __syncthreads();
+    pdl_wait();                    // nothing of the caller's memory is touched before this point
 
     const int lg = a.lanes_log2, lanes = 1 << lg;
     const int64_t total_blocks = a.g.total_chunks >> lg;
@@ -315,8 +321,10 @@ template <typename Tout, int GRID, int LAYOUT>
 __global__ void __launch_bounds__(kThreads) unpack_generic_kernel(const CodecArgs a)
 {
     __shared__ float lev[32];
+    pdl_launch_dependents();
     build_levels<GRID>(lev);
     __syncthreads();
+    pdl_wait();                    // nothing of the caller's memory is touched before this point
 
     const int B = a.g.block;
     const int64_t padded = a.g.cpr * kChunk;
@@ -363,9 +371,9 @@ static int launch_codec(K kernel, const CodecArgs &a, int64_t items_per_cta, int
     const int64_t resident = (int64_t)d.sms * per_sm;
     if (ctas > resident) ctas = resident;
     if (ctas < 1) ctas = 1;
-    kernel<<<(unsigned)ctas, kThreads, 0, stream>>>(a);
+    const bool launched = launch_overlapped(kernel, (unsigned)ctas, kThreads, 0, stream, a) == cudaSuccess;
     count_launch();
-    return check_launch();
+    return launched ? check_launch() : AXS6_ERR_LAUNCH;
 }
 
 template <typename Tin, int GRID, int ROUND>
@@ -631,19 +639,21 @@ __global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_bulk_kernel(con
     const int tid = threadIdx.x;
     const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
     const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    pdl_launch_dependents();
+    build_key_table(table, tid, kFastBlocks);              // module constants: may run while the previous kernel drains
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
         fence_barrier_init();
         fence_async_smem();
-        // the first tiles are on their way while the table is being built
+        pdl_wait();                                        // caller memory is read from here on
         for (int k = 0; k < kStages && k < nk; ++k) {
             mbar_expect_tx(bar0 + 8 * k, kStageBytes);
             tma_load_2d(smem_u32(in0 + k * kStageBytes), &xmap, bar0 + 8 * k, 0,
                         (int)(((int64_t)blockIdx.x + k * (int64_t)gridDim.x) * kFastBlocks));
         }
     }
-    build_key_table(table, tid, kFastBlocks);
     __syncthreads();
+    pdl_wait();
     // this thread's block is row `tid` of a tile; 16-byte piece i of a row sits at piece i ^ ((row >> 1) & 3)
     uint32_t piece[4];
 #pragma unroll
@@ -685,7 +695,11 @@ __global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_bulk_kernel(con
         for (int i = 1; i < 7; ++i) o32[i] = W[i];
         fence_async_smem();                    // my words are visible to the TMA unit after the barrier
         if (tid == 0) bulk_wait_read<0>();     // the previous iteration's store has left the other buffer
-        if (__syncthreads_or(!ok)) break;      // somebody's wait gave up: the whole CTA leaves
+        if (__syncthreads_or(!ok)) {           // somebody's wait gave up: the whole CTA leaves, once the issuing
+            if (tid == 0)                      // thread has waited for the tile loads that are still armed
+                drain_ring(bar0, kStages, s, ph, (int)(nk - k < kStages ? nk - k : kStages), kWaitLimit);
+            break;
+        }
         const int64_t nb = nblocks - grp * kFastBlocks;
         if (nb >= kFastBlocks) {
             if (tid == 0) {
@@ -736,10 +750,10 @@ static int launch_pack_bulk(const void *x, void *out, int64_t nblocks, int hdr, 
     if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&pack_bf16_nf5_b32_bulk_kernel<1>), smem_bytes<1>()) ||
         !ensure_dynamic_smem(reinterpret_cast<const void *>(&pack_bf16_nf5_b32_bulk_kernel<2>), smem_bytes<2>()))
         return AXS6_ERR_LAUNCH;
-    if (hdr == 1) pack_bf16_nf5_b32_bulk_kernel<1><<<(unsigned)ctas, kFastBlocks, smem_bytes<1>(), st>>>(map, o, nblocks);
-    else          pack_bf16_nf5_b32_bulk_kernel<2><<<(unsigned)ctas, kFastBlocks, smem_bytes<2>(), st>>>(map, o, nblocks);
+    const cudaError_t le = hdr == 1 ? launch_overlapped(pack_bf16_nf5_b32_bulk_kernel<1>, (unsigned)ctas, kFastBlocks, smem_bytes<1>(), st, map, o, nblocks)
+                                    : launch_overlapped(pack_bf16_nf5_b32_bulk_kernel<2>, (unsigned)ctas, kFastBlocks, smem_bytes<2>(), st, map, o, nblocks);
     count_launch();
-    return check_launch();
+    return le == cudaSuccess ? check_launch() : AXS6_ERR_LAUNCH;
 }
 
 // ------------------------------------------------------------------------------------------ fp32 pack, TMA-fed
@@ -767,18 +781,21 @@ __global__ void __launch_bounds__(kFastBlocks) pack_f32_nf5_b32_bulk_kernel(cons
     const int tid = threadIdx.x;
     const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
     const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    pdl_launch_dependents();
+    build_reverse_lut(rev);                                 // module constants: may run while the previous kernel drains
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
         fence_barrier_init();
         fence_async_smem();
+        pdl_wait();                                        // caller memory is read from here on
         for (int k = 0; k < kStages && k < nk; ++k) {
             mbar_expect_tx(bar0 + 8 * k, kF32Tile);
             tma_load_2d(smem_u32(in0 + k * kF32Tile), &xmap, bar0 + 8 * k, 0,
                         (int)(((int64_t)blockIdx.x + k * (int64_t)gridDim.x) * kFastBlocks));
         }
     }
-    build_reverse_lut(rev);
     __syncthreads();
+    pdl_wait();
     uint32_t piece[8];                       // row tid, 16-byte piece i at piece i ^ (row & 7)
 #pragma unroll
     for (int i = 0; i < 8; ++i) piece[i] = (uint32_t)tid * 128u + (uint32_t)((i ^ (tid & 7)) << 4);
@@ -843,7 +860,10 @@ __global__ void __launch_bounds__(kFastBlocks) pack_f32_nf5_b32_bulk_kernel(cons
         for (int i = 1; i < 7; ++i) o32[i] = W[i];
         fence_async_smem();
         if (tid == 0) bulk_wait_read<0>();
-        if (__syncthreads_or(!ok)) break;
+        if (__syncthreads_or(!ok)) {
+            if (tid == 0) drain_ring(bar0, kStages, s, ph, (int)(nk - k < kStages ? nk - k : kStages), kWaitLimit);
+            break;
+        }
         const int64_t nb = nblocks - grp * kFastBlocks;
         if (nb >= kFastBlocks) {
             if (tid == 0) {
@@ -894,10 +914,10 @@ static int launch_pack_f32_bulk(const void *x, void *out, int64_t nblocks, int h
         !ensure_dynamic_smem(reinterpret_cast<const void *>(&pack_f32_nf5_b32_bulk_kernel<2>), pack_f32_smem_bytes<2>()))
         return AXS6_ERR_LAUNCH;
     uint8_t *o = static_cast<uint8_t *>(out);
-    if (hdr == 1) pack_f32_nf5_b32_bulk_kernel<1><<<(unsigned)ctas, kFastBlocks, pack_f32_smem_bytes<1>(), st>>>(map, o, nblocks);
-    else          pack_f32_nf5_b32_bulk_kernel<2><<<(unsigned)ctas, kFastBlocks, pack_f32_smem_bytes<2>(), st>>>(map, o, nblocks);
+    const cudaError_t le = hdr == 1 ? launch_overlapped(pack_f32_nf5_b32_bulk_kernel<1>, (unsigned)ctas, kFastBlocks, pack_f32_smem_bytes<1>(), st, map, o, nblocks)
+                                    : launch_overlapped(pack_f32_nf5_b32_bulk_kernel<2>, (unsigned)ctas, kFastBlocks, pack_f32_smem_bytes<2>(), st, map, o, nblocks);
     count_launch();
-    return check_launch();
+    return le == cudaSuccess ? check_launch() : AXS6_ERR_LAUNCH;
 }
 
 // ------------------------------------------------------------------------------------------ unpack, TMA-fed
@@ -940,19 +960,7 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
     const int tid = threadIdx.x;
     const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
     const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
-        fence_barrier_init();
-        fence_async_smem();
-        // a group with fewer than 256 records (the last one) is fetched by the threads themselves
-        for (int k = 0; k < kStages && k < nk; ++k) {
-            const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
-            if (nblocks - grp * kFastBlocks >= kFastBlocks) {
-                mbar_expect_tx(bar0 + 8 * k, kIn);
-                bulk_load(smem_u32(in0 + k * kIn), in + grp * kIn, kIn, bar0 + 8 * k);
-            }
-        }
-    }
+    pdl_launch_dependents();
     if (tid < 64) {
         const uint32_t bits = g_codebook_bits[tid & 31];
         const uint32_t sign = (uint32_t)tid >> 5;
@@ -965,7 +973,22 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
         }
         if (tid < 32) lev[tid] = __uint_as_float(bits);
     }
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
+        fence_barrier_init();
+        fence_async_smem();
+        pdl_wait();                                        // caller memory is read from here on
+        // a group with fewer than 256 records (the last one) is fetched by the threads themselves
+        for (int k = 0; k < kStages && k < nk; ++k) {
+            const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
+            if (nblocks - grp * kFastBlocks >= kFastBlocks) {
+                mbar_expect_tx(bar0 + 8 * k, kIn);
+                bulk_load(smem_u32(in0 + k * kIn), in + grp * kIn, kIn, bar0 + 8 * k);
+            }
+        }
+    }
     __syncthreads();
+    pdl_wait();
 
     const uint32_t wb = (uint32_t)(REC * tid) >> 2, sh = (uint32_t)(REC * tid) & 3u;
     const uint32_t sft = 8u * (sh + HDR);
@@ -1051,7 +1074,15 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
         }
         fence_async_smem();
         if (tid == 0) bulk_wait_read<0>();     // the previous iteration's store has left the other tile
-        if (__syncthreads_or(!ok)) break;
+        if (__syncthreads_or(!ok)) {
+            if (tid == 0) {                    // wait for the record loads still armed (whole groups only)
+                int ahead = 0;
+                for (int j = 0; j < kStages && k + j < nk; ++j)
+                    if (nblocks - (grp + j * (int64_t)gridDim.x) * kFastBlocks >= kFastBlocks) ahead = j + 1;
+                drain_ring(bar0, kStages, s, ph, ahead, kWaitLimit);
+            }
+            break;
+        }
         if (tid == 0) {
             tma_store_2d(&ymap, smem_u32(tile), 0, (int)(grp * kFastBlocks));
             bulk_commit();
@@ -1096,10 +1127,10 @@ static int launch_unpack_bulk(const void *in, void *y, int64_t nblocks, int hdr,
         !ensure_dynamic_smem(reinterpret_cast<const void *>(&unpack_nf5_b32_bulk_kernel<Tout, 2>), unpack_smem_bytes<Tout, 2>()))
         return AXS6_ERR_LAUNCH;
     const uint8_t *src = static_cast<const uint8_t *>(in);
-    if (hdr == 1) unpack_nf5_b32_bulk_kernel<Tout, 1><<<(unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 1>(), st>>>(map, src, nblocks);
-    else          unpack_nf5_b32_bulk_kernel<Tout, 2><<<(unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 2>(), st>>>(map, src, nblocks);
+    const cudaError_t le = hdr == 1 ? launch_overlapped(unpack_nf5_b32_bulk_kernel<Tout, 1>, (unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 1>(), st, map, src, nblocks)
+                                    : launch_overlapped(unpack_nf5_b32_bulk_kernel<Tout, 2>, (unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 2>(), st, map, src, nblocks);
     count_launch();
-    return check_launch();
+    return le == cudaSuccess ? check_launch() : AXS6_ERR_LAUNCH;
 }
 
 }  // namespace bulk

@@ -39,6 +39,33 @@ int gemm_packed_launch(const void *a, const void *a_exps, int64_t lda, const voi
                        const float *bias, int64_t M, int64_t N, int64_t K, int64_t ldc, int a_mn, int b_mn, int c_dtype,
                        int bias_via_bf16, cudaStream_t stream);
 
+// Programmatic dependent launch.  A kernel launched with launch_overlapped() may become resident while the kernel
+// before it on the stream is still draining: its CTAs run their prologue (barrier initialisation, tables copied
+// from the module image into shared memory) and then block in pdl_wait() until that earlier kernel has completed
+// and its writes are visible.  Everything that reads or writes caller memory comes after pdl_wait(), so the result
+// is the same as with an ordinary launch; what is saved is the launch gap and the prologue between back-to-back
+// kernels, which matters for launches of a few tens of microseconds.  Without the launch attribute the two
+// device calls do nothing.  Tune key 15 = 1 turns the attribute off.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t stream,
+                                     Args &&...args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tune_value(15) == 1 ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline int check_launch()

@@ -79,7 +79,8 @@ __device__ __forceinline__ void accumulate_record(const uint32_t (&W)[7], uint32
 template <typename Tout, int HDR>
 __global__ void __launch_bounds__(kThreadsX) unpack_sum_bulk_kernel(const __grid_constant__ CUtensorMap ymap,
                                                                    const uint8_t *__restrict__ in, int64_t nsrc,
-                                                                   int64_t src_stride, int64_t nblocks, float divisor)
+                                                                   int64_t src_stride, int64_t nblocks, float divisor,
+                                                                   uint32_t wait_limit, int producer_muted)
 {
     constexpr bool kBf16 = sizeof(Tout) == 2;
     constexpr int REC = HDR + 24;
@@ -113,20 +114,28 @@ __global__ void __launch_bounds__(kThreadsX) unpack_sum_bulk_kernel(const __grid
 
     if (tid >= kBlocks) {
         // ---------------------------------------------------------------- producer warp (one lane)
-        if (tid == kBlocks) {
+        if (tid == kBlocks && !producer_muted) {
             int s = 0;
             uint32_t ph = 0;
-            for (int64_t k = 0; k < nk; ++k) {
+            long long armed = 0;                                   // loads issued so far
+            bool ok = true;
+            for (int64_t k = 0; k < nk && ok; ++k) {
                 const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
                 if (nblocks - grp * kBlocks < kBlocks) break;      // the ragged last group is read by the consumers
-                bool ok = true;
                 for (int64_t r = 0; r < nsrc; ++r) {
-                    if (!mbar_wait_bounded(empty0 + 8 * s, ph ^ 1u, 2, &g_exchange_status, kWaitLimit)) { ok = false; break; }
+                    if (!mbar_wait_bounded(empty0 + 8 * s, ph ^ 1u, 2, &g_exchange_status, wait_limit)) { ok = false; break; }
                     mbar_expect_tx(full0 + 8 * s, kIn);
                     bulk_load(smem_u32(in0 + s * kIn), in + r * src_stride + grp * kIn, kIn, full0 + 8 * s);
+                    ++armed;
                     if (++s == kStagesX) { s = 0; ph ^= 1u; }
                 }
-                if (!ok) break;
+            }
+            // This thread leaves last: the shared memory of the CTA stays allocated until it does, so it waits
+            // (bounded) until every load it issued has landed.  After a normal run the consumers have already seen
+            // all of them and the waits return at once.
+            for (long long back = 0; back < kStagesX && back < armed; ++back) {
+                const long long idx = armed - 1 - back;
+                mbar_wait_quiet(full0 + 8 * (uint32_t)(idx % kStagesX), (uint32_t)((idx / kStagesX) & 1), wait_limit);
             }
         }
         return;
@@ -153,7 +162,7 @@ __global__ void __launch_bounds__(kThreadsX) unpack_sum_bulk_kernel(const __grid
             uint32_t W[7];
             uint32_t sft_r = sft, head_shift = 8u * sh;
             if (whole) {
-                if (ok) ok = mbar_wait_bounded(full0 + 8 * s, ph, 1, &g_exchange_status, kWaitLimit);
+                if (ok) ok = mbar_wait_bounded(full0 + 8 * s, ph, 1, &g_exchange_status, wait_limit);
                 const uint32_t *r32 = reinterpret_cast<const uint32_t *>(in0 + s * kIn) + wb;
 #pragma unroll
                 for (int i = 0; i < 7; ++i) W[i] = r32[i];
@@ -263,8 +272,12 @@ static int launch_bulk(const uint8_t *in, int64_t nsrc, int64_t src_stride, void
     if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&unpack_sum_bulk_kernel<Tout, 1>), smem_bytes<Tout, 1>()) ||
         !ensure_dynamic_smem(reinterpret_cast<const void *>(&unpack_sum_bulk_kernel<Tout, 2>), smem_bytes<Tout, 2>()))
         return AXS6_ERR_LAUNCH;
-    if (hdr == 1) unpack_sum_bulk_kernel<Tout, 1><<<(unsigned)ctas, kThreadsX, smem_bytes<Tout, 1>(), st>>>(map, in, nsrc, src_stride, nblocks, divisor);
-    else          unpack_sum_bulk_kernel<Tout, 2><<<(unsigned)ctas, kThreadsX, smem_bytes<Tout, 2>(), st>>>(map, in, nsrc, src_stride, nblocks, divisor);
+    // tune key 13: poll limit of the waits (0 = built-in); tune key 14 = 1: the producer issues no load at all, so the
+    // consumers' first wait runs out with nothing in flight (exists so that the give-up path can be exercised safely)
+    const uint32_t limit = tune_value(13) > 0 ? (uint32_t)tune_value(13) : kWaitLimit;
+    const int muted = tune_value(14) == 1 ? 1 : 0;
+    if (hdr == 1) unpack_sum_bulk_kernel<Tout, 1><<<(unsigned)ctas, kThreadsX, smem_bytes<Tout, 1>(), st>>>(map, in, nsrc, src_stride, nblocks, divisor, limit, muted);
+    else          unpack_sum_bulk_kernel<Tout, 2><<<(unsigned)ctas, kThreadsX, smem_bytes<Tout, 2>(), st>>>(map, in, nsrc, src_stride, nblocks, divisor, limit, muted);
     count_launch();
     return check_launch();
 }

@@ -89,8 +89,10 @@ template <typename Tin, typename Tout, int GRID, int ROUND, int U>
 __global__ void __launch_bounds__(kThreads) fq_vec_kernel(const FqArgs a)
 {
     __shared__ __align__(16) float tab[GRID == AXS6_GRID_NF5 ? 1024 : 32];
+    pdl_launch_dependents();
     if (GRID == AXS6_GRID_NF5) build_value_lut(tab); else build_levels<GRID>(tab);
     __syncthreads();
+    pdl_wait();                    // nothing of the caller's memory is touched before this point
 
     const int lanes = a.g.block / kChunk;
     const uint64_t offset = (ROUND == kPhilox) ? a.offset + *a.epoch : 0ull;
@@ -139,8 +141,10 @@ template <typename Tin, typename Tout, int GRID, int ROUND>
 __global__ void __launch_bounds__(kThreads) fq_generic_kernel(const FqArgs a)
 {
     __shared__ __align__(16) float tab[GRID == AXS6_GRID_NF5 ? 1024 : 32];
+    pdl_launch_dependents();
     if (GRID == AXS6_GRID_NF5) build_value_lut(tab); else build_levels<GRID>(tab);
     __syncthreads();
+    pdl_wait();
 
     const int lane = threadIdx.x & 31;
     const uint64_t offset = (ROUND == kPhilox) ? a.offset + *a.epoch : 0ull;
@@ -191,9 +195,9 @@ static int launch_persistent(K kernel, const FqArgs &a, int64_t work_items_per_c
     const int64_t resident = (int64_t)d.sms * per_sm;
     if (ctas > resident) ctas = resident;
     if (ctas < 1) ctas = 1;
-    kernel<<<(unsigned)ctas, kThreads, 0, stream>>>(a);
+    const bool launched = launch_overlapped(kernel, (unsigned)ctas, kThreads, 0, stream, a) == cudaSuccess;
     count_launch();
-    return check_launch();
+    return launched ? check_launch() : AXS6_ERR_LAUNCH;
 }
 
 template <typename Tin, typename Tout, int GRID, int ROUND>
@@ -300,16 +304,7 @@ __global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __
     const int tid = threadIdx.x;
     const int64_t groups = (nblocks + kBlocksB - 1) / kBlocksB;
     const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    if (tid == 0) {
-        for (int s = 0; s < kSlots; ++s) mbar_init(bar0 + 8 * s, 1);
-        fence_barrier_init();
-        fence_async_smem();
-        for (int k = 0; k < 2 && k < nk; ++k) {                // two tiles ahead; the third slot is the one being stored
-            mbar_expect_tx(bar0 + 8 * k, kSlotBytes);
-            tma_load_2d(smem_u32(slot0 + k * kSlotBytes), &xmap, bar0 + 8 * k, 0,
-                        (int)(((int64_t)blockIdx.x + k * (int64_t)gridDim.x) * kBlocksB));
-        }
-    }
+    pdl_launch_dependents();
     if (ROUND == kNearest) {
         for (int i = tid; i < (kKeyLim + 8) / 8; i += kBlocksB)
             reinterpret_cast<uint4 *>(table)[i] = reinterpret_cast<const uint4 *>(g_key_level_bf16)[i];
@@ -317,7 +312,19 @@ __global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __
         for (int i = tid; i < 1024 / 8; i += kBlocksB)
             reinterpret_cast<uint4 *>(lvl)[i] = reinterpret_cast<const uint4 *>(g_lut_level_bf16)[i];
     }
+    if (tid == 0) {
+        for (int s = 0; s < kSlots; ++s) mbar_init(bar0 + 8 * s, 1);
+        fence_barrier_init();
+        fence_async_smem();
+        pdl_wait();                                            // the first loads of caller memory come after this
+        for (int k = 0; k < 2 && k < nk; ++k) {                // two tiles ahead; the third slot is the one being stored
+            mbar_expect_tx(bar0 + 8 * k, kSlotBytes);
+            tma_load_2d(smem_u32(slot0 + k * kSlotBytes), &xmap, bar0 + 8 * k, 0,
+                        (int)(((int64_t)blockIdx.x + k * (int64_t)gridDim.x) * kBlocksB));
+        }
+    }
     __syncthreads();
+    pdl_wait();
     const uint64_t offset = ROUND == kPhilox ? offset0 + *epoch : 0ull;
 
     uint32_t piece[4];
@@ -434,7 +441,12 @@ __global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __
                 *reinterpret_cast<uint4 *>(slot + piece[i]) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
         }
         fence_async_smem();
-        if (__syncthreads_or(!ok)) break;
+        if (__syncthreads_or(!ok)) {
+            // somebody's wait gave up: the whole CTA leaves, after the issuing thread has waited for the (at most two)
+            // tile loads that are still armed
+            if (tid == 0) drain_ring(bar0, kSlots, s, ph, (int)(nk - k < 2 ? nk - k : 2), kWaitLimit);
+            break;
+        }
         if (tid == 0) {
             tma_store_2d(&ymap, smem_u32(slot), 0, (int)(grp * kBlocksB));
             bulk_commit();
@@ -481,10 +493,11 @@ static int launch(const void *x, void *y, int64_t nblocks, int round, uint64_t s
         !ensure_dynamic_smem(reinterpret_cast<const void *>(&fq_bf16_nf5_b32_bulk_kernel<kPhilox>), kSmemBytes))
         return AXS6_ERR_LAUNCH;
     const Axs6PhiloxKeys keys = axs6_philox_keys(seed);
-    if (round == kNearest) fq_bf16_nf5_b32_bulk_kernel<kNearest><<<(unsigned)ctas, kBlocksB, kSmemBytes, st>>>(xm, ym, nblocks, 0, 0, nullptr, keys);
-    else                   fq_bf16_nf5_b32_bulk_kernel<kPhilox><<<(unsigned)ctas, kBlocksB, kSmemBytes, st>>>(xm, ym, nblocks, seed, offset, epoch, keys);
+    cudaError_t le;
+    if (round == kNearest) le = launch_overlapped(fq_bf16_nf5_b32_bulk_kernel<kNearest>, (unsigned)ctas, kBlocksB, kSmemBytes, st, xm, ym, nblocks, 0ull, 0ull, (const unsigned long long *)nullptr, keys);
+    else                   le = launch_overlapped(fq_bf16_nf5_b32_bulk_kernel<kPhilox>, (unsigned)ctas, kBlocksB, kSmemBytes, st, xm, ym, nblocks, seed, offset, epoch, keys);
     count_launch();
-    return check_launch();
+    return le == cudaSuccess ? check_launch() : AXS6_ERR_LAUNCH;
 }
 
 }  // namespace fqb

@@ -60,6 +60,9 @@ struct Params {
     int splits;               // split-K factor (>= 2: fp32 output accumulated with red.add into a zero-filled C)
     int tail_begin;           // 2-CTA kernel: tiles from this one on are computed as two K halves (0 = none)
     uint32_t mn_box_bytes;    // bytes of one MN-major TMA box: 128 B x bk rows
+    float *ws;                // split-K workspace (null: partials are added into C with red.add): partial `part` of the
+    long long ws_stride;      // product is stored at ws + part * ws_stride as an (M, ws_ld) fp32 matrix and a second
+    int ws_ld;                // kernel adds the partials in index order, which makes the sum reproducible
 };
 
 // ------------------------------------------------------------------------------------- PTX helpers
@@ -127,8 +130,10 @@ __device__ __forceinline__ uint32_t instr_desc(int a_mn, int b_mn, uint32_t fmt)
 // Drains one 128 x 256 fp32 accumulator: this thread owns TMEM lane (= output row) `row` and walks
 // the 256 columns in chunks of 32 (tcgen05.ld 32x32b.x32), adds the bias, converts and stores.
 __device__ __forceinline__ void epilogue_tile(const Params &p, uint32_t taddr, int row, int n0, bool vec_ok,
-                                              bool accumulate = false, bool add_bias = true)
+                                              bool accumulate = false, bool add_bias = true, int part = 0)
 {
+    const bool to_ws = accumulate && p.ws != nullptr;
+    if (to_ws) add_bias = false;                       // the reducing kernel adds the bias
 #pragma unroll 1
     for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -164,6 +169,17 @@ __device__ __forceinline__ void epilogue_tile(const Params &p, uint32_t taddr, i
                 } else {
                     for (int i = 0; i < 32; ++i)
                         if (col0 + i < p.N) dst[i] = __float2bfloat16_rn(v[i]);
+                }
+            } else if (to_ws) {
+                // split-K partial kept apart: plain stores into this part's slice of the workspace
+                float *dst = p.ws + (long long)part * p.ws_stride + (long long)row * p.ws_ld + col0;
+                if (full) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                } else {
+                    for (int i = 0; i < 32; ++i)
+                        if (col0 + i < p.N) dst[i] = v[i];
                 }
             } else if (accumulate) {
                 // split-K partial: add into the zero-initialised fp32 output.  With two partials the
@@ -308,7 +324,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-            epilogue_tile(p, taddr, row, n0, vec_ok, splits > 1, (t % splits) == 0);
+            epilogue_tile(p, taddr, row, n0, vec_ok, splits > 1, (t % splits) == 0, t % splits);
             tc_fence_before();
             mbar_arrive(tempty_bar(acc));
             acc ^= 1;
@@ -330,7 +346,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 // k-block instead of 48 KB), the leader CTA (cluster rank 0) issues M256 N256 K16 instructions
 // that read both CTAs' shared memory and write 128 accumulator rows into each CTA's TMEM.
 // Less shared-memory traffic per flop and a 6-deep ring in the same amount of shared memory.
-//   * every TMA load (no multicast) of either CTA reports its bytes to the LEADER's stage
+//   * every TMA load of either CTA (each CTA fetches its own tiles) reports its bytes to the LEADER's stage
 //     barrier, which the leader arms with the bytes of both CTAs;
 //   * "stage free" and "accumulator ready" are committed by the leader to its own barrier and,
 //     with a second tcgen05.commit, to the peer's barrier at the same offset;
@@ -514,7 +530,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TN);
-            epilogue_tile(p, taddr, row, n0, vec_ok, unit_split(t), unit_part(t) == 0);
+            epilogue_tile(p, taddr, row, n0, vec_ok, unit_split(t), unit_part(t) == 0, unit_part(t));
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
@@ -533,6 +549,40 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
 }
 
 #include "gemm_packed_kernel.cuh"
+
+// c (M, N) = sum over parts of ws[part] (+ bias), partials added in index order: the second half of a split-K
+// product whose partials were kept apart, so that the result does not depend on the order in which CTAs finished.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ ws, int parts, long long ws_stride, int ws_ld,
+                                                            float *__restrict__ c, long long ldc, const float *__restrict__ bias,
+                                                            int bias_bf16, int M, int N)
+{
+    const int chunks = ws_ld / 4;
+    const long long total = (long long)M * chunks;
+    const bool vec = ((reinterpret_cast<uintptr_t>(c) & 15u) == 0) && (ldc % 4 == 0);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int row = (int)(i / chunks), col = (int)(i - (long long)row * chunks) * 4;
+        float4 acc = *reinterpret_cast<const float4 *>(ws + (long long)row * ws_ld + col);
+        for (int s = 1; s < parts; ++s) {
+            const float4 v = *reinterpret_cast<const float4 *>(ws + s * ws_stride + (long long)row * ws_ld + col);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        float o[4] = {acc.x, acc.y, acc.z, acc.w};
+        if (bias) {
+            for (int j = 0; j < 4; ++j)
+                if (col + j < N) {
+                    const float bv = bias[col + j];
+                    o[j] += bias_bf16 ? __bfloat162float(__float2bfloat16_rn(bv)) : bv;
+                }
+        }
+        float *dst = c + (long long)row * ldc + col;
+        if (vec && col + 4 <= N) {
+            *reinterpret_cast<float4 *>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+            for (int j = 0; j < 4; ++j)
+                if (col + j < N) dst[j] = o[j];
+        }
+    }
+}
 
 // ------------------------------------------------------------------------------------- host
 using acp::EncodeTiledFn;
@@ -629,6 +679,7 @@ static int launch_gemm_packed(const void *a, const void *a_exps, int64_t lda, co
     p.bias = bias; p.bias_bf16 = bias_via_bf16;
     p.tiles_m = (int)((M + BM - 1) / BM); p.tiles_n = (int)((N + BN - 1) / BN);
     p.bk = BK; p.mn_box_bytes = 128u * BK; p.splits = 1; p.tail_begin = 0;
+    p.ws = nullptr; p.ws_stride = 0; p.ws_ld = 0;
     p.a_lbo = a_mn ? p.mn_box_bytes : 0u; p.a_sbo = 1024u; p.a_kstep = a_mn ? 16u * 128u : 32u;
     p.b_lbo = b_mn ? p.mn_box_bytes : 0u; p.b_sbo = 1024u; p.b_kstep = b_mn ? 16u * 128u : 32u;
 
@@ -646,10 +697,25 @@ static int launch_gemm_packed(const void *a, const void *a_exps, int64_t lda, co
     return check_launch();
 }
 
+// Split-K plan for a problem with few output tiles and a long contraction (fp32 output): how many K ranges per tile
+// so that most SMs get a work unit.  `cap` bounds the number of partials.
+static int64_t plan_pair_splits(const DeviceInfo &d, int64_t M, int64_t N, int64_t K, int64_t cap)
+{
+    const int64_t pair_tiles = ((M + 255) / 256) * ((N + Pair::TN - 1) / Pair::TN);
+    if (pair_tiles >= d.sms / 2) return 1;
+    const int64_t total_kb = (K + BK - 1) / BK;
+    int64_t splits = (d.sms / 2) / pair_tiles;
+    if (splits > total_kb / 16) splits = total_kb / 16;
+    if (splits > cap) splits = cap;
+    return splits < 1 ? 1 : splits;
+}
+
+static int64_t ws_ld_of(int64_t N) { return (N + 3) / 4 * 4; }
+
 template <bool kTf32>
 static int launch_gemm(const void *a, const void *b, void *c, const float *bias, int64_t M, int64_t N, int64_t K,
                        int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn, int c_dtype, int bias_via_bf16,
-                       cudaStream_t stream)
+                       cudaStream_t stream, void *ws = nullptr, int64_t ws_bytes = 0)
 {
     constexpr int esize = kTf32 ? 4 : 2;
     constexpr int bk = 128 / esize;                     // values per k-block
@@ -679,12 +745,15 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     const int64_t pair_tiles = ((M + 255) / 256) * ((N + Pair::TN - 1) / Pair::TN);
     const int64_t mode = tune_value(7);
     int64_t pair_splits = 1;
-    if (!kTf32 && may_split && pair_tiles < d.sms / 2) {
-        const int64_t total_kb = (K + BK - 1) / BK;
-        pair_splits = (d.sms / 2) / pair_tiles;
-        if (pair_splits > total_kb / 16) pair_splits = total_kb / 16;
-        if (pair_splits > max_pair_splits) pair_splits = max_pair_splits;
-        if (pair_splits < 1) pair_splits = 1;
+    bool use_ws = false;
+    if (!kTf32 && may_split) {
+        pair_splits = plan_pair_splits(d, M, N, K, max_pair_splits);
+        // With a workspace the partials are kept apart and added in a fixed order by a second kernel: more than two
+        // partials without giving up reproducibility.
+        if (ws && aligned16(ws) && split_mode != 2) {
+            const int64_t want = plan_pair_splits(d, M, N, K, 8);
+            if (want > 2 && ws_bytes >= want * M * ws_ld_of(N) * 4) { pair_splits = want; use_ws = true; }
+        }
     }
     const bool pairs = !kTf32 && mode != 1 && (mode == 2 || pair_tiles * pair_splits >= d.sms / 4);
 
@@ -707,6 +776,7 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     p.mn_box_bytes = 128u * bk;
     p.splits = 1;
     p.tail_begin = 0;
+    p.ws = nullptr; p.ws_stride = 0; p.ws_ld = 0;
     // K-major, 128-byte swizzle: 8-row groups are 1024 B apart, one MMA K step is 32 B.
     // MN-major: 128-byte chunks of the output index are one TMA box (bk k-rows x 128 B) apart,
     // groups of 8 k-rows 1024 B apart, one MMA K step (32 B / esize rows) is that many rows x 128 B.
@@ -736,11 +806,22 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
                     return AXS6_ERR_LAUNCH;
             }
         }
-        if (p.splits > 1 &&
-            cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess)
+        if (use_ws && p.splits > 2) {
+            p.ws = static_cast<float *>(ws); p.ws_ld = (int)ws_ld_of(N); p.ws_stride = (long long)M * p.ws_ld;
+        } else if (p.splits > 1 &&
+                   cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess) {
             return AXS6_ERR_LAUNCH;
+        }
         gemm2_kernel<<<2 * clusters, kThreadsGemm, Pair::kSmemBytes, stream>>>(ma, mb, p);
         count_launch();
+        if (p.ws) {
+            const long long chunks = (long long)M * (p.ws_ld / 4);
+            int64_t ctas = (chunks + 255) / 256;
+            if (ctas > (int64_t)d.sms * 8) ctas = (int64_t)d.sms * 8;
+            splitk_reduce_kernel<<<(unsigned)ctas, 256, 0, stream>>>(p.ws, p.splits, p.ws_stride, p.ws_ld, static_cast<float *>(c),
+                                                                    ldc, bias, bias_via_bf16, (int)M, (int)N);
+            count_launch();
+        }
         return check_launch();
     }
 
@@ -804,6 +885,25 @@ AXS6_API int axs6_gemm_bf16(const void *a, const void *b, void *c, const float *
 {
     return axs6::gemm::launch_gemm<false>(a, b, c, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, c_dtype, 0,
                                           static_cast<cudaStream_t>(stream));
+}
+
+// The same with a caller-owned workspace for split-K partials (see axs6_gemm_workspace_bytes).
+AXS6_API int axs6_gemm_bf16_ws(const void *a, const void *b, void *c, const float *bias, int64_t M, int64_t N, int64_t K,
+                               int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn, int c_dtype, void *ws,
+                               int64_t ws_bytes, axs6_stream_t stream)
+{
+    return axs6::gemm::launch_gemm<false>(a, b, c, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, c_dtype, 0,
+                                          static_cast<cudaStream_t>(stream), ws, ws_bytes);
+}
+
+AXS6_API int64_t axs6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int c_dtype)
+{
+    using namespace axs6;
+    if (M <= 0 || N <= 0 || K <= 0 || c_dtype != AXS6_F32) return 0;
+    const DeviceInfo &d = device_info();
+    if (!d.valid || !d.ok) return 0;
+    const int64_t want = gemm::plan_pair_splits(d, M, N, K, 8);
+    return want > 2 ? want * M * gemm::ws_ld_of(N) * 4 : 0;
 }
 
 // Same with fp32 operands consumed as TF32 by the tensor cores (the low 13 mantissa bits of each

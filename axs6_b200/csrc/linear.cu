@@ -70,28 +70,64 @@ static int cast_to_bf16(const void *x, int dtype, void *y, int64_t rows, int64_t
 // Linear for tensors that are not quantised.
 template <typename Tin>
 __global__ void __launch_bounds__(256) cast_tf32_kernel(const Tin *x, float *y, int64_t rows, int64_t cols,
-                                                        int64_t ldx, int64_t ldy)
+                                                        int64_t ldx, int64_t ldy, int round)
 {
     const int64_t total = rows * cols;
     for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = e / cols, col = e - r * cols;
-        uint32_t t;
-        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"((float)x[r * ldx + col]));
+        const float v = (float)x[r * ldx + col];
+        uint32_t t = __float_as_uint(v);
+        if (round) asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v));
         y[r * ldy + col] = __uint_as_float(t);
     }
 }
 
 static int cast_to_tf32(const void *x, int dtype, void *y, int64_t rows, int64_t cols, int64_t ldx, int64_t ldy,
-                        cudaStream_t st)
+                        cudaStream_t st, int round = 1)
 {
     const DeviceInfo &d = device_info();
     int64_t ctas = (rows * cols + 255) / 256;
     if (ctas > (int64_t)d.sms * 8) ctas = (int64_t)d.sms * 8;
     if (ctas < 1) ctas = 1;
     if (dtype == AXS6_F32)
-        cast_tf32_kernel<float><<<(unsigned)ctas, 256, 0, st>>>(static_cast<const float *>(x), static_cast<float *>(y), rows, cols, ldx, ldy);
+        cast_tf32_kernel<float><<<(unsigned)ctas, 256, 0, st>>>(static_cast<const float *>(x), static_cast<float *>(y), rows, cols, ldx, ldy, round);
     else
-        cast_tf32_kernel<__nv_bfloat16><<<(unsigned)ctas, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), static_cast<float *>(y), rows, cols, ldx, ldy);
+        cast_tf32_kernel<__nv_bfloat16><<<(unsigned)ctas, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), static_cast<float *>(y), rows, cols, ldx, ldy, round);
+    count_launch();
+    return check_launch();
+}
+
+// ------------------------------------------------------------------------------ fp32 as two TF32 parts
+// out (rows, 3 * ld) = three column blocks built from x = hi + lo, hi = the nearest TF32 value, lo = the nearest
+// TF32 value of the remainder:  which = 0 (left operand)  [hi | hi | lo],  which = 1 (right operand)  [hi | lo | hi].
+// The product of a left and a right operand over the tripled contraction is hi*hi + hi*lo + lo*hi: the fp32 product
+// to about 2^-21 instead of the 2^-11 of a single TF32 product.  Columns >= cols of each block are zero.
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float *x, float *out, int64_t rows, int64_t cols, int64_t ldx,
+                                                         int64_t ld, int which)
+{
+    const int64_t total = rows * ld;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = e / ld, c = e - r * ld;
+        const float v = c < cols ? x[r * ldx + c] : 0.0f;
+        uint32_t hb, lb;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(v));
+        const float hi = __uint_as_float(hb);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lb) : "f"(v - hi));
+        const float lo = __uint_as_float(lb);
+        float *o = out + r * 3 * ld + c;
+        o[0] = hi;
+        o[ld] = which ? lo : hi;
+        o[2 * ld] = which ? hi : lo;
+    }
+}
+
+static int split_tf32(const float *x, float *out, int64_t rows, int64_t cols, int64_t ldx, int64_t ld, int which, cudaStream_t st)
+{
+    const DeviceInfo &d = device_info();
+    int64_t ctas = (rows * ld + 255) / 256;
+    if (ctas > (int64_t)d.sms * 8) ctas = (int64_t)d.sms * 8;
+    if (ctas < 1) ctas = 1;
+    split_tf32_kernel<<<(unsigned)ctas, 256, 0, st>>>(x, out, rows, cols, ldx, ld, which);
     count_launch();
     return check_launch();
 }
@@ -101,14 +137,20 @@ static int cast_to_tf32(const void *x, int dtype, void *y, int64_t rows, int64_t
 // instruction takes K-major operands only, so the two backward products of the fp32 graph read
 // transposed copies of their operands.
 __global__ void __launch_bounds__(256) transpose_f32_kernel(const float *in, float *out, int64_t rows, int64_t cols,
-                                                            int64_t ldin, int64_t ldout)
+                                                            int64_t ldin, int64_t ldout, int round_tf32)
 {
     __shared__ float tile[32][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;       // 32 x 8
     const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
     for (int i = ty; i < 32; i += 8) {
         const int64_t r = r0 + i, c = c0 + tx;
-        tile[i][tx] = (r < rows && c < cols) ? in[r * ldin + c] : 0.0f;
+        float v = (r < rows && c < cols) ? in[r * ldin + c] : 0.0f;
+        if (round_tf32) {                // the TF32 tensor core would truncate: round to nearest here instead
+            uint32_t t;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v));
+            v = __uint_as_float(t);
+        }
+        tile[i][tx] = v;
     }
     __syncthreads();
     for (int i = ty; i < 32; i += 8) {
@@ -117,11 +159,12 @@ __global__ void __launch_bounds__(256) transpose_f32_kernel(const float *in, flo
     }
 }
 
-static int transpose_f32(const float *in, float *out, int64_t rows, int64_t cols, int64_t ldin, int64_t ldout, cudaStream_t st)
+static int transpose_f32(const float *in, float *out, int64_t rows, int64_t cols, int64_t ldin, int64_t ldout, cudaStream_t st,
+                         int round_tf32 = 0)
 {
     dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
     if (grid.y > 65535u) return AXS6_ERR_UNSUPPORTED;
-    transpose_f32_kernel<<<grid, 256, 0, st>>>(in, out, rows, cols, ldin, ldout);
+    transpose_f32_kernel<<<grid, 256, 0, st>>>(in, out, rows, cols, ldin, ldout, round_tf32);
     count_launch();
     return check_launch();
 }
@@ -275,6 +318,9 @@ AXS6_API int64_t axs6_linear_workspace_bytes(int what, int64_t M, int64_t N, int
     case 8: return packed_bytes(M, K);              // xq as codes (AXS6_LINEAR_OPERANDS_PACKED)
     case 9: return packed_bytes(N, K);              // wq as codes
     case 10: return packed_bytes(M, N);             // gq as codes
+    case 12: return M * round_up4(K) * 16;          // xq of AXS6_LINEAR_FP32_ACCURACY: fp32 (M, ld) + its three-part split (M, 3 ld)
+    case 13: return N * round_up4(K) * 16;          // wq, the same
+    case 11: return axs6_gemm_workspace_bytes(N, K, M, AXS6_F32);   // split-K partials of dw (0: none useful)
     default: return -1;
     }
 }
@@ -287,8 +333,10 @@ AXS6_API int axs6_linear_fwd(const void *x, int x_dtype, int64_t ldx, const void
     if (!valid_dtype(x_dtype) || !valid_dtype(w_dtype) || !valid_dtype(y_dtype) || !valid_block(block)) return AXS6_ERR_ARG;
     if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
     if (M < 0 || N < 0 || K < 0 || ldx < K || ldw < K || ldy < N) return AXS6_ERR_ARG;
-    if (flags & ~(AXS6_LINEAR_QUANTIZE_INPUT | AXS6_LINEAR_COMPUTE_TF32 | AXS6_LINEAR_BIAS_VIA_BF16 | AXS6_LINEAR_OPERANDS_PACKED))
+    if (flags & ~(AXS6_LINEAR_QUANTIZE_INPUT | AXS6_LINEAR_COMPUTE_TF32 | AXS6_LINEAR_BIAS_VIA_BF16 | AXS6_LINEAR_OPERANDS_PACKED |
+                  AXS6_LINEAR_FP32_ACCURACY))
         return AXS6_ERR_ARG;
+    if ((flags & AXS6_LINEAR_FP32_ACCURACY) && !(flags & AXS6_LINEAR_COMPUTE_TF32)) return AXS6_ERR_ARG;
     if (M == 0 || N == 0) return AXS6_OK;
     if (!x || !w || !y || !xq || !wq || K == 0) return AXS6_ERR_ARG;
     if (!aligned16(xq) || !aligned16(wq)) return AXS6_ERR_ALIGN;
@@ -310,6 +358,24 @@ AXS6_API int axs6_linear_fwd(const void *x, int x_dtype, int64_t ldx, const void
         // fp32 graph (axs/unified/functional_unified.py:107-131, axs/nn/functional.py:101-129): operands
         // fake-quantised in fp32, rounded to TF32, product on the TF32 tensor cores
         const int64_t ld4 = round_up4(K);
+        if (flags & AXS6_LINEAR_FP32_ACCURACY) {
+            // fp32 accuracy on the TF32 tensor cores: the fake-quantised operands stay full fp32 (xq keeps them for
+            // backward), each is split into two TF32 parts, and one product over the tripled contraction adds
+            // hi*hi + hi*lo + lo*hi (axs/unified/triton_kernels.py:262 asks its dot product for "ieee" precision)
+            float *xf = static_cast<float *>(xq), *wf = static_cast<float *>(wq);
+            float *xs = xf + M * ld4, *ws = wf + N * ld4;
+            int rc3 = axs6_fq(w, wf, w_dtype, AXS6_F32, N, K, ldw, ld4, block, grid, AXS6_ROUND_NEAREST, 0, 0, 0, stream);
+            if (rc3) return rc3;
+            rc3 = (flags & AXS6_LINEAR_QUANTIZE_INPUT)
+                      ? axs6_fq(x, xf, x_dtype, AXS6_F32, M, K, ldx, ld4, block, grid, AXS6_ROUND_NEAREST, 0, 0, 0, stream)
+                      : cast_to_tf32(x, x_dtype, xf, M, K, ldx, ld4, st, 0);
+            if (rc3) return rc3;
+            rc3 = split_tf32(xf, xs, M, K, ld4, ld4, 0, st);
+            if (rc3) return rc3;
+            rc3 = split_tf32(wf, ws, N, K, ld4, ld4, 1, st);
+            if (rc3) return rc3;
+            return axs6_gemm_tf32(xs, ws, y, bias, M, N, 3 * ld4, 3 * ld4, 3 * ld4, ldy, 0, 0, y_dtype, stream);
+        }
         int rc4 = axs6_fq(w, wq, w_dtype, AXS6_F32, N, K, ldw, ld4, block, grid, AXS6_ROUND_NEAREST,
                           AXS6_FLAG_OUTPUT_TF32, 0, 0, stream);
         if (rc4) return rc4;
@@ -346,8 +412,9 @@ AXS6_API int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void
     if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
     if (M < 0 || N < 0 || K < 0 || ldg < N) return AXS6_ERR_ARG;
     if (flags & ~(AXS6_LINEAR_QUANTIZE_GRAD | AXS6_LINEAR_COMPUTE_TF32 | AXS6_LINEAR_BIAS_FROM_QUANTIZED |
-                  AXS6_LINEAR_REUSE_WQ | AXS6_LINEAR_REUSE_GQ | AXS6_LINEAR_OPERANDS_PACKED))
+                  AXS6_LINEAR_REUSE_WQ | AXS6_LINEAR_REUSE_GQ | AXS6_LINEAR_OPERANDS_PACKED | AXS6_LINEAR_SPLITK_WORKSPACE))
         return AXS6_ERR_ARG;
+    if ((flags & AXS6_LINEAR_SPLITK_WORKSPACE) && ((flags & AXS6_LINEAR_COMPUTE_TF32) || !tf32_scratch)) return AXS6_ERR_WORKSPACE;
     if ((flags & AXS6_LINEAR_COMPUTE_TF32) && (flags & (AXS6_LINEAR_REUSE_WQ | AXS6_LINEAR_REUSE_GQ))) return AXS6_ERR_UNSUPPORTED;
     if (M == 0 || N == 0 || K == 0) return AXS6_OK;
     if (!g || !gq) return AXS6_ERR_ARG;
@@ -379,16 +446,17 @@ AXS6_API int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void
             rc = axs6_fq(w, wq, w_dtype, AXS6_F32, N, K, ldw, ld4, block, grid, AXS6_ROUND_NEAREST,
                          AXS6_FLAG_OUTPUT_TF32, 0, 0, stream);
             if (rc) return rc;
-            rc = transpose_f32(static_cast<const float *>(wq), wqT, N, K, ld4, ldn4, st);
+            rc = transpose_f32(static_cast<const float *>(wq), wqT, N, K, ld4, ldn4, st, 1);
             if (rc) return rc;
             // dx (M, K) = gq (M, N) * wq (N, K) = gq * (wq^T)^T with both operands K-major
             rc = axs6_gemm_tf32(gq, wqT, dx, nullptr, M, K, N, ldg4, ldn4, lddx, 0, 0, dx_dtype, stream);
             if (rc) return rc;
         }
         if (dw) {
-            rc = transpose_f32(static_cast<const float *>(gq), gqT, M, N, ldg4, ldm4, st);
+            rc = transpose_f32(static_cast<const float *>(gq), gqT, M, N, ldg4, ldm4, st, 1);
             if (rc) return rc;
-            rc = transpose_f32(static_cast<const float *>(xq), xqT, M, K, ld4, ldm4, st);
+            // xq may hold full-precision fp32 (forward with AXS6_LINEAR_FP32_ACCURACY): rounded to TF32 on the way
+            rc = transpose_f32(static_cast<const float *>(xq), xqT, M, K, ld4, ldm4, st, 1);
             if (rc) return rc;
             // dw (N, K) = gq^T (N, M) * xq (M, K)
             rc = axs6_gemm_tf32(gqT, xqT, dw, nullptr, N, K, M, ldm4, ldm4, lddw, 0, 0, AXS6_F32, stream);
@@ -446,7 +514,10 @@ AXS6_API int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void
     // with dx / db and AXS6_LINEAR_REUSE_GQ).
     if (dw) {
         // dw (N, K) = gq^T (N, M) * xq (M, K): contraction over M; both operands (contraction, output) row-major
-        rc = axs6_gemm_bf16(gq, xq, dw, nullptr, N, K, M, ldgq, ldq, lddw, 1, 1, AXS6_F32, stream);
+        rc = (flags & AXS6_LINEAR_SPLITK_WORKSPACE)
+                 ? axs6_gemm_bf16_ws(gq, xq, dw, nullptr, N, K, M, ldgq, ldq, lddw, 1, 1, AXS6_F32, tf32_scratch,
+                                     axs6_gemm_workspace_bytes(N, K, M, AXS6_F32), stream)
+                 : axs6_gemm_bf16(gq, xq, dw, nullptr, N, K, M, ldgq, ldq, lddw, 1, 1, AXS6_F32, stream);
         if (rc) return rc;
     }
     if (dx) {

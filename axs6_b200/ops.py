@@ -363,12 +363,22 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None
     bias_f = None
     if bias is not None:
         bias_f = bias.to(device=a.device, dtype=torch.float32).contiguous()
-    fn = _lib.load().axs6_gemm_bf16 if a.dtype == torch.bfloat16 else _lib.load().axs6_gemm_tf32
+    lib = _lib.load()
     with _on(a.device):
-        st = fn(a.data_ptr(), b.data_ptr(), c.data_ptr(),
-                bias_f.data_ptr() if bias_f is not None else None, M, N, K,
-                _row_pitch(a), _row_pitch(b), N,
-                int(a_mn), int(b_mn), _DT[out_dtype], _stream(a.device))
+        # fp32 results of bf16 products with few output tiles: a workspace lets the library split the contraction
+        # more than two ways and still add the partials in a fixed order
+        ws_bytes = _splitk_bytes(M, N, K) if (a.dtype == torch.bfloat16 and out_dtype == torch.float32) else 0
+        if ws_bytes:
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
+            st = lib.axs6_gemm_bf16_ws(a.data_ptr(), b.data_ptr(), c.data_ptr(), bias_f.data_ptr() if bias_f is not None else None,
+                                       M, N, K, _row_pitch(a), _row_pitch(b), N, int(a_mn), int(b_mn), _DT[out_dtype],
+                                       ws.data_ptr(), ws_bytes, _stream(a.device))
+        else:
+            fn = lib.axs6_gemm_bf16 if a.dtype == torch.bfloat16 else lib.axs6_gemm_tf32
+            st = fn(a.data_ptr(), b.data_ptr(), c.data_ptr(),
+                    bias_f.data_ptr() if bias_f is not None else None, M, N, K,
+                    _row_pitch(a), _row_pitch(b), N,
+                    int(a_mn), int(b_mn), _DT[out_dtype], _stream(a.device))
     _lib.check("axs6_gemm", st)
     return c
 
@@ -484,6 +494,8 @@ def _ws_bytes(what: int, M: int, N: int, K: int) -> int:
     if what == 5: return N * _r4(K) * 4
     if what == 6: return M * _r4(N) * 4
     if what == 7: return (K * _r4(N) + N * _r4(M) + K * _r4(M)) * 4
+    if what == 12: return M * _r4(K) * 16
+    if what == 13: return N * _r4(K) * 16
     if what in (8, 9, 10):
         rows, cols = {8: (M, K), 9: (N, K), 10: (M, N)}[what]
         nblk = (cols + 31) // 32
@@ -508,20 +520,23 @@ def _carve(dev, sizes: list[int]) -> list[int]:
 
 def linear_fwd(x2: torch.Tensor, w: torch.Tensor, bias_f32: torch.Tensor | None, block_size: int, grid: int,
                quantize_input: bool, out_dtype: torch.dtype, tf32: bool = False, bias_via_bf16: bool = False,
-               return_wq: bool = False, packed: bool = False):
+               return_wq: bool = False, packed: bool = False, fp32_accuracy: bool = False):
     """-> (y (M, N), xq workspace holding the quantised activations that backward needs); with
     ``return_wq`` also the workspace that holds the quantised weight (backward can reuse it while the
     weight is unchanged).  ``tf32``: the fp32 graph (operands fake-quantised in fp32, TF32 tensor cores)
     instead of bf16.  ``packed``: the workspaces hold 6-bit codes and the GEMM decodes them on load
-    (``linear_packed_ok`` says whether the shapes allow it)."""
+    (``linear_packed_ok`` says whether the shapes allow it).  ``fp32_accuracy`` (with ``tf32``): three TF32
+    products per output instead of one, for fp32 accuracy (what the reference's forward has)."""
     M, K = x2.shape
     N = w.shape[0]
     dev = x2.device
-    xq = torch.empty(max(_ws_bytes(8 if packed else (4 if tf32 else 0), M, N, K), 16), dtype=torch.uint8, device=dev)
-    wq = torch.empty(max(_ws_bytes(9 if packed else (5 if tf32 else 1), M, N, K), 16), dtype=torch.uint8, device=dev)
+    x3 = bool(fp32_accuracy and tf32)
+    xq = torch.empty(max(_ws_bytes(8 if packed else (12 if x3 else (4 if tf32 else 0)), M, N, K), 16), dtype=torch.uint8, device=dev)
+    wq = torch.empty(max(_ws_bytes(9 if packed else (13 if x3 else (5 if tf32 else 1)), M, N, K), 16), dtype=torch.uint8, device=dev)
     y = torch.empty((M, N), dtype=out_dtype, device=dev)
     flags = (_lib.LINEAR_QUANTIZE_INPUT if quantize_input else 0) | (_lib.LINEAR_COMPUTE_TF32 if tf32 else 0) | \
-            (_lib.LINEAR_BIAS_VIA_BF16 if bias_via_bf16 else 0) | (_lib.LINEAR_OPERANDS_PACKED if packed else 0)
+            (_lib.LINEAR_BIAS_VIA_BF16 if bias_via_bf16 else 0) | (_lib.LINEAR_OPERANDS_PACKED if packed else 0) | \
+            (_lib.LINEAR_FP32_ACCURACY if x3 else 0)
     with _on(dev):
         st = _lib.load().axs6_linear_fwd(x2.data_ptr(), _DT[x2.dtype], x2.stride(0) if M > 1 else K,
                                          w.data_ptr(), _DT[w.dtype], w.stride(0) if N > 1 else K,
@@ -529,6 +544,10 @@ def linear_fwd(x2: torch.Tensor, w: torch.Tensor, bias_f32: torch.Tensor | None,
                                          y.data_ptr(), _DT[out_dtype], N, M, N, K, block_size, grid, flags,
                                          xq.data_ptr(), wq.data_ptr(), _stream(dev))
     _lib.check("axs6_linear_fwd", st)
+    if x3:
+        # backward needs the fp32 quantised activations only (the head of the buffer): keep a copy of that part
+        # and let the three-part split go
+        xq = xq[: M * _r4(K) * 4].clone()
     if return_wq:
         return y, xq, wq
     return y, xq
@@ -543,6 +562,9 @@ def linear_bwd(g2: torch.Tensor, xq: torch.Tensor, w: torch.Tensor, M: int, N: i
     quantised weight is recomputed."""
     dev = g2.device
     reuse_wq = wq is not None and need_dx and not tf32
+    splitk = 0
+    if need_dw and not tf32 and not packed:
+        splitk = _splitk_bytes(N, K, M)
     dx = torch.empty((M, K), dtype=dx_dtype, device=dev) if need_dx else None
     dw = torch.empty((N, K), dtype=torch.float32, device=dev) if need_dw else None
     db = torch.empty((N,), dtype=torch.float32, device=dev) if need_db else None
@@ -550,7 +572,7 @@ def linear_bwd(g2: torch.Tensor, xq: torch.Tensor, w: torch.Tensor, M: int, N: i
         _ws_bytes(10 if packed else (6 if tf32 else 2), M, N, K),
         _ws_bytes(9 if packed else (5 if tf32 else 1), M, N, K) if (need_dx and not reuse_wq) else 0,
         _ws_bytes(3, M, N, K) if need_db else 0,
-        _ws_bytes(7, M, N, K) if (tf32 and (need_dx or need_dw)) else 0])
+        _ws_bytes(7, M, N, K) if (tf32 and (need_dx or need_dw)) else splitk])
     seed, off = (0, 0)
     nz = None
     if quantize_grad:
@@ -560,7 +582,7 @@ def linear_bwd(g2: torch.Tensor, xq: torch.Tensor, w: torch.Tensor, M: int, N: i
             seed, off = next_philox(M * (-(-N // block_size)) * block_size)
     flags = (_lib.LINEAR_QUANTIZE_GRAD if quantize_grad else 0) | (_lib.LINEAR_COMPUTE_TF32 if tf32 else 0) | \
             (_lib.LINEAR_BIAS_FROM_QUANTIZED if bias_from_quantized else 0) | (_lib.LINEAR_REUSE_WQ if reuse_wq else 0) | \
-            (_lib.LINEAR_OPERANDS_PACKED if packed else 0)
+            (_lib.LINEAR_OPERANDS_PACKED if packed else 0) | (_lib.LINEAR_SPLITK_WORKSPACE if splitk else 0)
     if reuse_wq:
         p_wq = wq.data_ptr()
     with _on(dev):
@@ -570,10 +592,23 @@ def linear_bwd(g2: torch.Tensor, xq: torch.Tensor, w: torch.Tensor, M: int, N: i
             dx.data_ptr() if need_dx else None, _DT[dx_dtype], K, dw.data_ptr() if need_dw else None, K,
             db.data_ptr() if need_db else None, M, N, K, block_size, grid, flags, seed, off,
             nz.data_ptr() if nz is not None else None, p_gq, p_wq if need_dx else None,
-            p_part if need_db else None, p_tscr if (tf32 and (need_dx or need_dw)) else None, _stream(dev))
+            p_part if need_db else None, p_tscr if ((tf32 and (need_dx or need_dw)) or splitk) else None, _stream(dev))
     _lib.check("axs6_linear_bwd", st)
     del keep
     return dx, dw, db
+
+
+_SPLITK_CACHE: dict = {}
+
+
+def _splitk_bytes(M: int, N: int, K: int) -> int:
+    """Workspace from which the (M, N) = (., K) fp32 product profits (see axs6_gemm_workspace_bytes); cached per shape."""
+    key = (M, N, K, torch.cuda.current_device())
+    v = _SPLITK_CACHE.get(key)
+    if v is None:
+        v = int(_lib.load().axs6_gemm_workspace_bytes(M, N, K, F32))
+        _SPLITK_CACHE[key] = v
+    return v
 
 
 def linear_packed_ok(N: int, K: int, block_size: int, quantize_input: bool, quantize_grad: bool) -> bool:

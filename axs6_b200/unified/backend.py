@@ -57,7 +57,7 @@ def accelerated_linear(input: torch.Tensor, weight: torch.Tensor, bias: torch.Te
     all_bf16 = x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     b32 = bias.float().contiguous() if bias is not None else None
     y, _ = ops.linear_fwd(x2, w, b32, block_size, ops.GRID_NF5, bool(quantize_input),
-                          torch.bfloat16 if all_bf16 else torch.float32, tf32=not all_bf16)
+                          torch.bfloat16 if all_bf16 else torch.float32, tf32=not all_bf16, fp32_accuracy=not all_bf16)
     return y.reshape(*input.shape[:-1], weight.shape[0])
 
 

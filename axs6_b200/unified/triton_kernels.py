@@ -49,6 +49,6 @@ def triton_fused_linear(input: torch.Tensor, weight: torch.Tensor, bias: torch.T
     x2 = input.reshape(-1, input.shape[-1]).contiguous().float()
     w = weight.contiguous().float()
     b32 = bias.float().contiguous() if bias is not None else None
-    y, _ = ops.linear_fwd(x2, w, b32, 32, ops.GRID_NF5, bool(quantize_input), torch.float32, tf32=True)
+    y, _ = ops.linear_fwd(x2, w, b32, 32, ops.GRID_NF5, bool(quantize_input), torch.float32, tf32=True, fp32_accuracy=True)
     y = y.reshape(*input.shape[:-1], weight.shape[0])
     return y if orig_dtype == torch.float32 else y.to(orig_dtype)

@@ -1,7 +1,8 @@
 """Runs ONE kernel of the library a few times on a small, larger-than-L2 case, for profilers.
 
     python bench.py --case {fq_f32|fq_bf16|fq_bf16_stochastic|pack_wire|pack_wire_f32|unpack_wire|unpack_wire_bf16|
-                            unpack_sum4|gemm_fwd|gemm_dx|gemm_dw|fq_f32_full} [--launches n]
+                            unpack_sum4|gemm_fwd|gemm_dx|gemm_dw|gemm_packed_fwd|gemm_packed_fwd_w|gemm_packed_dx|
+                            gemm_packed_dw|fq_f32_full} [--launches n]
 
 Device footprint stays under 1 GB so that a multi-pass capture finishes quickly (fq_f32_full is the
 benchmark's own 32768 x 8192 launch, 2 GiB, meant for single-pass metrics only).
@@ -76,6 +77,20 @@ def run_case(what: str = "fq_f32", n: int = 3) -> None:
         c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
         run = lambda: lib.axs6_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), None, M, N, K, a.stride(0), b.stride(0),
                                          N, a_mn, b_mn, 1, st)
+    elif what in ("gemm_packed_fwd", "gemm_packed_dx", "gemm_packed_dw", "gemm_packed_fwd_w"):
+        from axs6_b200 import ops
+        M, N, K = 8192, 4096, 4096
+        a_mn, b_mn = {"gemm_packed_fwd": (0, 0), "gemm_packed_fwd_w": (0, 0), "gemm_packed_dx": (0, 1), "gemm_packed_dw": (1, 1)}[what]
+        a = torch.randn((K, M) if a_mn else (M, K), generator=g, device=dev).to(torch.bfloat16)
+        b = torch.randn((K, N) if b_mn else (N, K), generator=g, device=dev).to(torch.bfloat16)
+        pa, pb = ops.pack_split(a), ops.pack_split(b)
+        c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        if what == "gemm_packed_fwd_w":          # only the weight as codes
+            run = lambda: lib.axs6_gemm_packed(a.data_ptr(), None, K, pb.codes.data_ptr(), pb.exps.data_ptr(), 0, c.data_ptr(), None,
+                                               M, N, K, N, a_mn, b_mn, 1, st)
+        else:
+            run = lambda: lib.axs6_gemm_packed(pa.codes.data_ptr(), pa.exps.data_ptr(), 0, pb.codes.data_ptr(), pb.exps.data_ptr(), 0,
+                                               c.data_ptr(), None, M, N, K, N, a_mn, b_mn, 1, st)
     else:
         raise SystemExit(f"unknown case {what}")
     for _ in range(n):

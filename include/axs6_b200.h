@@ -75,6 +75,20 @@ enum { AXS6_LAYOUT_PLANES = 0, /* AXSTensor planes: u8 exponent (rows,nblk), u8 
                                          0.78 bytes per value.  Equal to the bf16 path except where an operand holds
                                          an exact zero, which codes cannot express (see axs6_gemm_packed)        */
 
+#define AXS6_LINEAR_SPLITK_WORKSPACE 256u /* backward, bf16 graph: `tf32_scratch` holds axs6_linear_workspace_bytes(11, M, N, K)
+                                         bytes in which the weight-gradient product keeps split-K partials apart; they
+                                         are added in a fixed order, so dw is bit-reproducible with more than two
+                                         partials (small layers with long contractions) */
+
+#define AXS6_LINEAR_FP32_ACCURACY 512u  /* forward, with AXS6_LINEAR_COMPUTE_TF32: the product of the fp32 fake-quantised
+                                         operands to fp32 accuracy (about 2^-21 relative) instead of TF32 accuracy
+                                         (2^-11): each operand is split into two TF32 parts and three TF32 products are
+                                         accumulated in one GEMM over the tripled contraction.  What the reference's
+                                         fused kernel computes (`input_precision="ieee"`, triton_kernels.py:262) and its
+                                         tests hold it to (tests/test_triton_fused_linear.py:33-35: 1e-3 absolute).
+                                         xq / wq are workspace codes 12 / 13; xq starts with the fp32 quantised
+                                         activations, which is what backward reads                              */
+
 #define AXS6_OK 0
 #define AXS6_ERR_ARG (-1)         /* null pointer, negative size, bad enum, bad block size  */
 #define AXS6_ERR_ALIGN (-2)       /* pointer or leading dimension violates a stated alignment */
@@ -104,7 +118,11 @@ int64_t axs6_query(int what);
  *   key 7   GEMM kernel: 1 single-CTA, 2 CTA pairs
  *   key 8   SMs the GEMM leaves free (for a collective on another stream)
  *   key 11  1 = general unpack / unpack-and-sum kernels only (no TMA-fed kernel)
- *   key 12  1 = general fake-quantise kernel only (no TMA-fed bf16 kernel) */
+ *   key 12  1 = general fake-quantise kernel only (no TMA-fed bf16 kernel)
+ *   key 13  poll limit of the bounded waits inside axs6_unpack_sum's fast kernel (default 2^22 polls)
+ *   key 14  1 = the producer warp of that kernel issues no load at all, so that the consumers' first wait runs
+ *           out with nothing in flight and the kernel returns with status 11: exists only so that a test can
+ *           walk the give-up path without faulting or hanging the GPU */
 int axs6_tune(int key, int64_t value);
 
 /* Every stochastic kernel adds a per-device, device-resident epoch to its Philox counter offset.
@@ -184,6 +202,19 @@ int64_t axs6_record_bytes(int layout, int block);
 int axs6_gemm_bf16(const void *a, const void *b, void *c, const float *bias,
                    int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                    int a_mn, int b_mn, int c_dtype, axs6_stream_t stream);
+
+/* axs6_gemm_bf16 with a caller-owned workspace.  A product with few output tiles and a long contraction (fp32
+ * output: the weight gradient of a small layer) is split along K so that most SMs get work.  Without a workspace at
+ * most two partial products are formed and added into C in either order (bit-reproducible).  With `ws` of
+ * axs6_gemm_workspace_bytes(M, N, K, c_dtype) bytes (16-byte aligned) up to eight partials are kept apart in it and
+ * added in index order by a second kernel: as reproducible, and faster on such shapes.  A workspace that is null or
+ * too small is ignored.  (No counterpart in the reference: torch.matmul owns its workspace.) */
+int axs6_gemm_bf16_ws(const void *a, const void *b, void *c, const float *bias,
+                      int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                      int a_mn, int b_mn, int c_dtype, void *ws, int64_t ws_bytes, axs6_stream_t stream);
+
+/* Bytes of workspace from which axs6_gemm_bf16_ws can profit for this product on the current device (0: none). */
+int64_t axs6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int c_dtype);
 
 /* The same product with one or both operands held as AXS-6 codes and decoded to bf16 inside the kernel
  * ("quantise on load"): the data flow of the reference's fused linear kernel, which produces the quantised
@@ -308,7 +339,9 @@ int axs6_bias_grad_static(const void *g, int g_dtype, int64_t ldg, int64_t rows,
 
 /* Bytes of a caller-owned work buffer: what 0 = xq, 1 = wq, 2 = gq (bf16 compute), 3 = db_partial,
  * 4 = xq, 5 = wq, 6 = gq of the AXS6_LINEAR_COMPUTE_TF32 graph (fp32), 7 = its tf32_scratch,
- * 8 = xq, 9 = wq, 10 = gq of AXS6_LINEAR_OPERANDS_PACKED (codes). */
+ * 12 = xq, 13 = wq of AXS6_LINEAR_FP32_ACCURACY,
+ * 8 = xq, 9 = wq, 10 = gq of AXS6_LINEAR_OPERANDS_PACKED (codes), 11 = split-K partials of dw for
+ * AXS6_LINEAR_SPLITK_WORKSPACE (0 when the product would not be split further). */
 int64_t axs6_linear_workspace_bytes(int what, int64_t M, int64_t N, int64_t K);
 
 #ifdef __cplusplus

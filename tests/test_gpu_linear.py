@@ -440,6 +440,40 @@ class _DecoderBlock(torch.nn.Module):
         return x + self.fc2(F.gelu(self.fc1(h)))
 
 
+@pytest.mark.parametrize("M,N,K,bias", [(1024, 1024, 8192, False), (512, 1000, 4096, True), (256, 256, 16384, False)])
+def test_split_k_with_workspace_is_reproducible(M, N, K, bias):
+    """Few output tiles, long contraction (a small layer's weight gradient): with a workspace the product is split more
+    than two ways, the partials are added in index order, and two runs agree bit for bit; without one at most two
+    partials are formed.  Both within 1e-5 of the fp32 product."""
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(M + N + K)
+    A = torch.randn(K, M, generator=g).to(torch.bfloat16).cuda()
+    B = torch.randn(K, N, generator=g).to(torch.bfloat16).cuda()
+    bv = torch.randn(N, generator=g).cuda() if bias else None
+    ref = A.float().t().double() @ B.float().double() + (bv.double() if bias else 0.0)
+    need = int(lib.axs6_gemm_workspace_bytes(M, N, K, 0))
+    assert need > 0 and int(lib.axs6_gemm_workspace_bytes(M, N, K, 1)) == 0
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    outs = []
+    for _ in range(3):
+        c = torch.full((M, N), float("nan"), device="cuda")
+        assert lib.axs6_gemm_bf16_ws(A.data_ptr(), B.data_ptr(), c.data_ptr(), bv.data_ptr() if bias else None, M, N, K, M,
+                                     ops._row_pitch(B), N, 1, 1, 0, ws.data_ptr(), need, st) == 0
+        outs.append(c)
+    gemm_status_ok()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert rel(outs[0], ref.cuda()) < 1e-5
+    plain = torch.empty(M, N, device="cuda")
+    assert lib.axs6_gemm_bf16(A.data_ptr(), B.data_ptr(), plain.data_ptr(), bv.data_ptr() if bias else None, M, N, K, M,
+                              ops._row_pitch(B), N, 1, 1, 0, st) == 0
+    assert rel(plain, ref.cuda()) < 1e-5
+    small = torch.empty(M, N, device="cuda")          # a workspace that is too small is ignored
+    assert lib.axs6_gemm_bf16_ws(A.data_ptr(), B.data_ptr(), small.data_ptr(), bv.data_ptr() if bias else None, M, N, K, M,
+                                 ops._row_pitch(B), N, 1, 1, 0, ws.data_ptr(), 1024, st) == 0
+    assert torch.equal(small, plain)
+
+
 def test_minigpt_block_trains_with_axs6_linears():
     """A decoder block built on AXSLinearMixedPrecision: forward/backward run, gradients reach every
     parameter, a few AdamW steps reduce the loss (convergence smoke test in the spirit of
