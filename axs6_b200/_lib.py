@@ -33,6 +33,7 @@ SIGNATURES = {
     "axs6_record_bytes": (_i64, [_int, _int]),
     "axs6_tune": (_int, [_int, _i64]),
     "axs6_philox_advance": (_int, [_u64, _int, _ptr]),
+    "axs6_philox_epoch": (_int, [ctypes.POINTER(_u64)]),
     "axs6_repack": (_int, [_int, _int, _int, _i64, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "axs6_fq": (_int, [_ptr, _ptr, _int, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _u32, _u64, _u64, _ptr]),
     "axs6_fq_with_noise": (_int, [_ptr, _ptr, _int, _int, _i64, _i64, _i64, _i64, _int, _int, _u32, _ptr, _ptr]),

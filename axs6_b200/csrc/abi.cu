@@ -124,6 +124,17 @@ AXS6_API int axs6_tune(int key, int64_t value)
     return AXS6_OK;
 }
 
+AXS6_API int axs6_philox_epoch(uint64_t *epoch)
+{
+    if (!epoch) return AXS6_ERR_ARG;
+    const axs6::DeviceInfo &d = axs6::device_info();
+    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+    unsigned long long v = 0;
+    if (cudaMemcpyFromSymbol(&v, axs6::g_philox_epoch, sizeof(v)) != cudaSuccess) return AXS6_ERR_DEVICE;
+    *epoch = v;
+    return AXS6_OK;
+}
+
 AXS6_API int axs6_philox_advance(uint64_t delta, int reset, axs6_stream_t stream)
 {
     const axs6::DeviceInfo &d = axs6::device_info();

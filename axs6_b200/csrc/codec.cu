@@ -30,6 +30,15 @@ struct CodecArgs {
 };
 
 constexpr int kPlanes = 0, kBytes = 1;
+
+// Split layout: position of block `blk` (row-major index over rows x nblk) in the exponent plane, which is stored by
+// PAIRS of blocks: (ceil(nblk / 2), rows, 2) bytes.  The exponents that one GEMM operand tile needs (two consecutive
+// blocks of 128 rows, or four blocks of 64 rows) are then contiguous runs that a bulk copy can fetch.
+__device__ __forceinline__ int64_t split_exp_index(int64_t blk, int64_t nblk, int64_t rows)
+{
+    const int64_t row = blk / nblk, b = blk - row * nblk;
+    return ((b >> 1) * rows + row) * 2 + (b & 1);
+}
 constexpr int kU = 2;                               // chunks per thread per iteration
 constexpr int kStageBytes = kU * kThreads * 8;      // worst case: B = 8, 8-byte records
 
@@ -81,7 +90,6 @@ __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
 {
     __shared__ __align__(16) uint8_t rev[GRID == AXS6_GRID_NF5 ? 1024 : 16];
     __shared__ __align__(16) uint8_t stage[LAYOUT == kBytes ? kStageBytes : 16];
-    pdl_launch_dependents();
     if (GRID == AXS6_GRID_NF5) build_reverse_lut(rev);
     __syncthreads();
     pdl_wait();                    // nothing of the caller's memory is touched before this point
@@ -94,6 +102,7 @@ __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
     const int lb_thread = (int)threadIdx.x >> lg;           // block of this thread inside a 256-chunk group
     const int blocks_per_group = kThreads >> lg;
     for (int64_t base = (int64_t)blockIdx.x * kThreads * kU; base < a.g.total_chunks; base += step) {
+        if (base + step >= a.g.total_chunks) pdl_launch_dependents();      // last iteration of this CTA: the next kernel may move in
         uint32_t v[kU][8];
         bool act[kU];
 #pragma unroll
@@ -147,7 +156,7 @@ __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
                         s[0] = (uint8_t)((se << 2) & 0xFF);
                         s[1] = (uint8_t)(se >> 6);
                     } else if (act[k]) {
-                        a.p1[c >> lg] = (uint8_t)se;            // split layout: exponents in a plane of their own
+                        a.p1[split_exp_index(c >> lg, a.g.cpr >> lg, a.g.rows)] = (uint8_t)se;   // split layout: exponent plane
                     }
                 }
                 s += a.hdr + 6 * j;
@@ -176,7 +185,6 @@ template <typename Tin, int GRID, int ROUND, int LAYOUT>
 __global__ void __launch_bounds__(kThreads) pack_generic_kernel(const CodecArgs a)
 {
     __shared__ __align__(16) uint8_t rev[GRID == AXS6_GRID_NF5 ? 1024 : 16];
-    pdl_launch_dependents();
     if (GRID == AXS6_GRID_NF5) build_reverse_lut(rev);
     __syncthreads();
     pdl_wait();                    // nothing of the caller's memory is touched before this point
@@ -190,6 +198,7 @@ __global__ void __launch_bounds__(kThreads) pack_generic_kernel(const CodecArgs 
     const int64_t tiles = a.g.rows * tiles_per_row;
     const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
     for (int64_t t = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); t < tiles; t += warps) {
+        if (t + warps >= tiles) pdl_launch_dependents();
         const int64_t row = t / tiles_per_row;
         const int64_t pc = (t - row * tiles_per_row) * 32 + lane;
         const bool in_pad = pc < padded;
@@ -228,7 +237,7 @@ __global__ void __launch_bounds__(kThreads) pack_generic_kernel(const CodecArgs 
                     r[0] = (uint8_t)((s.se << 2) & 0xFF);
                     r[1] = (uint8_t)(s.se >> 6);
                 } else {
-                    a.p1[blk] = (uint8_t)s.se;
+                    a.p1[split_exp_index(blk, nblk, a.g.rows)] = (uint8_t)s.se;
                 }
             }
             const int q = i & 3;
@@ -247,7 +256,6 @@ __global__ void __launch_bounds__(kThreads) unpack_vec_kernel(const CodecArgs a)
 {
     __shared__ float lev[32];
     __shared__ __align__(16) uint8_t stage[LAYOUT == kBytes ? kStageBytes : 16];
-    pdl_launch_dependents();
     build_levels<GRID>(lev);
     __syncthreads();
     pdl_wait();                    // nothing of the caller's memory is touched before this point
@@ -259,6 +267,7 @@ __global__ void __launch_bounds__(kThreads) unpack_vec_kernel(const CodecArgs a)
     const int lb_thread = (int)threadIdx.x >> lg;
     const int blocks_per_group = kThreads >> lg;
     for (int64_t base = (int64_t)blockIdx.x * kThreads * kU; base < a.g.total_chunks; base += step) {
+        if (base + step >= a.g.total_chunks) pdl_launch_dependents();      // last iteration of this CTA: the next kernel may move in
         if (LAYOUT == kBytes) {
             const int64_t blk0 = base >> lg;
             int nb = (kU * kThreads) >> lg;
@@ -296,7 +305,7 @@ __global__ void __launch_bounds__(kThreads) unpack_vec_kernel(const CodecArgs a)
                 const int lb = k * blocks_per_group + lb_thread;
                 const uint8_t *s = stage + lb * a.rec;
                 se = (a.hdr == 1) ? (uint32_t)s[0] : (a.hdr == 2) ? (((uint32_t)s[0] | ((uint32_t)s[1] << 8)) >> 2) & 0xFFu
-                                                                  : (uint32_t)a.p1[c >> lg];
+                                                                  : (uint32_t)a.p1[split_exp_index(c >> lg, a.g.cpr >> lg, a.g.rows)];
                 s += a.hdr + 6 * j;
                 const uint32_t lo = (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
                 const uint32_t hi = (uint32_t)s[4] | ((uint32_t)s[5] << 8);
@@ -321,7 +330,6 @@ template <typename Tout, int GRID, int LAYOUT>
 __global__ void __launch_bounds__(kThreads) unpack_generic_kernel(const CodecArgs a)
 {
     __shared__ float lev[32];
-    pdl_launch_dependents();
     build_levels<GRID>(lev);
     __syncthreads();
     pdl_wait();                    // nothing of the caller's memory is touched before this point
@@ -332,6 +340,7 @@ __global__ void __launch_bounds__(kThreads) unpack_generic_kernel(const CodecArg
     const int64_t total = a.g.rows * a.g.cols;
     const int64_t nthreads = (int64_t)gridDim.x * kThreads;
     for (int64_t e = (int64_t)blockIdx.x * kThreads + threadIdx.x; e < total; e += nthreads) {
+        if (e + nthreads >= total) pdl_launch_dependents();
         const int64_t row = e / a.g.cols;
         const int64_t pc = e - row * a.g.cols;
         const int i = (int)(pc % B);
@@ -344,7 +353,7 @@ __global__ void __launch_bounds__(kThreads) unpack_generic_kernel(const CodecArg
         } else {
             const uint8_t *r = a.p0 + blk * a.rec;
             se = (a.hdr == 1) ? (uint32_t)r[0] : (a.hdr == 2) ? (((uint32_t)r[0] | ((uint32_t)r[1] << 8)) >> 2) & 0xFFu
-                                                              : (uint32_t)a.p1[blk];
+                                                              : (uint32_t)a.p1[split_exp_index(blk, nblk, a.g.rows)];
             const int bit = 6 * i, k = bit >> 3, sh = bit & 7;
             uint32_t w = r[a.hdr + k];
             if (sh > 2) w |= (uint32_t)r[a.hdr + k + 1] << 8;
@@ -639,7 +648,6 @@ __global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_bulk_kernel(con
     const int tid = threadIdx.x;
     const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
     const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    pdl_launch_dependents();
     build_key_table(table, tid, kFastBlocks);              // module constants: may run while the previous kernel drains
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
@@ -667,6 +675,7 @@ __global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_bulk_kernel(con
     int s = 0;
     uint32_t ph = 0;
     for (int64_t k = 0; k < nk; ++k) {
+        if (k + 1 == nk) pdl_launch_dependents();                             // last tile of this CTA: the next kernel may move in
         const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
         const int64_t b = grp * kFastBlocks + tid;
         uint8_t *ost = out0 + (k & 1) * kOut;
@@ -781,7 +790,6 @@ __global__ void __launch_bounds__(kFastBlocks) pack_f32_nf5_b32_bulk_kernel(cons
     const int tid = threadIdx.x;
     const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
     const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    pdl_launch_dependents();
     build_reverse_lut(rev);                                 // module constants: may run while the previous kernel drains
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
@@ -807,6 +815,7 @@ __global__ void __launch_bounds__(kFastBlocks) pack_f32_nf5_b32_bulk_kernel(cons
     int s = 0;
     uint32_t ph = 0;
     for (int64_t k = 0; k < nk; ++k) {
+        if (k + 1 == nk) pdl_launch_dependents();                             // last tile of this CTA: the next kernel may move in
         const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
         const int64_t b = grp * kFastBlocks + tid;
         uint8_t *ost = out0 + (k & 1) * kOut;
@@ -960,7 +969,6 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
     const int tid = threadIdx.x;
     const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
     const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    pdl_launch_dependents();
     if (tid < 64) {
         const uint32_t bits = g_codebook_bits[tid & 31];
         const uint32_t sign = (uint32_t)tid >> 5;
@@ -1001,6 +1009,7 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
     int s = 0;
     uint32_t ph = 0;
     for (int64_t k = 0; k < nk; ++k) {
+        if (k + 1 == nk) pdl_launch_dependents();                             // last tile of this CTA: the next kernel may move in
         const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
         const int64_t b = grp * kFastBlocks + tid;
         const int64_t nb = nblocks - grp * kFastBlocks;

@@ -42,7 +42,9 @@ int gemm_packed_launch(const void *a, const void *a_exps, int64_t lda, const voi
 // Programmatic dependent launch.  A kernel launched with launch_overlapped() may become resident while the kernel
 // before it on the stream is still draining: its CTAs run their prologue (barrier initialisation, tables copied
 // from the module image into shared memory) and then block in pdl_wait() until that earlier kernel has completed
-// and its writes are visible.  Everything that reads or writes caller memory comes after pdl_wait(), so the result
+// and its writes are visible.  A CTA calls pdl_launch_dependents() when it enters its LAST loop iteration, so the
+// next kernel moves in only while this one drains (signalled at kernel start, the waiting CTAs of the next kernel
+// sat on the SMs for the whole run and cost the bf16 fake-quantise kernel 20 % of its bandwidth).  Everything that reads or writes caller memory comes after pdl_wait(), so the result
 // is the same as with an ordinary launch; what is saved is the launch gap and the prologue between back-to-back
 // kernels, which matters for launches of a few tens of microseconds.  Without the launch attribute the two
 // device calls do nothing.  Tune key 15 = 1 turns the attribute off.

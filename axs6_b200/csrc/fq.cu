@@ -89,7 +89,6 @@ template <typename Tin, typename Tout, int GRID, int ROUND, int U>
 __global__ void __launch_bounds__(kThreads) fq_vec_kernel(const FqArgs a)
 {
     __shared__ __align__(16) float tab[GRID == AXS6_GRID_NF5 ? 1024 : 32];
-    pdl_launch_dependents();
     if (GRID == AXS6_GRID_NF5) build_value_lut(tab); else build_levels<GRID>(tab);
     __syncthreads();
     pdl_wait();                    // nothing of the caller's memory is touched before this point
@@ -98,6 +97,7 @@ __global__ void __launch_bounds__(kThreads) fq_vec_kernel(const FqArgs a)
     const uint64_t offset = (ROUND == kPhilox) ? a.offset + *a.epoch : 0ull;
     const int64_t step = (int64_t)gridDim.x * kThreads * U;
     for (int64_t base = (int64_t)blockIdx.x * kThreads * U; base < a.g.total_chunks; base += step) {
+        if (base + step >= a.g.total_chunks) pdl_launch_dependents();      // last iteration of this CTA: the next kernel may move in
         uint32_t v[U][8];
         int64_t yo[U], cidx[U];
         bool act[U];
@@ -141,7 +141,6 @@ template <typename Tin, typename Tout, int GRID, int ROUND>
 __global__ void __launch_bounds__(kThreads) fq_generic_kernel(const FqArgs a)
 {
     __shared__ __align__(16) float tab[GRID == AXS6_GRID_NF5 ? 1024 : 32];
-    pdl_launch_dependents();
     if (GRID == AXS6_GRID_NF5) build_value_lut(tab); else build_levels<GRID>(tab);
     __syncthreads();
     pdl_wait();
@@ -153,6 +152,7 @@ __global__ void __launch_bounds__(kThreads) fq_generic_kernel(const FqArgs a)
     const int64_t tiles = a.g.rows * tiles_per_row;
     const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
     for (int64_t t = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); t < tiles; t += warps) {
+        if (t + warps >= tiles) pdl_launch_dependents();
         const int64_t row = t / tiles_per_row;
         const int64_t pc = (t - row * tiles_per_row) * 32 + lane;
         const bool act = pc < a.g.cols;
@@ -304,7 +304,6 @@ __global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __
     const int tid = threadIdx.x;
     const int64_t groups = (nblocks + kBlocksB - 1) / kBlocksB;
     const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    pdl_launch_dependents();
     if (ROUND == kNearest) {
         for (int i = tid; i < (kKeyLim + 8) / 8; i += kBlocksB)
             reinterpret_cast<uint4 *>(table)[i] = reinterpret_cast<const uint4 *>(g_key_level_bf16)[i];
@@ -334,6 +333,7 @@ __global__ void __launch_bounds__(kBlocksB) fq_bf16_nf5_b32_bulk_kernel(const __
     int s = 0;
     uint32_t ph = 0;
     for (int64_t k = 0; k < nk; ++k) {
+        if (k + 1 == nk) pdl_launch_dependents();                             // last tile of this CTA: the next kernel may move in
         const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
         const int64_t b = grp * kBlocksB + tid;
         uint8_t *slot = slot0 + s * kSlotBytes;

@@ -640,7 +640,7 @@ static int launch_gemm_packed(const void *a, const void *a_exps, int64_t lda, co
     if (!a || !b || !c || K == 0 || ldc < N) return AXS6_ERR_ARG;
     if (!a_exps && !b_exps) return AXS6_ERR_ARG;                 // nothing packed: axs6_gemm_bf16 is the entry point
     if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return AXS6_ERR_UNSUPPORTED;
-    if (!aligned16(a) || !aligned16(b)) return AXS6_ERR_ALIGN;
+    if (!aligned16(a) || !aligned16(b) || (a_exps && !aligned16(a_exps)) || (b_exps && !aligned16(b_exps))) return AXS6_ERR_ALIGN;
     const DeviceInfo &d = device_info();
     if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
     // stored shape of each operand: (rows, cols) with cols contiguous
@@ -648,12 +648,13 @@ static int launch_gemm_packed(const void *a, const void *a_exps, int64_t lda, co
     const int64_t b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;
     CUtensorMap ma, mb;
     PackedParams q;
+    q.dbg = (int)tune_value(9);
     q.a_exps = static_cast<const uint8_t *>(a_exps); q.b_exps = static_cast<const uint8_t *>(b_exps);
     q.a_nblk = (int)(a_cols / 32); q.b_nblk = (int)(b_cols / 32);
     q.a_rows = (int)a_rows; q.b_rows = (int)b_rows;
     bool ok = true;
     if (a_exps) {
-        if (a_cols % 64) return AXS6_ERR_UNSUPPORTED;            // payload rows must be 16-byte multiples
+        if (a_cols % 64 || a_rows % 8) return AXS6_ERR_UNSUPPORTED;   // payload rows and exponent runs must be 16-byte multiples
         ok = ok && make_byte_map(&ma, a, (uint64_t)a_cols * 3 / 4, (uint64_t)a_rows, a_mn ? 96 : 48, a_mn ? 64 : 128);
     } else {
         if (lda < a_cols) return AXS6_ERR_ARG;
@@ -662,7 +663,7 @@ static int launch_gemm_packed(const void *a, const void *a_exps, int64_t lda, co
                          : make_map(&ma, a, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 128));
     }
     if (b_exps) {
-        if (b_cols % 64) return AXS6_ERR_UNSUPPORTED;
+        if (b_cols % 64 || b_rows % 8) return AXS6_ERR_UNSUPPORTED;
         ok = ok && make_byte_map(&mb, b, (uint64_t)b_cols * 3 / 4, (uint64_t)b_rows, b_mn ? 96 : 48, b_mn ? 64 : 128);
     } else {
         if (ldb < b_cols) return AXS6_ERR_ARG;

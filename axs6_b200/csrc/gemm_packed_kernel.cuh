@@ -7,20 +7,21 @@
 //
 // Included by gemm.cu inside namespace axs6::gemm.
 //
-// CTA pair on a 256 x 256 tile as in gemm2_kernel; 14 warps per CTA:
+// CTA pair on a 256 x 256 tile as in gemm2_kernel; 22 warps per CTA:
 //   warp 0       producer: per k-block, TMA-loads this CTA's tile of every bf16 operand straight into the
-//                MMA stage (bytes counted on the leader's "full" barrier), and the payload tile of every packed
-//                operand (128 rows x 48 B, or 64 k-rows x 96 B for an MN-major operand) into a raw stage
-//                (bytes counted on this CTA's "raw full" barrier)
+//                MMA stage (bytes counted on the leader's "full" barrier), and for every packed operand the
+//                payload tile (128 rows x 48 B, or 64 k-rows x 96 B for an MN-major operand) plus its 256
+//                exponent bytes (one or two contiguous runs of the pair-major exponent plane, bulk copies) into a
+//                raw stage (bytes counted on this CTA's "raw full" barrier)
 //   warp 1       MMA issuer (leader CTA), unchanged
 //   warps 2..5   epilogue, unchanged
-//   warps 6..13  decode: thread t owns block t of the 256 blocks of a packed operand tile: reads its 24-byte
-//                payload from the raw stage and its exponent byte from global memory (fetched one k-block
-//                ahead), looks every 6-bit code up in a per-lane copy of the 64-entry table (bf16 level with
-//                the exponent field lowered by 120, sign included; bank-conflict free), adds the block
-//                exponent to the exponent fields of two values at a time, and writes four 16-byte pieces to
-//                the 128-byte-swizzled position the UMMA descriptor expects; then fence.proxy.async and one
-//                arrival per warp on the leader's "full" barrier and on the own "raw empty" barrier.
+//   warps 6..21  decode: thread t owns half-block t (16 values) of the 512 half-blocks of a packed operand tile:
+//                reads its 12 payload bytes and its exponent byte from the raw stage, looks two 6-bit codes at a
+//                time up in a 4096-entry table (two bf16 levels with the exponent field lowered by 120, signs
+//                included), adds the block exponent to both exponent fields with one integer add, and writes
+//                two 16-byte pieces to the 128-byte-swizzled position the UMMA descriptor expects; then
+//                fence.proxy.async and one arrival per warp on the leader's "full" barrier and on the own
+//                "raw empty" barrier.  One lane of each warp polls the barriers.
 // A bf16 value is (level bits - 120 << 7) + (se - 7 << 7): exact, because the power-of-two block scale
 // only moves the exponent field (blocks with se < 8 or se = 255, where that field would leave its range,
 // use the fp32 product and one rounding instead; all-zero blocks have se = 0).
@@ -29,12 +30,15 @@
 // Every wait is bounded; on giving up a role records a code (5 decode/raw tile, 6 decode/stage free,
 // 7 producer/raw stage free) and all roles leave, as in the other kernels.
 
-constexpr int kThreadsPacked = 448;
-constexpr int kDecodeWarps = 8;
+constexpr int kDecodeWarps = 16;
+constexpr int kThreadsPacked = (6 + kDecodeWarps) * 32;       // 704
 
 struct PackedParams {
-    const uint8_t *a_exps, *b_exps;     // exponent planes (null: operand is bf16)
-    int a_nblk, b_nblk;                 // blocks per row of the exponent plane
+    int dbg;                            // timing experiments only (tune key 9): 1 = decode threads store zeros instead of
+                                        // decoding, 2 = no proxy fence, 4 = the producer loads no payload / exponent bytes
+                                        // (results are then wrong; never set outside measurements)
+    const uint8_t *a_exps, *b_exps;     // exponent planes, pair-major (null: operand is bf16)
+    int a_nblk, b_nblk;                 // blocks per row of the stored operand matrix
     int a_rows, b_rows;                 // rows of the stored operand matrix (K-major: M or N; MN-major: K)
 };
 
@@ -43,9 +47,10 @@ struct PairQ {
     static constexpr int kABytes = 128 * BK * 2, kBBytes = 128 * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;          // 32 KB
     static constexpr int kRawOp = 128 * 48;                        // payload tile of one operand: 6 KB
-    static constexpr int kRawBytes = 2 * kRawOp;
-    static constexpr int kLutBytes = 2 * 64 * 32 * 4;              // two per-lane tables of 8 KB
-    static constexpr int kSmemBytes = 8192 /*alignment slack for the tables*/ + kLutBytes + kStages * (kStageBytes + kRawBytes) + 512;
+    static constexpr int kExpOp = 256;                             // its 256 exponent bytes
+    static constexpr int kRawBytes = 2 * (kRawOp + kExpOp);
+    static constexpr int kLutBytes = 4096 * 4;                     // code pair -> two bf16 values
+    static constexpr int kSmemBytes = 16384 /*alignment slack for the table*/ + kLutBytes + kStages * (kStageBytes + kRawBytes) + 512;
 };
 
 __device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_addr)
@@ -53,38 +58,36 @@ __device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_add
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
-// Decodes one block (24-byte payload at shared address `raw`, exponent `se`) into 32 bf16 values = 16 words.
-// `lut_lo` / `lut_hi` are this lane's table bases (value in the low / high half of the word).
-__device__ __forceinline__ void decode_block(uint32_t raw, uint32_t se, uint32_t lut_lo, uint32_t lut_hi, uint32_t (&o)[16])
+// Decodes half a block: 16 codes = 12 payload bytes at shared address `raw` (4-byte aligned), exponent `se`, into
+// 16 bf16 values = 8 words.  `lut` is the shared address of the pair table (16 KB aligned, so that an offset can be
+// OR-ed in): entry (c1 << 6 | c0) holds the two table values of codes c0 (low half) and c1 (high half).
+__device__ __forceinline__ void decode_half_block(uint32_t raw, uint32_t se, uint32_t lut, uint32_t (&o)[8])
 {
-    uint32_t pay[6];
-    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(pay[0]), "=r"(pay[1]) : "r"(raw));
-    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(pay[2]), "=r"(pay[3]) : "r"(raw + 8u));
-    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(pay[4]), "=r"(pay[5]) : "r"(raw + 16u));
+    uint32_t w[3];
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[0]) : "r"(raw));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[1]) : "r"(raw + 4u));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[2]) : "r"(raw + 8u));
     if (se >= 8u && se <= 254u) {
         const uint32_t kk = (se - 7u) * 0x00800080u;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-            uint32_t v[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                // table offset of code c is c * 128 (32 lanes x 4 bytes per entry)
-                const int bit = 6 * (i + e), word = bit >> 5, off = bit & 31;
-                uint32_t x;
-                if (off < 7) x = pay[word] << (7 - off);
-                else if (off <= 26) x = pay[word] >> (off - 7);
-                else x = __funnelshift_r(pay[word], pay[word + 1], off - 7);
-                const uint32_t addr = (x & 0x1F80u) | (e ? lut_hi : lut_lo);
-                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v[e]) : "r"(addr));
-            }
-            o[i >> 1] = v[0] + v[1] + kk;
+        for (int p = 0; p < 8; ++p) {
+            // byte offset of pair p's entry: its 12 bits start at bit 12 p of the 96-bit payload
+            const int bit = 12 * p, word = bit >> 5, off = bit & 31;
+            uint32_t x;
+            if (off == 0) x = w[word] << 2;
+            else if (off <= 20) x = w[word] >> (off - 2);
+            else x = __funnelshift_r(w[word], w[word + 1 < 3 ? word + 1 : 2], off - 2);
+            uint32_t v;
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"((x & 0x3FFCu) | lut));
+            o[p] = v + kk;
         }
     } else {
+        // all-zero blocks (se = 0) and blocks at the ends of the exponent range: fp32 product, one rounding
         const float scale = axs6_scale_decode(se);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < 16; ++i) {
             const int bit = 6 * i, word = bit >> 5, off = bit & 31;
-            const uint32_t code = (off <= 26 ? (pay[word] >> off) : __funnelshift_r(pay[word], pay[word + 1], off)) & 63u;
+            const uint32_t code = (off <= 26 ? (w[word] >> off) : __funnelshift_r(w[word], w[word + 1 < 3 ? word + 1 : 2], off)) & 63u;
             const float y = axs6_decode_value(code >> 5, __uint_as_float(g_codebook_bits[code & 31u]), scale);
             const uint32_t h = axs6_f32_to_bf16_bits(y);
             if (i & 1) o[i >> 1] |= h << 16; else o[i >> 1] = h;
@@ -100,9 +103,9 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     constexpr int S = PairQ::kStages, kA2 = PairQ::kABytes, kStage = PairQ::kStageBytes, kRaw = PairQ::kRawBytes;
     constexpr int TN = 256;
     extern __shared__ uint8_t smem_raw[];
-    const uint32_t lut = (smem_u32(smem_raw) + 8191u) & ~8191u;              // tables: 8 KB aligned (address bits OR-ed in)
+    const uint32_t lut = (smem_u32(smem_raw) + 16383u) & ~16383u;            // pair table: 16 KB aligned
     const uint32_t base = lut + PairQ::kLutBytes;                            // MMA stages (1024-aligned)
-    const uint32_t raw0 = base + S * kStage;                                 // raw stages
+    const uint32_t raw0 = base + S * kStage;                                 // raw stages: [A payload | B payload | A exps | B exps]
     const uint32_t bar0 = raw0 + S * kRaw;
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
@@ -111,7 +114,7 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     auto tfull_bar = [&](int a) { return bar0 + 8u * (4 * S + a); };
     auto tempty_bar = [&](int a) { return bar0 + 8u * (4 * S + 2 + a); };
     const uint32_t tmem_slot = bar0 + 8u * (4 * S + 4);
-    uint8_t *smem_gen = smem_raw + (lut - smem_u32(smem_raw));               // generic pointer to the tables
+    uint8_t *smem_gen = smem_raw + (lut - smem_u32(smem_raw));               // generic pointer to the table
     volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(smem_gen + (tmem_slot - lut));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -125,26 +128,27 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
-            // full: (leader's expect_tx arrival if a bf16 operand is loaded) + one arrival per decode warp, packed operand and CTA
-            mbar_init(full_bar(s), (kAnyTma ? 1 : 0) + 2 * kDecodeWarps * kPacked);
+            // full: (leader's expect_tx arrival if a bf16 operand is loaded) + one arrival per decode warp of both CTAs
+            mbar_init(full_bar(s), (kAnyTma ? 1 : 0) + 2 * kDecodeWarps);
             mbar_init(empty_bar(s), 1);
             mbar_init(rfull_bar(s), 1);
-            mbar_init(rempty_bar(s), kDecodeWarps * kPacked);
+            mbar_init(rempty_bar(s), kDecodeWarps);
         }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    // per-lane copies of the 64-entry code table: entry c of lane l at (c * 32 + l) * 4
     {
         uint32_t *tl = reinterpret_cast<uint32_t *>(smem_gen);
-        uint32_t *th = tl + 64 * 32;
-        for (int i = threadIdx.x; i < 64 * 32; i += kThreadsPacked) {
-            const int c = i >> 5;
-            const uint32_t bits = g_codebook_bits[c & 31];
-            const uint32_t v = ((uint32_t)axs6_f32_to_bf16_bits(__uint_as_float(bits)) - (120u << 7)) | ((uint32_t)(c >> 5) << 15);
-            tl[i] = v;
-            th[i] = v << 16;
+        for (int i = threadIdx.x; i < 4096; i += kThreadsPacked) {
+            uint32_t v[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int c = (i >> (6 * e)) & 63;
+                const uint32_t bits = g_codebook_bits[c & 31];
+                v[e] = ((uint32_t)axs6_f32_to_bf16_bits(__uint_as_float(bits)) - (120u << 7)) | ((uint32_t)(c >> 5) << 15);
+            }
+            tl[i] = v[0] | (v[1] << 16);
         }
     }
     if (warp == 1) {
@@ -164,6 +168,31 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             uint32_t ph = 0;
             bool ok = true;
             int armed = 0;                                   // raw loads issued so far (for the drain at the end)
+            // exponent bytes of one operand tile: K-major = 256 contiguous bytes (pair kb, rows o0 .. o0 + 127);
+            // MN-major = two runs of 128 bytes (pairs o0 / 64 and o0 / 64 + 1, rows k0 .. k0 + 63).  Returns the bytes
+            // requested (runs are clipped to the rows that exist).
+            auto load_exps = [&](const uint8_t *exps, int nblk, int rows, bool mn, int o0, int kb, uint32_t dst, uint32_t bar) -> uint32_t {
+                const int npair = (nblk + 1) >> 1;
+                uint32_t bytes = 0;
+                if (!mn) {
+                    const int n = rows - o0 < 128 ? rows - o0 : 128;
+                    if (n > 0 && kb < npair) {
+                        bytes = (uint32_t)n * 2u;
+                        acp::bulk_load(dst, exps + ((long long)kb * rows + o0) * 2, bytes, bar);
+                    }
+                } else {
+                    const int k0 = kb * BK;
+                    const int n = rows - k0 < 64 ? rows - k0 : 64;
+                    for (int i = 0; i < 2; ++i) {
+                        const int pr = (o0 >> 6) + i;
+                        if (n > 0 && pr < npair) {
+                            acp::bulk_load(dst + 128u * i, exps + ((long long)pr * rows + k0) * 2, (uint32_t)n * 2u, bar);
+                            bytes += (uint32_t)n * 2u;
+                        }
+                    }
+                }
+                return bytes;
+            };
             for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
                 const int m0 = (t / tiles_n) * 256 + (int)rank * 128;
                 const int n0 = (t % tiles_n) * TN + (int)rank * 128;
@@ -185,8 +214,21 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     }
                     if (kPacked) {
                         if (!mbar_wait(rempty_bar(s), ph ^ 1u, 7)) { ok = false; break; }
-                        mbar_expect_tx(rfull_bar(s), kPacked * PairQ::kRawOp);
                         const uint32_t ra = raw0 + s * kRaw, rb = ra + PairQ::kRawOp;
+                        const uint32_t ea = ra + 2 * PairQ::kRawOp, eb = ea + PairQ::kExpOp;
+                        // the exponent runs first: their byte count is known only after clipping, and the barrier is armed
+                        // with the total before any copy can complete the phase (a copy that lands early only makes the
+                        // pending count negative for a moment)
+                        if (q.dbg & 4) {
+                            mbar_arrive(rfull_bar(s));
+                            ++armed;
+                            if (++s == S) { s = 0; ph ^= 1u; }
+                            continue;
+                        }
+                        uint32_t bytes = kPacked * PairQ::kRawOp;
+                        if (QA) bytes += load_exps(q.a_exps, q.a_nblk, q.a_rows, p.a_mn, m0, kb, ea, rfull_bar(s));
+                        if (QB) bytes += load_exps(q.b_exps, q.b_nblk, q.b_rows, p.b_mn, n0, kb, eb, rfull_bar(s));
+                        mbar_expect_tx(rfull_bar(s), bytes);
                         // payload bytes: 3/4 byte per value along the contiguous dimension
                         if (QA) {
                             if (!p.a_mn) tma_load_2d(ra, &map_a, rfull_bar(s), k0 * 3 / 4, m0);      // box {48 B, 128 rows}
@@ -205,7 +247,7 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             if (kPacked && !ok) {
                 for (int back = 0; back < S && back < armed; ++back) {
                     const int idx = armed - 1 - back;
-                    mbar_wait(rfull_bar(idx % S), (uint32_t)((idx / S) & 1), 7);
+                    acp::mbar_wait_quiet(rfull_bar(idx % S), (uint32_t)((idx / S) & 1), kSpinLimit);
                 }
             }
         }
@@ -263,97 +305,74 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             if (acc == 0) aph ^= 1u;
         }
     } else if (kPacked) {
-        // ------------------------------------------------------------------ decode (warps 6..13, both CTAs)
-        const int dt = threadIdx.x - 6 * 32;                 // 0..255: block of the operand tile
-        const uint32_t lut_lo = lut + 4u * lane, lut_hi = lut_lo + 64u * 32u * 4u;
-        // geometry of this thread's block inside a tile, per operand layout
-        //   K-major:  tile row r = dt >> 1 (output index), block j = dt & 1 of the 64 contraction values
-        //   MN-major: k-row r = dt >> 2, block b = dt & 3 of the 128 output values
-        auto dst_off = [&](bool mn) -> uint32_t {            // byte offset of piece 0's row inside the operand's stage half
-            return mn ? (uint32_t)((dt & 3) >> 1) * 8192u + (uint32_t)(dt >> 2) * 128u : (uint32_t)(dt >> 1) * 128u;
+        // ------------------------------------------------------------------ decode (warps 6..21, both CTAs)
+        // thread dt owns half-block dt of the 512 half-blocks (16 values each) of a packed operand tile:
+        // block = dt >> 1 in row-major order of the raw tile, half = dt & 1
+        const int dt = threadIdx.x - 6 * 32;
+        const int blk = dt >> 1, half = dt & 1;
+        struct Geo { uint32_t raw, exp, dst0, dst1; int row, col; };
+        auto geo = [&](bool mn) -> Geo {
+            Geo g;
+            g.raw = (uint32_t)blk * 24u + (uint32_t)half * 12u;
+            if (!mn) {               // tile row r = blk >> 1 (output index), j = blk & 1 of the two contraction blocks
+                const uint32_t r = (uint32_t)blk >> 1, j = (uint32_t)blk & 1u;
+                g.exp = (uint32_t)blk;
+                const uint32_t p0 = 4u * j + 2u * (uint32_t)half;
+                g.dst0 = r * 128u + (((p0) ^ (r & 7u)) << 4);
+                g.dst1 = r * 128u + (((p0 + 1u) ^ (r & 7u)) << 4);
+                g.row = (int)r; g.col = (int)j;
+            } else {                 // k-row r = blk >> 2, b = blk & 3 of the four output blocks
+                const uint32_t r = (uint32_t)blk >> 2, b = (uint32_t)blk & 3u;
+                g.exp = (b >> 1) * 128u + r * 2u + (b & 1u);
+                const uint32_t p0 = 4u * (b & 1u) + 2u * (uint32_t)half;
+                g.dst0 = (b >> 1) * 8192u + r * 128u + (((p0) ^ (r & 7u)) << 4);
+                g.dst1 = (b >> 1) * 8192u + r * 128u + (((p0 + 1u) ^ (r & 7u)) << 4);
+                g.row = (int)r; g.col = (int)b;
+            }
+            return g;
         };
-        auto piece0 = [&](bool mn) -> uint32_t { return mn ? 4u * ((uint32_t)dt & 1u) : 4u * ((uint32_t)dt & 1u); };
-        auto swz = [&](bool mn) -> uint32_t { return mn ? ((uint32_t)(dt >> 2) & 7u) : ((uint32_t)(dt >> 1) & 7u); };
-        auto raw_off = [&](bool mn) -> uint32_t { return (uint32_t)dt * 24u; };    // both layouts: block dt of the tile in row-major order
-        const uint32_t a_dst = dst_off(p.a_mn), a_p0 = piece0(p.a_mn), a_sw = swz(p.a_mn);
-        const uint32_t b_dst = dst_off(p.b_mn), b_p0 = piece0(p.b_mn), b_sw = swz(p.b_mn);
-        // exponent of this thread's block for (tile origin o0 along the output index, k-block kb); 0x100 = outside
-        auto fetch = [&](const uint8_t *exps, int nblk, int rows, bool mn, int o0, int kb) -> uint32_t {
-            int row, blk;
-            if (!mn) { row = o0 + (dt >> 1); blk = 2 * kb + (dt & 1); }
-            else { row = kb * BK + (dt >> 2); blk = (o0 >> 5) + (dt & 3); }
-            if (row >= rows || blk >= nblk) return 0x100u;
-            return (uint32_t)__ldg(exps + (long long)row * nblk + blk);
+        const Geo ga = geo(p.a_mn), gb = geo(p.b_mn);
+        // is this thread's block inside the operand?  K-major: row o0 + row < rows, block 2 kb + col < nblk;
+        // MN-major: k-row kb * 64 + row < rows, block o0 / 32 + col < nblk
+        auto inside = [&](const Geo &g, bool mn, int rows, int nblk, int o0, int kb) -> bool {
+            return mn ? (kb * BK + g.row < rows && (o0 >> 5) + g.col < nblk) : (o0 + g.row < rows && 2 * kb + g.col < nblk);
+        };
+        auto put = [&](uint32_t stage_half, const Geo &g, bool valid, uint32_t raw_op, uint32_t exp_op) {
+            uint32_t o[8];
+            if (valid && !(q.dbg & 1)) {
+                uint32_t se;
+                asm volatile("ld.shared.u8 %0, [%1];" : "=r"(se) : "r"(exp_op + g.exp));
+                decode_half_block(raw_op + g.raw, se, lut, o);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = 0u;
+            }
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage_half + g.dst0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage_half + g.dst1), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
         };
         int s = 0;
         uint32_t ph = 0;
         bool ok = true;
-        uint32_t ea = 0x100u, eb = 0x100u;
-        bool have = false;
         for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
             const int m0 = (t / tiles_n) * 256 + (int)rank * 128;
             const int n0 = (t % tiles_n) * TN + (int)rank * 128;
-            if (!have) {
-                if (QA) ea = fetch(q.a_exps, q.a_nblk, q.a_rows, p.a_mn, m0, 0);
-                if (QB) eb = fetch(q.b_exps, q.b_nblk, q.b_rows, p.b_mn, n0, 0);
-                have = true;
-            }
             for (int kb = 0; kb < total_kb; ++kb) {
-                // exponents of the next k-block (or of the next tile's first one), in flight while this one is decoded
-                uint32_t na = 0x100u, nb = 0x100u;
-                {
-                    int nt = t, nkb = kb + 1;
-                    if (nkb == total_kb) { nt = t + num_clusters; nkb = 0; }
-                    if (nt < num_tiles) {
-                        const int nm0 = (nt / tiles_n) * 256 + (int)rank * 128;
-                        const int nn0 = (nt % tiles_n) * TN + (int)rank * 128;
-                        if (QA) na = fetch(q.a_exps, q.a_nblk, q.a_rows, p.a_mn, nm0, nkb);
-                        if (QB) nb = fetch(q.b_exps, q.b_nblk, q.b_rows, p.b_mn, nn0, nkb);
-                    }
-                }
-                if (!mbar_wait(rfull_bar(s), ph, 5)) { ok = false; break; }
-                if (!mbar_wait(empty_bar(s), ph ^ 1u, 6)) { ok = false; break; }
+                // one lane polls, the warp follows
+                int go = 1;
+                if (lane == 0) go = (mbar_wait(rfull_bar(s), ph, 5) && mbar_wait(empty_bar(s), ph ^ 1u, 6)) ? 1 : 0;
+                go = __shfl_sync(0xFFFFFFFFu, go, 0);
+                if (!go) { ok = false; break; }
                 const uint32_t sa = base + s * kStage, sb = sa + kA2;
                 const uint32_t ra = raw0 + s * kRaw, rb = ra + PairQ::kRawOp;
-                if (QA) {
-                    uint32_t o[16];
-                    if (ea < 0x100u) decode_block(ra + raw_off(p.a_mn), ea, lut_lo, lut_hi, o);
-                    else {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) o[i] = 0u;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t addr = sa + a_dst + (((a_p0 + i) ^ a_sw) << 4);
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[4 * i]), "r"(o[4 * i + 1]),
-                                     "r"(o[4 * i + 2]), "r"(o[4 * i + 3]) : "memory");
-                    }
-                }
-                if (QB) {
-                    uint32_t o[16];
-                    if (eb < 0x100u) decode_block(rb + raw_off(p.b_mn), eb, lut_lo, lut_hi, o);
-                    else {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) o[i] = 0u;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t addr = sb + b_dst + (((b_p0 + i) ^ b_sw) << 4);
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[4 * i]), "r"(o[4 * i + 1]),
-                                     "r"(o[4 * i + 2]), "r"(o[4 * i + 3]) : "memory");
-                    }
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // decoded tile visible to the tensor core's reads
+                const uint32_t ea = ra + 2 * PairQ::kRawOp, eb = ea + PairQ::kExpOp;
+                if (QA) put(sa, ga, inside(ga, p.a_mn, q.a_rows, q.a_nblk, m0, kb), ra, ea);
+                if (QB) put(sb, gb, inside(gb, p.b_mn, q.b_rows, q.b_nblk, n0, kb), rb, eb);
+                if (!(q.dbg & 2)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // decoded tile visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) {
-                    const uint32_t lead_full = map_to_cta(full_bar(s), 0);
-#pragma unroll
-                    for (int i = 0; i < kPacked; ++i) {
-                        mbar_arrive_release_cluster(lead_full);
-                        mbar_arrive(rempty_bar(s));
-                    }
+                    mbar_arrive_release_cluster(map_to_cta(full_bar(s), 0));
+                    mbar_arrive(rempty_bar(s));
                 }
-                ea = na; eb = nb;
                 if (++s == S) { s = 0; ph ^= 1u; }
             }
         }

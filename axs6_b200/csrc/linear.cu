@@ -272,9 +272,12 @@ static int column_sums(const void *g, int dtype, float *out, float *partial, int
 
 static int64_t round_up8(int64_t v) { return (v + 7) / 8 * 8; }
 // A (rows, cols) operand held as codes: the payload plane (rows * cols/32 * 24 bytes, rounded up to 256) followed by
-// the exponent plane (rows * cols/32 bytes).
+// the exponent plane (stored by pairs of blocks: ceil(nblk / 2) * rows * 2 bytes).
 static int64_t packed_exps_offset(int64_t rows, int64_t cols) { return (rows * ((cols + 31) / 32) * 24 + 255) / 256 * 256; }
-static int64_t packed_bytes(int64_t rows, int64_t cols) { return packed_exps_offset(rows, cols) + rows * ((cols + 31) / 32); }
+static int64_t packed_bytes(int64_t rows, int64_t cols)
+{
+    return packed_exps_offset(rows, cols) + ((((cols + 31) / 32) + 1) / 2) * rows * 2;
+}
 static int pack_operand(const void *x, int dtype, int64_t rows, int64_t cols, int64_t ld, int rounding, uint64_t seed,
                         uint64_t offset, const float *noise, void *ws, axs6_stream_t stream)
 {
@@ -345,7 +348,7 @@ AXS6_API int axs6_linear_fwd(const void *x, int x_dtype, int64_t ldx, const void
         // quantise on load: both operands go to HBM as 6-bit codes (0.78 bytes per value) and are decoded to bf16
         // inside the GEMM; xq (codes) is what backward keeps
         if ((flags & AXS6_LINEAR_COMPUTE_TF32) || !(flags & AXS6_LINEAR_QUANTIZE_INPUT) || block != 32 || grid != AXS6_GRID_NF5 ||
-            K % 64 || N % 64)
+            K % 64 || N % 64 || M % 8)
             return AXS6_ERR_UNSUPPORTED;
         int rcp = pack_operand(w, w_dtype, N, K, ldw, AXS6_ROUND_NEAREST, 0, 0, nullptr, wq, stream);
         if (rcp) return rcp;
@@ -471,7 +474,7 @@ AXS6_API int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void
     }
     if (flags & AXS6_LINEAR_OPERANDS_PACKED) {
         if ((flags & (AXS6_LINEAR_COMPUTE_TF32 | AXS6_LINEAR_BIAS_FROM_QUANTIZED)) || !(flags & AXS6_LINEAR_QUANTIZE_GRAD) ||
-            block != 32 || grid != AXS6_GRID_NF5 || K % 64 || N % 64)
+            block != 32 || grid != AXS6_GRID_NF5 || K % 64 || N % 64 || M % 8)
             return AXS6_ERR_UNSUPPORTED;
         if (!(flags & AXS6_LINEAR_REUSE_GQ)) {
             rc = pack_operand(g, g_dtype, M, N, ldg, AXS6_ROUND_STOCHASTIC, seed, offset, noise, gq, stream);

@@ -46,6 +46,24 @@ def philox_advance(delta: int = 1 << 40, reset: bool = False, device=None) -> No
     _lib.check("axs6_philox_advance", st)
 
 
+def philox_epoch(device=None) -> int:
+    """The device-resident epoch that ``philox_advance`` maintains (one 8-byte read; synchronises the device)."""
+    import ctypes
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    out = ctypes.c_uint64(0)
+    with _on(dev):
+        st = _lib.load().axs6_philox_epoch(ctypes.byref(out))
+    _lib.check("axs6_philox_epoch", st)
+    return int(out.value)
+
+
+def set_philox_epoch(value: int, device=None) -> None:
+    """Restore a saved epoch: reset, then advance by ``value``."""
+    philox_advance(0, reset=True, device=device)
+    if value:
+        philox_advance(int(value), device=device)
+
+
 def _rounding(rounding: str) -> int:
     if rounding == "nearest":
         return ROUND_NEAREST
@@ -385,7 +403,8 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None
 
 class PackedOperand:
     """A matrix held as AXS-6 codes in the split layout: ``codes`` uint8 (rows, cols // 32, 24), ``exps`` uint8
-    (rows, cols // 32); NF5 grid, blocks of 32 along the columns."""
+    (cols // 64, rows, 2) -- the exponent of block b of row r is ``exps[b // 2, r, b % 2]``; NF5 grid, blocks of 32
+    along the columns."""
 
     def __init__(self, codes: torch.Tensor, exps: torch.Tensor, rows: int, cols: int):
         self.codes, self.exps, self.rows, self.cols = codes, exps, rows, cols
@@ -402,7 +421,7 @@ def pack_split(x: torch.Tensor, rounding: str = "nearest", via_bf16: bool = Fals
     assert x.dim() == 2 and x.shape[1] % 64 == 0, "pack_split takes a 2-D tensor whose last dimension is a multiple of 64"
     rows, cols = x.shape
     codes = torch.empty((rows, cols // 32, 24), dtype=torch.uint8, device=x.device)
-    exps = torch.empty((rows, cols // 32), dtype=torch.uint8, device=x.device)
+    exps = torch.empty((cols // 64, rows, 2), dtype=torch.uint8, device=x.device)
     x2, _, _, ldx = _as_rows(x)
     rnd = _rounding(rounding)
     seed, off, nz = 0, 0, None
@@ -499,7 +518,7 @@ def _ws_bytes(what: int, M: int, N: int, K: int) -> int:
     if what in (8, 9, 10):
         rows, cols = {8: (M, K), 9: (N, K), 10: (M, N)}[what]
         nblk = (cols + 31) // 32
-        return (rows * nblk * 24 + 255) // 256 * 256 + rows * nblk
+        return (rows * nblk * 24 + 255) // 256 * 256 + (nblk + 1) // 2 * rows * 2
     raise ValueError(what)
 
 

@@ -56,8 +56,8 @@ class _AXSLinearBF16Function(torch.autograd.Function):
         b32 = None
         if bias is not None:                      # F.linear sees bf16(bias): rounded inside the GEMM epilogue
             b32 = bias if (bias.dtype == torch.float32 and bias.is_contiguous()) else bias.float().contiguous()
-        packed = PACKED_OPERANDS and ops.linear_packed_ok(weight.shape[0], weight.shape[1], block_size, bool(quantize_input),
-                                                          bool(quantize_grad))
+        packed = PACKED_OPERANDS and x2.shape[0] % 8 == 0 and ops.linear_packed_ok(
+            weight.shape[0], weight.shape[1], block_size, bool(quantize_input), bool(quantize_grad))
         y, xq, wq = ops.linear_fwd(x2, w, b32, block_size, ops.GRID_NF5, bool(quantize_input), torch.bfloat16,
                                    bias_via_bf16=True, return_wq=True, packed=packed)
         ctx.packed = packed

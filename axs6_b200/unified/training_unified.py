@@ -4,8 +4,11 @@
 Same constructor arguments, ``training_step`` result keys, checkpoint contents and ``stats`` as the
 reference.  Two things are done the GPU way: the gradients are unscaled and checked for inf/NaN by ONE
 fused multi-tensor kernel with a single host read (the reference divides and scans parameter by parameter,
-with two host syncs per parameter), and the checkpoint also carries this library's Philox counter, so a
-resumed run continues the stochastic-rounding stream where the saved one stopped.
+with two host syncs per parameter), and the checkpoint also carries this library's Philox counter (the
+host-side offset and the device-resident epoch that CUDA-graph replays advance), so a resumed run continues
+the stochastic-rounding stream where the saved one stopped.  The fused unscale multiplies by ``1 / loss_scale``
+where the reference divides by ``loss_scale``: identical for the power-of-two scales the pipeline itself
+produces (initial 2^k, doubling / halving), up to one ulp for any other scale a caller sets.
 """
 from __future__ import annotations
 
@@ -156,7 +159,9 @@ class AXSTrainingPipelineUnified:
             "warmup_steps": self.warmup_steps,
             "rng": {"python": torch.random.get_rng_state(),
                     "cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None,
-                    "axs6_philox_offset": ops.philox_offset()},
+                    "axs6_philox_offset": ops.philox_offset(),
+                    # the device-resident addend that CUDA-graph replays advance (zero unless philox_advance is used)
+                    "axs6_philox_epoch": ops.philox_epoch() if torch.cuda.is_available() else 0},
         }
         if self.scheduler is not None:
             state["scheduler"] = self.scheduler.state_dict()
@@ -188,6 +193,8 @@ class AXSTrainingPipelineUnified:
             torch.cuda.set_rng_state(rng["cuda"].cpu())
         if "axs6_philox_offset" in rng:
             ops.reset_philox(int(rng["axs6_philox_offset"]))
+        if "axs6_philox_epoch" in rng and torch.cuda.is_available():
+            ops.set_philox_epoch(int(rng["axs6_philox_epoch"]))
         logger.info("Loaded checkpoint from %s (step %d)", path, self._total_steps)
         return state.get("extra", {})
 

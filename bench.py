@@ -243,11 +243,13 @@ def cpu_baseline(x) -> dict:
 # --------------------------------------------------------------------------------------- our arm
 WORKLOAD = f"NF5 fake-quantize {ROWS}x{COLS} fp32, block {BLOCK}, nearest (fake-quantize sweep, largest size)"
 
-# DRAM bytes (read + write) of ONE launch of the headline kernel, from an ncu capture of this workload's launch
-# (profiles/fq_vec_kernel_f32_32768x8192.md); None where no capture of that shard size exists.
-TRAFFIC_BYTES_PER_LAUNCH: dict[int, float] = {}
-TRAFFIC_CAPTURED = {"rows": 8192, "cols": 8192, "dram_bytes": 486.1e6, "algorithmic_bytes": 8192 * 8192 * 8,
-                    "source": "profiles/fq_vec_kernel_f32_8192x8192.md"}
+# DRAM bytes (read + write) of ONE launch of the headline kernel, by shard rows, each from an ncu capture of a launch of
+# exactly that size with the two DRAM byte counters only (profiles/fq_vec_kernel_f32_32768x8192.md); None where no
+# capture of that shard size exists.
+TRAFFIC_BYTES_PER_LAUNCH: dict[int, float] = {32768: 2.09e9, 8192: 485.5e6}
+TRAFFIC_CAPTURED = {"rows": 32768, "cols": 8192, "dram_bytes_read": 1.07e9, "dram_bytes_write": 1.02e9,
+                    "algorithmic_bytes": 32768 * 8192 * 8, "passes": 1,
+                    "source": "profiles/fq_vec_kernel_f32_32768x8192.md"}
 
 
 def run_ours(args, rank: int, local_rank: int, world: int) -> None:

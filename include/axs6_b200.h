@@ -36,10 +36,12 @@ enum { AXS6_LAYOUT_PLANES = 0, /* AXSTensor planes: u8 exponent (rows,nblk), u8 
        AXS6_LAYOUT_SPEC = 2,   /* per block: u16 LE (exponent<<2 | config 0) + 6-bit codes,
                                   26 B for block 32 (axs/core.py:97-118, FORMAT_SPEC.md:29-48) */
        AXS6_LAYOUT_SPLIT = 3 };/* the bytes of a WIRE record in two planes: payloads (rows, nblk, 3*block/4)
-                                  and exponents u8 (rows, nblk).  Rows of the payload plane start 16-byte
-                                  aligned when cols is a multiple of 64, which is what lets the TMA unit
-                                  fetch operand tiles of packed codes for axs6_gemm_packed.  (No
-                                  counterpart in the reference; same 25 bytes per block of 32.)          */
+                                  and exponents u8 stored by pairs of blocks, (ceil(nblk/2), rows, 2): the
+                                  exponent of block b of row r is byte ((b/2)*rows + r)*2 + b%2.  Rows of the
+                                  payload plane start 16-byte aligned when cols is a multiple of 64 and the
+                                  exponents of an operand tile are contiguous runs, which is what lets the
+                                  TMA unit fetch tiles of packed codes for axs6_gemm_packed.  (No counterpart
+                                  in the reference; same 25 bytes per block of 32.)                         */
 
 /* flags */
 #define AXS6_FLAG_INPUT_VIA_BF16 1u /* round an fp32 input to bf16 before quantising: the
@@ -70,8 +72,8 @@ enum { AXS6_LAYOUT_PLANES = 0, /* AXSTensor planes: u8 exponent (rows,nblk), u8 
 #define AXS6_LINEAR_OPERANDS_PACKED 128u /* quantise on load: xq / wq / gq hold 6-bit codes (payload plane, then the exponent
                                          plane at the next 256-byte boundary; workspace codes 8, 9, 10) instead of bf16,
                                          and the GEMMs decode them in shared memory (axs6_gemm_packed).  Needs
-                                         AXS6_LINEAR_QUANTIZE_INPUT / _GRAD, NF5, block 32, K and N multiples of 64
-                                         (AXS6_ERR_UNSUPPORTED otherwise).  The saved activation shrinks from 2 to
+                                         AXS6_LINEAR_QUANTIZE_INPUT / _GRAD, NF5, block 32, K and N multiples of 64, M a
+                                         multiple of 8 (AXS6_ERR_UNSUPPORTED otherwise).  The saved activation shrinks from 2 to
                                          0.78 bytes per value.  Equal to the bf16 path except where an operand holds
                                          an exact zero, which codes cannot express (see axs6_gemm_packed)        */
 
@@ -133,6 +135,10 @@ int axs6_tune(int key, int64_t value);
  * counterpart in the reference, which draws a new seed on the host for every launch.) */
 int axs6_philox_advance(uint64_t delta, int reset, axs6_stream_t stream);
 
+/* Reads the current device's epoch into *epoch (synchronises the device: meant for checkpoints, which store it next
+ * to the host-side offset and restore it with axs6_philox_advance(0, 1, s) followed by axs6_philox_advance(value, 0, s)). */
+int axs6_philox_epoch(uint64_t *epoch);
+
 /* Fake-quantise: y = dequantise(quantise(x)) in one pass.
  * Replaces fused_fake_quantize (axs/unified/quantize_unified.py:121-204), the Triton
  * launcher triton_fused_fake_quantize (axs/unified/triton_kernels.py:295-370) and, with
@@ -162,7 +168,7 @@ int axs6_fq_with_noise(const void *x, void *y, int in_dtype, int out_dtype,
  * layout PLANES: out0 = exponents u8 (rows*nblk), out1 = signs u8 (rows*nblk*block),
  *                out2 = magnitudes u8 (rows*nblk*block).
  * layout WIRE/SPEC: out0 = rows*nblk records of (1|2) + block*3/4 bytes; out1/out2 unused.
- * layout SPLIT: out0 = rows*nblk payloads of block*3/4 bytes, out1 = rows*nblk exponent bytes.
+ * layout SPLIT: out0 = rows*nblk payloads of block*3/4 bytes, out1 = ceil(nblk/2)*rows*2 exponent bytes.
  * `noise` (may be NULL) as in axs6_fq_with_noise; if NULL and rounding is stochastic the
  * Philox stream (seed, offset) is used. */
 int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, int64_t ldx,
@@ -222,8 +228,8 @@ int64_t axs6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int c_dtype);
  * HBM as bf16.  An operand with a non-null exponent plane (`a_exps` / `b_exps`) is packed: its pointer is the
  * payload plane of AXS6_LAYOUT_SPLIT (NF5 grid, block 32, blocks along the operand's contiguous dimension,
  * as written by axs6_pack for the stored matrix: (M,K) or (K,M) for A, (N,K) or (K,N) for B) and its
- * leading dimension is ignored; its contiguous extent must be a multiple of 64 (AXS6_ERR_UNSUPPORTED
- * otherwise).  An operand with a null exponent plane is bf16 as in axs6_gemm_bf16.  At least one operand
+ * leading dimension is ignored; its contiguous extent must be a multiple of 64 and its row count a multiple
+ * of 8 (AXS6_ERR_UNSUPPORTED otherwise), both planes 16-byte aligned.  An operand with a null exponent plane is bf16 as in axs6_gemm_bf16.  At least one operand
  * must be packed.  The decoded values are bit-identical to axs6_unpack(..., AXS6_BF16) of the same codes;
  * note that codes cannot express an exact zero (axs/unified/quantize_unified.py:273, :300-302: a zero
  * input packs to the smallest level), which is where this differs from fake-quantising the operand. */

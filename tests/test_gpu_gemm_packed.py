@@ -49,7 +49,8 @@ def test_split_layout_matches_oracle_and_wire(rows, cols, dtype):
     xo = xt.float().cpu().numpy()
     se, sg, mg = oracle.quantize(xo, 32, oracle.GRID_NF5)
     wire = oracle.pack_bytes(se, sg, mg, oracle.LAYOUT_WIRE).reshape(rows, cols // 32, 25)
-    assert np.array_equal(pk.exps.cpu().numpy(), wire[:, :, 0])
+    assert pk.exps.shape == (cols // 64, rows, 2)            # exponents by pairs of blocks: [b // 2, row, b % 2]
+    assert np.array_equal(pk.exps.permute(1, 0, 2).reshape(rows, cols // 32).cpu().numpy(), wire[:, :, 0])
     assert np.array_equal(pk.codes.cpu().numpy(), wire[:, :, 1:])
     for odt in (torch.float32, torch.bfloat16):
         back = ops.unpack_split(pk, odt)
@@ -64,7 +65,8 @@ def test_split_layout_stochastic_with_supplied_draws():
     pk = ops.pack_split(torch.from_numpy(x).cuda(), rounding="stochastic", noise=torch.from_numpy(u).cuda())
     se, sg, mg = oracle.quantize(x, 32, oracle.GRID_NF5, u.reshape(-1))
     wire = oracle.pack_bytes(se, sg, mg, oracle.LAYOUT_WIRE).reshape(64, 8, 25)
-    assert np.array_equal(pk.exps.cpu().numpy(), wire[:, :, 0]) and np.array_equal(pk.codes.cpu().numpy(), wire[:, :, 1:])
+    assert np.array_equal(pk.exps.permute(1, 0, 2).reshape(64, 8).cpu().numpy(), wire[:, :, 0])
+    assert np.array_equal(pk.codes.cpu().numpy(), wire[:, :, 1:])
 
 
 def _operands(M, N, K, a_mn, b_mn, seed):
@@ -141,8 +143,9 @@ def test_gemm_packed_argument_checks():
     p = z.data_ptr()
     # nothing packed
     assert lib.axs6_gemm_packed(p, None, 64, p, None, 64, c.data_ptr(), None, 64, 64, 64, 64, 0, 0, 0, st) == -1
-    # contraction length of a K-major packed operand not a multiple of 64
+    # contraction length of a K-major packed operand not a multiple of 64; row count not a multiple of 8
     assert lib.axs6_gemm_packed(p, p, 0, p, p, 0, c.data_ptr(), None, 64, 64, 96, 64, 0, 0, 0, st) == -6
+    assert lib.axs6_gemm_packed(p, p, 0, p, p, 0, c.data_ptr(), None, 60, 64, 64, 64, 0, 0, 0, st) == -6
     # misaligned payload plane
     assert lib.axs6_gemm_packed(p + 8, p, 0, p, p, 0, c.data_ptr(), None, 64, 64, 64, 64, 0, 0, 0, st) == -2
 

@@ -401,6 +401,33 @@ def test_philox_epoch_changes_draws_and_reset_restores_them():
     assert torch.equal(a, c) and not torch.equal(a, b)
 
 
+def test_philox_epoch_can_be_read_and_restored():
+    """What a checkpoint does: read the device-resident epoch, later put it back; the draws continue where they were."""
+    x = torch.randn(64, 256, device="cuda")
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+
+    def run():
+        y = torch.empty_like(x)
+        assert lib.axs6_fq(x.data_ptr(), y.data_ptr(), 0, 0, 64, 256, 256, 256, 32, 1, 1, 0, 7, 0, st) == 0
+        return y
+
+    try:
+        assert ops.philox_epoch() == 0
+        ops.philox_advance(12345)
+        ops.philox_advance(1 << 40)
+        saved = ops.philox_epoch()
+        assert saved == 12345 + (1 << 40)
+        want = run()
+        ops.philox_advance(0, reset=True)
+        assert ops.philox_epoch() == 0
+        ops.set_philox_epoch(saved)
+        assert ops.philox_epoch() == saved
+        assert torch.equal(run(), want)
+    finally:
+        ops.philox_advance(0, reset=True)
+
+
 @pytest.mark.parametrize("layout", [ops.LAYOUT_WIRE, ops.LAYOUT_SPEC])
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 @pytest.mark.parametrize("shape", [(1, 32), (255, 32), (257, 32), (3, 96), (777, 1056), (2048, 4096)])
