@@ -380,7 +380,7 @@ static int launch_codec(K kernel, const CodecArgs &a, int64_t items_per_cta, int
     const int64_t resident = (int64_t)d.sms * per_sm;
     if (ctas > resident) ctas = resident;
     if (ctas < 1) ctas = 1;
-    const bool launched = launch_overlapped(kernel, (unsigned)ctas, kThreads, 0, stream, a) == cudaSuccess;
+    const bool launched = launch_overlapped(false, kernel, (unsigned)ctas, kThreads, 0, stream, a) == cudaSuccess;
     count_launch();
     return launched ? check_launch() : AXS6_ERR_LAUNCH;
 }
@@ -623,6 +623,7 @@ namespace bulk {
 
 using namespace acp;
 
+constexpr int64_t kOverlapBlocks = 1ll << 21;     // launches of up to this many blocks ask for programmatic dependent launch
 constexpr int kStages = 2;                        // with 4 CTAs per SM: 128 KB of loads in flight
 constexpr int kStageBytes = kFastBlocks * 64;
 constexpr uint32_t kWaitLimit = 1u << 22;
@@ -646,6 +647,7 @@ __global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_bulk_kernel(con
     __shared__ __align__(16) uint8_t table[kKeyLimit + 16];   // static: its address is an immediate of every lookup
     const uint32_t bar0 = smem_u32(base);
     const int tid = threadIdx.x;
+    pdl_launch_dependents();                               // the next launch may take up residence now (it waits in pdl_wait)
     const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
     const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     build_key_table(table, tid, kFastBlocks);              // module constants: may run while the previous kernel drains
@@ -675,7 +677,6 @@ __global__ void __launch_bounds__(kFastBlocks) pack_bf16_nf5_b32_bulk_kernel(con
     int s = 0;
     uint32_t ph = 0;
     for (int64_t k = 0; k < nk; ++k) {
-        if (k + 1 == nk) pdl_launch_dependents();                             // last tile of this CTA: the next kernel may move in
         const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
         const int64_t b = grp * kFastBlocks + tid;
         uint8_t *ost = out0 + (k & 1) * kOut;
@@ -759,8 +760,8 @@ static int launch_pack_bulk(const void *x, void *out, int64_t nblocks, int hdr, 
     if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&pack_bf16_nf5_b32_bulk_kernel<1>), smem_bytes<1>()) ||
         !ensure_dynamic_smem(reinterpret_cast<const void *>(&pack_bf16_nf5_b32_bulk_kernel<2>), smem_bytes<2>()))
         return AXS6_ERR_LAUNCH;
-    const cudaError_t le = hdr == 1 ? launch_overlapped(pack_bf16_nf5_b32_bulk_kernel<1>, (unsigned)ctas, kFastBlocks, smem_bytes<1>(), st, map, o, nblocks)
-                                    : launch_overlapped(pack_bf16_nf5_b32_bulk_kernel<2>, (unsigned)ctas, kFastBlocks, smem_bytes<2>(), st, map, o, nblocks);
+    const cudaError_t le = hdr == 1 ? launch_overlapped(nblocks <= kOverlapBlocks, pack_bf16_nf5_b32_bulk_kernel<1>, (unsigned)ctas, kFastBlocks, smem_bytes<1>(), st, map, o, nblocks)
+                                    : launch_overlapped(nblocks <= kOverlapBlocks, pack_bf16_nf5_b32_bulk_kernel<2>, (unsigned)ctas, kFastBlocks, smem_bytes<2>(), st, map, o, nblocks);
     count_launch();
     return le == cudaSuccess ? check_launch() : AXS6_ERR_LAUNCH;
 }
@@ -788,6 +789,7 @@ __global__ void __launch_bounds__(kFastBlocks) pack_f32_nf5_b32_bulk_kernel(cons
     uint8_t *out0 = in0 + kStages * kF32Tile;
     const uint32_t bar0 = smem_u32(base);
     const int tid = threadIdx.x;
+    pdl_launch_dependents();                               // the next launch may take up residence now (it waits in pdl_wait)
     const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
     const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     build_reverse_lut(rev);                                 // module constants: may run while the previous kernel drains
@@ -815,7 +817,6 @@ __global__ void __launch_bounds__(kFastBlocks) pack_f32_nf5_b32_bulk_kernel(cons
     int s = 0;
     uint32_t ph = 0;
     for (int64_t k = 0; k < nk; ++k) {
-        if (k + 1 == nk) pdl_launch_dependents();                             // last tile of this CTA: the next kernel may move in
         const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
         const int64_t b = grp * kFastBlocks + tid;
         uint8_t *ost = out0 + (k & 1) * kOut;
@@ -923,8 +924,8 @@ static int launch_pack_f32_bulk(const void *x, void *out, int64_t nblocks, int h
         !ensure_dynamic_smem(reinterpret_cast<const void *>(&pack_f32_nf5_b32_bulk_kernel<2>), pack_f32_smem_bytes<2>()))
         return AXS6_ERR_LAUNCH;
     uint8_t *o = static_cast<uint8_t *>(out);
-    const cudaError_t le = hdr == 1 ? launch_overlapped(pack_f32_nf5_b32_bulk_kernel<1>, (unsigned)ctas, kFastBlocks, pack_f32_smem_bytes<1>(), st, map, o, nblocks)
-                                    : launch_overlapped(pack_f32_nf5_b32_bulk_kernel<2>, (unsigned)ctas, kFastBlocks, pack_f32_smem_bytes<2>(), st, map, o, nblocks);
+    const cudaError_t le = hdr == 1 ? launch_overlapped(nblocks <= kOverlapBlocks, pack_f32_nf5_b32_bulk_kernel<1>, (unsigned)ctas, kFastBlocks, pack_f32_smem_bytes<1>(), st, map, o, nblocks)
+                                    : launch_overlapped(nblocks <= kOverlapBlocks, pack_f32_nf5_b32_bulk_kernel<2>, (unsigned)ctas, kFastBlocks, pack_f32_smem_bytes<2>(), st, map, o, nblocks);
     count_launch();
     return le == cudaSuccess ? check_launch() : AXS6_ERR_LAUNCH;
 }
@@ -967,6 +968,7 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
     uint8_t *in0 = tile0 + 2 * kTile;
     const uint32_t bar0 = smem_u32(base);
     const int tid = threadIdx.x;
+    pdl_launch_dependents();                               // the next launch may take up residence now (it waits in pdl_wait)
     const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
     const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     if (tid < 64) {
@@ -1009,7 +1011,6 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
     int s = 0;
     uint32_t ph = 0;
     for (int64_t k = 0; k < nk; ++k) {
-        if (k + 1 == nk) pdl_launch_dependents();                             // last tile of this CTA: the next kernel may move in
         const int64_t grp = (int64_t)blockIdx.x + k * (int64_t)gridDim.x;
         const int64_t b = grp * kFastBlocks + tid;
         const int64_t nb = nblocks - grp * kFastBlocks;
@@ -1136,8 +1137,8 @@ static int launch_unpack_bulk(const void *in, void *y, int64_t nblocks, int hdr,
         !ensure_dynamic_smem(reinterpret_cast<const void *>(&unpack_nf5_b32_bulk_kernel<Tout, 2>), unpack_smem_bytes<Tout, 2>()))
         return AXS6_ERR_LAUNCH;
     const uint8_t *src = static_cast<const uint8_t *>(in);
-    const cudaError_t le = hdr == 1 ? launch_overlapped(unpack_nf5_b32_bulk_kernel<Tout, 1>, (unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 1>(), st, map, src, nblocks)
-                                    : launch_overlapped(unpack_nf5_b32_bulk_kernel<Tout, 2>, (unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 2>(), st, map, src, nblocks);
+    const cudaError_t le = hdr == 1 ? launch_overlapped(nblocks <= kOverlapBlocks, unpack_nf5_b32_bulk_kernel<Tout, 1>, (unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 1>(), st, map, src, nblocks)
+                                    : launch_overlapped(nblocks <= kOverlapBlocks, unpack_nf5_b32_bulk_kernel<Tout, 2>, (unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 2>(), st, map, src, nblocks);
     count_launch();
     return le == cudaSuccess ? check_launch() : AXS6_ERR_LAUNCH;
 }

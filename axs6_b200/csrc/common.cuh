@@ -39,21 +39,21 @@ int gemm_packed_launch(const void *a, const void *a_exps, int64_t lda, const voi
                        const float *bias, int64_t M, int64_t N, int64_t K, int64_t ldc, int a_mn, int b_mn, int c_dtype,
                        int bias_via_bf16, cudaStream_t stream);
 
-// Programmatic dependent launch.  A kernel launched with launch_overlapped() may become resident while the kernel
-// before it on the stream is still draining: its CTAs run their prologue (barrier initialisation, tables copied
-// from the module image into shared memory) and then block in pdl_wait() until that earlier kernel has completed
-// and its writes are visible.  A CTA calls pdl_launch_dependents() when it enters its LAST loop iteration, so the
-// next kernel moves in only while this one drains (signalled at kernel start, the waiting CTAs of the next kernel
-// sat on the SMs for the whole run and cost the bf16 fake-quantise kernel 20 % of its bandwidth).  Everything that reads or writes caller memory comes after pdl_wait(), so the result
-// is the same as with an ordinary launch; what is saved is the launch gap and the prologue between back-to-back
-// kernels, which matters for launches of a few tens of microseconds.  Without the launch attribute the two
-// device calls do nothing.  Tune key 15 = 1 turns the attribute off.
+// Programmatic dependent launch.  A kernel launched with launch_overlapped(true, ...) may become resident while the
+// kernel before it on the stream is still running: its CTAs run their prologue (barrier initialisation, tables
+// copied from the module image into shared memory) and then block in pdl_wait() until that earlier kernel has
+// completed and its writes are visible.  Everything that reads or writes caller memory comes after pdl_wait(), so
+// the result is the same as with an ordinary launch; what is saved is the launch gap and the prologue between
+// back-to-back kernels.  Measured on B200: worth 10-20 % for the TMA-fed pack / unpack kernels at 20-30 us per launch
+// (8192 x 4096), but the fake-quantise kernels lose 10 % at 32768 x 8192 (the CTAs of the next launch, released all at
+// once, stream in lockstep), so only short launches of the TMA-fed codec kernels ask for it.  Without the launch
+// attribute the two device calls do nothing.  Tune key 15 = 1 turns the attribute off everywhere.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t stream,
-                                     Args &&...args)
+inline cudaError_t launch_overlapped(bool overlap, void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem,
+                                     cudaStream_t stream, Args &&...args)
 {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
@@ -64,7 +64,7 @@ inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned grid, un
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = tune_value(15) == 1 ? 0 : 1;
+    cfg.numAttrs = (overlap && tune_value(15) != 1) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

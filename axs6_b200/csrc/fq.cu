@@ -195,7 +195,7 @@ static int launch_persistent(K kernel, const FqArgs &a, int64_t work_items_per_c
     const int64_t resident = (int64_t)d.sms * per_sm;
     if (ctas > resident) ctas = resident;
     if (ctas < 1) ctas = 1;
-    const bool launched = launch_overlapped(kernel, (unsigned)ctas, kThreads, 0, stream, a) == cudaSuccess;
+    const bool launched = launch_overlapped(false, kernel, (unsigned)ctas, kThreads, 0, stream, a) == cudaSuccess;
     count_launch();
     return launched ? check_launch() : AXS6_ERR_LAUNCH;
 }
@@ -494,8 +494,8 @@ static int launch(const void *x, void *y, int64_t nblocks, int round, uint64_t s
         return AXS6_ERR_LAUNCH;
     const Axs6PhiloxKeys keys = axs6_philox_keys(seed);
     cudaError_t le;
-    if (round == kNearest) le = launch_overlapped(fq_bf16_nf5_b32_bulk_kernel<kNearest>, (unsigned)ctas, kBlocksB, kSmemBytes, st, xm, ym, nblocks, 0ull, 0ull, (const unsigned long long *)nullptr, keys);
-    else                   le = launch_overlapped(fq_bf16_nf5_b32_bulk_kernel<kPhilox>, (unsigned)ctas, kBlocksB, kSmemBytes, st, xm, ym, nblocks, seed, offset, epoch, keys);
+    if (round == kNearest) le = launch_overlapped(false, fq_bf16_nf5_b32_bulk_kernel<kNearest>, (unsigned)ctas, kBlocksB, kSmemBytes, st, xm, ym, nblocks, 0ull, 0ull, (const unsigned long long *)nullptr, keys);
+    else                   le = launch_overlapped(false, fq_bf16_nf5_b32_bulk_kernel<kPhilox>, (unsigned)ctas, kBlocksB, kSmemBytes, st, xm, ym, nblocks, seed, offset, epoch, keys);
     count_launch();
     return le == cudaSuccess ? check_launch() : AXS6_ERR_LAUNCH;
 }

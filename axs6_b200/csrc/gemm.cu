@@ -648,7 +648,6 @@ static int launch_gemm_packed(const void *a, const void *a_exps, int64_t lda, co
     const int64_t b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;
     CUtensorMap ma, mb;
     PackedParams q;
-    q.dbg = (int)tune_value(9);
     q.a_exps = static_cast<const uint8_t *>(a_exps); q.b_exps = static_cast<const uint8_t *>(b_exps);
     q.a_nblk = (int)(a_cols / 32); q.b_nblk = (int)(b_cols / 32);
     q.a_rows = (int)a_rows; q.b_rows = (int)b_rows;
@@ -681,6 +680,7 @@ static int launch_gemm_packed(const void *a, const void *a_exps, int64_t lda, co
     p.tiles_m = (int)((M + BM - 1) / BM); p.tiles_n = (int)((N + BN - 1) / BN);
     p.bk = BK; p.mn_box_bytes = 128u * BK; p.splits = 1; p.tail_begin = 0;
     p.ws = nullptr; p.ws_stride = 0; p.ws_ld = 0;
+
     p.a_lbo = a_mn ? p.mn_box_bytes : 0u; p.a_sbo = 1024u; p.a_kstep = a_mn ? 16u * 128u : 32u;
     p.b_lbo = b_mn ? p.mn_box_bytes : 0u; p.b_sbo = 1024u; p.b_kstep = b_mn ? 16u * 128u : 32u;
 

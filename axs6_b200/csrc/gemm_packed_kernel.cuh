@@ -34,23 +34,20 @@ constexpr int kDecodeWarps = 16;
 constexpr int kThreadsPacked = (6 + kDecodeWarps) * 32;       // 704
 
 struct PackedParams {
-    int dbg;                            // timing experiments only (tune key 9): 1 = decode threads store zeros instead of
-                                        // decoding, 2 = no proxy fence, 4 = the producer loads no payload / exponent bytes
-                                        // (results are then wrong; never set outside measurements)
     const uint8_t *a_exps, *b_exps;     // exponent planes, pair-major (null: operand is bf16)
     int a_nblk, b_nblk;                 // blocks per row of the stored operand matrix
     int a_rows, b_rows;                 // rows of the stored operand matrix (K-major: M or N; MN-major: K)
 };
 
 struct PairQ {
-    static constexpr int kStages = 4;
+    static constexpr int kStages = 5;                              // decoded (MMA) stages
+    static constexpr int kRawStages = 3;                           // payload + exponent stages
     static constexpr int kABytes = 128 * BK * 2, kBBytes = 128 * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;          // 32 KB
     static constexpr int kRawOp = 128 * 48;                        // payload tile of one operand: 6 KB
     static constexpr int kExpOp = 256;                             // its 256 exponent bytes
     static constexpr int kRawBytes = 2 * (kRawOp + kExpOp);
-    static constexpr int kLutBytes = 4096 * 4;                     // code pair -> two bf16 values
-    static constexpr int kSmemBytes = 16384 /*alignment slack for the table*/ + kLutBytes + kStages * (kStageBytes + kRawBytes) + 512;
+    static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kRawStages * kRawBytes + 512;   // dynamic part
 };
 
 __device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_addr)
@@ -59,9 +56,9 @@ __device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_add
 }
 
 // Decodes half a block: 16 codes = 12 payload bytes at shared address `raw` (4-byte aligned), exponent `se`, into
-// 16 bf16 values = 8 words.  `lut` is the shared address of the pair table (16 KB aligned, so that an offset can be
-// OR-ed in): entry (c1 << 6 | c0) holds the two table values of codes c0 (low half) and c1 (high half).
-__device__ __forceinline__ void decode_half_block(uint32_t raw, uint32_t se, uint32_t lut, uint32_t (&o)[8])
+// 16 bf16 values = 8 words.  `lut` is the pair table in static shared memory (its address folds into the load
+// instruction): entry (c1 << 6 | c0) holds the two table values of codes c0 (low half) and c1 (high half).
+__device__ __forceinline__ void decode_half_block(uint32_t raw, uint32_t se, const uint32_t *lut, uint32_t (&o)[8])
 {
     uint32_t w[3];
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[0]) : "r"(raw));
@@ -77,8 +74,7 @@ __device__ __forceinline__ void decode_half_block(uint32_t raw, uint32_t se, uin
             if (off == 0) x = w[word] << 2;
             else if (off <= 20) x = w[word] >> (off - 2);
             else x = __funnelshift_r(w[word], w[word + 1 < 3 ? word + 1 : 2], off - 2);
-            uint32_t v;
-            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"((x & 0x3FFCu) | lut));
+            const uint32_t v = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(lut) + (x & 0x3FFCu));
             o[p] = v + kk;
         }
     } else {
@@ -100,22 +96,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsPacked, 1)
 gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p,
               const PackedParams q)
 {
-    constexpr int S = PairQ::kStages, kA2 = PairQ::kABytes, kStage = PairQ::kStageBytes, kRaw = PairQ::kRawBytes;
+    constexpr int S = PairQ::kStages, R = PairQ::kRawStages, kA2 = PairQ::kABytes, kStage = PairQ::kStageBytes, kRaw = PairQ::kRawBytes;
     constexpr int TN = 256;
     extern __shared__ uint8_t smem_raw[];
-    const uint32_t lut = (smem_u32(smem_raw) + 16383u) & ~16383u;            // pair table: 16 KB aligned
-    const uint32_t base = lut + PairQ::kLutBytes;                            // MMA stages (1024-aligned)
+    __shared__ __align__(16) uint32_t lut[4096];                             // code pair -> two bf16 values (16 KB, static)
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;             // MMA stages (1024-aligned)
     const uint32_t raw0 = base + S * kStage;                                 // raw stages: [A payload | B payload | A exps | B exps]
-    const uint32_t bar0 = raw0 + S * kRaw;
+    const uint32_t bar0 = raw0 + R * kRaw;
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
     auto rfull_bar = [&](int s) { return bar0 + 8u * (2 * S + s); };
-    auto rempty_bar = [&](int s) { return bar0 + 8u * (3 * S + s); };
-    auto tfull_bar = [&](int a) { return bar0 + 8u * (4 * S + a); };
-    auto tempty_bar = [&](int a) { return bar0 + 8u * (4 * S + 2 + a); };
-    const uint32_t tmem_slot = bar0 + 8u * (4 * S + 4);
-    uint8_t *smem_gen = smem_raw + (lut - smem_u32(smem_raw));               // generic pointer to the table
-    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(smem_gen + (tmem_slot - lut));
+    auto rempty_bar = [&](int s) { return bar0 + 8u * (2 * S + R + s); };
+    auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * S + 2 * R + a); };
+    auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * S + 2 * R + 2 + a); };
+    const uint32_t tmem_slot = bar0 + 8u * (2 * S + 2 * R + 4);
+    uint8_t *smem_gen = smem_raw + (base - smem_u32(smem_raw));              // generic pointer to the 1024-aligned base
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(smem_gen + (tmem_slot - base));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -131,6 +127,8 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             // full: (leader's expect_tx arrival if a bf16 operand is loaded) + one arrival per decode warp of both CTAs
             mbar_init(full_bar(s), (kAnyTma ? 1 : 0) + 2 * kDecodeWarps);
             mbar_init(empty_bar(s), 1);
+        }
+        for (int s = 0; s < R; ++s) {
             mbar_init(rfull_bar(s), 1);
             mbar_init(rempty_bar(s), kDecodeWarps);
         }
@@ -139,7 +137,7 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     {
-        uint32_t *tl = reinterpret_cast<uint32_t *>(smem_gen);
+        uint32_t *tl = lut;
         for (int i = threadIdx.x; i < 4096; i += kThreadsPacked) {
             uint32_t v[2];
 #pragma unroll
@@ -164,8 +162,8 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     if (warp == 0) {
         // ------------------------------------------------------------------ producer (both CTAs)
         if (lane == 0) {
-            int s = 0;
-            uint32_t ph = 0;
+            int s = 0, rs = 0;
+            uint32_t ph = 0, rph = 0;
             bool ok = true;
             int armed = 0;                                   // raw loads issued so far (for the drain at the end)
             // exponent bytes of one operand tile: K-major = 256 contiguous bytes (pair kb, rows o0 .. o0 + 127);
@@ -213,30 +211,26 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                         }
                     }
                     if (kPacked) {
-                        if (!mbar_wait(rempty_bar(s), ph ^ 1u, 7)) { ok = false; break; }
-                        const uint32_t ra = raw0 + s * kRaw, rb = ra + PairQ::kRawOp;
+                        if (!mbar_wait(rempty_bar(rs), rph ^ 1u, 7)) { ok = false; break; }
+                        const uint32_t ra = raw0 + rs * kRaw, rb = ra + PairQ::kRawOp;
                         const uint32_t ea = ra + 2 * PairQ::kRawOp, eb = ea + PairQ::kExpOp;
+                        const uint32_t rfull = rfull_bar(rs);
+                        if (++rs == R) { rs = 0; rph ^= 1u; }
                         // the exponent runs first: their byte count is known only after clipping, and the barrier is armed
                         // with the total before any copy can complete the phase (a copy that lands early only makes the
                         // pending count negative for a moment)
-                        if (q.dbg & 4) {
-                            mbar_arrive(rfull_bar(s));
-                            ++armed;
-                            if (++s == S) { s = 0; ph ^= 1u; }
-                            continue;
-                        }
                         uint32_t bytes = kPacked * PairQ::kRawOp;
-                        if (QA) bytes += load_exps(q.a_exps, q.a_nblk, q.a_rows, p.a_mn, m0, kb, ea, rfull_bar(s));
-                        if (QB) bytes += load_exps(q.b_exps, q.b_nblk, q.b_rows, p.b_mn, n0, kb, eb, rfull_bar(s));
-                        mbar_expect_tx(rfull_bar(s), bytes);
+                        if (QA) bytes += load_exps(q.a_exps, q.a_nblk, q.a_rows, p.a_mn, m0, kb, ea, rfull);
+                        if (QB) bytes += load_exps(q.b_exps, q.b_nblk, q.b_rows, p.b_mn, n0, kb, eb, rfull);
+                        mbar_expect_tx(rfull, bytes);
                         // payload bytes: 3/4 byte per value along the contiguous dimension
                         if (QA) {
-                            if (!p.a_mn) tma_load_2d(ra, &map_a, rfull_bar(s), k0 * 3 / 4, m0);      // box {48 B, 128 rows}
-                            else tma_load_2d(ra, &map_a, rfull_bar(s), m0 * 3 / 4, k0);               // box {96 B, 64 k-rows}
+                            if (!p.a_mn) tma_load_2d(ra, &map_a, rfull, k0 * 3 / 4, m0);      // box {48 B, 128 rows}
+                            else tma_load_2d(ra, &map_a, rfull, m0 * 3 / 4, k0);               // box {96 B, 64 k-rows}
                         }
                         if (QB) {
-                            if (!p.b_mn) tma_load_2d(rb, &map_b, rfull_bar(s), k0 * 3 / 4, n0);
-                            else tma_load_2d(rb, &map_b, rfull_bar(s), n0 * 3 / 4, k0);
+                            if (!p.b_mn) tma_load_2d(rb, &map_b, rfull, k0 * 3 / 4, n0);
+                            else tma_load_2d(rb, &map_b, rfull, n0 * 3 / 4, k0);
                         }
                         ++armed;
                     }
@@ -245,9 +239,9 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             }
             // never leave while a raw load may still be landing: wait (bounded) for the last phase armed on every stage
             if (kPacked && !ok) {
-                for (int back = 0; back < S && back < armed; ++back) {
+                for (int back = 0; back < R && back < armed; ++back) {
                     const int idx = armed - 1 - back;
-                    acp::mbar_wait_quiet(rfull_bar(idx % S), (uint32_t)((idx / S) & 1), kSpinLimit);
+                    acp::mbar_wait_quiet(rfull_bar(idx % R), (uint32_t)((idx / R) & 1), kSpinLimit);
                 }
             }
         }
@@ -339,7 +333,7 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         };
         auto put = [&](uint32_t stage_half, const Geo &g, bool valid, uint32_t raw_op, uint32_t exp_op) {
             uint32_t o[8];
-            if (valid && !(q.dbg & 1)) {
+            if (valid) {
                 uint32_t se;
                 asm volatile("ld.shared.u8 %0, [%1];" : "=r"(se) : "r"(exp_op + g.exp));
                 decode_half_block(raw_op + g.raw, se, lut, o);
@@ -350,8 +344,8 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage_half + g.dst0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
             asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage_half + g.dst1), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
         };
-        int s = 0;
-        uint32_t ph = 0;
+        int s = 0, rs = 0;
+        uint32_t ph = 0, rph = 0;
         bool ok = true;
         for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
             const int m0 = (t / tiles_n) * 256 + (int)rank * 128;
@@ -359,21 +353,22 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             for (int kb = 0; kb < total_kb; ++kb) {
                 // one lane polls, the warp follows
                 int go = 1;
-                if (lane == 0) go = (mbar_wait(rfull_bar(s), ph, 5) && mbar_wait(empty_bar(s), ph ^ 1u, 6)) ? 1 : 0;
+                if (lane == 0) go = (mbar_wait(rfull_bar(rs), rph, 5) && mbar_wait(empty_bar(s), ph ^ 1u, 6)) ? 1 : 0;
                 go = __shfl_sync(0xFFFFFFFFu, go, 0);
                 if (!go) { ok = false; break; }
                 const uint32_t sa = base + s * kStage, sb = sa + kA2;
-                const uint32_t ra = raw0 + s * kRaw, rb = ra + PairQ::kRawOp;
+                const uint32_t ra = raw0 + rs * kRaw, rb = ra + PairQ::kRawOp;
                 const uint32_t ea = ra + 2 * PairQ::kRawOp, eb = ea + PairQ::kExpOp;
                 if (QA) put(sa, ga, inside(ga, p.a_mn, q.a_rows, q.a_nblk, m0, kb), ra, ea);
                 if (QB) put(sb, gb, inside(gb, p.b_mn, q.b_rows, q.b_nblk, n0, kb), rb, eb);
-                if (!(q.dbg & 2)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // decoded tile visible to the tensor core's reads
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // decoded tile visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive_release_cluster(map_to_cta(full_bar(s), 0));
-                    mbar_arrive(rempty_bar(s));
+                    mbar_arrive(rempty_bar(rs));
                 }
                 if (++s == S) { s = 0; ph ^= 1u; }
+                if (++rs == R) { rs = 0; rph ^= 1u; }
             }
         }
     }
