@@ -391,6 +391,19 @@ __device__ __forceinline__ void tc_commit2(uint32_t bar_cluster)
 {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
 }
+// The 64-bit shared-memory descriptor as two words.  Only the 14-bit start-address field of the low word changes from
+// one MMA to the next (stage and K step), so the issuing thread keeps the words of stage 0 / K step 0 in registers and
+// ADDS (byte offset >> 4) to the low word: one integer add per operand per MMA instead of rebuilding the descriptor.
+// (Shared memory ends below 256 KB, so the sum never carries out of the field.)
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo) { return ((addr & 0x3FFFFu) >> 4) | ((lbo >> 4) << 16); }
+__device__ __forceinline__ uint32_t desc_hi(uint32_t sbo) { return (sbo >> 4) | (1u << 14) | (2u << 29); }
+__device__ __forceinline__ void tc_mma2_words(uint32_t tmem_d, uint32_t alo, uint32_t ahi, uint32_t blo, uint32_t bhi,
+                                              uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %6, 0;\n mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n"
+                 " tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}"
+                 ::"r"(tmem_d), "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tc_mma2(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
@@ -490,23 +503,29 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             int s = 0, acc = 0;
             uint32_t ph = 0, aph = 0;
             bool ok = true;
+            // descriptor words of stage 0, K step 0; per stage / K step only the low words move (see desc_lo)
+            const uint32_t a_lo0 = desc_lo(base, p.a_lbo), b_lo0 = desc_lo(base + kA2Bytes, p.b_lbo);
+            const uint32_t a_hi = desc_hi(p.a_sbo), b_hi = desc_hi(p.b_sbo);
+            const uint32_t a_kinc = p.a_kstep >> 4, b_kinc = p.b_kstep >> 4;
+            const uint32_t peer_empty0 = map_to_cta(empty_bar(0), 1);
             for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
                 if (!mbar_wait(tempty_bar(acc), aph ^ 1u, 2)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * TN);
-                const int kb0 = kb_begin(t);
-                for (int kb = kb0; kb < kb_end(t); ++kb) {
+                const int kb0 = kb_begin(t), kb1 = kb_end(t);
+                uint32_t fresh = 0u;                                // 0 for the first product of the tile (overwrites the accumulator)
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(full_bar(s), ph, 3)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t sa = base + s * kStage2Bytes, sb = sa + kA2Bytes;
+                    const uint32_t soff = (uint32_t)(s * kStage2Bytes) >> 4;
+                    uint32_t alo = a_lo0 + soff, blo = b_lo0 + soff;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        const uint64_t ad = smem_desc(sa + k * p.a_kstep, p.a_lbo, p.a_sbo);
-                        const uint64_t bd = smem_desc(sb + k * p.b_kstep, p.b_lbo, p.b_sbo);
-                        tc_mma2(d_tmem, ad, bd, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
+                        tc_mma2_words(d_tmem, alo, a_hi, blo, b_hi, idesc, fresh);
+                        fresh = 1u;
+                        alo += a_kinc; blo += b_kinc;
                     }
                     tc_commit2(empty_bar(s));                       // frees the stage here ...
-                    tc_commit2(map_to_cta(empty_bar(s), 1));        // ... and in the peer
+                    tc_commit2(peer_empty0 + 8u * (uint32_t)s);     // ... and in the peer
                     if (++s == kStages2) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
@@ -542,6 +561,168 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();                                  // the peer's shared memory and barriers stay alive until both are done
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------- 2-CTA kernel, 256 x 512 tiles
+// Per k-block a pair of the kernel above fetches 64 KB (A 256 x 64 + B 256 x 64) for one 256 x 256 x 64 product.
+// This variant gives a pair a 256 x 512 tile: the A tile of a k-block feeds TWO
+// products (output columns 0..255 and 256..511), so a pair fetches 96 KB per two products = 48 KB per 256 x 256 x 64,
+// a quarter less.  Price: the two 256-column accumulators fill tensor memory (512 columns), so there is no second
+// accumulator set for the next tile; instead each accumulator has its own "ready" / "drained" barriers and its own
+// group of four epilogue warps, the leader issues a k-block's products in the order accumulator 0, accumulator 1, and
+// the first products of the next tile start as soon as accumulator 0 has been drained.
+// Stage = A (128 rows) 16 KB + two B halves (128 columns each) 32 KB = 48 KB, 4 stages.  10 warps: producer, MMA
+// issuer, epilogue group 0 (warps 2..5), epilogue group 1 (warps 6..9).  No split-K here (the launcher takes this
+// kernel only when every tile is computed whole).
+struct PairW {
+    static constexpr int TN = 512;
+    static constexpr int kStages = 4;
+    static constexpr int kABytes = 128 * BK * 2;
+    static constexpr int kBHalf = 128 * BK * 2;                // this CTA's 128 columns of one 256-column product
+    static constexpr int kStageBytes = kABytes + 2 * kBHalf;   // 48 KB
+    static constexpr int kThreads = 320;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairW::kThreads, 1)
+gemm2w_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p)
+{
+    constexpr int S = PairW::kStages, kA = PairW::kABytes, kBH = PairW::kBHalf, kStage = PairW::kStageBytes, TN = PairW::TN;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar0 = base + S * kStage;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
+    auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * S + a); };
+    auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * S + 2 + a); };
+    const uint32_t tmem_slot = bar0 + 8u * (2 * S + 4);
+    uint8_t *smem_gen = smem_raw + (base - smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(smem_gen + S * kStage + 8 * (2 * S + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+    const int tiles_m = (p.M + 255) / 256, tiles_n = (p.N + TN - 1) / TN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int total_kb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+                const int m0 = (t / tiles_n) * 256 + (int)rank * 128;
+                const int nbase = (t % tiles_n) * TN + (int)rank * 128;      // product h uses columns nbase + 256 h .. + 127
+                for (int kb = 0; kb < total_kb; ++kb) {
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, 1)) { ok = false; break; }
+                    const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+                    if (rank == 0) mbar_expect_tx(full_bar(s), 2 * kStage);
+                    const uint32_t sa = base + s * kStage, sb = sa + kA;
+                    const int k0 = kb * BK;
+                    if (!p.a_mn) {
+                        tma_load_2d_pair(sa, &map_a, lead_full, k0, m0);
+                    } else {
+                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(sa + j * 8192, &map_a, lead_full, m0 + 64 * j, k0);
+                    }
+                    for (int h = 0; h < 2; ++h) {
+                        const int n0 = nbase + 256 * h;
+                        if (!p.b_mn) {
+                            tma_load_2d_pair(sb + h * kBH, &map_b, lead_full, k0, n0);
+                        } else {
+                            for (int j = 0; j < 2; ++j) tma_load_2d_pair(sb + h * kBH + j * 8192, &map_b, lead_full, n0 + 64 * j, k0);
+                        }
+                    }
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
+                                   ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            int s = 0;
+            uint32_t ph = 0, aph = 0;
+            bool ok = true;
+            const uint32_t a_lo0 = desc_lo(base, p.a_lbo), b_lo0 = desc_lo(base + kA, p.b_lbo);
+            const uint32_t a_hi = desc_hi(p.a_sbo), b_hi = desc_hi(p.b_sbo);
+            const uint32_t a_kinc = p.a_kstep >> 4, b_kinc = p.b_kstep >> 4;
+            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+                for (int kb = 0; kb < total_kb && ok; ++kb) {
+                    if (!mbar_wait(full_bar(s), ph, 3)) { ok = false; break; }
+                    const uint32_t soff = (uint32_t)(s * kStage) >> 4;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        // the first products of a tile into accumulator h wait until the epilogue has drained it
+                        if (kb == 0) {
+                            if (!mbar_wait(tempty_bar(h), aph ^ 1u, 2)) { ok = false; break; }
+                            tc_fence_after();
+                        }
+                        uint32_t alo = a_lo0 + soff, blo = b_lo0 + soff + (uint32_t)(h * kBH >> 4);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            tc_mma2_words(tmem_base + (uint32_t)(h * 256), alo, a_hi, blo, b_hi, idesc, (kb | k) != 0 ? 1u : 0u);
+                            alo += a_kinc; blo += b_kinc;
+                        }
+                        if (kb == total_kb - 1) {              // accumulator h is complete with these products
+                            tc_commit2(tfull_bar(h));
+                            tc_commit2(map_to_cta(tfull_bar(h), 1));
+                        }
+                    }
+                    if (!ok) break;
+                    tc_commit2(empty_bar(s));
+                    tc_commit2(map_to_cta(empty_bar(s), 1));
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                }
+                aph ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue: group h = (warp - 2) / 4 drains accumulator h
+        const int h = (warp - 2) >> 2;
+        const int q = warp & 3;                          // TMEM lane quarter this warp may read
+        uint32_t aph = 0;
+        bool ok = true;
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) && (p.ldc % 8 == 0);
+        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+            const int m0 = (t / tiles_n) * 256 + (int)rank * 128, n0 = (t % tiles_n) * TN + 256 * h;
+            if (!mbar_wait(tfull_bar(h), aph, 4)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * 256);
+            epilogue_tile(p, taddr, row, n0, vec_ok, false, true);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(h), 0));
+            aph ^= 1u;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
@@ -756,7 +937,7 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
             if (want > 2 && ws_bytes >= want * M * ws_ld_of(N) * 4) { pair_splits = want; use_ws = true; }
         }
     }
-    const bool pairs = !kTf32 && mode != 1 && (mode == 2 || pair_tiles * pair_splits >= d.sms / 4);
+    const bool pairs = !kTf32 && mode != 1 && (mode == 2 || mode == 3 || pair_tiles * pair_splits >= d.sms / 4);
 
     CUtensorMap ma, mb;
     const bool oka = a_mn ? make_map(&ma, a, esize, (uint64_t)M, (uint64_t)K, (uint64_t)lda, bk)
@@ -786,9 +967,34 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     p.b_lbo = b_mn ? p.mn_box_bytes : 0u; p.b_sbo = 1024u; p.b_kstep = b_mn ? mn_kstep : 32u;
 
     if (pairs) {
-        if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm2_kernel), Pair::kSmemBytes)) return AXS6_ERR_LAUNCH;
         if (may_split && split_mode == 2 && K >= 16 * BK) p.splits = 2;
         if (pair_splits > 1) p.splits = (int)pair_splits;
+        // 256 x 512 tiles (a quarter less operand feed per flop): taken when no split is planned and the wider tiles fill
+        // their waves of clusters about as well as the 256 x 256 ones (tune key 7: 3 forces them, 2 forbids them)
+        {
+            const int64_t usable_c = usable_sms(d) / 2;
+            const int64_t wide_tiles = ((M + 255) / 256) * ((N + PairW::TN - 1) / PairW::TN);
+            auto fill = [&](int64_t tiles) { return (double)tiles / (double)(((tiles + usable_c - 1) / usable_c) * usable_c); };
+            // work per tile differs by 2: compare time = waves x tile time
+            const double t_narrow = (double)((pair_tiles + usable_c - 1) / usable_c) * 1.0;
+            const double t_wide = (double)((wide_tiles + usable_c - 1) / usable_c) * 2.0 * 0.85;     // 0.85: measured gain per flop
+            // measured: the wide tile pays only for long contractions (16384 x 4096 x 4096 equal; dW with K = 16384 +4 %,
+            // K = 32000 +8 %; K = 1024 is 30 % slower because its two accumulators are drained one tile at a time)
+            bool wide = p.splits == 1 && mode != 2 && wide_tiles >= usable_c && t_wide <= t_narrow && N > 256 && K >= 8192;
+            if (p.splits == 1 && may_split && K >= 32 * BK && pair_tiles > usable_c) {
+                const int64_t rem = pair_tiles % usable_c;
+                if (rem > 0 && 2 * rem <= usable_c) wide = wide && fill(wide_tiles) >= 0.9;      // the tail split would help the narrow kernel
+            }
+            if (mode == 3 && p.splits == 1 && N > 256) wide = true;
+            if (wide) {
+                if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm2w_kernel), PairW::kSmemBytes)) return AXS6_ERR_LAUNCH;
+                const int clusters = (int)(wide_tiles < usable_c ? wide_tiles : usable_c);
+                gemm2w_kernel<<<2 * clusters, PairW::kThreads, PairW::kSmemBytes, stream>>>(ma, mb, p);
+                count_launch();
+                return check_launch();
+            }
+        }
+        if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm2_kernel), Pair::kSmemBytes)) return AXS6_ERR_LAUNCH;
         const int64_t units = pair_tiles * p.splits;
         const int64_t usable = usable_sms(d);
         const int clusters = (int)(units < usable / 2 ? units : usable / 2);

@@ -96,8 +96,10 @@ def _parity(case: _Case) -> dict:
             "against": "fp32 matmul (TF32 off) of the step's own quantised operands, 64 sampled rows per product"}
 
 
-def _time_steps(case: _Case, steps: int, world: int, dist, group, allreduce: bool, reserve: int, lib, dev):
-    """CUDA-event time per step, max over ranks; kernel launches of this library per step."""
+def _time_steps(case: _Case, steps: int, world: int, dist, group, allreduce: bool, reserve: int, lib, dev, warm: int = 3):
+    """CUDA-event time per step, max over ranks; kernel launches of this library per step.  `warm` untimed steps come
+    first (the variants compared with each other all take the same, longer warm-up, so that none is measured on a
+    cooler GPU than the others)."""
     pending = [None, None]
 
     def step(i):
@@ -127,7 +129,7 @@ def _time_steps(case: _Case, steps: int, world: int, dist, group, allreduce: boo
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(3):
+    for i in range(warm):
         step(i)
     drain()
     barrier()
@@ -214,13 +216,14 @@ def run(args, rank: int, world: int, dev, pk: dict, steps: int | None = None) ->
     res_weak = {"ms_per_step": ms, "TFLOPs": world * flops_weak / (ms * 1e-3) / 1e12, "rows_per_gpu": M_ROWS}
     reserve_sweep = {}
     if world > 1:
-        for n in (0, 8, 24):
-            m_n, _ = _time_steps(weak, max(5, steps // 2), world, dist, group, True, n, lib, dev)
+        # the same step with 0 / 8 / 16 / 24 SMs left to the collective and with the all-reduce off, each after the same
+        # 30-step warm-up (sustained clocks), so that the five figures can be compared with each other
+        for n in (0, 8, 16, 24):
+            m_n, _ = _time_steps(weak, steps, world, dist, group, True, n, lib, dev, warm=30)
             reserve_sweep[str(n)] = m_n
-        reserve_sweep["16"] = ms
-        m_off, _ = _time_steps(weak, max(5, steps // 2), world, dist, group, False, 0, lib, dev)
-        res_weak["ms_per_step_allreduce_off"] = m_off
-        res_weak["ms_per_step_by_reserved_sms"] = reserve_sweep
+        m_off, _ = _time_steps(weak, steps, world, dist, group, False, 0, lib, dev, warm=30)
+        res_weak["sustained_ms_per_step_allreduce_off"] = m_off
+        res_weak["sustained_ms_per_step_by_reserved_sms"] = reserve_sweep
     status = int(lib.axs6_gemm_status())
 
     # the three GEMMs and the fake-quantise passes alone, and the library GEMM (cuBLAS through torch.matmul) on the

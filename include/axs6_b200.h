@@ -117,7 +117,7 @@ int64_t axs6_query(int what);
  *           split, 2 = two-way split of every tile in the CTA-pair kernel, 3 = allow up to 8 / 16 partials
  *           for problems with few tiles: faster weight gradients of small layers, but the partials are added
  *           in no fixed order and the last bits can differ from run to run
- *   key 7   GEMM kernel: 1 single-CTA, 2 CTA pairs
+ *   key 7   GEMM kernel: 1 single-CTA, 2 CTA pairs on 256 x 256 tiles, 3 CTA pairs on 256 x 512 tiles
  *   key 8   SMs the GEMM leaves free (for a collective on another stream)
  *   key 11  1 = general unpack / unpack-and-sum kernels only (no TMA-fed kernel)
  *   key 12  1 = general fake-quantise kernel only (no TMA-fed bf16 kernel)

@@ -157,6 +157,42 @@ def test_gemm_multi_wave_shapes(name, M, N, K, a_mn, b_mn):
     check_sampled_rows(c32, a, b, bool(a_mn), bool(b_mn), 64, fp32_tol(K), 5)
 
 
+WIDE = [(512, 512, 256), (1000, 776, 520), (4096, 4096, 1024), (256, 520, 4096), (19208, 4104, 520), (37 * 256, 1024 + 8, 1032)]
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1)])
+@pytest.mark.parametrize("M,N,K", WIDE)
+def test_gemm_wide_tiles_forced(M, N, K, a_mn, b_mn):
+    """The 256 x 512 tile kernel (one A tile feeds two 256-column products, two accumulators with their own epilogue
+    groups) on every operand layout, forced with tune key 7 = 3: few and many tiles, a second product that is partly or
+    wholly outside the matrix, ragged M, K not a multiple of 64; bf16 and fp32 outputs."""
+    lib = _lib.load()
+    g = torch.Generator(device="cuda").manual_seed(M + N + K + 3 * a_mn + b_mn)
+    a = torch.randn((K, M) if a_mn else (M, K), generator=g, device="cuda").to(torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), generator=g, device="cuda").to(torch.bfloat16)
+    bias = torch.randn(N, generator=g, device="cuda")
+    ref = fp32_matmul(a, b, bool(a_mn), bool(b_mn)) + bias
+    try:
+        lib.axs6_tune(7, 3)
+        c32 = ops.gemm_bf16(a, b, bias=bias, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.float32)
+        c16 = ops.gemm_bf16(a, b, bias=bias, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.bfloat16)
+        again = ops.gemm_bf16(a, b, bias=bias, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.float32)
+    finally:
+        lib.axs6_tune(7, 0)
+    gemm_status_ok()
+    assert rel(c32, ref) < fp32_tol(K)
+    check_bf16_output(c16, ref)
+    assert torch.equal(c32, again)
+    lib.axs6_tune(7, 2)                      # the 256 x 256 kernel on the same operands
+    try:
+        narrow = ops.gemm_bf16(a, b, bias=bias, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.float32)
+    finally:
+        lib.axs6_tune(7, 0)
+    if K < 2048:                             # no K split in either kernel: the same fp32 sums in the same order
+        assert torch.equal(c32, narrow)
+    assert rel(c32, narrow) < 1e-6
+
+
 def test_linear_forward_backward_at_benchmark_size():
     """axs_linear_mixed_precision at M = 16384, K = N = 4096 with supplied rounding draws: y, dX (bf16) and dW (fp32
     accumulator), db against products of the CPU oracle's fake-quantised operands (mixed_precision.py:86-155)."""
