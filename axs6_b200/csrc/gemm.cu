@@ -27,6 +27,7 @@
 // code in g_gemm_status and all roles leave their loops, TMEM is freed and the kernel returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <string.h>
 
 #include "async_copy.cuh"
 #include "common.cuh"
@@ -60,6 +61,7 @@ struct Params {
     int splits;               // split-K factor (>= 2: fp32 output accumulated with red.add into a zero-filled C)
     int tail_begin;           // 2-CTA kernel: tiles from this one on are computed as two K halves (0 = none)
     uint32_t mn_box_bytes;    // bytes of one MN-major TMA box: 128 B x bk rows
+    int c_tma;                // CTA-pair kernel: bf16 output leaves through shared memory and a tensor map (aligned C)
     float *ws;                // split-K workspace (null: partials are added into C with red.add): partial `part` of the
     long long ws_stride;      // product is stored at ws + part * ws_stride as an (M, ws_ld) fp32 matrix and a second
     int ws_ld;                // kernel adds the partials in index order, which makes the sum reproducible
@@ -246,6 +248,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    pdl_wait();                                          // barriers, tensor memory and descriptors are set up; caller memory from here on
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -332,6 +335,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
     }
 
+    pdl_launch_dependents();
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -358,7 +362,8 @@ struct Pair {
     static constexpr int kABytes = 128 * BK * 2;               // this CTA's 128 rows of A
     static constexpr int kBBytes = (TN / 2) * BK * 2;          // this CTA's half of the TN output columns of B
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static constexpr int kOutBytes = 4 * 2 * 4096;             // epilogue staging: per epilogue warp two 32 x 64 bf16 pieces
+    static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + 1024 + 256;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank()
@@ -411,21 +416,78 @@ __device__ __forceinline__ void tc_mma2(uint32_t tmem_d, uint64_t adesc, uint64_
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// Drains one 128 x 256 fp32 accumulator to a bf16 C through shared memory and the TMA unit: this warp owns 32 rows;
+// per 64 columns each thread converts its row's 64 values, writes them as eight 16-byte pieces into a 128-byte-swizzled
+// 32 x 128 B piece (two pieces per warp, alternating), and one lane hands the piece to a tensor-map store, which writes
+// whole 128-byte lines and drops rows and columns outside C.  (The direct path stores 16 bytes per thread and row: 32
+// half-used sectors per instruction.)  Returns after the last tensor-memory read; the stores finish asynchronously.
+__device__ __forceinline__ void epilogue_tile_tma(const Params &p, const CUtensorMap *map_c, uint32_t taddr, uint32_t stag,
+                                                  int m_row0, int n0, int lane, uint32_t &piece)
+{
+#pragma unroll 1
+    for (int cc = 0; cc < 4; ++cc) {
+        const int col0 = n0 + cc * 64;
+        if (col0 >= p.N || m_row0 >= p.M) break;                 // nothing of this piece lies inside C
+        uint32_t r0[32], r1[32];
+        AXS6_TMEM_LD32(taddr + (uint32_t)(cc * 64), r0);
+        AXS6_TMEM_LD32(taddr + (uint32_t)(cc * 64 + 32), r1);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        uint32_t w[32];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            float v0 = __uint_as_float(r0[i]), v1 = __uint_as_float(r0[i + 1]);
+            float u0 = __uint_as_float(r1[i]), u1 = __uint_as_float(r1[i + 1]);
+            if (p.bias) {
+                float b0 = col0 + i < p.N ? __ldg(p.bias + col0 + i) : 0.0f, b1 = col0 + i + 1 < p.N ? __ldg(p.bias + col0 + i + 1) : 0.0f;
+                float c0 = col0 + 32 + i < p.N ? __ldg(p.bias + col0 + 32 + i) : 0.0f;
+                float c1 = col0 + 33 + i < p.N ? __ldg(p.bias + col0 + 33 + i) : 0.0f;
+                if (p.bias_bf16) {
+                    b0 = __bfloat162float(__float2bfloat16_rn(b0)); b1 = __bfloat162float(__float2bfloat16_rn(b1));
+                    c0 = __bfloat162float(__float2bfloat16_rn(c0)); c1 = __bfloat162float(__float2bfloat16_rn(c1));
+                }
+                v0 += b0; v1 += b1; u0 += c0; u1 += c1;
+            }
+            const __nv_bfloat162 h0 = __floats2bfloat162_rn(v0, v1), h1 = __floats2bfloat162_rn(u0, u1);
+            w[i >> 1] = *reinterpret_cast<const uint32_t *>(&h0);
+            w[16 + (i >> 1)] = *reinterpret_cast<const uint32_t *>(&h1);
+        }
+        const uint32_t buf = stag + (piece & 1u) * 4096u;
+        // the store issued two pieces ago read this buffer: it must have finished reading before it is overwritten
+        if (lane == 0) acp::bulk_wait_read<1>();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t addr = buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * j]), "r"(w[4 * j + 1]), "r"(w[4 * j + 2]),
+                         "r"(w[4 * j + 3]) : "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            acp::tma_store_2d(map_c, buf, col0, m_row0);
+            acp::bulk_commit();
+        }
+        ++piece;
+    }
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsGemm, 1)
-gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p)
+gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+             const __grid_constant__ CUtensorMap map_c, const Params p)
 {
     constexpr int TN = Pair::TN;
     constexpr int kStages2 = Pair::kStages, kA2Bytes = Pair::kABytes, kStage2Bytes = Pair::kStageBytes;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bar0 = base + kStages2 * kStage2Bytes;
+    const uint32_t stag0 = base + kStages2 * kStage2Bytes;             // epilogue staging (1024-aligned)
+    const uint32_t bar0 = stag0 + Pair::kOutBytes;
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (kStages2 + s); };
     auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * kStages2 + a); };
     auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * kStages2 + 2 + a); };
     const uint32_t tmem_slot = bar0 + 8u * (2 * kStages2 + 4);
     uint8_t *smem_gen = smem_raw + (base - smem_u32(smem_raw));
-    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(smem_gen + kStages2 * kStage2Bytes + 8 * (2 * kStages2 + 4));
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(smem_gen + kStages2 * kStage2Bytes + Pair::kOutBytes + 8 * (2 * kStages2 + 4));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();            // 0 = leader
@@ -463,6 +525,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     cluster_sync_all();                                  // both CTAs' barriers exist before any remote signal
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    pdl_wait();                                          // barriers, tensor memory and descriptors are set up; caller memory from here on
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -539,7 +602,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
         const int q = warp & 3;
         int acc = 0;
-        uint32_t aph = 0;
+        uint32_t aph = 0, piece = 0;
         bool ok = true;
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) && (p.ldc % 8 == 0);
         for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
@@ -549,15 +612,18 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TN);
-            epilogue_tile(p, taddr, row, n0, vec_ok, unit_split(t), unit_part(t) == 0, unit_part(t));
+            if (p.c_tma) epilogue_tile_tma(p, &map_c, taddr, stag0 + (uint32_t)q * 8192u, m0 + q * 32, n0, lane, piece);
+            else epilogue_tile(p, taddr, row, n0, vec_ok, unit_split(t), unit_part(t) == 0, unit_part(t));
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
             acc ^= 1;
             if (acc == 0) aph ^= 1u;
         }
+        if (p.c_tma && lane == 0) acp::bulk_wait<0>();          // every tensor-map store of this warp has completed
     }
 
+    pdl_launch_dependents();                             // this CTA has no more work to start: the next kernel may set up
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();                                  // the peer's shared memory and barriers stay alive until both are done
@@ -625,6 +691,7 @@ gemm2w_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    pdl_wait();                                          // barriers, tensor memory and descriptors are set up; caller memory from here on
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -720,6 +787,7 @@ gemm2w_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         }
     }
 
+    pdl_launch_dependents();                             // this CTA has no more work to start: the next kernel may set up
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();
@@ -737,6 +805,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
                                                             float *__restrict__ c, long long ldc, const float *__restrict__ bias,
                                                             int bias_bf16, int M, int N)
 {
+    pdl_wait();
     const int chunks = ws_ld / 4;
     const long long total = (long long)M * chunks;
     const bool vec = ((reinterpret_cast<uintptr_t>(c) & 15u) == 0) && (ldc % 4 == 0);
@@ -861,6 +930,7 @@ static int launch_gemm_packed(const void *a, const void *a_exps, int64_t lda, co
     p.tiles_m = (int)((M + BM - 1) / BM); p.tiles_n = (int)((N + BN - 1) / BN);
     p.bk = BK; p.mn_box_bytes = 128u * BK; p.splits = 1; p.tail_begin = 0;
     p.ws = nullptr; p.ws_stride = 0; p.ws_ld = 0;
+    p.c_tma = 0;
 
     p.a_lbo = a_mn ? p.mn_box_bytes : 0u; p.a_sbo = 1024u; p.a_kstep = a_mn ? 16u * 128u : 32u;
     p.b_lbo = b_mn ? p.mn_box_bytes : 0u; p.b_sbo = 1024u; p.b_kstep = b_mn ? 16u * 128u : 32u;
@@ -959,6 +1029,7 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     p.splits = 1;
     p.tail_begin = 0;
     p.ws = nullptr; p.ws_stride = 0; p.ws_ld = 0;
+    p.c_tma = 0;
     // K-major, 128-byte swizzle: 8-row groups are 1024 B apart, one MMA K step is 32 B.
     // MN-major: 128-byte chunks of the output index are one TMA box (bk k-rows x 128 B) apart,
     // groups of 8 k-rows 1024 B apart, one MMA K step (32 B / esize rows) is that many rows x 128 B.
@@ -989,7 +1060,7 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
             if (wide) {
                 if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm2w_kernel), PairW::kSmemBytes)) return AXS6_ERR_LAUNCH;
                 const int clusters = (int)(wide_tiles < usable_c ? wide_tiles : usable_c);
-                gemm2w_kernel<<<2 * clusters, PairW::kThreads, PairW::kSmemBytes, stream>>>(ma, mb, p);
+                if (launch_overlapped(true, gemm2w_kernel, 2 * clusters, PairW::kThreads, PairW::kSmemBytes, stream, ma, mb, p) != cudaSuccess) return AXS6_ERR_LAUNCH;
                 count_launch();
                 return check_launch();
             }
@@ -1019,14 +1090,29 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
                    cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess) {
             return AXS6_ERR_LAUNCH;
         }
-        gemm2_kernel<<<2 * clusters, kThreadsGemm, Pair::kSmemBytes, stream>>>(ma, mb, p);
+        // bf16 output into an aligned C: the epilogue stores through shared memory and a tensor map
+        CUtensorMap mc;
+        memset(&mc, 0, sizeof(mc));
+        p.c_tma = 0;
+        if (c_dtype == AXS6_BF16 && aligned16(c) && ldc % 8 == 0 && tune_value(5) != 1) {
+            EncodeTiledFn fn = encode_fn();
+            const cuuint64_t gdim[2] = {(cuuint64_t)N, (cuuint64_t)M};
+            const cuuint64_t gstride[1] = {(cuuint64_t)ldc * 2};
+            const cuuint32_t box[2] = {64, 32};
+            const cuuint32_t estr[2] = {1, 1};
+            if (fn && fn(&mc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+                p.c_tma = 1;
+        }
+        if (launch_overlapped(true, gemm2_kernel, 2 * clusters, kThreadsGemm, Pair::kSmemBytes, stream, ma, mb, mc, p) != cudaSuccess) return AXS6_ERR_LAUNCH;
         count_launch();
         if (p.ws) {
             const long long chunks = (long long)M * (p.ws_ld / 4);
             int64_t ctas = (chunks + 255) / 256;
             if (ctas > (int64_t)d.sms * 8) ctas = (int64_t)d.sms * 8;
-            splitk_reduce_kernel<<<(unsigned)ctas, 256, 0, stream>>>(p.ws, p.splits, p.ws_stride, p.ws_ld, static_cast<float *>(c),
-                                                                    ldc, bias, bias_via_bf16, (int)M, (int)N);
+            if (launch_overlapped(true, splitk_reduce_kernel, (unsigned)ctas, 256, 0, stream, (const float *)p.ws, p.splits, p.ws_stride,
+                                  p.ws_ld, static_cast<float *>(c), (long long)ldc, bias, bias_via_bf16, (int)M, (int)N) != cudaSuccess)
+                return AXS6_ERR_LAUNCH;
             count_launch();
         }
         return check_launch();
@@ -1048,7 +1134,7 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     if (p.splits > 1 &&
         cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess)
         return AXS6_ERR_LAUNCH;
-    gemm_kernel<kTf32><<<ctas, kThreadsGemm, kSmemBytes, stream>>>(ma, mb, p);
+    if (launch_overlapped(true, gemm_kernel<kTf32>, ctas, kThreadsGemm, kSmemBytes, stream, ma, mb, p) != cudaSuccess) return AXS6_ERR_LAUNCH;
     count_launch();
     return check_launch();
 }

@@ -179,6 +179,7 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const T *g, float *
 {
     // CTA: 64 columns x (256/64 = 4 row lanes); grid (ceil(cols/64), kSplits)
     __shared__ float red[4][64];
+    pdl_launch_dependents();                          // the second phase may set up; it waits for this grid before it reads
     const int cx = threadIdx.x & 63, ry = threadIdx.x >> 6;
     const int64_t col = (int64_t)blockIdx.x * 64 + cx;
     const int64_t per = (rows + kSplits - 1) / kSplits;
@@ -201,6 +202,7 @@ __global__ void __launch_bounds__(256) colsum_partial_vec_kernel(const T *g, flo
 {
     constexpr int V = 16 / (int)sizeof(T);            // values per 16-byte chunk
     __shared__ float red[8][32 * V + 1];
+    pdl_launch_dependents();
     const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
     const int64_t col0 = ((int64_t)blockIdx.x * 32 + cx) * V;
     const int64_t per = (rows + kSplits - 1) / kSplits;
@@ -242,6 +244,7 @@ __global__ void __launch_bounds__(256) colsum_partial_vec_kernel(const T *g, flo
 __global__ void __launch_bounds__(256) colsum_final_kernel(const float *partial, float *out, int64_t cols)
 {
     const int64_t col = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_wait();                                       // phase 1 has finished and its partial sums are visible
     if (col >= cols) return;
     float acc = 0.0f;
     for (int s = 0; s < kSplits; ++s) acc += partial[(int64_t)s * cols + col];
@@ -265,7 +268,8 @@ static int column_sums(const void *g, int dtype, float *out, float *partial, int
         else
             colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(g), partial, rows, cols, ld);
     }
-    colsum_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(partial, out, cols);
+    if (launch_overlapped(true, colsum_final_kernel, (unsigned)((cols + 255) / 256), 256, 0, st, (const float *)partial, out, cols) != cudaSuccess)
+        return AXS6_ERR_LAUNCH;
     count_launch(2);
     return check_launch();
 }

@@ -117,6 +117,8 @@ int64_t axs6_query(int what);
  *           split, 2 = two-way split of every tile in the CTA-pair kernel, 3 = allow up to 8 / 16 partials
  *           for problems with few tiles: faster weight gradients of small layers, but the partials are added
  *           in no fixed order and the last bits can differ from run to run
+ *   key 5   1 = the CTA-pair GEMM writes bf16 outputs with per-thread stores instead of staging each tile
+ *           in shared memory for a TMA store
  *   key 7   GEMM kernel: 1 single-CTA, 2 CTA pairs on 256 x 256 tiles, 3 CTA pairs on 256 x 512 tiles
  *   key 8   SMs the GEMM leaves free (for a collective on another stream)
  *   key 11  1 = general unpack / unpack-and-sum kernels only (no TMA-fed kernel)
@@ -124,7 +126,9 @@ int64_t axs6_query(int what);
  *   key 13  poll limit of the bounded waits inside axs6_unpack_sum's fast kernel (default 2^22 polls)
  *   key 14  1 = the producer warp of that kernel issues no load at all, so that the consumers' first wait runs
  *           out with nothing in flight and the kernel returns with status 11: exists only so that a test can
- *           walk the give-up path without faulting or hanging the GPU */
+ *           walk the give-up path without faulting or hanging the GPU
+ *   key 15  1 = no kernel is launched with the programmatic-dependent-launch attribute (each kernel then
+ *           starts only after the one before it on the stream has finished) */
 int axs6_tune(int key, int64_t value);
 
 /* Every stochastic kernel adds a per-device, device-resident epoch to its Philox counter offset.
