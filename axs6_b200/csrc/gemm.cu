@@ -61,7 +61,7 @@ struct Params {
     int splits;               // split-K factor (>= 2: fp32 output accumulated with red.add into a zero-filled C)
     int tail_begin;           // 2-CTA kernel: tiles from this one on are computed as two K halves (0 = none)
     uint32_t mn_box_bytes;    // bytes of one MN-major TMA box: 128 B x bk rows
-    int c_tma;                // CTA-pair kernel: bf16 output leaves through shared memory and a tensor map (aligned C)
+    int c_tma;                // CTA-pair kernel: output leaves through shared memory and tensor maps (aligned C): 1 bf16, 2 fp32
     float *ws;                // split-K workspace (null: partials are added into C with red.add): partial `part` of the
     long long ws_stride;      // product is stored at ws + part * ws_stride as an (M, ws_ld) fp32 matrix and a second
     int ws_ld;                // kernel adds the partials in index order, which makes the sum reproducible
@@ -471,9 +471,51 @@ __device__ __forceinline__ void epilogue_tile_tma(const Params &p, const CUtenso
     }
 }
 
+// The same for an fp32 C: a piece is 32 rows x 32 columns (128 B per row).  `how`: 0 store into C, 1 add into the
+// zero-filled C (a partial product of a split contraction; the adds are done by the memory system, and with two
+// addends per element their order does not matter), 2 store into slice `part` of the split-K workspace (3-D map).
+__device__ __forceinline__ void epilogue_tile_tma_f32(const Params &p, const CUtensorMap *map, uint32_t taddr, uint32_t stag,
+                                                      int m_row0, int n0, int lane, uint32_t &piece, int how, int part,
+                                                      bool add_bias)
+{
+#pragma unroll 1
+    for (int cc = 0; cc < 8; ++cc) {
+        const int col0 = n0 + cc * 32;
+        if (col0 >= p.N || m_row0 >= p.M) break;
+        uint32_t w[32];
+        AXS6_TMEM_LD32(taddr + (uint32_t)(cc * 32), w);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (p.bias && add_bias) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float bv = col0 + i < p.N ? __ldg(p.bias + col0 + i) : 0.0f;
+                w[i] = __float_as_uint(__uint_as_float(w[i]) + (p.bias_bf16 ? __bfloat162float(__float2bfloat16_rn(bv)) : bv));
+            }
+        }
+        const uint32_t buf = stag + (piece & 1u) * 4096u;
+        if (lane == 0) acp::bulk_wait_read<1>();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t addr = buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * j]), "r"(w[4 * j + 1]), "r"(w[4 * j + 2]),
+                         "r"(w[4 * j + 3]) : "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            if (how == 0) acp::tma_store_2d(map, buf, col0, m_row0);
+            else if (how == 1) acp::tma_reduce_add_2d(map, buf, col0, m_row0);
+            else acp::tma_store_3d(map, buf, col0, m_row0, part);
+            acp::bulk_commit();
+        }
+        ++piece;
+    }
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsGemm, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-             const __grid_constant__ CUtensorMap map_c, const Params p)
+             const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_ws, const Params p)
 {
     constexpr int TN = Pair::TN;
     constexpr int kStages2 = Pair::kStages, kA2Bytes = Pair::kABytes, kStage2Bytes = Pair::kStageBytes;
@@ -612,8 +654,15 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TN);
-            if (p.c_tma) epilogue_tile_tma(p, &map_c, taddr, stag0 + (uint32_t)q * 8192u, m0 + q * 32, n0, lane, piece);
-            else epilogue_tile(p, taddr, row, n0, vec_ok, unit_split(t), unit_part(t) == 0, unit_part(t));
+            if (p.c_tma == 1) {
+                epilogue_tile_tma(p, &map_c, taddr, stag0 + (uint32_t)q * 8192u, m0 + q * 32, n0, lane, piece);
+            } else if (p.c_tma == 2) {
+                const bool acc_unit = unit_split(t), to_ws = acc_unit && p.ws != nullptr;
+                epilogue_tile_tma_f32(p, to_ws ? &map_ws : &map_c, taddr, stag0 + (uint32_t)q * 8192u, m0 + q * 32, n0, lane, piece,
+                                      to_ws ? 2 : (acc_unit ? 1 : 0), unit_part(t), !to_ws && unit_part(t) == 0);
+            } else {
+                epilogue_tile(p, taddr, row, n0, vec_ok, unit_split(t), unit_part(t) == 0, unit_part(t));
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
@@ -1090,21 +1139,39 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
                    cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess) {
             return AXS6_ERR_LAUNCH;
         }
-        // bf16 output into an aligned C: the epilogue stores through shared memory and a tensor map
-        CUtensorMap mc;
+        // Output into an aligned C (and an aligned split-K workspace): the epilogue stores through shared memory and
+        // tensor maps
+        CUtensorMap mc, mw;
         memset(&mc, 0, sizeof(mc));
+        memset(&mw, 0, sizeof(mw));
         p.c_tma = 0;
-        if (c_dtype == AXS6_BF16 && aligned16(c) && ldc % 8 == 0 && tune_value(5) != 1) {
+        if (aligned16(c) && tune_value(5) != 1) {
             EncodeTiledFn fn = encode_fn();
-            const cuuint64_t gdim[2] = {(cuuint64_t)N, (cuuint64_t)M};
-            const cuuint64_t gstride[1] = {(cuuint64_t)ldc * 2};
-            const cuuint32_t box[2] = {64, 32};
-            const cuuint32_t estr[2] = {1, 1};
-            if (fn && fn(&mc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
-                p.c_tma = 1;
+            const cuuint32_t estr[3] = {1, 1, 1};
+            if (c_dtype == AXS6_BF16 && ldc % 8 == 0) {
+                const cuuint64_t gdim[2] = {(cuuint64_t)N, (cuuint64_t)M};
+                const cuuint64_t gstride[1] = {(cuuint64_t)ldc * 2};
+                const cuuint32_t box[2] = {64, 32};
+                if (fn && fn(&mc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+                    p.c_tma = 1;
+            } else if (c_dtype == AXS6_F32 && ldc % 4 == 0 && (!p.ws || (aligned16(p.ws) && p.ws_ld % 4 == 0 && p.ws_stride % 4 == 0))) {
+                const cuuint64_t gdim[2] = {(cuuint64_t)N, (cuuint64_t)M};
+                const cuuint64_t gstride[1] = {(cuuint64_t)ldc * 4};
+                const cuuint32_t box[2] = {32, 32};
+                bool ok = fn && fn(&mc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, c, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+                if (ok && p.ws) {
+                    const cuuint64_t wdim[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)p.splits};
+                    const cuuint64_t wstride[2] = {(cuuint64_t)p.ws_ld * 4, (cuuint64_t)p.ws_stride * 4};
+                    const cuuint32_t wbox[3] = {32, 32, 1};
+                    ok = fn(&mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, p.ws, wdim, wstride, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+                }
+                if (ok) p.c_tma = 2;
+            }
         }
-        if (launch_overlapped(true, gemm2_kernel, 2 * clusters, kThreadsGemm, Pair::kSmemBytes, stream, ma, mb, mc, p) != cudaSuccess) return AXS6_ERR_LAUNCH;
+        if (launch_overlapped(true, gemm2_kernel, 2 * clusters, kThreadsGemm, Pair::kSmemBytes, stream, ma, mb, mc, mw, p) != cudaSuccess) return AXS6_ERR_LAUNCH;
         count_launch();
         if (p.ws) {
             const long long chunks = (long long)M * (p.ws_ld / 4);
