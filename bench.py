@@ -25,6 +25,9 @@ Prints ONE JSON line on rank 0:
              restatement under oracle/ when that copy is absent
   codec, linear   the two other metrics of the path (pack->unpack GB/s, fused-linear TFLOP/s)
   fq_sweep, minigpt   the fake-quantise sweep (fp32 + bf16) and the MiniGPT-style training step
+  gpu_reference   the unmodified reference (baseline/_ref) run on the SAME GPU on the same tensors: its eager
+             and Triton fake-quantise and its mixed-precision Linear step, each beside this library's time and with
+             a bit-for-bit comparison of the fake-quantise outputs (N = 1 only; see bench_gpu_reference.py)
 `--impl reference` times that CPU arm alone, on the first 4096 rows of the same seeded tensor, and
 prints the same line shape (rank 0 only under torchrun).
 """
@@ -398,6 +401,17 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         if rank == 0:
             extra["linear"] = {"error": repr(e)}
 
+    if world == 1 and rank == 0 and "gpu_reference" in sections:
+        try:
+            import bench_gpu_reference
+            xr = make_input(ROWS, COLS, 1000, dev)
+            lin_ms = extra.get("linear", {}).get("ms_per_step")
+            extra["gpu_reference"] = bench_gpu_reference.run(dev, xr, ms_per_step, lin_ms)
+            del xr
+        except Exception as e:
+            extra["gpu_reference"] = {"error": repr(e)[:300]}
+        torch.cuda.empty_cache()
+
     if world > 1 and "grad_exchange" in sections:
         try:
             import bench_exchange
@@ -589,7 +603,7 @@ def main() -> None:
     ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
                     help="what N GPUs means for the headline: strong = the one 32768x8192 tensor split by rows (default), "
                          "weak = one such tensor per GPU; the other reading is reported under `other_scaling`")
-    ap.add_argument("--sections", default="codec,fq_sweep,linear,grad_exchange,minigpt",
+    ap.add_argument("--sections", default="codec,fq_sweep,linear,gpu_reference,grad_exchange,minigpt",
                     help="extra sections of the JSON line to measure after the headline (comma list; empty = none)")
     ap.add_argument("--case", default=None,
                     help="run ONE kernel a few times on a small larger-than-L2 case and exit (for profilers); see bench_cases.py")

@@ -233,3 +233,40 @@ def test_linear_forward_backward_at_benchmark_size():
     check_sampled_rows(wt.grad, gq, xq, True, True, 64, fp32_tol(M), 21)
     check_sampled_rows(y.detach().float() - bt.detach().to(torch.bfloat16).float(), xq, wq, False, False, 64, 4e-3, 22)
     check_sampled_rows(xt.grad, gq, wq, False, True, 64, 4e-3, 23)
+
+
+EPILOGUES = [  # name, M, N, K, a_mn, b_mn: store, reduce-add (tail split) and workspace-partial pieces, full and ragged
+    ("ragged_store", 15 * 256 - 56, 5 * 256 - 24, 2056, 0, 0),
+    ("tail_split_dw", 4096, 4096, 16384, 1, 1),
+    ("workspace_split_dw", 1024, 1024, 8192, 1, 1),
+    ("workspace_split_ragged", 1000, 776, 8200, 1, 1),
+]
+
+
+@pytest.mark.parametrize("name,M,N,K,a_mn,b_mn", EPILOGUES, ids=[e[0] for e in EPILOGUES])
+def test_tensor_map_epilogue_equals_per_thread_stores(name, M, N, K, a_mn, b_mn):
+    """The CTA-pair kernel's outputs leave through shared memory and tensor-map stores (tune key 5 = 0) or through
+    per-thread stores (key 5 = 1); with and without programmatic dependent launch (key 15).  Same accumulators, same
+    rounding, same order of the (at most two, or workspace-ordered) partials: the results are bit-identical."""
+    lib = _lib.load()
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn((K, M) if a_mn else (M, K), generator=g, device="cuda").to(torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), generator=g, device="cuda").to(torch.bfloat16)
+    outs = {}
+    try:
+        lib.axs6_tune(7, 2)
+        for k5, k15 in ((0, 0), (1, 0), (0, 1)):
+            lib.axs6_tune(5, k5)
+            lib.axs6_tune(15, k15)
+            outs[(k5, k15)] = (ops.gemm_bf16(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.float32),
+                               ops.gemm_bf16(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.bfloat16))
+    finally:
+        lib.axs6_tune(5, 0)
+        lib.axs6_tune(15, 0)
+        lib.axs6_tune(7, 0)
+    gemm_status_ok()
+    ref = fp32_matmul(a, b, bool(a_mn), bool(b_mn))
+    assert rel(outs[(0, 0)][0], ref) < fp32_tol(K)
+    for key in ((1, 0), (0, 1)):
+        assert torch.equal(outs[key][0], outs[(0, 0)][0]), f"fp32 output differs with knobs {key}"
+        assert torch.equal(outs[key][1], outs[(0, 0)][1]), f"bf16 output differs with knobs {key}"
