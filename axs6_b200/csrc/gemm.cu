@@ -61,6 +61,7 @@ struct Params {
     int splits;               // split-K factor (>= 2: fp32 output accumulated with red.add into a zero-filled C)
     int tail_begin;           // 2-CTA kernel: tiles from this one on are computed as two K halves (0 = none)
     uint32_t mn_box_bytes;    // bytes of one MN-major TMA box: 128 B x bk rows
+    int a_mn4, b_mn4;         // CTA-pair kernel: the MN-major operand arrives as ONE 4-D box per stage (see make_mn4_map)
     int c_tma;                // CTA-pair kernel: output leaves through shared memory and tensor maps (aligned C): 1 bf16, 2 fp32
     float *ws;                // split-K workspace (null: partials are added into C with red.add): partial `part` of the
     long long ws_stride;      // product is stored at ws + part * ws_stride as an (M, ws_ld) fp32 matrix and a second
@@ -392,6 +393,11 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1) : "memory");
 }
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster, int c0, int c1, int c2, int c3)
+{
+    asm volatile("cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 __device__ __forceinline__ void tc_commit2(uint32_t bar_cluster)
 {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
@@ -587,11 +593,15 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                     const int k0 = kb * BK;
                     if (!p.a_mn) {
                         tma_load_2d_pair(sa, &map_a, lead_full, k0, m0);
+                    } else if (p.a_mn4) {
+                        tma_load_4d_pair(sa, &map_a, lead_full, 0, 0, m0 >> 6, k0 >> 3);
                     } else {
                         for (int j = 0; j < 2; ++j) tma_load_2d_pair(sa + j * 8192, &map_a, lead_full, m0 + 64 * j, k0);
                     }
                     if (!p.b_mn) {
                         tma_load_2d_pair(sb, &map_b, lead_full, k0, n0);
+                    } else if (p.b_mn4) {
+                        tma_load_4d_pair(sb, &map_b, lead_full, 0, 0, n0 >> 6, k0 >> 3);
                     } else {
                         for (int j = 0; j < TN / 128; ++j) tma_load_2d_pair(sb + j * 8192, &map_b, lead_full, n0 + 64 * j, k0);
                     }
@@ -906,6 +916,30 @@ static bool make_map(CUtensorMap *map, const void *ptr, int esize, uint64_t inne
 
 
 
+// MN-major bf16 operand (`k_rows` rows of `mn` contiguous values, `ld` values apart) for the CTA-pair kernel, as a 4-D
+// view whose box is a whole 128 x 64 stage tile: dim 0 = 64 values (one 128-byte swizzle row), dim 1 = 8 consecutive
+// k-rows, dim 2 = 64-value chunk along MN, dim 3 = group of 8 k-rows; box {64, 8, 2, 8}.  In shared memory the 1 KB
+// swizzle atoms then lie [k-group][MN chunk]: the two chunks that one MMA reads for a k-group are adjacent (descriptor
+// strides: 1 KB between MN chunks, 2 KB between k-groups, 4 KB per K step of 16) and the tile arrives with ONE copy
+// instead of two.  Needs mn % 64 == 0 and k_rows % 8 == 0 so that coordinates past the edges fall outside the view
+// (zero fill) instead of wrapping into the next row.
+static bool make_mn4_map(CUtensorMap *map, const void *ptr, uint64_t mn, uint64_t k_rows, uint64_t ld)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || mn % 64 != 0 || k_rows % 8 != 0) return false;
+    const cuuint64_t gdim[4] = {64, 8, mn / 64, k_rows / 8};
+    const cuuint64_t gstride[3] = {ld * 2, 128, 8 * ld * 2};
+    const cuuint32_t box[4] = {64, 8, 2, 8};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUtensorMap tmp;
+    if (fn(&tmp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(ptr), gdim, gstride, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;                                   // the caller keeps its 2-D map
+    *map = tmp;
+    return true;
+}
+
 // SMs the GEMM may use: all of them, minus the reserve of tune key 8 (left to a collective on another stream).
 static int64_t usable_sms(const DeviceInfo &d)
 {
@@ -971,7 +1005,7 @@ static int launch_gemm_packed(const void *a, const void *a_exps, int64_t lda, co
     }
     if (!ok) return AXS6_ERR_DEVICE;
 
-    Params p;
+    Params p = {};
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.a_mn = a_mn; p.b_mn = b_mn;
     p.c = c; p.ldc = ldc; p.c_bf16 = (c_dtype == AXS6_BF16) ? 1 : 0;
@@ -1065,7 +1099,7 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
                           : make_map(&mb, b, esize, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, pairs ? Pair::TN / 2 : BN);
     if (!oka || !okb) return AXS6_ERR_DEVICE;
 
-    Params p;
+    Params p = {};
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.a_mn = a_mn; p.b_mn = b_mn;
     p.c = c; p.ldc = ldc; p.c_bf16 = (c_dtype == AXS6_BF16) ? 1 : 0;
@@ -1079,6 +1113,7 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     p.tail_begin = 0;
     p.ws = nullptr; p.ws_stride = 0; p.ws_ld = 0;
     p.c_tma = 0;
+    p.a_mn4 = p.b_mn4 = 0;
     // K-major, 128-byte swizzle: 8-row groups are 1024 B apart, one MMA K step is 32 B.
     // MN-major: 128-byte chunks of the output index are one TMA box (bk k-rows x 128 B) apart,
     // groups of 8 k-rows 1024 B apart, one MMA K step (32 B / esize rows) is that many rows x 128 B.
@@ -1115,6 +1150,14 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
             }
         }
         if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm2_kernel), Pair::kSmemBytes)) return AXS6_ERR_LAUNCH;
+        if (tune_value(4) != 1) {
+            if (a_mn && make_mn4_map(&ma, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda)) {
+                p.a_mn4 = 1; p.a_lbo = 1024u; p.a_sbo = 2048u; p.a_kstep = 4096u;
+            }
+            if (b_mn && make_mn4_map(&mb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb)) {
+                p.b_mn4 = 1; p.b_lbo = 1024u; p.b_sbo = 2048u; p.b_kstep = 4096u;
+            }
+        }
         const int64_t units = pair_tiles * p.splits;
         const int64_t usable = usable_sms(d);
         const int clusters = (int)(units < usable / 2 ? units : usable / 2);

@@ -1,7 +1,7 @@
 """Runs ONE kernel of the library a few times on a small, larger-than-L2 case, for profilers.
 
     python bench.py --case {fq_f32|fq_bf16|fq_bf16_stochastic|pack_wire|pack_wire_f32|unpack_wire|unpack_wire_bf16|
-                            unpack_sum4|gemm_fwd|gemm_dx|gemm_dw|gemm_packed_fwd|gemm_packed_fwd_w|gemm_packed_dx|
+                            unpack_sum4|gemm_fwd|gemm_dx|gemm_dw|gemm_fwd_full|gemm_dw_full|gemm_packed_fwd|gemm_packed_fwd_w|gemm_packed_dx|
                             gemm_packed_dw|fq_f32_full} [--launches n]
 
 Device footprint stays under 1 GB so that a multi-pass capture finishes quickly (fq_f32_full is the
@@ -69,14 +69,19 @@ def run_case(what: str = "fq_f32", n: int = 3) -> None:
         x = torch.randn(rows, cols, generator=g, device=dev).to(torch.bfloat16)
         y = torch.empty_like(x)
         run = lambda: lib.axs6_fq(x.data_ptr(), y.data_ptr(), 1, 1, rows, cols, cols, cols, 32, 1, 1, 0, 99, 0, st)
-    elif what in ("gemm_fwd", "gemm_dx", "gemm_dw"):
+    elif what in ("gemm_fwd", "gemm_dx", "gemm_dw", "gemm_fwd_full", "gemm_dw_full"):
         M, N, K = 8192, 4096, 4096                 # operands 64 + 32 MiB, output 64 MiB
-        a_mn, b_mn = {"gemm_fwd": (0, 0), "gemm_dx": (0, 1), "gemm_dw": (1, 1)}[what]
+        out_dt, out_code = torch.bfloat16, 1
+        if what == "gemm_fwd_full":                # the Linear benchmark's forward product (bf16 out)
+            M = 16384
+        if what == "gemm_dw_full":                 # its weight gradient: 4096 x 4096 outputs over 16384 rows, fp32 out
+            M, N, K, out_dt, out_code = 4096, 4096, 16384, torch.float32, 0
+        a_mn, b_mn = {"gemm_fwd": (0, 0), "gemm_dx": (0, 1), "gemm_dw": (1, 1), "gemm_fwd_full": (0, 0), "gemm_dw_full": (1, 1)}[what]
         a = torch.randn((K, M) if a_mn else (M, K), generator=g, device=dev).to(torch.bfloat16)
         b = torch.randn((K, N) if b_mn else (N, K), generator=g, device=dev).to(torch.bfloat16)
-        c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        c = torch.empty(M, N, dtype=out_dt, device=dev)
         run = lambda: lib.axs6_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), None, M, N, K, a.stride(0), b.stride(0),
-                                         N, a_mn, b_mn, 1, st)
+                                         N, a_mn, b_mn, out_code, st)
     elif what in ("gemm_packed_fwd", "gemm_packed_dx", "gemm_packed_dw", "gemm_packed_fwd_w"):
         from axs6_b200 import ops
         M, N, K = 8192, 4096, 4096

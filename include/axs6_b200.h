@@ -117,6 +117,8 @@ int64_t axs6_query(int what);
  *           split, 2 = two-way split of every tile in the CTA-pair kernel, 3 = allow up to 8 / 16 partials
  *           for problems with few tiles: faster weight gradients of small layers, but the partials are added
  *           in no fixed order and the last bits can differ from run to run
+ *   key 4   1 = MN-major operands of the CTA-pair GEMM arrive as two 2-D boxes per stage (64-value chunks one after the
+ *           other) instead of one 4-D box (the two chunks of a group of 8 k-rows side by side)
  *   key 5   1 = the CTA-pair GEMM writes bf16 outputs with per-thread stores instead of staging each tile
  *           in shared memory for a TMA store
  *   key 7   GEMM kernel: 1 single-CTA, 2 CTA pairs on 256 x 256 tiles, 3 CTA pairs on 256 x 512 tiles

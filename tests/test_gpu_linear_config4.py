@@ -246,27 +246,29 @@ EPILOGUES = [  # name, M, N, K, a_mn, b_mn: store, reduce-add (tail split) and w
 @pytest.mark.parametrize("name,M,N,K,a_mn,b_mn", EPILOGUES, ids=[e[0] for e in EPILOGUES])
 def test_tensor_map_epilogue_equals_per_thread_stores(name, M, N, K, a_mn, b_mn):
     """The CTA-pair kernel's outputs leave through shared memory and tensor-map stores (tune key 5 = 0) or through
-    per-thread stores (key 5 = 1); with and without programmatic dependent launch (key 15).  Same accumulators, same
-    rounding, same order of the (at most two, or workspace-ordered) partials: the results are bit-identical."""
+    per-thread stores (key 5 = 1); with and without programmatic dependent launch (key 15); MN-major operands arrive as
+    one 4-D box per stage (key 4 = 0) or as two 2-D boxes (key 4 = 1).  Same accumulators, same rounding, same order of
+    the (at most two, or workspace-ordered) partials: the results are bit-identical."""
     lib = _lib.load()
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     a = torch.randn((K, M) if a_mn else (M, K), generator=g, device="cuda").to(torch.bfloat16)
     b = torch.randn((K, N) if b_mn else (N, K), generator=g, device="cuda").to(torch.bfloat16)
     outs = {}
+    knobs = ((0, 0, 0), (0, 1, 0), (0, 0, 1), (1, 0, 0))
     try:
         lib.axs6_tune(7, 2)
-        for k5, k15 in ((0, 0), (1, 0), (0, 1)):
+        for k4, k5, k15 in knobs:
+            lib.axs6_tune(4, k4)
             lib.axs6_tune(5, k5)
             lib.axs6_tune(15, k15)
-            outs[(k5, k15)] = (ops.gemm_bf16(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.float32),
-                               ops.gemm_bf16(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.bfloat16))
+            outs[(k4, k5, k15)] = (ops.gemm_bf16(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.float32),
+                                   ops.gemm_bf16(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.bfloat16))
     finally:
-        lib.axs6_tune(5, 0)
-        lib.axs6_tune(15, 0)
-        lib.axs6_tune(7, 0)
+        for key in (4, 5, 15, 7):
+            lib.axs6_tune(key, 0)
     gemm_status_ok()
     ref = fp32_matmul(a, b, bool(a_mn), bool(b_mn))
-    assert rel(outs[(0, 0)][0], ref) < fp32_tol(K)
-    for key in ((1, 0), (0, 1)):
-        assert torch.equal(outs[key][0], outs[(0, 0)][0]), f"fp32 output differs with knobs {key}"
-        assert torch.equal(outs[key][1], outs[(0, 0)][1]), f"bf16 output differs with knobs {key}"
+    assert rel(outs[knobs[0]][0], ref) < fp32_tol(K)
+    for key in knobs[1:]:
+        assert torch.equal(outs[key][0], outs[knobs[0]][0]), f"fp32 output differs with knobs {key}"
+        assert torch.equal(outs[key][1], outs[knobs[0]][1]), f"bf16 output differs with knobs {key}"
