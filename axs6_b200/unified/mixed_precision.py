@@ -25,6 +25,13 @@ KEEP_QUANTIZED_WEIGHT = True
 # default: the two-pass path is the one that reproduces the reference at exact zeros (codes have no zero).
 PACKED_OPERANDS = False
 
+# Saved activation as 25-byte wire records (0.78 bytes per value instead of 2) WITHOUT the decode-on-load GEMM: the
+# forward packs the bf16 input once more (the codes decode to the fake-quantised input, except at exact zeros, which
+# codes cannot express), the backward unpacks them into a transient bf16 buffer for the weight-gradient product.
+# Costs one pack and one unpack pass per layer and step (about 6 % of the step at 16384 x 4096 x 4096).  Off by
+# default for the same reason as PACKED_OPERANDS.
+SAVE_PACKED_INPUT = False
+
 # Test hook: when set to a tensor, the next backward uses these U[0,1) draws for the gradient's
 # stochastic rounding (padded (M, nblk, block) layout) instead of the Philox stream.
 _noise_for_next_backward: torch.Tensor | None = None
@@ -61,6 +68,12 @@ class _AXSLinearBF16Function(torch.autograd.Function):
         y, xq, wq = ops.linear_fwd(x2, w, b32, block_size, ops.GRID_NF5, bool(quantize_input), torch.bfloat16,
                                    bias_via_bf16=True, return_wq=True, packed=packed)
         ctx.packed = packed
+        ctx.x_records = None
+        if (SAVE_PACKED_INPUT and not packed and quantize_input and block_size == 32 and x2.shape[1] % 32 == 0
+                and ctx.needs_input_grad[1]):
+            xb = x2 if x2.dtype == torch.bfloat16 else x2.to(torch.bfloat16)
+            ctx.x_records = (x2.shape[0], x2.shape[1])
+            xq = ops.pack(xb, 32, ops.GRID_NF5, "nearest", ops.LAYOUT_WIRE, who="axs_linear_mixed_precision")
         ctx.save_for_backward(xq, weight, bias)
         # The quantised weight is kept for backward and used there if the weight is still the same version
         # (the reference recomputes it, mixed_precision.py:130, to save memory; the bits are the same).
@@ -81,6 +94,8 @@ class _AXSLinearBF16Function(torch.autograd.Function):
         w = weight if weight.dtype in (torch.float32, torch.bfloat16) else weight.float()
         w = w if w.stride(-1) == 1 else w.contiguous()
         noise, _noise_for_next_backward = _noise_for_next_backward, None
+        if ctx.x_records is not None:             # the saved activation is a buffer of records: back to bf16 for the product
+            xq = ops.unpack(ops.LAYOUT_WIRE, xq, ctx.x_records[0], ctx.x_records[1], 32, ops.GRID_NF5, torch.bfloat16)
         dx, dw, db = ops.linear_bwd(g2, xq, w, M, N, K, ctx.block_size, ops.GRID_NF5, ctx.quantize_grad,
                                     ctx.needs_input_grad[0], ctx.needs_input_grad[1],
                                     bias is not None and ctx.needs_input_grad[2], torch.bfloat16, noise,

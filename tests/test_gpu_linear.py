@@ -495,3 +495,37 @@ def test_minigpt_block_trains_with_axs6_linears():
     assert all(p.grad is not None for p in params)
     assert losses[-1] < losses[0] * 0.9
     gemm_status_ok()
+
+
+@pytest.mark.parametrize("M,K,N", [(512, 1024, 768), (300, 96, 200)])
+def test_saved_activation_as_records_gives_the_same_gradients(M, K, N):
+    """SAVE_PACKED_INPUT keeps the activation for backward as 25-byte wire records (25/64 of the bf16 bytes).  The
+    records decode to the fake-quantised input wherever the input is not exactly zero, so on an input without
+    zeros y, dX, dW and db are bit-identical to the default path (same draws for the gradient's rounding)."""
+    g = torch.Generator(device="cuda").manual_seed(M + K + N)
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    x = torch.where(x == 0, torch.full_like(x, 0.5), x)
+    w = (torch.randn(N, K, generator=g, device="cuda") * 0.05)
+    b = torch.randn(N, generator=g, device="cuda")
+    go = torch.randn(M, N, generator=g, device="cuda").to(torch.bfloat16)
+    nblk = -(-N // 32)
+    noise = torch.rand(M, nblk, 32, generator=g, device="cuda")
+    res = {}
+    saved_bytes = {}
+    for flag in (False, True):
+        mp.SAVE_PACKED_INPUT = flag
+        try:
+            xi = x.clone().requires_grad_(True)
+            wi = w.clone().requires_grad_(True)
+            bi = b.clone().requires_grad_(True)
+            y = mp.axs_linear_mixed_precision(xi, wi, bi, 32, True, True)
+            saved = y.grad_fn.saved_tensors[0]
+            saved_bytes[flag] = saved.numel() * saved.element_size()
+            mp._noise_for_next_backward = noise
+            y.backward(go)
+            res[flag] = (y.detach(), xi.grad, wi.grad, bi.grad)
+        finally:
+            mp.SAVE_PACKED_INPUT = False
+    assert saved_bytes[True] == M * (K // 32) * 25 and saved_bytes[False] == M * K * 2
+    for got, want, name in zip(res[True], res[False], ("y", "dx", "dw", "db")):
+        assert torch.equal(got, want), name
