@@ -960,8 +960,13 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
     constexpr int kTile = kFastBlocks * UnpackOut<Tout>::kRowBytes;
     constexpr int kPieces = UnpackOut<Tout>::kPieces;
     extern __shared__ uint8_t raw[];
-    __shared__ __align__(16) uint32_t tlo[64];      // code -> value bits (bf16: in the low half)
-    __shared__ __align__(16) uint32_t thi[64];      // bf16 only: the same in the high half
+    // code -> value bits (bf16: in the low half), one copy per lane: entry (code, lane) is word code * 32 + lane, so a
+    // warp's 32 lookups always hit 32 different banks (with one shared copy the codes of a warp collide about three
+    // deep, and the lookups, not DRAM, bounded the kernel)
+    // (bf16 output only: with fp32 output the kernel is not bound by the lookups and the larger table costs 2 %)
+    constexpr int kCopies = kBf16 ? 32 : 1;
+    constexpr int kCodeShift = kBf16 ? 7 : 2;       // byte offset of an entry = code << kCodeShift (+ lane * 4)
+    __shared__ __align__(128) uint32_t tlo[64 * kCopies];
     __shared__ float lev[32];
     uint8_t *base = raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u);
     uint8_t *tile0 = base + kCtrlBytes;             // 1024-aligned output tiles
@@ -971,18 +976,15 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
     pdl_launch_dependents();                               // the next launch may take up residence now (it waits in pdl_wait)
     const int64_t groups = (nblocks + kFastBlocks - 1) / kFastBlocks;
     const int64_t nk = (int64_t)blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    if (tid < 64) {
-        const uint32_t bits = g_codebook_bits[tid & 31];
-        const uint32_t sign = (uint32_t)tid >> 5;
-        if (kBf16) {
-            const uint32_t v = ((uint32_t)axs6_f32_to_bf16_bits(__uint_as_float(bits)) - (120u << 7)) | (sign << 15);
-            tlo[tid] = v;
-            thi[tid] = v << 16;
-        } else {
-            tlo[tid] = (bits - (120u << 23)) | (sign << 31);
-        }
-        if (tid < 32) lev[tid] = __uint_as_float(bits);
+    for (int i = tid; i < 64 * kCopies; i += kFastBlocks) {
+        const uint32_t code = (uint32_t)i / kCopies;
+        const uint32_t bits = g_codebook_bits[code & 31u];
+        const uint32_t sign = code >> 5;
+        tlo[i] = kBf16 ? (((uint32_t)axs6_f32_to_bf16_bits(__uint_as_float(bits)) - (120u << 7)) | (sign << 15))
+                       : ((bits - (120u << 23)) | (sign << 31));
     }
+    if (tid < 32) lev[tid] = __uint_as_float(g_codebook_bits[tid]);
+    const uint32_t lane4 = kBf16 ? ((uint32_t)tid & 31u) << 2 : 0u;
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
         fence_barrier_init();
@@ -1041,23 +1043,22 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
                 const uint32_t kk = kBf16 ? (se - 7u) * 0x00800080u : (se - 7u) << 23;
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    uint32_t a[2];                      // byte offsets (code * 4) of values i and i + 1
+                    uint32_t a[2];                      // byte offsets of the table entries of values i and i + 1
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int bit = 6 * (i + e), word = bit >> 5, off = bit & 31;
-                        uint32_t v;
-                        if (off == 0) v = pay[word] << 2;
-                        else if (off == 1) v = pay[word] << 1;
-                        else if (off <= 26) v = pay[word] >> (off - 2);
-                        else v = __funnelshift_r(pay[word], pay[word + 1], off - 2);
-                        a[e] = v & 0xFCu;
+                        uint32_t v;                     // the code at bits kCodeShift .. kCodeShift + 5
+                        if (off < kCodeShift) v = pay[word] << (kCodeShift - off);
+                        else if (off == kCodeShift) v = pay[word];
+                        else if (off <= 26) v = pay[word] >> (off - kCodeShift);
+                        else v = __funnelshift_r(pay[word], pay[word + 1], off - kCodeShift);
+                        a[e] = (v & (0x3Fu << kCodeShift)) | lane4;
                     }
                     const uint32_t v0 = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(tlo) + a[0]);
+                    const uint32_t v1 = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(tlo) + a[1]);
                     if (kBf16) {
-                        const uint32_t v1 = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(thi) + a[1]);
-                        o[i >> 1] = v0 + v1 + kk;
+                        o[i >> 1] = (v1 << 16) + v0 + kk;
                     } else {
-                        const uint32_t v1 = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(tlo) + a[1]);
                         o[i] = v0 + kk;
                         o[i + 1] = v1 + kk;
                     }
