@@ -82,6 +82,11 @@ def load() -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.restype = res
             fn.argtypes = args
+        # experiment knobs from the environment: AXS6_TUNE="key=value,key=value" (see axs6_tune in the header)
+        for item in filter(None, os.environ.get("AXS6_TUNE", "").split(",")):
+            key, _, value = item.partition("=")
+            if lib.axs6_tune(int(key), int(value)) != 0:
+                raise ValueError(f"AXS6_TUNE: bad entry {item!r}")
         _lib = lib
     return _lib
 

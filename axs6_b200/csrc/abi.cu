@@ -13,6 +13,8 @@ static std::atomic<long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 static std::atomic<long long> g_tune[16];
+static std::atomic<int> g_last_cuda_error{0};
+void note_cuda_error(cudaError_t e) { if (e != cudaSuccess) g_last_cuda_error.store((int)e, std::memory_order_relaxed); }
 
 int64_t tune_value(int key) { return (key >= 0 && key < 16) ? g_tune[key].load(std::memory_order_relaxed) : 0; }
 
@@ -113,6 +115,7 @@ AXS6_API int64_t axs6_query(int what)
     case 1: { const axs6::DeviceInfo &d = axs6::device_info(); return d.valid ? d.sms : 0; }
     case 2: return 1;
     case 3: return axs6::g_launches.load(std::memory_order_relaxed);
+    case 4: return axs6::g_last_cuda_error.load(std::memory_order_relaxed);
     default: return -1;
     }
 }

@@ -39,6 +39,8 @@ int gemm_packed_launch(const void *a, const void *a_exps, int64_t lda, const voi
                        const float *bias, int64_t M, int64_t N, int64_t K, int64_t ldc, int a_mn, int b_mn, int c_dtype,
                        int bias_via_bf16, cudaStream_t stream);
 
+void note_cuda_error(cudaError_t e);      // remembers the last CUDA error a launch returned (axs6_query(4))
+
 // Programmatic dependent launch.  A kernel launched with launch_overlapped(true, ...) may become resident while the
 // kernel before it on the stream is still running: its CTAs run their prologue (barrier initialisation, tables
 // copied from the module image into shared memory) and then block in pdl_wait() until that earlier kernel has
@@ -65,14 +67,18 @@ inline cudaError_t launch_overlapped(bool overlap, void (*kernel)(KArgs...), uns
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (overlap && tune_value(15) != 1) ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    note_cuda_error(e);
+    return e;
 }
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline int check_launch()
 {
-    return cudaGetLastError() == cudaSuccess ? AXS6_OK : AXS6_ERR_LAUNCH;
+    const cudaError_t e = cudaGetLastError();
+    note_cuda_error(e);
+    return e == cudaSuccess ? AXS6_OK : AXS6_ERR_LAUNCH;
 }
 
 inline bool valid_block(int b) { return b == 8 || b == 16 || b == 32; }

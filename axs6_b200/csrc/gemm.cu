@@ -61,6 +61,7 @@ struct Params {
     int splits;               // split-K factor (>= 2: fp32 output accumulated with red.add into a zero-filled C)
     int tail_begin;           // 2-CTA kernel: tiles from this one on are computed as two K halves (0 = none)
     uint32_t mn_box_bytes;    // bytes of one MN-major TMA box: 128 B x bk rows
+    int dynamic;              // CTA-pair kernel: one cluster per work unit, units taken over through cluster launch control
     int a_mn4, b_mn4;         // CTA-pair kernel: the MN-major operand arrives as ONE 4-D box per stage (see make_mn4_map)
     int c_tma;                // CTA-pair kernel: output leaves through shared memory and tensor maps (aligned C): 1 bf16, 2 fp32
     float *ws;                // split-K workspace (null: partials are added into C with red.add): partial `part` of the
@@ -364,7 +365,9 @@ struct Pair {
     static constexpr int kBBytes = (TN / 2) * BK * 2;          // this CTA's half of the TN output columns of B
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kOutBytes = 4 * 2 * 4096;             // epilogue staging: per epilogue warp two 32 x 64 bf16 pieces
-    static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + 1024 + 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + 1024 + 512;
+    static constexpr int kThreads = 224;                       // producer, MMA issuer, 4 epilogue warps, tile scheduler
+    static constexpr int kUnitSlots = 4;                       // work units handed out ahead of their use (dynamic schedule)
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank()
@@ -387,6 +390,52 @@ __device__ __forceinline__ void cluster_sync_all()
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
 {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Cluster launch control: a running cluster asks the hardware for the launch of a cluster of this grid that has not
+// started yet; if there is one, that cluster never starts and its first CTA's index comes back (16 bytes written to
+// shared memory, counted on an mbarrier), so the asking cluster does that work unit itself.  With a grid of one
+// cluster per unit this is a persistent kernel whose units go to whichever cluster is free: a cluster that starts late
+// or shares its SMs with another kernel (a collective on another stream) simply takes fewer units.
+__device__ __forceinline__ void clc_try_cancel(uint32_t resp, uint32_t bar)
+{
+    asm volatile("clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];"
+                 ::"r"(resp), "r"(bar) : "memory");
+}
+// blockIdx.x of the first CTA of the cluster whose launch was taken over, or -1 when none was left
+__device__ __forceinline__ int clc_result(uint32_t resp)
+{
+    uint32_t x, ok;
+    asm volatile("{\n\t"
+                 ".reg .pred p;\n\t"
+                 ".reg .b128 r;\n\t"
+                 "ld.shared.b128 r, [%2];\n\t"
+                 "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p, r;\n\t"
+                 "selp.u32 %1, 1, 0, p;\n\t"
+                 "mov.u32 %0, 0;\n\t"
+                 "@p clusterlaunchcontrol.query_cancel.get_first_ctaid::x.b32.b128 %0, r;\n\t"
+                 "}"
+                 : "=r"(x), "=r"(ok) : "r"(resp) : "memory");
+    return ok ? (int)x : -1;
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v)
+{
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// Bounded wait whose acquire covers writes made from the other CTA of the cluster before its (cluster-scope) arrive.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int code)
+{
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (i > 64) {
+            __nanosleep(40);
+            if ((i & 255u) == 0u && *(volatile int *)&g_gemm_status != 0) return false;
+        }
+    }
+    atomicCAS(&g_gemm_status, 0, code);
+    return false;
 }
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster, int c0, int c1)
 {
@@ -519,7 +568,7 @@ __device__ __forceinline__ void epilogue_tile_tma_f32(const Params &p, const CUt
     }
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsGemm, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Pair::kThreads, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
              const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_ws, const Params p)
 {
@@ -534,6 +583,15 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * kStages2 + a); };
     auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * kStages2 + 2 + a); };
     const uint32_t tmem_slot = bar0 + 8u * (2 * kStages2 + 4);
+    // dynamic schedule: a ring of kUnitSlots unit numbers, each with a "published" barrier (in both CTAs) and a "read by
+    // every role of both CTAs" barrier (the leader's is the one used); one barrier and 16 bytes for the launch-control answer
+    constexpr int kSlots = Pair::kUnitSlots;
+    const uint32_t sched0 = bar0 + 8u * (2 * kStages2 + 5);
+    auto sfull_bar = [&](int i) { return sched0 + 8u * i; };
+    auto sempty_bar = [&](int i) { return sched0 + 8u * (kSlots + i); };
+    const uint32_t clc_bar = sched0 + 8u * (2 * kSlots);
+    const uint32_t clc_resp = (clc_bar + 8u + 15u) & ~15u;
+    const uint32_t unit_slot0 = clc_resp + 16u;
     uint8_t *smem_gen = smem_raw + (base - smem_u32(smem_raw));
     volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(smem_gen + kStages2 * kStage2Bytes + Pair::kOutBytes + 8 * (2 * kStages2 + 4));
 
@@ -561,6 +619,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         for (int s = 0; s < kStages2; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         // accumulator drained: one arrival per epilogue warp of both CTAs (on the leader's barrier)
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 8); }
+        // a unit number is read by the producer and the 4 epilogue warps of each CTA and by the MMA issuer of the
+        // leader; every reader arrives on its OWN CTA's "read" barrier (a CTA-scope arrive: a cluster-scope release
+        // in the thread that issues the MMAs waits for the products in flight), and the peer's forwarding thread
+        // passes the peer's five on to the leader's barrier as one arrival: 6 + 1 there, 5 in the peer
+        for (int i = 0; i < kSlots; ++i) { mbar_init(sfull_bar(i), 1); mbar_init(sempty_bar(i), cluster_ctarank() == 0 ? 7 : 5); }
+        mbar_init(clc_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -575,13 +639,31 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     const uint32_t tmem_base = *tmem_slot_ptr;
     pdl_wait();                                          // barriers, tensor memory and descriptors are set up; caller memory from here on
 
+    // The next work unit of this cluster, for one thread of a role; false = no more (or a wait gave up).
+    // Static schedule: units cluster_id, cluster_id + num_clusters, ...  Dynamic: the numbers the scheduler publishes.
+    auto next_unit = [&](int &t, int &slot, uint32_t &sph, bool &first) -> bool {
+        if (!p.dynamic) {
+            t = first ? cluster_id : t + num_clusters;
+            first = false;
+            return t < num_tiles;
+        }
+        // in the peer CTA the number was stored by the leader's scheduler thread through the cluster's shared window
+        if (!(rank == 0 ? mbar_wait(sfull_bar(slot), sph, 10) : mbar_wait_cluster(sfull_bar(slot), sph, 10))) return false;
+        asm volatile("ld.shared.s32 %0, [%1];" : "=r"(t) : "r"(unit_slot0 + 4u * (uint32_t)slot) : "memory");
+        mbar_arrive(sempty_bar(slot));
+        if (++slot == kSlots) { slot = 0; sph ^= 1u; }
+        return t >= 0;
+    };
+
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
-            bool ok = true;
-            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+            bool ok = true, first = true;
+            int t = 0, uslot = 0;
+            uint32_t uph = 0;
+            while (ok && next_unit(t, uslot, uph, first)) {
                 const int tile = unit_tile(t);
                 const int m0 = (tile / tiles_n) * 256 + (int)rank * 128;
                 const int n0 = (tile % tiles_n) * TN + (int)rank * (TN / 2);
@@ -623,7 +705,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             const uint32_t a_hi = desc_hi(p.a_sbo), b_hi = desc_hi(p.b_sbo);
             const uint32_t a_kinc = p.a_kstep >> 4, b_kinc = p.b_kstep >> 4;
             const uint32_t peer_empty0 = map_to_cta(empty_bar(0), 1);
-            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+            bool first = true;
+            int t = 0, uslot = 0;
+            uint32_t uph = 0;
+            while (ok && next_unit(t, uslot, uph, first)) {
                 if (!mbar_wait(tempty_bar(acc), aph ^ 1u, 2)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * TN);
@@ -650,6 +735,43 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                 if (acc == 0) aph ^= 1u;
             }
         }
+    } else if (warp == 6) {
+        // ------------------------------------------------------------------ unit scheduler (leader CTA, dynamic schedule)
+        if (lane == 0 && rank == 1 && p.dynamic) {
+            // peer: once its five readers have read a slot, tell the leader's scheduler (one cluster-scope arrival)
+            int slot = 0;
+            uint32_t ph = 0;
+            for (;;) {
+                int t;
+                if (!mbar_wait_cluster(sfull_bar(slot), ph, 11)) break;
+                asm volatile("ld.shared.s32 %0, [%1];" : "=r"(t) : "r"(unit_slot0 + 4u * (uint32_t)slot) : "memory");
+                if (!mbar_wait(sempty_bar(slot), ph, 12)) break;
+                mbar_arrive_cluster(map_to_cta(sempty_bar(slot), 0));
+                if (t < 0) break;
+                if (++slot == kSlots) { slot = 0; ph ^= 1u; }
+            }
+        }
+        if (lane == 0 && rank == 0 && p.dynamic) {
+            int slot = 0, cur = cluster_id;              // the cluster's own unit first
+            uint32_t eph = 0, cph = 0;
+            for (;;) {
+                if (!mbar_wait(sempty_bar(slot), eph ^ 1u, 8)) break;
+                const uint32_t sa = unit_slot0 + 4u * (uint32_t)slot;
+                asm volatile("st.shared.s32 [%0], %1;" ::"r"(sa), "r"(cur) : "memory");
+                st_cluster_u32(map_to_cta(sa, 1), (uint32_t)cur);
+                mbar_arrive_cluster(map_to_cta(sfull_bar(slot), 0));
+                mbar_arrive_cluster(map_to_cta(sfull_bar(slot), 1));
+                if (++slot == kSlots) { slot = 0; eph ^= 1u; }
+                if (cur < 0) break;                      // the end mark has been published
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_expect_tx(clc_bar, 16);
+                clc_try_cancel(clc_resp, clc_bar);
+                if (!mbar_wait(clc_bar, cph, 9)) break;
+                cph ^= 1u;
+                const int x = clc_result(clc_resp);
+                cur = x < 0 ? -1 : (x >> 1);
+            }
+        }
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
         const int q = warp & 3;
@@ -657,7 +779,15 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         uint32_t aph = 0, piece = 0;
         bool ok = true;
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) && (p.ldc % 8 == 0);
-        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        bool first = true;
+        int t = 0, uslot = 0;
+        uint32_t uph = 0;
+        while (ok) {
+            int more = 0;
+            if (lane == 0) more = next_unit(t, uslot, uph, first) ? 1 : 0;
+            more = __shfl_sync(0xFFFFFFFFu, more, 0);
+            t = __shfl_sync(0xFFFFFFFFu, t, 0);
+            if (!more) break;
             const int tile = unit_tile(t);
             const int m0 = (tile / tiles_n) * 256 + (int)rank * 128, n0 = (tile % tiles_n) * TN;
             if (!mbar_wait(tfull_bar(acc), aph, 4)) { ok = false; break; }
@@ -1182,6 +1312,10 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
                    cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream) != cudaSuccess) {
             return AXS6_ERR_LAUNCH;
         }
+        // One cluster per work unit and units taken over through cluster launch control (tune key 6 = 1), unless SMs
+        // are to be left free (tune key 8), which only a fixed number of clusters can do
+        const int64_t dyn_units = p.tail_begin > 0 ? p.tail_begin + (pair_tiles - p.tail_begin) * 2 : pair_tiles * p.splits;
+        p.dynamic = (tune_value(6) == 1 && usable == d.sms && dyn_units > clusters && 2 * dyn_units < (1ll << 30)) ? 1 : 0;
         // Output into an aligned C (and an aligned split-K workspace): the epilogue stores through shared memory and
         // tensor maps
         CUtensorMap mc, mw;
@@ -1214,7 +1348,7 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
                 if (ok) p.c_tma = 2;
             }
         }
-        if (launch_overlapped(true, gemm2_kernel, 2 * clusters, kThreadsGemm, Pair::kSmemBytes, stream, ma, mb, mc, mw, p) != cudaSuccess) return AXS6_ERR_LAUNCH;
+        if (launch_overlapped(true, gemm2_kernel, (unsigned)(p.dynamic ? 2 * dyn_units : 2 * clusters), Pair::kThreads, Pair::kSmemBytes, stream, ma, mb, mc, mw, p) != cudaSuccess) return AXS6_ERR_LAUNCH;
         count_launch();
         if (p.ws) {
             const long long chunks = (long long)M * (p.ws_ld / 4);

@@ -103,7 +103,8 @@ enum { AXS6_LAYOUT_PLANES = 0, /* AXSTensor planes: u8 exponent (rows,nblk), u8 
 const char *axs6_strerror(int status);
 
 /* what: 0 = 1 if the current device can run the kernels (cc 10.x) else 0, 1 = SM count,
- * 2 = ABI version, 3 = number of kernels launched by this process so far. */
+ * 2 = ABI version, 3 = number of kernels launched by this process so far, 4 = the last CUDA error code
+ * a launch of this library returned (0 = none; a debugging aid for AXS6_ERR_LAUNCH). */
 int64_t axs6_query(int what);
 
 /* Performance knobs for experiments and tests (process-wide, never needed for correct results;
@@ -121,6 +122,9 @@ int64_t axs6_query(int what);
  *           other) instead of one 4-D box (the two chunks of a group of 8 k-rows side by side)
  *   key 5   1 = the CTA-pair GEMM writes bf16 outputs with per-thread stores instead of staging each tile
  *           in shared memory for a TMA store
+ *   key 6   1 = the CTA-pair GEMM is launched with one cluster per work unit and running clusters take over the units of
+ *           clusters that have not started (cluster launch control) instead of a fixed assignment of units to 74
+ *           clusters: same results; measured 1-2 % slower alone, better only next to a kernel that holds SMs
  *   key 7   GEMM kernel: 1 single-CTA, 2 CTA pairs on 256 x 256 tiles, 3 CTA pairs on 256 x 512 tiles
  *   key 8   SMs the GEMM leaves free (for a collective on another stream)
  *   key 11  1 = general unpack / unpack-and-sum kernels only (no TMA-fed kernel)

@@ -247,24 +247,26 @@ EPILOGUES = [  # name, M, N, K, a_mn, b_mn: store, reduce-add (tail split) and w
 def test_tensor_map_epilogue_equals_per_thread_stores(name, M, N, K, a_mn, b_mn):
     """The CTA-pair kernel's outputs leave through shared memory and tensor-map stores (tune key 5 = 0) or through
     per-thread stores (key 5 = 1); with and without programmatic dependent launch (key 15); MN-major operands arrive as
-    one 4-D box per stage (key 4 = 0) or as two 2-D boxes (key 4 = 1).  Same accumulators, same rounding, same order of
-    the (at most two, or workspace-ordered) partials: the results are bit-identical."""
+    one 4-D box per stage (key 4 = 0) or as two 2-D boxes (key 4 = 1); work units assigned to clusters up front (key 6 = 0)
+    or taken over through cluster launch control (key 6 = 1).  Same accumulators, same rounding, same order of the (at
+    most two, or workspace-ordered) partials: the results are bit-identical."""
     lib = _lib.load()
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     a = torch.randn((K, M) if a_mn else (M, K), generator=g, device="cuda").to(torch.bfloat16)
     b = torch.randn((K, N) if b_mn else (N, K), generator=g, device="cuda").to(torch.bfloat16)
     outs = {}
-    knobs = ((0, 0, 0), (0, 1, 0), (0, 0, 1), (1, 0, 0))
+    knobs = ((0, 0, 0, 0), (0, 1, 0, 0), (0, 0, 1, 0), (1, 0, 0, 0), (0, 0, 0, 1))
     try:
         lib.axs6_tune(7, 2)
-        for k4, k5, k15 in knobs:
+        for k4, k5, k15, k6 in knobs:
             lib.axs6_tune(4, k4)
             lib.axs6_tune(5, k5)
             lib.axs6_tune(15, k15)
-            outs[(k4, k5, k15)] = (ops.gemm_bf16(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.float32),
+            lib.axs6_tune(6, k6)
+            outs[(k4, k5, k15, k6)] = (ops.gemm_bf16(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.float32),
                                    ops.gemm_bf16(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.bfloat16))
     finally:
-        for key in (4, 5, 15, 7):
+        for key in (4, 5, 6, 15, 7):
             lib.axs6_tune(key, 0)
     gemm_status_ok()
     ref = fp32_matmul(a, b, bool(a_mn), bool(b_mn))
