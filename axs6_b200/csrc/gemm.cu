@@ -82,6 +82,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
     return acp::mbar_wait_bounded(bar, parity, code, &g_gemm_status, kSpinLimit);
 }
 
+// On the way out of a kernel in which a wait gave up: tile loads and products that were already issued may still be
+// running, and their barriers live partly in the other CTA of the pair, so they cannot all be waited for one by one.
+// Every thread lingers for a fifth of a millisecond instead (loads and products complete within microseconds) before
+// shared and tensor memory are released.  Costs nothing on the normal path (one read of the status word).
+__device__ __forceinline__ void linger_if_failed()
+{
+    if (*(volatile int *)&g_gemm_status != 0)
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -337,6 +347,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
     }
 
+    linger_if_failed();
     pdl_launch_dependents();
     tc_fence_before();
     __syncthreads();
@@ -812,6 +823,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         if (p.c_tma && lane == 0) acp::bulk_wait<0>();          // every tensor-map store of this warp has completed
     }
 
+    linger_if_failed();
     pdl_launch_dependents();                             // this CTA has no more work to start: the next kernel may set up
     tc_fence_before();
     __syncthreads();
@@ -976,6 +988,7 @@ gemm2w_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         }
     }
 
+    linger_if_failed();
     pdl_launch_dependents();                             // this CTA has no more work to start: the next kernel may set up
     tc_fence_before();
     __syncthreads();

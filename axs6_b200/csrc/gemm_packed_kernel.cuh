@@ -373,6 +373,7 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         }
     }
 
+    linger_if_failed();
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();
