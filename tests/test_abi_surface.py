@@ -86,3 +86,17 @@ def test_unified_package_exports_the_reference_names():
     assert set(names) <= set(u.__all__)
     u.clear_int8_weight_cache()
     assert u.detect_best_backend() == u.get_backend()
+
+
+def test_environment_knobs_are_applied_and_checked():
+    """AXS6_TUNE="key=value,..." is handed to axs6_tune when the library is loaded; a key outside the table is an error."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = "from axs6_b200 import _lib; _lib.load(); print('loaded')"
+    ok = subprocess.run([sys.executable, "-c", code], cwd=root, env=dict(os.environ, AXS6_TUNE="8=32,15=1"),
+                        capture_output=True, text=True, timeout=300)
+    assert ok.returncode == 0 and "loaded" in ok.stdout, ok.stderr[-1000:]
+    bad = subprocess.run([sys.executable, "-c", code], cwd=root, env=dict(os.environ, AXS6_TUNE="99=1"),
+                         capture_output=True, text=True, timeout=300)
+    assert bad.returncode != 0 and "AXS6_TUNE" in bad.stderr
