@@ -23,23 +23,29 @@ class RoundingMode(Enum):
 
 
 class ErrorFeedbackState:
-    """Per-parameter residual buffers for error-feedback quantisation (quantize.py:47-88)."""
+    """Per-parameter residual buffers for error-feedback quantisation: same methods as the
+    reference's class (quantize.py:47-88)."""
 
     def __init__(self) -> None:
         self._buffers: dict[str, torch.Tensor] = {}
 
-    def get_error(self, name: str, shape: torch.Size, device: torch.device) -> torch.Tensor:
+    def get_buffer(self, name: str, like: torch.Tensor) -> torch.Tensor:
+        """The residual of ``name`` (zeros the first time, and again when the shape changes)."""
         buf = self._buffers.get(name)
-        if buf is None or buf.shape != shape:
-            buf = torch.zeros(shape, device=device, dtype=torch.float32)
+        if buf is None or buf.shape != like.shape:
+            buf = torch.zeros_like(like)
             self._buffers[name] = buf
         return buf
 
-    def update_error(self, name: str, error: torch.Tensor) -> None:
-        self._buffers[name] = error.detach().clone()
+    def update_buffer(self, name: str, error: torch.Tensor) -> None:
+        self._buffers[name] = error.detach()
 
     def reset(self) -> None:
         self._buffers.clear()
+
+    @property
+    def buffer_names(self) -> list[str]:
+        return list(self._buffers.keys())
 
 
 _global_ef_state = ErrorFeedbackState()
@@ -58,10 +64,9 @@ def quantize_with_error_feedback(tensor: torch.Tensor, block_size: int = DEFAULT
                                  state: ErrorFeedbackState | None = None) -> AXSTensor:
     """x + residual -> quantise -> residual = corrected - dequantise (quantize.py:149-200)."""
     st = state if state is not None else _global_ef_state
-    err = st.get_error(param_name, tensor.shape, tensor.device)
-    corrected = tensor.float() + err
+    corrected = tensor + st.get_buffer(param_name, tensor)
     q = quantize(corrected, block_size=block_size, rounding=rounding)
-    st.update_error(param_name, corrected - dequantize(q))
+    st.update_buffer(param_name, corrected - dequantize(q).to(corrected.dtype))
     return q
 
 

@@ -42,9 +42,19 @@ def axs_linear_unified(input: torch.Tensor, weight: torch.Tensor, bias: torch.Te
 def axs_matmul_unified(a: torch.Tensor, b: torch.Tensor, block_size: int = DEFAULT_BLOCK_SIZE,
                        quantize_inputs: bool = True) -> torch.Tensor:
     """NF5 quantised matmul, forward only (functional_unified.py:204-227): both operands are
-    fake-quantised along their LAST dimension, then multiplied; ``a`` (*, M, K), ``b`` (K, N)."""
+    fake-quantised along their LAST dimension, then multiplied; ``a`` (*, M, K), ``b`` (*, K, N) with
+    broadcasting batch dimensions.  Without quantisation the reference's function IS ``torch.matmul``
+    (nothing of the AXS-6 path takes part), and so is this one."""
     from .backend import accelerated_matmul
-    if quantize_inputs:
-        a = _accel_fq(a, block_size, "nearest")
-        b = _accel_fq(b, block_size, "nearest")
-    return accelerated_matmul(a, b)
+    if not quantize_inputs:
+        return torch.matmul(a, b)
+    a = _accel_fq(a, block_size, "nearest")
+    b = _accel_fq(b, block_size, "nearest")
+    if b.dim() <= 2:
+        return accelerated_matmul(a, b)
+    # batched right operand: one product per batch entry
+    batch = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])
+    a3 = a.expand(*batch, *a.shape[-2:]).reshape(-1, *a.shape[-2:])
+    b3 = b.expand(*batch, *b.shape[-2:]).reshape(-1, *b.shape[-2:])
+    out = torch.stack([accelerated_matmul(a3[i], b3[i]) for i in range(a3.shape[0])])
+    return out.reshape(*batch, a.shape[-2], b.shape[-1])

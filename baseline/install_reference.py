@@ -6,9 +6,10 @@
   (``--no-index --no-deps --target``; the checkout is copied to a temporary folder first because
   pip writes build files into the source tree and the checkout is read-only);
 * copies the reference's three CUDA-only test files (``tests/test_triton_kernels.py``,
-  ``tests/test_triton_fused_linear.py``, ``tests/test_mixed_precision.py``) into
-  ``baseline/_ref/reference_tests/`` so that they can be run, unchanged, against this library
-  through the shim of ``tests/reference_shim/`` on a machine with a GPU.
+  ``tests/test_triton_fused_linear.py``, ``tests/test_mixed_precision.py``) and three of its CPU test
+  files (``tests/test_core.py``, ``tests/test_quantize.py``, ``tests/test_unified.py``) into
+  ``baseline/_ref/reference_tests/`` so that they can be run, unchanged, against this library on a
+  machine with a GPU (``axs6_b200.reference_shim`` / ``axs6_b200.reference_alias``).
 
 ``baseline/_ref/`` is git-ignored: nothing of the reference enters this repository's history.
 ``bench.py --impl reference`` and the ``cpu_baseline`` leg time the reference's own eager
@@ -25,14 +26,17 @@ import tempfile
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 TARGET = os.path.join(HERE, "_ref")
-TESTS = ("test_triton_kernels.py", "test_triton_fused_linear.py", "test_mixed_precision.py")
+TESTS = ("test_triton_kernels.py", "test_triton_fused_linear.py", "test_mixed_precision.py",
+         "test_core.py", "test_quantize.py", "test_unified.py")
 
 
 def install(checkout: str = "/root/reference", force: bool = False) -> str | None:
     """Returns the target folder, or None when no checkout is present (e.g. on the GPU box)."""
     if not os.path.isdir(os.path.join(checkout, "axs")):
         return TARGET if os.path.isdir(os.path.join(TARGET, "axs")) else None
-    if os.path.isdir(os.path.join(TARGET, "axs")) and not force:
+    complete = os.path.isdir(os.path.join(TARGET, "axs")) and all(
+        os.path.exists(os.path.join(TARGET, "reference_tests", name)) for name in TESTS)
+    if complete and not force:
         return TARGET
     if os.path.isdir(TARGET):
         shutil.rmtree(TARGET)
@@ -52,4 +56,5 @@ def install(checkout: str = "/root/reference", force: bool = False) -> str | Non
 
 
 if __name__ == "__main__":
-    print(install(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force="--force" in sys.argv))
+    paths = [a for a in sys.argv[1:] if not a.startswith("--")]
+    print(install(paths[0] if paths else "/root/reference", force="--force" in sys.argv))
