@@ -1,6 +1,6 @@
 """V1 (uniform grid) modules, mirror of ``axs/nn/modules.py``: ``AXSLinear`` (:36-102), ``AXSLayerNorm`` (:190-216),
-``AXSEmbedding`` (:223-252), ``AXSMultiheadAttention`` (:259-319) and ``convert_to_axs`` (:326-411).  ``AXSConv2d``
-(:110-183) is outside the path this package accelerates; ``convert_to_axs`` leaves ``nn.Conv2d`` layers alone."""
+``AXSEmbedding`` (:223-252), ``AXSMultiheadAttention`` (:259-319), ``AXSConv2d`` (:110-183: this package's
+quantiser around the library's convolution) and ``convert_to_axs`` (:326-411)."""
 from __future__ import annotations
 
 import math
@@ -12,7 +12,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..core import DEFAULT_BLOCK_SIZE
-from .functional import axs_linear, fake_quantize
+from .functional import axs_conv2d, axs_linear, fake_quantize
 
 
 class AXSLinear(nn.Module):
@@ -44,6 +44,38 @@ class AXSLinear(nn.Module):
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "
                 f"block_size={self.block_size}, quantize_input={self.quantize_input}, quantize_grad={self.quantize_grad}")
+
+
+class AXSConv2d(nn.Module):
+    """``nn.Conv2d`` whose weight, input and gradient pass through the uniform-grid quantiser."""
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1,
+                 groups: int = 1, bias: bool = True, block_size: int = DEFAULT_BLOCK_SIZE) -> None:
+        super().__init__()
+        as_pair = lambda v: v if isinstance(v, tuple) else (v, v)
+        self.in_channels, self.out_channels, self.groups, self.block_size = in_channels, out_channels, groups, block_size
+        self.kernel_size, self.stride = as_pair(kernel_size), as_pair(stride)
+        self.padding, self.dilation = as_pair(padding), as_pair(dilation)
+        self.weight = nn.Parameter(torch.empty(out_channels, in_channels // groups, *self.kernel_size))
+        if bias:
+            self.bias = nn.Parameter(torch.empty(out_channels))
+        else:
+            self.register_parameter("bias", None)
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
+        if self.bias is not None:
+            bound = 1 / math.sqrt(self.weight.shape[1] * self.kernel_size[0] * self.kernel_size[1])
+            nn.init.uniform_(self.bias, -bound, bound)
+
+    def forward(self, input: torch.Tensor) -> torch.Tensor:
+        return axs_conv2d(input, self.weight, self.bias, self.stride, self.padding, self.dilation, self.groups,
+                          self.block_size)
+
+    def extra_repr(self) -> str:
+        return (f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}, stride={self.stride}, "
+                f"padding={self.padding}, block_size={self.block_size}")
 
 
 class AXSLayerNorm(nn.Module):
@@ -109,8 +141,8 @@ class AXSMultiheadAttention(nn.Module):
 
 def convert_to_axs(model: nn.Module, block_size: int = DEFAULT_BLOCK_SIZE, quantize_input: bool = True,
                    quantize_grad: bool = True, skip_layers: set[str] | None = None, inplace: bool = False) -> nn.Module:
-    """Swap ``nn.Linear`` / ``nn.LayerNorm`` / ``nn.Embedding`` for their V1 AXS-6 counterparts, which take over the
-    old modules' parameters; deep copy unless ``inplace``.  ``nn.Conv2d`` is left as it is."""
+    """Swap ``nn.Linear`` / ``nn.Conv2d`` / ``nn.LayerNorm`` / ``nn.Embedding`` for their V1 AXS-6 counterparts, which
+    take over the old modules' parameters; deep copy unless ``inplace``."""
     if not inplace:
         model = copy.deepcopy(model)
     skip = skip_layers or set()
@@ -118,11 +150,18 @@ def convert_to_axs(model: nn.Module, block_size: int = DEFAULT_BLOCK_SIZE, quant
     def swap(parent: nn.Module, prefix: str) -> None:
         for name, child in list(parent.named_children()):
             full = f"{prefix}.{name}" if prefix else name
-            if full in skip or isinstance(child, (AXSLinear, AXSLayerNorm, AXSEmbedding)):
+            if full in skip or isinstance(child, (AXSLinear, AXSConv2d, AXSLayerNorm, AXSEmbedding)):
                 continue
             if isinstance(child, nn.Linear):
                 new = AXSLinear(child.in_features, child.out_features, child.bias is not None, block_size,
                                 quantize_input, quantize_grad).to(child.weight.device)
+                new.weight = child.weight
+                if child.bias is not None:
+                    new.bias = child.bias
+                setattr(parent, name, new)
+            elif isinstance(child, nn.Conv2d) and isinstance(child.padding, tuple) and child.padding_mode == "zeros":
+                new = AXSConv2d(child.in_channels, child.out_channels, child.kernel_size, child.stride, child.padding,
+                                child.dilation, child.groups, child.bias is not None, block_size).to(child.weight.device)
                 new.weight = child.weight
                 if child.bias is not None:
                     new.bias = child.bias

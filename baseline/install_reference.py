@@ -6,8 +6,9 @@
   (``--no-index --no-deps --target``; the checkout is copied to a temporary folder first because
   pip writes build files into the source tree and the checkout is read-only);
 * copies the reference's three CUDA-only test files (``tests/test_triton_kernels.py``,
-  ``tests/test_triton_fused_linear.py``, ``tests/test_mixed_precision.py``) and three of its CPU test
-  files (``tests/test_core.py``, ``tests/test_quantize.py``, ``tests/test_unified.py``) into
+  ``tests/test_triton_fused_linear.py``, ``tests/test_mixed_precision.py``) and five of its CPU test
+  files (``tests/test_core.py``, ``tests/test_quantize.py``, ``tests/test_unified.py``, ``tests/test_nn.py``,
+  ``tests/test_training.py``) into
   ``baseline/_ref/reference_tests/`` so that they can be run, unchanged, against this library on a
   machine with a GPU (``axs6_b200.reference_shim`` / ``axs6_b200.reference_alias``).
 
@@ -27,7 +28,7 @@ import tempfile
 HERE = os.path.dirname(os.path.abspath(__file__))
 TARGET = os.path.join(HERE, "_ref")
 TESTS = ("test_triton_kernels.py", "test_triton_fused_linear.py", "test_mixed_precision.py",
-         "test_core.py", "test_quantize.py", "test_unified.py")
+         "test_core.py", "test_quantize.py", "test_unified.py", "test_nn.py", "test_training.py")
 
 
 def install(checkout: str = "/root/reference", force: bool = False) -> str | None:

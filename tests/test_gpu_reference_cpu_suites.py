@@ -1,8 +1,9 @@
 """The reference's CPU unit-test files, run UNCHANGED against this library on the GPU.
 
-``tests/test_core.py``, ``tests/test_quantize.py`` and ``tests/test_unified.py`` of the reference pin the
-Python surface of the path (block and tensor round trips, rounding modes, NF5 tables, fake-quantise
-properties, the unified functional / module / pipeline API).  A child pytest loads
+``tests/test_core.py``, ``tests/test_quantize.py``, ``tests/test_unified.py``, ``tests/test_nn.py`` and
+``tests/test_training.py`` of the reference pin the Python surface of the path (block and tensor round trips,
+rounding modes, NF5 tables, fake-quantise properties, the functional / module / optimiser / pipeline API and
+the convergence of small fits).  A child pytest loads
 ``axs6_b200.reference_alias``, which makes ``import axs`` resolve to this package and CUDA the default
 device of new tensors, and runs the copies under ``baseline/_ref/reference_tests``.  Skipped when the
 copies are absent.
@@ -25,7 +26,7 @@ DESELECT: list[str] = [
 ]
 
 
-@pytest.mark.parametrize("name", ["test_core.py", "test_quantize.py", "test_unified.py"])
+@pytest.mark.parametrize("name", ["test_core.py", "test_quantize.py", "test_unified.py", "test_nn.py", "test_training.py"])
 def test_reference_cpu_file_passes_against_this_library(name):
     path = os.path.join(REF_TESTS, name)
     if not os.path.exists(path):
