@@ -179,9 +179,10 @@ __global__ void __launch_bounds__(kThreads) fq_generic_kernel(const FqArgs a)
     }
 }
 
-// Launches of up to this many 8-value chunks (2 Mi values) ask for programmatic dependent launch: they are bound by
-// launch latency (1024 x 1024 fp32: 6.2 -> 4.8 us back to back), while from 4096 x 4096 on the overlap costs 5-15 %.
-constexpr int64_t kSmallLaunch = 1ll << 18;
+// Launches of up to this many 8-value chunks (8 Mi values) ask for programmatic dependent launch: the small ones are
+// bound by launch latency (1024 x 1024 fp32: 6.2 -> 4.8 us back to back; a 12-layer GPT step with 8192 x 1024
+// activations: 25.2 -> 25.0 ms), while from 4096 x 4096 on the overlap costs 5-15 %.
+constexpr int64_t kSmallLaunch = 1ll << 20;
 
 // Persistent launch: at most `want_per_sm` CTAs per SM (0 = as many as fit).  Measured on B200:
 // a streaming kernel is fastest with about 48 KB of loads in flight per SM; more resident
