@@ -368,6 +368,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 //   * "stage free" and "accumulator ready" are committed by the leader to its own barrier and,
 //     with a second tcgen05.commit, to the peer's barrier at the same offset;
 //   * "accumulator drained" arrives on the leader's barrier from the epilogue warps of both CTAs.
+// Seven warps per CTA: TMA producer, MMA issuer (leader only), four epilogue warps (tensor memory -> registers ->
+// swizzled pieces in shared memory -> tensor-map stores), and a scheduler warp that is idle with the default static
+// schedule (unit u of cluster c is c + u * clusters) and hands out work units with the dynamic one (see clc_try_cancel).
 // All waits are bounded as in the 1-CTA kernel.
 struct Pair {
     static constexpr int TN = 256;                             // tile width
