@@ -39,6 +39,10 @@ def test_reference_cpu_file_passes_against_this_library(name):
         if d.startswith(name):
             cmd += ["--deselect", d]
     out = subprocess.run(cmd, env=env, cwd=REF_TESTS, capture_output=True, text=True, timeout=900)
+    if out.returncode != 0:
+        # a child that died before its tests ran (no summary line) is started once more; test failures are final
+        if " passed" not in out.stdout and " failed" not in out.stdout:
+            out = subprocess.run(cmd, env=env, cwd=REF_TESTS, capture_output=True, text=True, timeout=900)
     tail = (out.stdout + out.stderr)[-6000:]
     assert out.returncode == 0, f"reference test file {name} failed against this library:\n{tail}"
     assert " passed" in out.stdout, tail
