@@ -471,12 +471,18 @@ __device__ __forceinline__ void tc_commit2(uint32_t bar_cluster)
 // (Shared memory ends below 256 KB, so the sum never carries out of the field.)
 __device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo) { return ((addr & 0x3FFFFu) >> 4) | ((lbo >> 4) << 16); }
 __device__ __forceinline__ uint32_t desc_hi(uint32_t sbo) { return (sbo >> 4) | (1u << 14) | (2u << 29); }
+template <bool kTf32 = false>
 __device__ __forceinline__ void tc_mma2_words(uint32_t tmem_d, uint32_t alo, uint32_t ahi, uint32_t blo, uint32_t bhi,
                                               uint32_t idesc, uint32_t accumulate)
 {
-    asm volatile("{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %6, 0;\n mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n"
-                 " tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}"
-                 ::"r"(tmem_d), "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc), "r"(accumulate) : "memory");
+    if (kTf32)
+        asm volatile("{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %6, 0;\n mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n"
+                     " tcgen05.mma.cta_group::2.kind::tf32 [%0], da, db, %5, p;\n}"
+                     ::"r"(tmem_d), "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc), "r"(accumulate) : "memory");
+    else
+        asm volatile("{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %6, 0;\n mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n"
+                     " tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}"
+                     ::"r"(tmem_d), "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tc_mma2(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
@@ -582,11 +588,13 @@ __device__ __forceinline__ void epilogue_tile_tma_f32(const Params &p, const CUt
     }
 }
 
+template <bool kTf32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Pair::kThreads, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
              const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_ws, const Params p)
 {
     constexpr int TN = Pair::TN;
+    constexpr int kBK = kTf32 ? 32 : 64;                // values per k-block (128 bytes per row either way)
     constexpr int kStages2 = Pair::kStages, kA2Bytes = Pair::kABytes, kStage2Bytes = Pair::kStageBytes;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -618,7 +626,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     // contraction, accumulated into the zero-filled output with red.add; with two addends the sum does not
     // depend on their order.  p.splits > 1 splits every tile instead.
     const int splits = p.splits;
-    const int total_kb = (p.K + BK - 1) / BK;
+    const int total_kb = (p.K + kBK - 1) / kBK;
     const int all_tiles = tiles_m * tiles_n;
     const int tail_begin = splits > 1 ? 0 : ((p.tail_begin <= 0 || p.tail_begin > all_tiles) ? all_tiles : p.tail_begin);
     const int tail_parts = splits > 1 ? splits : 2;
@@ -686,7 +694,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                     const uint32_t lead_full = map_to_cta(full_bar(s), 0);
                     if (rank == 0) mbar_expect_tx(full_bar(s), 2 * kStage2Bytes);
                     const uint32_t sa = base + s * kStage2Bytes, sb = sa + kA2Bytes;
-                    const int k0 = kb * BK;
+                    const int k0 = kb * kBK;
                     if (!p.a_mn) {
                         tma_load_2d_pair(sa, &map_a, lead_full, k0, m0);
                     } else if (p.a_mn4) {
@@ -709,7 +717,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         // ------------------------------------------------------------------ MMA issuer (leader CTA only)
         if (lane == 0 && rank == 0) {
             // M = 256 (>> 4 = 16) over the pair, N = TN
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
+            constexpr uint32_t fmt = kTf32 ? 2u : 1u;   // operand format within the instruction kind: bf16 / tf32
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
                                    ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
             int s = 0, acc = 0;
             uint32_t ph = 0, aph = 0;
@@ -734,7 +743,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                     uint32_t alo = a_lo0 + soff, blo = b_lo0 + soff;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        tc_mma2_words(d_tmem, alo, a_hi, blo, b_hi, idesc, fresh);
+                        tc_mma2_words<kTf32>(d_tmem, alo, a_hi, blo, b_hi, idesc, fresh);
                         fresh = 1u;
                         alo += a_kinc; blo += b_kinc;
                     }
@@ -1180,11 +1189,11 @@ static int launch_gemm_packed(const void *a, const void *a_exps, int64_t lda, co
 
 // Split-K plan for a problem with few output tiles and a long contraction (fp32 output): how many K ranges per tile
 // so that most SMs get a work unit.  `cap` bounds the number of partials.
-static int64_t plan_pair_splits(const DeviceInfo &d, int64_t M, int64_t N, int64_t K, int64_t cap)
+static int64_t plan_pair_splits(const DeviceInfo &d, int64_t M, int64_t N, int64_t K, int64_t cap, int64_t bk)
 {
     const int64_t pair_tiles = ((M + 255) / 256) * ((N + Pair::TN - 1) / Pair::TN);
     if (pair_tiles >= d.sms / 2) return 1;
-    const int64_t total_kb = (K + BK - 1) / BK;
+    const int64_t total_kb = (K + bk - 1) / bk;
     int64_t splits = (d.sms / 2) / pair_tiles;
     if (splits > total_kb / 16) splits = total_kb / 16;
     if (splits > cap) splits = cap;
@@ -1227,16 +1236,17 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     const int64_t mode = tune_value(7);
     int64_t pair_splits = 1;
     bool use_ws = false;
-    if (!kTf32 && may_split) {
-        pair_splits = plan_pair_splits(d, M, N, K, max_pair_splits);
+    if (may_split) {
+        pair_splits = plan_pair_splits(d, M, N, K, max_pair_splits, bk);
         // With a workspace the partials are kept apart and added in a fixed order by a second kernel: more than two
         // partials without giving up reproducibility.
         if (ws && aligned16(ws) && split_mode != 2) {
-            const int64_t want = plan_pair_splits(d, M, N, K, 8);
+            const int64_t want = plan_pair_splits(d, M, N, K, 8, bk);
             if (want > 2 && ws_bytes >= want * M * ws_ld_of(N) * 4) { pair_splits = want; use_ws = true; }
         }
     }
-    const bool pairs = !kTf32 && mode != 1 && (mode == 2 || mode == 3 || pair_tiles * pair_splits >= d.sms / 4);
+    // (the TF32 instruction takes K-major operands only, and so does its CTA-pair instantiation)
+    const bool pairs = !(kTf32 && (a_mn || b_mn)) && mode != 1 && (mode == 2 || mode == 3 || pair_tiles * pair_splits >= d.sms / 4);
 
     CUtensorMap ma, mb;
     const bool oka = a_mn ? make_map(&ma, a, esize, (uint64_t)M, (uint64_t)K, (uint64_t)lda, bk)
@@ -1268,7 +1278,7 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
     p.b_lbo = b_mn ? p.mn_box_bytes : 0u; p.b_sbo = 1024u; p.b_kstep = b_mn ? mn_kstep : 32u;
 
     if (pairs) {
-        if (may_split && split_mode == 2 && K >= 16 * BK) p.splits = 2;
+        if (may_split && split_mode == 2 && K >= 16 * bk) p.splits = 2;
         if (pair_splits > 1) p.splits = (int)pair_splits;
         // 256 x 512 tiles (a quarter less operand feed per flop): taken when no split is planned and the wider tiles fill
         // their waves of clusters about as well as the 256 x 256 ones (tune key 7: 3 forces them, 2 forbids them)
@@ -1281,12 +1291,12 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
             const double t_wide = (double)((wide_tiles + usable_c - 1) / usable_c) * 2.0 * 0.85;     // 0.85: measured gain per flop
             // measured: the wide tile pays only for long contractions (16384 x 4096 x 4096 equal; dW with K = 16384 +4 %,
             // K = 32000 +8 %; K = 1024 is 30 % slower because its two accumulators are drained one tile at a time)
-            bool wide = p.splits == 1 && mode != 2 && wide_tiles >= usable_c && t_wide <= t_narrow && N > 256 && K >= 8192;
-            if (p.splits == 1 && may_split && K >= 32 * BK && pair_tiles > usable_c) {
+            bool wide = !kTf32 && p.splits == 1 && mode != 2 && wide_tiles >= usable_c && t_wide <= t_narrow && N > 256 && K >= 8192;
+            if (p.splits == 1 && may_split && K >= 32 * bk && pair_tiles > usable_c) {
                 const int64_t rem = pair_tiles % usable_c;
                 if (rem > 0 && 2 * rem <= usable_c) wide = wide && fill(wide_tiles) >= 0.9;      // the tail split would help the narrow kernel
             }
-            if (mode == 3 && p.splits == 1 && N > 256) wide = true;
+            if (mode == 3 && p.splits == 1 && N > 256 && !kTf32) wide = true;
             if (wide) {
                 if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm2w_kernel), PairW::kSmemBytes)) return AXS6_ERR_LAUNCH;
                 const int clusters = (int)(wide_tiles < usable_c ? wide_tiles : usable_c);
@@ -1295,8 +1305,8 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
                 return check_launch();
             }
         }
-        if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm2_kernel), Pair::kSmemBytes)) return AXS6_ERR_LAUNCH;
-        if (tune_value(4) != 1) {
+        if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm2_kernel<kTf32>), Pair::kSmemBytes)) return AXS6_ERR_LAUNCH;
+        if (!kTf32 && tune_value(4) != 1) {
             if (a_mn && make_mn4_map(&ma, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda)) {
                 p.a_mn4 = 1; p.a_lbo = 1024u; p.a_sbo = 2048u; p.a_kstep = 4096u;
             }
@@ -1311,7 +1321,7 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
         // computed as two K halves each, so that wave takes half the time.  Weight gradient 4096 x 4096 x 16384:
         // 256 tiles on 74 clusters, 3 full waves + 34 tiles -> 68 half units: 3.5 waves instead of 4.  The rows
         // that hold those tiles are zero-filled first.
-        if (p.splits == 1 && may_split && K >= 32 * BK && pair_tiles > clusters) {
+        if (p.splits == 1 && may_split && K >= 32 * bk && pair_tiles > clusters) {
             const int64_t rem = pair_tiles % clusters;
             if (rem > 0 && 2 * rem <= clusters) {
                 p.tail_begin = (int)(pair_tiles - rem);
@@ -1364,7 +1374,7 @@ static int launch_gemm(const void *a, const void *b, void *c, const float *bias,
                 if (ok) p.c_tma = 2;
             }
         }
-        if (launch_overlapped(true, gemm2_kernel, (unsigned)(p.dynamic ? 2 * dyn_units : 2 * clusters), Pair::kThreads, Pair::kSmemBytes, stream, ma, mb, mc, mw, p) != cudaSuccess) return AXS6_ERR_LAUNCH;
+        if (launch_overlapped(true, gemm2_kernel<kTf32>, (unsigned)(p.dynamic ? 2 * dyn_units : 2 * clusters), Pair::kThreads, Pair::kSmemBytes, stream, ma, mb, mc, mw, p) != cudaSuccess) return AXS6_ERR_LAUNCH;
         count_launch();
         if (p.ws) {
             const long long chunks = (long long)M * (p.ws_ld / 4);
@@ -1455,7 +1465,7 @@ AXS6_API int64_t axs6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int 
     if (M <= 0 || N <= 0 || K <= 0 || c_dtype != AXS6_F32) return 0;
     const DeviceInfo &d = device_info();
     if (!d.valid || !d.ok) return 0;
-    const int64_t want = gemm::plan_pair_splits(d, M, N, K, 8);
+    const int64_t want = gemm::plan_pair_splits(d, M, N, K, 8, gemm::BK);
     return want > 2 ? want * M * gemm::ws_ld_of(N) * 4 : 0;
 }
 

@@ -470,8 +470,11 @@ AXS6_API int axs6_linear_bwd(const void *g, int g_dtype, int64_t ldg, const void
             if (rc) return rc;
         }
         if (db) {
-            rc = (flags & AXS6_LINEAR_BIAS_FROM_QUANTIZED) ? axs6_bias_grad(gq, AXS6_F32, ldg4, M, N, db, db_partial, stream)
-                                                           : axs6_bias_grad(g, g_dtype, ldg, M, N, db, db_partial, stream);
+            // the quantised gradient's sums where the graph asks for them; without gradient quantisation gq is only the
+            // TF32-rounded copy of g for the products, and the sums are taken from g itself
+            const bool from_gq = (flags & AXS6_LINEAR_BIAS_FROM_QUANTIZED) && (flags & AXS6_LINEAR_QUANTIZE_GRAD);
+            rc = from_gq ? axs6_bias_grad(gq, AXS6_F32, ldg4, M, N, db, db_partial, stream)
+                         : axs6_bias_grad(g, g_dtype, ldg, M, N, db, db_partial, stream);
             if (rc) return rc;
         }
         return AXS6_OK;

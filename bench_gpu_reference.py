@@ -7,7 +7,8 @@ its own CUDA code paths are timed with CUDA events on the benchmark's tensors:
 * ``triton_fused_fake_quantize`` (axs/unified/triton_kernels.py:295-382): the reference's Triton kernel, when
   Triton can compile for this GPU,
 * ``AXSLinearMixedPrecision`` (axs/unified/mixed_precision.py:193-275) forward + backward at the Linear
-  benchmark's size: the reference's fake-quantise passes around ``F.linear`` (cuBLAS).
+  benchmark's size: the reference's fake-quantise passes around ``F.linear`` (cuBLAS),
+* ``axs_linear_unified`` (axs/unified/functional_unified.py:173-201), the fp32 graph of the same layer.
 
 Each result is also compared with this library's output on the same input (bit for bit for nearest rounding),
 which is a full-size parity check against the reference itself.  Nothing of this library runs inside the
@@ -102,5 +103,26 @@ def run(dev, x, ours_ms: float, linear_ms: float | None = None) -> dict:
         del layer, xin, go
     except Exception as e:
         out["linear_step"] = {"error": repr(e)[:300]}
+    torch.cuda.empty_cache()
+    try:
+        fu = importlib.import_module("axs.unified.functional_unified")
+        M, K, N = 16384, 4096, 4096
+        g = torch.Generator(device=dev).manual_seed(13)
+        xin = torch.randn(M, K, generator=g, device=dev).requires_grad_(True)
+        w = (torch.randn(N, K, generator=g, device=dev) * 0.02).requires_grad_(True)
+        b = torch.zeros(N, device=dev, requires_grad=True)
+        go = torch.randn(M, N, generator=g, device=dev)
+
+        def step32():
+            xin.grad = w.grad = b.grad = None
+            fu.axs_linear_unified(xin, w, b).backward(go)
+
+        ms = _time(torch, step32, 2, 5)
+        out["linear_step_fp32_graph"] = {
+            "ms_per_step": ms, "TFLOPs": 6.0 * M * N * K / (ms * 1e-3) / 1e12,
+            "workload": f"axs_linear_unified forward + backward, M={M}, K={K}, N={N}, fp32 tensors (compare linear.fp32_graph)"}
+        del xin, w, b, go
+    except Exception as e:
+        out["linear_step_fp32_graph"] = {"error": repr(e)[:300]}
     torch.cuda.empty_cache()
     return out

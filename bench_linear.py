@@ -201,6 +201,26 @@ def _packed_variant(lib, dev, steps: int, t_of) -> dict:
     return out
 
 
+def _fp32_graph(dev, t_of) -> dict:
+    """axs_linear_unified forward + backward at the same size with fp32 tensors (one GPU)."""
+    import importlib
+    fu = importlib.import_module("axs6_b200.unified.functional_unified")
+    g = torch.Generator(device=dev).manual_seed(4200)
+    x = torch.randn(M_ROWS, K, generator=g, device=dev).requires_grad_(True)
+    w = (torch.randn(N, K, generator=g, device=dev) * 0.02).requires_grad_(True)
+    b = torch.zeros(N, device=dev, requires_grad=True)
+    go = torch.randn(M_ROWS, N, generator=g, device=dev)
+
+    def step():
+        x.grad = w.grad = b.grad = None
+        fu.axs_linear_unified(x, w, b).backward(go)
+
+    ms = t_of(step, 5)
+    return {"ms_per_step": ms, "TFLOPs": 6.0 * M_ROWS * N * K / (ms * 1e-3) / 1e12,
+            "workload": f"axs_linear_unified forward + backward, M={M_ROWS}, K={K}, N={N}, fp32 tensors: fake-quantise in fp32, "
+                        "forward as three TF32 products (fp32 accuracy), backward products in TF32"}
+
+
 def run(args, rank: int, world: int, dev, pk: dict, steps: int | None = None) -> dict:
     import torch.distributed as dist
     lib = _lib.load()
@@ -304,6 +324,16 @@ def run(args, rank: int, world: int, dev, pk: dict, steps: int | None = None) ->
             packed = {"error": repr(e)}
         torch.cuda.empty_cache()
 
+    # the fp32 graph of the same layer (the unified Linear: fp32 in / out, fp32-accurate forward through three TF32
+    # products, TF32 backward products), through the Python operator
+    fp32_graph = None
+    if rank == 0:
+        try:
+            fp32_graph = _fp32_graph(dev, t_of)
+        except Exception as e:
+            fp32_graph = {"error": repr(e)[:300]}
+        torch.cuda.empty_cache()
+
     strong = None
     if world > 1:
         Ms = M_ROWS // world
@@ -337,6 +367,8 @@ def run(args, rank: int, world: int, dev, pk: dict, steps: int | None = None) ->
     out.update(parity)
     if packed is not None:
         out["operands_packed"] = packed
+    if fp32_graph is not None:
+        out["fp32_graph"] = fp32_graph
     if strong is not None:
         out["strong"] = strong
         out["nccl_max_ctas"] = nccl_ctas

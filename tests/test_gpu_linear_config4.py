@@ -274,3 +274,49 @@ def test_tensor_map_epilogue_equals_per_thread_stores(name, M, N, K, a_mn, b_mn)
     for key in knobs[1:]:
         assert torch.equal(outs[key][0], outs[knobs[0]][0]), f"fp32 output differs with knobs {key}"
         assert torch.equal(outs[key][1], outs[knobs[0]][1]), f"bf16 output differs with knobs {key}"
+
+
+@pytest.mark.parametrize("M,N,K", [(4096, 2048, 1024), (3000, 1544, 1032), (9472, 1024, 520)])
+def test_tf32_gemm_on_cta_pairs(M, N, K):
+    """fp32 operands at sizes where the TF32 instantiation of the CTA-pair kernel runs (at least 37 tile pairs):
+    operands pre-rounded to TF32 give the fp32 product up to accumulation order; the single-CTA kernel on the same
+    operands (tune key 7 = 1) agrees to the same bound."""
+    lib = _lib.load()
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g, device="cuda")
+    b = torch.randn(N, K, generator=g, device="cuda")
+    tf32 = lambda t: ((t.view(torch.int32) + 0x1000) & ~0x1FFF).view(torch.float32)
+    a, b = tf32(a), tf32(b)
+    ref = a.double() @ b.double().t()
+    c = ops.gemm_bf16(a, b)
+    gemm_status_ok()
+    assert rel(c, ref) < fp32_tol(K)
+    try:
+        lib.axs6_tune(7, 1)
+        c1 = ops.gemm_bf16(a, b)
+    finally:
+        lib.axs6_tune(7, 0)
+    gemm_status_ok()
+    assert rel(c1, ref) < fp32_tol(K)
+    assert rel(c, c1.double()) < fp32_tol(K)
+
+
+def test_fp32_graph_linear_at_a_pair_kernel_size():
+    """axs_linear_unified (fp32 in / out) at 4096 x 1024 -> 2048: forward within 1e-5 of the fp64 product of the
+    fake-quantised operands (three TF32 products), gradients within the TF32 bar of 1e-3."""
+    fu = importlib.import_module("axs6_b200.unified.functional_unified")
+    qu = importlib.import_module("axs6_b200.unified.quantize_unified")
+    M, K, N = 4096, 1024, 2048
+    g = torch.Generator(device="cuda").manual_seed(77)
+    x = torch.randn(M, K, generator=g, device="cuda").requires_grad_(True)
+    w = (torch.randn(N, K, generator=g, device="cuda") * 0.05).requires_grad_(True)
+    bias = torch.randn(N, generator=g, device="cuda").requires_grad_(True)
+    go = torch.randn(M, N, generator=g, device="cuda")
+    y = fu.axs_linear_unified(x, w, bias, quantize_grad=False)
+    y.backward(go)
+    gemm_status_ok()
+    xq, wq = qu.fused_fake_quantize(x.detach()).double(), qu.fused_fake_quantize(w.detach()).double()
+    assert rel(y.detach(), xq @ wq.t() + bias.detach().double()) < 1e-5
+    assert rel(x.grad, go.double() @ wq) < 1e-3
+    assert rel(w.grad, go.double().t() @ xq) < 1e-3
+    assert rel(bias.grad, go.double().sum(0)) < 1e-5
