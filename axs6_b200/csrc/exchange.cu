@@ -46,7 +46,7 @@ __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %
 // that word + header bytes)) added to, or for the first source stored into, the 32 accumulators.
 template <int HDR, bool kFirst>
 __device__ __forceinline__ void accumulate_record(const uint32_t (&W)[7], uint32_t head, uint32_t sft,
-                                                  const uint32_t *table, const float *lev, float (&acc)[32])
+                                                  const uint32_t *table, uint32_t lane4, const float *lev, float (&acc)[32])
 {
     uint32_t pay[6];
 #pragma unroll
@@ -57,11 +57,12 @@ __device__ __forceinline__ void accumulate_record(const uint32_t (&W)[7], uint32
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             const int bit = 6 * i, word = bit >> 5, off = bit & 31;
-            uint32_t v;
-            if (off == 0) v = pay[word] << 2;
-            else if (off <= 26) v = pay[word] >> (off - 2);
-            else v = __funnelshift_r(pay[word], pay[word + 1], off - 2);
-            const float val = __uint_as_float(*reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(table) + (v & 0xFCu)) + kk);
+            uint32_t v;                                 // the code at bits 7..12
+            if (off < 7) v = pay[word] << (7 - off);
+            else if (off == 7) v = pay[word];
+            else if (off <= 26) v = pay[word] >> (off - 7);
+            else v = __funnelshift_r(pay[word], pay[word + 1], off - 7);
+            const float val = __uint_as_float(*reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(table) + ((v & 0x1F80u) | lane4)) + kk);
             acc[i] = kFirst ? val : AXS6_ADD(acc[i], val);
         }
     } else {
@@ -88,7 +89,9 @@ __global__ void __launch_bounds__(kThreadsX) unpack_sum_bulk_kernel(const __grid
     constexpr int kTile = kBlocks * Out<Tout>::kRowBytes;
     constexpr int kPieces = Out<Tout>::kPieces;
     extern __shared__ uint8_t raw[];
-    __shared__ __align__(16) uint32_t table[64];     // code -> sign and level bits, exponent field lowered by 120
+    // code -> sign and level bits, exponent field lowered by 120; one copy per lane (entry (code, lane) is word
+    // code * 32 + lane), so that the 32 lookups of a warp always fall into 32 different banks
+    __shared__ __align__(128) uint32_t table[64 * 32];
     __shared__ float lev[32];
     __shared__ int gave_up[2];                       // by parity of the group: some consumer's wait ran out
     uint8_t *base = raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u);
@@ -102,11 +105,11 @@ __global__ void __launch_bounds__(kThreadsX) unpack_sum_bulk_kernel(const __grid
         fence_barrier_init();
         fence_async_smem();
     }
-    if (tid < 64) {
-        const uint32_t bits = g_codebook_bits[tid & 31];
-        table[tid] = (bits - (120u << 23)) | ((uint32_t)(tid >> 5) << 31);
-        if (tid < 32) lev[tid] = __uint_as_float(bits);
+    for (int i = tid; i < 64 * 32; i += kThreadsX) {
+        const uint32_t code = (uint32_t)i >> 5;
+        table[i] = (g_codebook_bits[code & 31u] - (120u << 23)) | ((code >> 5) << 31);
     }
+    if (tid < 32) lev[tid] = __uint_as_float(g_codebook_bits[tid]);
     __syncthreads();
 
     const int64_t groups = (nblocks + kBlocks - 1) / kBlocks;
@@ -144,6 +147,7 @@ __global__ void __launch_bounds__(kThreadsX) unpack_sum_bulk_kernel(const __grid
     // -------------------------------------------------------------------- consumers: one thread per block
     const uint32_t wb = (uint32_t)(REC * tid) >> 2, sh = (uint32_t)(REC * tid) & 3u;
     const uint32_t sft = 8u * (sh + HDR);
+    const uint32_t lane4 = ((uint32_t)tid & 31u) << 2;
     uint32_t piece[kPieces];
 #pragma unroll
     for (int i = 0; i < kPieces; ++i)
@@ -181,8 +185,8 @@ __global__ void __launch_bounds__(kThreadsX) unpack_sum_bulk_kernel(const __grid
                 head_shift = 0u;
             }
             if (ok && b < nblocks) {
-                if (r == 0) accumulate_record<HDR, true>(W, W[0] >> head_shift, sft_r, table, lev, acc);
-                else        accumulate_record<HDR, false>(W, W[0] >> head_shift, sft_r, table, lev, acc);
+                if (r == 0) accumulate_record<HDR, true>(W, W[0] >> head_shift, sft_r, table, lane4, lev, acc);
+                else        accumulate_record<HDR, false>(W, W[0] >> head_shift, sft_r, table, lane4, lev, acc);
             }
         }
         if (ok && b < nblocks) {
