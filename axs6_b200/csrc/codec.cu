@@ -950,7 +950,7 @@ struct UnpackOut<float> { static constexpr int kRowBytes = 128, kPieces = 8, kSw
 template <typename Tout, int HDR>
 constexpr int unpack_smem_bytes() { return 1024 + kCtrlBytes + 2 * kFastBlocks * UnpackOut<Tout>::kRowBytes + kStages * kFastBlocks * (HDR + 24); }
 
-template <typename Tout, int HDR>
+template <typename Tout, int HDR, bool kLane>
 __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const __grid_constant__ CUtensorMap ymap,
                                                                          const uint8_t *__restrict__ in, int64_t nblocks)
 {
@@ -963,9 +963,10 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
     // code -> value bits (bf16: in the low half), one copy per lane: entry (code, lane) is word code * 32 + lane, so a
     // warp's 32 lookups always hit 32 different banks (with one shared copy the codes of a warp collide about three
     // deep, and the lookups, not DRAM, bounded the kernel)
-    // (bf16 output only: with fp32 output the kernel is not bound by the lookups and the larger table costs 2 %)
-    constexpr int kCopies = kBf16 ? 32 : 1;
-    constexpr int kCodeShift = kBf16 ? 7 : 2;       // byte offset of an entry = code << kCodeShift (+ lane * 4)
+    // (kLane: bf16 output of up to 64 Mi values, where it is worth 10 %; for larger launches, which are bound by
+    // instruction issue, and for fp32 output the single shared copy is 2-4 % faster)
+    constexpr int kCopies = kLane ? 32 : 1;
+    constexpr int kCodeShift = kLane ? 7 : 2;       // byte offset of an entry = code << kCodeShift (+ lane * 4)
     __shared__ __align__(128) uint32_t tlo[64 * kCopies];
     __shared__ float lev[32];
     uint8_t *base = raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u);
@@ -984,7 +985,7 @@ __global__ void __launch_bounds__(kFastBlocks) unpack_nf5_b32_bulk_kernel(const 
                        : ((bits - (120u << 23)) | (sign << 31));
     }
     if (tid < 32) lev[tid] = __uint_as_float(g_codebook_bits[tid]);
-    const uint32_t lane4 = kBf16 ? ((uint32_t)tid & 31u) << 2 : 0u;
+    const uint32_t lane4 = kLane ? ((uint32_t)tid & 31u) << 2 : 0u;
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
         fence_barrier_init();
@@ -1134,12 +1135,21 @@ static int launch_unpack_bulk(const void *in, void *y, int64_t nblocks, int hdr,
     if (cap > 0 && cap < per_sm) per_sm = (int)cap;
     if (ctas > (int64_t)d.sms * per_sm) ctas = (int64_t)d.sms * per_sm;
     if (ctas < 1) ctas = 1;
-    if (!ensure_dynamic_smem(reinterpret_cast<const void *>(&unpack_nf5_b32_bulk_kernel<Tout, 1>), unpack_smem_bytes<Tout, 1>()) ||
-        !ensure_dynamic_smem(reinterpret_cast<const void *>(&unpack_nf5_b32_bulk_kernel<Tout, 2>), unpack_smem_bytes<Tout, 2>()))
-        return AXS6_ERR_LAUNCH;
     const uint8_t *src = static_cast<const uint8_t *>(in);
-    const cudaError_t le = hdr == 1 ? launch_overlapped(nblocks <= kOverlapBlocks, unpack_nf5_b32_bulk_kernel<Tout, 1>, (unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 1>(), st, map, src, nblocks)
-                                    : launch_overlapped(nblocks <= kOverlapBlocks, unpack_nf5_b32_bulk_kernel<Tout, 2>, (unsigned)ctas, kFastBlocks, unpack_smem_bytes<Tout, 2>(), st, map, src, nblocks);
+    const bool overlap = nblocks <= kOverlapBlocks;
+    cudaError_t le = cudaErrorUnknown;
+    auto go = [&](auto kernel, int smem) {
+        if (!ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), smem)) return;
+        le = launch_overlapped(overlap, kernel, (unsigned)ctas, kFastBlocks, (size_t)smem, st, map, src, nblocks);
+    };
+    const bool lane = kBf16 && nblocks <= kOverlapBlocks;      // per-lane code table (see the kernel)
+    if (hdr == 1) {
+        if (lane) go(unpack_nf5_b32_bulk_kernel<Tout, 1, true>, unpack_smem_bytes<Tout, 1>());
+        else go(unpack_nf5_b32_bulk_kernel<Tout, 1, false>, unpack_smem_bytes<Tout, 1>());
+    } else {
+        if (lane) go(unpack_nf5_b32_bulk_kernel<Tout, 2, true>, unpack_smem_bytes<Tout, 2>());
+        else go(unpack_nf5_b32_bulk_kernel<Tout, 2, false>, unpack_smem_bytes<Tout, 2>());
+    }
     count_launch();
     return le == cudaSuccess ? check_launch() : AXS6_ERR_LAUNCH;
 }
