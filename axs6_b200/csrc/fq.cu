@@ -25,6 +25,8 @@ struct FqArgs {
     Axs6PhiloxKeys keys;               // round keys of `seed`
     const unsigned long long *epoch;   // device counter added to `offset` (stochastic kernels only)
     const float *noise;
+    const long long *row_index;        // gather: input row r is row row_index[r] of x (null: row r)
+    long long table_rows;              // gather: rows of x; an index outside [0, table_rows) reads row 0 and sets the status word
 };
 
 // Nearest TF32 value (10-bit mantissa, ties away from zero), returned as fp32.
@@ -34,6 +36,8 @@ __device__ __forceinline__ float round_tf32(float v)
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
     return __uint_as_float(r);
 }
+
+__device__ int g_gather_status;        // 1 = axs6_fq_gather met an index outside the table (that row read row 0 instead)
 
 template <int GRID, int ROUND>
 __device__ __forceinline__ void fq_chunk(const uint32_t (&v)[8], float (&y)[8], const float *tab,
@@ -112,7 +116,12 @@ __global__ void __launch_bounds__(kThreads) fq_vec_kernel(const FqArgs a)
                 const int64_t row = c / a.g.cpr;
                 const int64_t col0 = (c - row * a.g.cpr) * kChunk;
                 act[k] = act[k] && col0 < a.g.cols;
-                xo = row * a.ldx + col0;
+                int64_t src = row;
+                if (a.row_index && act[k]) {
+                    src = a.row_index[row];
+                    if (src < 0 || src >= a.table_rows) { src = 0; g_gather_status = 1; }
+                }
+                xo = src * a.ldx + col0;
                 yo[k] = row * a.ldy + col0;
             }
             if (act[k]) {
@@ -156,7 +165,12 @@ __global__ void __launch_bounds__(kThreads) fq_generic_kernel(const FqArgs a)
         const int64_t row = t / tiles_per_row;
         const int64_t pc = (t - row * tiles_per_row) * 32 + lane;
         const bool act = pc < a.g.cols;
-        const uint32_t v = act ? ChunkIO<Tin>::load1(a.x, row * a.ldx + pc, a.via_bf16 != 0u) : 0u;
+        int64_t src = row;
+        if (a.row_index && act) {
+            src = a.row_index[row];
+            if (src < 0 || src >= a.table_rows) { src = 0; g_gather_status = 1; }
+        }
+        const uint32_t v = act ? ChunkIO<Tin>::load1(a.x, src * a.ldx + pc, a.via_bf16 != 0u) : 0u;
         const uint32_t ab = v & 0x7FFFFFFFu;
         const uint32_t amax = group_max(ab, a.g.block);
         const float u = element_uniform<ROUND>(row * padded + pc, act, a.keys, offset, a.noise);
@@ -518,7 +532,8 @@ int fq_status_fetch()
 
 static int fq_entry(const void *x, void *y, int in_dtype, int out_dtype, int64_t rows, int64_t cols,
                     int64_t ldx, int64_t ldy, int block, int grid, int round, uint32_t flags,
-                    uint64_t seed, uint64_t offset, const float *noise, cudaStream_t stream)
+                    uint64_t seed, uint64_t offset, const float *noise, cudaStream_t stream,
+                    const long long *row_index = nullptr, int64_t table_rows = 0)
 {
     if (!valid_dtype(in_dtype) || !valid_dtype(out_dtype) || !valid_block(block)) return AXS6_ERR_ARG;
     if (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM) return AXS6_ERR_ARG;
@@ -533,7 +548,8 @@ static int fq_entry(const void *x, void *y, int in_dtype, int out_dtype, int64_t
     FqArgs a;
     a.x = x; a.y = y; a.ldx = ldx; a.ldy = ldy;
     a.g = make_geom(rows, cols, block);
-    a.g.flat = (cols % block == 0 && ldx == cols && ldy == cols) ? 1 : 0;
+    a.g.flat = (cols % block == 0 && ldx == cols && ldy == cols && !row_index) ? 1 : 0;
+    a.row_index = row_index; a.table_rows = table_rows;
     a.via_bf16 = (flags & AXS6_FLAG_INPUT_VIA_BF16) ? 1u : 0u;
     a.out_tf32 = (flags & AXS6_FLAG_OUTPUT_TF32) ? 1u : 0u;
     a.seed = seed; a.offset = offset; a.noise = noise;
@@ -564,6 +580,25 @@ AXS6_API int axs6_fq(const void *x, void *y, int in_dtype, int out_dtype, int64_
     return axs6::fq_entry(x, y, in_dtype, out_dtype, rows, cols, ldx, ldy, block, grid,
                           rounding == AXS6_ROUND_NEAREST ? axs6::kNearest : axs6::kPhilox, flags, seed, offset,
                           nullptr, static_cast<cudaStream_t>(stream));
+}
+
+AXS6_API int axs6_fq_gather(const void *table, int64_t table_rows, const long long *row_index, void *y, int in_dtype,
+                            int out_dtype, int64_t rows, int64_t cols, int64_t ld_table, int64_t ldy, int block, int grid,
+                            int rounding, uint64_t seed, uint64_t offset, axs6_stream_t stream)
+{
+    if (rounding != AXS6_ROUND_NEAREST && rounding != AXS6_ROUND_STOCHASTIC) return AXS6_ERR_ARG;
+    if (!row_index || table_rows <= 0) return AXS6_ERR_ARG;
+    return axs6::fq_entry(table, y, in_dtype, out_dtype, rows, cols, ld_table, ldy, block, grid,
+                          rounding == AXS6_ROUND_NEAREST ? axs6::kNearest : axs6::kPhilox, 0, seed, offset,
+                          nullptr, static_cast<cudaStream_t>(stream), row_index, table_rows);
+}
+
+AXS6_API int axs6_fq_gather_status(void)
+{
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, axs6::g_gather_status, sizeof(int)) != cudaSuccess) return AXS6_ERR_DEVICE;
+    if (v != 0) cudaMemcpyToSymbol(axs6::g_gather_status, &zero, sizeof(int));
+    return v;
 }
 
 AXS6_API int axs6_fq_with_noise(const void *x, void *y, int in_dtype, int out_dtype, int64_t rows,

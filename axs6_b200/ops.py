@@ -153,6 +153,39 @@ def fake_quantize(x: torch.Tensor, block_size: int = 32, grid: int = GRID_NF5, r
     return y.reshape(x.shape)
 
 
+def fake_quantize_gather(table: torch.Tensor, index: torch.Tensor, block_size: int = 32, grid: int = GRID_NF5,
+                         rounding: str = "nearest", out_dtype: torch.dtype | None = None,
+                         who: str = "fake_quantize_gather") -> torch.Tensor:
+    """``fake_quantize(table[index])`` in one pass: the looked-up rows are never written to HBM unquantised.
+    ``table`` (rows, cols) fp32 / bf16 with unit inner stride, ``index`` any shape of integers; returns
+    ``index.shape + (cols,)``.  An index outside the table raises (after the launch, like torch's device assert)."""
+    _check_input(table, who)
+    _check_input(index, who)
+    assert block_size in VALID_BLOCK_SIZES, f"block_size must be one of {VALID_BLOCK_SIZES}"
+    assert table.dim() == 2 and table.dtype in _DT
+    t2 = table if table.stride(1) == 1 else table.contiguous()
+    idx = index.reshape(-1).to(torch.int64).contiguous()
+    rows, cols = idx.numel(), t2.shape[1]
+    odt = out_dtype if out_dtype is not None else t2.dtype
+    y = torch.empty((rows, cols), dtype=odt, device=table.device)
+    rnd = _rounding(rounding)
+    seed, off = (0, 0)
+    if rnd == ROUND_STOCHASTIC:
+        seed, off = next_philox(rows * (-(-cols // block_size)) * block_size)
+    lib = _lib.load()
+    with _on(table.device):
+        st = lib.axs6_fq_gather(t2.data_ptr(), t2.shape[0], idx.data_ptr(), y.data_ptr(), _DT[t2.dtype], _DT[odt], rows, cols,
+                                t2.stride(0) if t2.shape[0] > 1 else cols, cols, block_size, grid, rnd, seed, off,
+                                _stream(table.device))
+    _lib.check("axs6_fq_gather", st)
+    return y.reshape(*index.shape, cols)
+
+
+def gather_index_error() -> bool:
+    """True once after a ``fake_quantize_gather`` launch met an index outside its table (synchronises)."""
+    return bool(_lib.load().axs6_fq_gather_status())
+
+
 def unpack_sum(layout: int, buf: torch.Tensor, nsrc: int, src_stride: int, rows: int, cols: int, block_size: int = 32,
                grid: int = GRID_NF5, out_dtype: torch.dtype = torch.float32, divisor: float = 1.0,
                out: torch.Tensor | None = None) -> torch.Tensor:

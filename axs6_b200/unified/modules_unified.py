@@ -11,6 +11,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .. import ops
 from ..core import DEFAULT_BLOCK_SIZE
 from .functional_unified import axs_linear_unified, fake_quantize_unified
 
@@ -63,6 +64,23 @@ class AXSLayerNormUnified(nn.Module):
         return F.layer_norm(input, self.normalized_shape, self.weight, self.bias, self.eps)
 
 
+class _EmbeddingFQ(torch.autograd.Function):
+    """fake_quantize_unified(F.embedding(index, weight)) as one kernel (modules_unified.py:181-185); straight-through
+    gradient: the rows' gradients are summed into the table as in ``F.embedding``'s backward, the padding row gets none."""
+
+    @staticmethod
+    def forward(ctx, index, weight, padding_idx, block_size):
+        ctx.save_for_backward(index)
+        ctx.num_weights, ctx.padding_idx = weight.shape[0], -1 if padding_idx is None else padding_idx
+        return ops.fake_quantize_gather(weight, index, block_size, ops.GRID_NF5, "nearest", who="AXSEmbeddingUnified")
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (index,) = ctx.saved_tensors
+        gw = torch.ops.aten.embedding_dense_backward(grad_output.contiguous(), index, ctx.num_weights, ctx.padding_idx, False)
+        return None, gw, None, None
+
+
 class AXSEmbeddingUnified(nn.Module):
     """Embedding whose looked-up rows (not the whole table) go through the NF5 fake-quantiser, with a
     straight-through gradient; ``_warmup_active`` returns the raw rows."""
@@ -80,8 +98,12 @@ class AXSEmbeddingUnified(nn.Module):
         self._warmup_active: bool = False
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
-        rows = F.embedding(input, self.weight, self.padding_idx)
-        return rows if self._warmup_active else fake_quantize_unified(rows, self.block_size, "nearest")
+        if self._warmup_active:
+            return F.embedding(input, self.weight, self.padding_idx)
+        if self.weight.is_cuda and input.is_cuda and self.weight.dtype in (torch.float32, torch.bfloat16):
+            # gather and fake-quantise in one kernel: the raw rows never go to HBM
+            return _EmbeddingFQ.apply(input, self.weight, self.padding_idx, self.block_size)
+        return fake_quantize_unified(F.embedding(input, self.weight, self.padding_idx), self.block_size, "nearest")
 
 
 class AXSMultiheadAttentionUnified(nn.Module):

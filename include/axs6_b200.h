@@ -163,6 +163,16 @@ int axs6_fq(const void *x, void *y, int in_dtype, int out_dtype,
             int block, int grid, int rounding, uint32_t flags,
             uint64_t seed, uint64_t offset, axs6_stream_t stream);
 
+/* Fake-quantise of gathered rows in one pass: y[r, :] = FQ(table[row_index[r], :]) for r < rows.  Replaces the
+ * gather followed by a fake-quantise of the reference's embedding (axs/unified/modules_unified.py:181-185:
+ * F.embedding, then fake_quantize_unified on the looked-up rows) without writing the raw rows to HBM in between.
+ * `row_index`: `rows` int64 values on the device.  An index outside [0, table_rows) does not fault: that row is
+ * read from row 0 instead and axs6_fq_gather_status() returns 1 once (and clears the flag). */
+int axs6_fq_gather(const void *table, int64_t table_rows, const long long *row_index, void *y, int in_dtype, int out_dtype,
+                   int64_t rows, int64_t cols, int64_t ld_table, int64_t ldy, int block, int grid, int rounding,
+                   uint64_t seed, uint64_t offset, axs6_stream_t stream);
+int axs6_fq_gather_status(void);
+
 /* Same arithmetic with the uniform draws supplied by the caller: `noise` holds fp32
  * U[0,1) in the zero-padded (rows, nblk, block) layout, as torch.rand_like produces it in
  * the reference (quantize_unified.py:186-189, core.py:351-355).  Makes the stochastic

@@ -159,3 +159,35 @@ def test_v1_modules_and_conversion():
     uni = um.convert_to_axs_unified(v1)
     assert isinstance(uni[0], um.AXSEmbeddingUnified) and isinstance(uni[1], um.AXSLayerNormUnified)
     assert isinstance(uni[2], um.AXSLinearUnified) and torch.equal(uni[2].weight, model[2].weight)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("num,dim,shape", [(1000, 256, (4, 37)), (50, 100, (3,)), (32000, 1024, (8, 128))])
+def test_embedding_gather_and_fake_quantise_in_one_kernel(num, dim, shape, dtype):
+    """AXSEmbeddingUnified = fake_quantize_unified(F.embedding(...)) bit for bit (one fused kernel against the two-step
+    form), padding row included; its weight gradient equals F.embedding's; an index outside the table sets the status
+    flag instead of faulting."""
+    import importlib
+    mu = importlib.import_module("axs6_b200.unified.modules_unified")
+    fu = importlib.import_module("axs6_b200.unified.functional_unified")
+    from axs6_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(num + dim)
+    emb = mu.AXSEmbeddingUnified(num, dim, padding_idx=1).cuda().to(dtype)
+    idx = torch.randint(0, num, shape, generator=g, device="cuda")
+    idx.view(-1)[0] = 1
+    out = emb(idx)
+    want = fu.fake_quantize_unified(torch.nn.functional.embedding(idx, emb.weight.detach(), 1), emb.block_size, "nearest")
+    assert out.shape == (*shape, dim) and out.dtype == dtype
+    assert torch.equal(out.detach().view(torch.int16 if dtype == torch.bfloat16 else torch.int32),
+                       want.view(torch.int16 if dtype == torch.bfloat16 else torch.int32))
+    go = torch.randn(*shape, dim, generator=g, device="cuda").to(dtype)
+    out.backward(go)
+    w2 = emb.weight.detach().clone().requires_grad_(True)
+    torch.nn.functional.embedding(idx, w2, 1).backward(go)
+    assert torch.allclose(emb.weight.grad.float(), w2.grad.float(), rtol=1e-3 if dtype == torch.bfloat16 else 1e-6, atol=1e-6)
+    assert not ops.gather_index_error()
+    bad = idx.clone()
+    bad.view(-1)[-1] = num + 5
+    ops.fake_quantize_gather(emb.weight.detach(), bad)
+    torch.cuda.synchronize()
+    assert ops.gather_index_error() and not ops.gather_index_error()
