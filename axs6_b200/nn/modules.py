@@ -107,6 +107,10 @@ class AXSEmbedding(nn.Module):
                 self.weight[padding_idx].zero_()
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
+        if self.weight.is_cuda and input.is_cuda and self.weight.dtype in (torch.float32, torch.bfloat16):
+            from .. import ops
+            from ..unified.modules_unified import _EmbeddingFQ     # gather and fake-quantise in one kernel, fp32 out
+            return _EmbeddingFQ.apply(input, self.weight, self.padding_idx, self.block_size, ops.GRID_UNIFORM, torch.float32)
         return fake_quantize(F.embedding(input, self.weight, self.padding_idx), self.block_size)
 
 

@@ -69,16 +69,17 @@ class _EmbeddingFQ(torch.autograd.Function):
     gradient: the rows' gradients are summed into the table as in ``F.embedding``'s backward, the padding row gets none."""
 
     @staticmethod
-    def forward(ctx, index, weight, padding_idx, block_size):
+    def forward(ctx, index, weight, padding_idx, block_size, grid=ops.GRID_NF5, out_dtype=None):
         ctx.save_for_backward(index)
         ctx.num_weights, ctx.padding_idx = weight.shape[0], -1 if padding_idx is None else padding_idx
-        return ops.fake_quantize_gather(weight, index, block_size, ops.GRID_NF5, "nearest", who="AXSEmbeddingUnified")
+        ctx.w_dtype = weight.dtype
+        return ops.fake_quantize_gather(weight, index, block_size, grid, "nearest", out_dtype, who="AXSEmbedding")
 
     @staticmethod
     def backward(ctx, grad_output):
         (index,) = ctx.saved_tensors
         gw = torch.ops.aten.embedding_dense_backward(grad_output.contiguous(), index, ctx.num_weights, ctx.padding_idx, False)
-        return None, gw, None, None
+        return None, gw.to(ctx.w_dtype), None, None, None, None
 
 
 class AXSEmbeddingUnified(nn.Module):

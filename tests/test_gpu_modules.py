@@ -191,3 +191,15 @@ def test_embedding_gather_and_fake_quantise_in_one_kernel(num, dim, shape, dtype
     ops.fake_quantize_gather(emb.weight.detach(), bad)
     torch.cuda.synchronize()
     assert ops.gather_index_error() and not ops.gather_index_error()
+
+
+def test_v1_embedding_is_the_fused_kernel_on_the_uniform_grid():
+    from axs6_b200.nn import AXSEmbedding, fake_quantize
+    g = torch.Generator(device="cuda").manual_seed(5)
+    emb = AXSEmbedding(300, 96, padding_idx=0).cuda()
+    idx = torch.randint(0, 300, (5, 17), generator=g, device="cuda")
+    out = emb(idx)
+    want = fake_quantize(torch.nn.functional.embedding(idx, emb.weight.detach(), 0), emb.block_size)
+    assert out.dtype == torch.float32 and torch.equal(out.detach().view(torch.int32), want.view(torch.int32))
+    out.sum().backward()
+    assert emb.weight.grad is not None and float(emb.weight.grad[0].abs().sum()) == 0.0
