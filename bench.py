@@ -25,6 +25,7 @@ Prints ONE JSON line on rank 0:
              restatement under oracle/ when that copy is absent
   codec, linear   the two other metrics of the path (pack->unpack GB/s, fused-linear TFLOP/s)
   fq_sweep, minigpt   the fake-quantise sweep (fp32 + bf16) and the MiniGPT-style training step
+  embedding_gather   the embedding lookup: gather + fake-quantise in one kernel against the two-step form
   gpu_reference   the unmodified reference (baseline/_ref) run on the SAME GPU on the same tensors: its eager
              and Triton fake-quantise and its mixed-precision Linear step, each beside this library's time and with
              a bit-for-bit comparison of the fake-quantise outputs (N = 1 only; see bench_gpu_reference.py)
@@ -392,6 +393,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     torch.cuda.empty_cache()
     if rank == 0 and "fq_sweep" in sections:
         extra["fq_sweep"] = bench_sweep(torch, lib, dev, pk)
+        try:
+            extra["embedding_gather"] = bench_embedding(torch, dev)
+        except Exception as e:
+            extra["embedding_gather"] = {"error": repr(e)[:300]}
     torch.cuda.empty_cache()
     try:
         extra_linear = linear_section(args, rank, world, dev, pk) if "linear" in sections else None
@@ -539,6 +544,36 @@ def bench_codec(torch, lib, udist, dev, pk) -> dict:
                        "-> fp32, unpack_bf16 = records -> bf16 (4 rotating buffer sets, 4 x 355 MiB > L2); pack_planes / unpack_planes = fp32 <-> "
                        "AXSTensor planes (exponent, sign and magnitude bytes: quantize_unified / dequantize_unified), 2 buffer sets")
     return res
+
+
+def bench_embedding(torch, dev) -> dict:
+    """The embedding lookup of the path: 8192 rows of a 32000 x 1024 fp32 table gathered and fake-quantised by ONE
+    kernel (axs6_fq_gather) against the reference's two steps on the same GPU ops (F.embedding, then fake-quantise)."""
+    import importlib
+    from axs6_b200 import ops
+    fu = importlib.import_module("axs6_b200.unified.functional_unified")
+    g = torch.Generator(device=dev).manual_seed(31)
+    table = torch.randn(32000, 1024, generator=g, device=dev)
+    idx = torch.randint(0, 32000, (8, 1024), generator=g, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def t_of(fn, n=50):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3
+
+    fused = t_of(lambda: ops.fake_quantize_gather(table, idx))
+    two = t_of(lambda: fu.fake_quantize_unified(torch.nn.functional.embedding(idx, table), 32, "nearest"))
+    a = ops.fake_quantize_gather(table, idx)
+    b = fu.fake_quantize_unified(torch.nn.functional.embedding(idx, table), 32, "nearest")
+    return {"fused_us": fused, "gather_then_fake_quantize_us": two, "bit_identical": bool(torch.equal(a, b)),
+            "workload": "8192 looked-up rows of a 32000 x 1024 fp32 table, NF5, block 32 (64 MiB of rows in + out)"}
 
 
 def bench_sweep(torch, lib, dev, pk) -> list:
