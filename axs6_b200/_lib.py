@@ -39,6 +39,7 @@ SIGNATURES = {
     "axs6_fq_with_noise": (_int, [_ptr, _ptr, _int, _int, _i64, _i64, _i64, _i64, _int, _int, _u32, _ptr, _ptr]),
     "axs6_fq_gather": (_int, [_ptr, _i64, _ptr, _ptr, _int, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _u64, _u64, _ptr]),
     "axs6_fq_gather_status": (_int, []),
+    "axs6_pack_ef": (_int, [_ptr, _ptr, _i64, _i64, _i64, _int, _int, _int, _u64, _u64, _ptr, _ptr, _ptr, _ptr]),
     "axs6_pack": (_int, [_ptr, _int, _i64, _i64, _i64, _int, _int, _int, _u32, _u64, _u64, _ptr, _int,
                          _ptr, _ptr, _ptr, _ptr]),
     "axs6_unpack": (_int, [_int, _ptr, _ptr, _ptr, _ptr, _int, _i64, _i64, _i64, _int, _int, _ptr]),

@@ -24,6 +24,7 @@ struct CodecArgs {
     Axs6PhiloxKeys keys;               // round keys of `seed`
     const unsigned long long *epoch;   // device counter added to `offset` (stochastic kernels only)
     const float *noise;
+    float *err;              // error feedback (pack, fp32 in, planes out): residual added to x before, replaced after
     uint8_t *p0, *p1, *p2;   // planes (exp, sign, mag) or p0 = records
     int rec, hdr;            // record bytes and header bytes of the byte layout
     int lanes_log2;          // log2(block / 8): lanes that share one block
@@ -85,12 +86,17 @@ __device__ __forceinline__ void chunk_codes(const uint32_t (&v)[8], uint32_t (&c
     }
 }
 
-template <typename Tin, int GRID, int ROUND, int LAYOUT>
+// kEf (fp32 input, planes out): error feedback in the same pass.  corrected = x + err (one fp32 addition), the codes
+// are those of `corrected`, and err becomes corrected - reconstruction (the arithmetic of unpack_vec_kernel), as in
+// quantize_with_error_feedback of the reference (axs/quantize.py:190-199) without its four extra passes over HBM.
+template <typename Tin, int GRID, int ROUND, int LAYOUT, bool kEf = false>
 __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
 {
     __shared__ __align__(16) uint8_t rev[GRID == AXS6_GRID_NF5 ? 1024 : 16];
     __shared__ __align__(16) uint8_t stage[LAYOUT == kBytes ? kStageBytes : 16];
+    __shared__ float lev[kEf ? 32 : 1];
     if (GRID == AXS6_GRID_NF5) build_reverse_lut(rev);
+    if (kEf) build_levels<GRID>(lev);
     __syncthreads();
     pdl_wait();                    // nothing of the caller's memory is touched before this point
 
@@ -105,6 +111,7 @@ __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
         if (base + step >= a.g.total_chunks) pdl_launch_dependents();      // last iteration of this CTA: the next kernel may move in
         uint32_t v[kU][8];
         bool act[kU];
+        int64_t eo[kU];                                     // kEf: offset of the chunk's residuals, -1 = none
 #pragma unroll
         for (int k = 0; k < kU; ++k) {
             const int64_t c = base + (int64_t)k * kThreads + threadIdx.x;
@@ -117,8 +124,16 @@ __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
                 has = has && col0 < a.g.cols;
                 xo = row * a.ld + col0;
             }
+            eo[k] = has ? xo : -1;
             if (has) {
                 ChunkIO<Tin>::load(a.x, xo, v[k], a.via_bf16 != 0u);
+                if (kEf) {
+                    const uint4 e0 = ld_stream16(a.err + xo), e1 = ld_stream16(a.err + xo + 4);
+                    const uint32_t e[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        v[k][i] = __float_as_uint(AXS6_ADD(__uint_as_float(v[k][i]), __uint_as_float(e[i])));
+                }
             } else {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[k][i] = 0u;
@@ -132,6 +147,15 @@ __global__ void __launch_bounds__(kThreads) pack_vec_kernel(const CodecArgs a)
             int se;
             chunk_uniforms<ROUND>(u, c, act[k], a.keys, offset, a.noise);
             chunk_codes<GRID, ROUND>(v[k], code, se, rev, lanes, u);
+            if (kEf && eo[k] >= 0) {
+                const float scale = axs6_scale_decode((uint32_t)se);
+                uint32_t r[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    r[i] = __float_as_uint(AXS6_SUB(__uint_as_float(v[k][i]), axs6_decode_value(code[i] >> 5, lev[code[i] & 31u], scale)));
+                st_stream16(a.err + eo[k], make_uint4(r[0], r[1], r[2], r[3]));
+                st_stream16(a.err + eo[k] + 4, make_uint4(r[4], r[5], r[6], r[7]));
+            }
             if (LAYOUT == kPlanes) {
                 if (act[k]) {
                     uint2 sg, mg;
@@ -1246,6 +1270,43 @@ AXS6_API int64_t axs6_record_bytes(int layout, int block)
     return 0;
 }
 
+AXS6_API int axs6_pack_ef(const float *x, float *err, int64_t rows, int64_t cols, int64_t ld, int block, int grid,
+                          int rounding, uint64_t seed, uint64_t offset, void *out_exp, void *out_sign, void *out_mag,
+                          axs6_stream_t stream)
+{
+    using namespace axs6;
+    if (!valid_block(block) || (grid != AXS6_GRID_NF5 && grid != AXS6_GRID_UNIFORM)) return AXS6_ERR_ARG;
+    if (rounding != AXS6_ROUND_NEAREST && rounding != AXS6_ROUND_STOCHASTIC) return AXS6_ERR_ARG;
+    if (rows < 0 || cols < 0 || ld < cols) return AXS6_ERR_ARG;
+    if (rows == 0 || cols == 0) return AXS6_OK;
+    if (!x || !err || !out_exp || !out_sign || !out_mag) return AXS6_ERR_ARG;
+    const DeviceInfo &d = device_info();
+    if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
+    if (!(aligned16(x) && aligned16(err) && cols % kChunk == 0 && ld % kChunk == 0 && aligned16(out_exp) && aligned16(out_sign) &&
+          aligned16(out_mag)))
+        return AXS6_ERR_UNSUPPORTED;      // the caller composes the steps from axs6_pack / axs6_unpack instead
+    CodecArgs a;
+    a.x = x; a.y = nullptr; a.ld = ld; a.err = err;
+    a.g = make_geom(rows, cols, block);
+    a.g.flat = (cols % block == 0 && ld == cols) ? 1 : 0;
+    a.via_bf16 = 0u;
+    a.seed = seed; a.offset = offset; a.noise = nullptr;
+    a.keys = axs6_philox_keys(seed);
+    a.epoch = philox_epoch_ptr();
+    const bool stochastic = rounding == AXS6_ROUND_STOCHASTIC;
+    if (stochastic && !a.epoch) return AXS6_ERR_DEVICE;
+    a.p0 = static_cast<uint8_t *>(out_exp); a.p1 = static_cast<uint8_t *>(out_sign); a.p2 = static_cast<uint8_t *>(out_mag);
+    a.rec = 0; a.hdr = 0;
+    a.lanes_log2 = block == 32 ? 2 : (block == 16 ? 1 : 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t per_cta = (int64_t)kThreads * kU;
+    if (grid == AXS6_GRID_UNIFORM)
+        return stochastic ? launch_codec(pack_vec_kernel<float, AXS6_GRID_UNIFORM, kPhilox, kPlanes, true>, a, per_cta, a.g.total_chunks, st)
+                          : launch_codec(pack_vec_kernel<float, AXS6_GRID_UNIFORM, kNearest, kPlanes, true>, a, per_cta, a.g.total_chunks, st);
+    return stochastic ? launch_codec(pack_vec_kernel<float, AXS6_GRID_NF5, kPhilox, kPlanes, true>, a, per_cta, a.g.total_chunks, st)
+                      : launch_codec(pack_vec_kernel<float, AXS6_GRID_NF5, kNearest, kPlanes, true>, a, per_cta, a.g.total_chunks, st);
+}
+
 AXS6_API int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, int64_t ldx, int block, int grid,
                          int rounding, uint32_t flags, uint64_t seed, uint64_t offset, const float *noise,
                          int layout, void *out0, void *out1, void *out2, axs6_stream_t stream)
@@ -1265,7 +1326,7 @@ AXS6_API int axs6_pack(const void *x, int in_dtype, int64_t rows, int64_t cols, 
 
     const int round = rounding == AXS6_ROUND_NEAREST ? kNearest : (noise ? kNoise : kPhilox);
     CodecArgs a;
-    a.x = x; a.y = nullptr; a.ld = ldx;
+    a.x = x; a.y = nullptr; a.ld = ldx; a.err = nullptr;
     a.g = make_geom(rows, cols, block);
     a.g.flat = (cols % block == 0 && ldx == cols) ? 1 : 0;
     a.via_bf16 = (flags & AXS6_FLAG_INPUT_VIA_BF16) ? 1u : 0u;
@@ -1316,7 +1377,7 @@ AXS6_API int axs6_unpack(int layout, const void *in0, const void *in1, const voi
     if (!d.valid || !d.ok) return AXS6_ERR_DEVICE;
 
     CodecArgs a;
-    a.x = nullptr; a.y = y; a.ld = ldy;
+    a.x = nullptr; a.y = y; a.ld = ldy; a.err = nullptr;
     a.g = make_geom(rows, cols, block);
     a.g.flat = (cols % block == 0 && ldy == cols) ? 1 : 0;
     a.via_bf16 = 0; a.seed = 0; a.offset = 0; a.noise = nullptr; a.epoch = nullptr;

@@ -308,6 +308,33 @@ def fake_quantize_host(src: torch.Tensor, dst: torch.Tensor | None = None, block
     return dst
 
 
+def pack_error_feedback(x: torch.Tensor, err: torch.Tensor, block_size: int = 32, grid: int = GRID_UNIFORM,
+                        rounding: str = "nearest"):
+    """Planes of ``x + err`` and ``err <- (x + err) - reconstruction`` in ONE kernel, or None when the tensors do not
+    qualify (fp32, contiguous, same shape, last dimension a multiple of 8): the caller then composes the steps."""
+    if not (x.is_cuda and err.is_cuda and x.dtype == torch.float32 and err.dtype == torch.float32 and x.shape == err.shape
+            and x.dim() >= 1 and x.is_contiguous() and err.is_contiguous() and x.shape[-1] % 8 == 0 and x.numel() > 0):
+        return None
+    assert block_size in VALID_BLOCK_SIZES, f"block_size must be one of {VALID_BLOCK_SIZES}"
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    nblk = -(-cols // block_size)
+    se = torch.empty((rows, nblk), dtype=torch.uint8, device=x.device)
+    sg = torch.empty((rows, nblk, block_size), dtype=torch.bool, device=x.device)
+    mg = torch.empty((rows, nblk, block_size), dtype=torch.uint8, device=x.device)
+    rnd = _rounding(rounding)
+    seed, off = (0, 0)
+    if rnd == ROUND_STOCHASTIC:
+        seed, off = next_philox(rows * nblk * block_size)
+    with _on(x.device):
+        st = _lib.load().axs6_pack_ef(x.data_ptr(), err.data_ptr(), rows, cols, cols, block_size, grid, rnd, seed, off,
+                                      se.data_ptr(), sg.data_ptr(), mg.data_ptr(), _stream(x.device))
+    if st == -6:          # AXS6_ERR_UNSUPPORTED: misaligned pointers
+        return None
+    _lib.check("axs6_pack_ef", st)
+    return se, sg, mg
+
+
 def record_bytes(layout: int, block_size: int) -> int:
     return int(_lib.load().axs6_record_bytes(layout, block_size))
 

@@ -64,7 +64,15 @@ def quantize_with_error_feedback(tensor: torch.Tensor, block_size: int = DEFAULT
                                  state: ErrorFeedbackState | None = None) -> AXSTensor:
     """x + residual -> quantise -> residual = corrected - dequantise (quantize.py:149-200)."""
     st = state if state is not None else _global_ef_state
-    corrected = tensor + st.get_buffer(param_name, tensor)
+    buf = st.get_buffer(param_name, tensor)
+    # one kernel (add the residual, quantise, write the new residual) when the tensors qualify ...
+    planes = ops.pack_error_feedback(tensor, buf, block_size, ops.GRID_UNIFORM, rounding) if tensor.is_cuda else None
+    if planes is not None:
+        se, sg, mg = planes
+        return AXSTensor(shared_exponents=se, signs=sg, magnitudes=mg, block_size=block_size,
+                         original_shape=tensor.shape, num_blocks=se.shape[-1])
+    # ... else the same arithmetic as four tensor operations
+    corrected = tensor + buf
     q = quantize(corrected, block_size=block_size, rounding=rounding)
     st.update_buffer(param_name, corrected - dequantize(q).to(corrected.dtype))
     return q

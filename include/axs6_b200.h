@@ -163,6 +163,14 @@ int axs6_fq(const void *x, void *y, int in_dtype, int out_dtype,
             int block, int grid, int rounding, uint32_t flags,
             uint64_t seed, uint64_t offset, axs6_stream_t stream);
 
+/* Quantise with error feedback in one pass (reference: quantize_with_error_feedback, axs/quantize.py:149-200, which
+ * adds the residual, quantises, dequantises and subtracts as four tensor operations): corrected = x + err (fp32),
+ * planes <- codes of corrected, err <- corrected - reconstruction.  fp32 x and err with the same leading dimension,
+ * AXSTensor planes out; needs 16-byte aligned pointers and cols, ld multiples of 8 (AXS6_ERR_UNSUPPORTED otherwise:
+ * compose axs6_pack / axs6_unpack instead).  Bit-identical to the four-step form. */
+int axs6_pack_ef(const float *x, float *err, int64_t rows, int64_t cols, int64_t ld, int block, int grid, int rounding,
+                 uint64_t seed, uint64_t offset, void *out_exp, void *out_sign, void *out_mag, axs6_stream_t stream);
+
 /* Fake-quantise of gathered rows in one pass: y[r, :] = FQ(table[row_index[r], :]) for r < rows.  Replaces the
  * gather followed by a fake-quantise of the reference's embedding (axs/unified/modules_unified.py:181-185:
  * F.embedding, then fake_quantize_unified on the looked-up rows) without writing the raw rows to HBM in between.

@@ -68,3 +68,29 @@ def test_quantization_error_matches_the_reference(blocks, B):
     want = blocks[f"qerr.b{B}"]
     got = np.array([e["mse"], e["rmse"], e["max_abs_error"], e["mean_abs_error"], e["signal_to_noise_db"]])
     assert np.allclose(got, want, rtol=1e-5)
+
+
+@pytest.mark.parametrize("shape", [(64, 64), (7, 96), (3, 5, 40), (1024, 1000)])
+@pytest.mark.parametrize("rounding", ["nearest", "stochastic"])
+def test_error_feedback_in_one_kernel_equals_the_four_steps(shape, rounding):
+    """quantize_with_error_feedback on a contiguous fp32 CUDA tensor runs as ONE kernel (axs6_pack_ef); its codes and
+    its residual buffer equal, bit for bit and step after step, those of add -> quantize -> dequantize -> subtract
+    (axs/quantize.py:190-199) with the same draws."""
+    from axs6_b200 import ops
+    from axs6_b200.core import dequantize, quantize
+    from axs6_b200.quantize import ErrorFeedbackState, quantize_with_error_feedback
+    g = torch.Generator(device="cuda").manual_seed(sum(shape))
+    xs = [torch.randn(*shape, generator=g, device="cuda") * (0.1 + i) for i in range(3)]
+    state = ErrorFeedbackState()
+    manual = torch.zeros(*shape, device="cuda")
+    for step, x in enumerate(xs):
+        ops.reset_philox(1000 * step)
+        q = quantize_with_error_feedback(x, 32, rounding, "p", state)
+        ops.reset_philox(1000 * step)
+        corrected = x + manual
+        q2 = quantize(corrected, 32, rounding)
+        manual = corrected - dequantize(q2)
+        assert torch.equal(q.shared_exponents, q2.shared_exponents)
+        assert torch.equal(q.signs, q2.signs) and torch.equal(q.magnitudes, q2.magnitudes)
+        assert torch.equal(state.get_buffer("p", x).view(torch.int32), manual.view(torch.int32))
+    assert ops.pack_error_feedback(xs[0], torch.zeros_like(xs[0])) is not None       # the fused path was the one taken
