@@ -2,7 +2,7 @@
 
     python bench.py --case {fq_f32|fq_bf16|fq_bf16_stochastic|pack_wire|pack_wire_f32|unpack_wire|unpack_wire_bf16|
                             unpack_sum4|gemm_fwd|gemm_dx|gemm_dw|gemm_fwd_full|gemm_dw_full|gemm_packed_fwd|gemm_packed_fwd_w|gemm_packed_dx|
-                            gemm_packed_dw|fq_f32_full} [--launches n]
+                            gemm_packed_dw|fq_f32_full|fq_gather|pack_ef} [--launches n]
 
 Device footprint stays under 1 GB so that a multi-pass capture finishes quickly (fq_f32_full is the
 benchmark's own 32768 x 8192 launch, 2 GiB, meant for single-pass metrics only).
@@ -65,6 +65,20 @@ def run_case(what: str = "fq_f32", n: int = 3) -> None:
         assert lib.axs6_pack(x.data_ptr(), 1, rows, cols, cols, 32, 1, 0, 0, 0, 0, None, 1, w.data_ptr(), None, None, st) == 0
         y = torch.empty(rows, cols, device=dev)
         run = lambda: lib.axs6_unpack(1, w.data_ptr(), None, None, y.data_ptr(), 0, rows, cols, cols, 32, 1, st)
+    elif what == "fq_gather":                  # embedding lookup: 65536 rows of a 32000 x 1024 fp32 table (256 MiB in + out)
+        table = torch.randn(32000, 1024, generator=g, device=dev)
+        idx = torch.randint(0, 32000, (65536,), generator=g, device=dev)
+        y = torch.empty(65536, 1024, device=dev)
+        run = lambda: lib.axs6_fq_gather(table.data_ptr(), 32000, idx.data_ptr(), y.data_ptr(), 0, 0, 65536, 1024, 1024, 1024,
+                                         32, 1, 0, 0, 0, st)
+    elif what == "pack_ef":                    # error feedback in one pass, 8192 x 8192 fp32, uniform grid, planes out
+        x = torch.randn(rows, cols, generator=g, device=dev)
+        err = torch.zeros_like(x)
+        se = torch.empty(rows * cols // 32, dtype=torch.uint8, device=dev)
+        sg = torch.empty(rows * cols, dtype=torch.uint8, device=dev)
+        mg = torch.empty(rows * cols, dtype=torch.uint8, device=dev)
+        run = lambda: lib.axs6_pack_ef(x.data_ptr(), err.data_ptr(), rows, cols, cols, 32, 0, 0, 0, 0, se.data_ptr(), sg.data_ptr(),
+                                       mg.data_ptr(), st)
     elif what == "fq_bf16_stochastic":
         x = torch.randn(rows, cols, generator=g, device=dev).to(torch.bfloat16)
         y = torch.empty_like(x)
