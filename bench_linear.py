@@ -10,7 +10,9 @@ weight gradient summed with an NCCL all-reduce.  The backward is issued as two c
 produces dW, whose all-reduce starts at once on NCCL's stream; the second produces dX and db under
 it, with a few SMs left free for the collective's CTAs (``axs6_tune(8, n)``).  Both readings of
 "N GPUs" are timed: ``weak`` = 16384 rows per GPU, ``strong`` = 16384 rows in total, and for the
-strong case also the compute alone (all-reduce off).
+strong case also the compute alone (all-reduce off).  The split over output columns (whole batch on
+every rank, N/world rows of W each; all-gather of y, all-reduce of the partial dX) is timed beside the
+strong case as ``column_split``.
 """
 from __future__ import annotations
 
@@ -62,6 +64,129 @@ class _Case:
 
     def bwd_all(self, i):
         self._bwd(i, self.dx.data_ptr(), self.dws[i % 2].data_ptr(), self.db.data_ptr(), FLAG_QGRAD | FLAG_REUSE_WQ)
+
+
+class _ColumnCase:
+    """The other way the Linear splits: output columns.  Every rank holds the whole batch (x and the incoming
+    gradient are replicated) and N/world rows of W.  Forward: y[:, mine] = FQ(x) FQ(W_mine)^T, then an all-gather of the
+    column blocks.  Backward: dW_mine and db_mine are local; dX is a sum over the ranks' column blocks, so the bf16
+    partial dX is all-reduced -- started right after the dX product so that it runs under the dW product."""
+
+    def __init__(self, lib, dev, rank: int, world: int, seed: int):
+        self.lib, self.world, self.rank = lib, world, rank
+        M, Nl = M_ROWS, N // world
+        self.M, self.Nl = M, Nl
+        g = torch.Generator(device=dev).manual_seed(seed)        # the same seed on every rank: replicated operands
+        self.x = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+        self.w_full = torch.randn(N, K, generator=g, device=dev) * 0.02
+        self.go_full = torch.randn(M, N, generator=g, device=dev).to(torch.bfloat16)
+        self.w = self.w_full[rank * Nl:(rank + 1) * Nl]
+        self.go = self.go_full[:, rank * Nl:(rank + 1) * Nl]     # a column block: row pitch N
+        self.bias = torch.zeros(Nl, device=dev)
+        self.y_mine = torch.empty(M, Nl, dtype=torch.bfloat16, device=dev)
+        self.y_blocks = torch.empty(world, M, Nl, dtype=torch.bfloat16, device=dev)
+        self.y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        self.dx = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+        self.dw = torch.empty(Nl, K, dtype=torch.float32, device=dev)
+        self.db = torch.empty(Nl, dtype=torch.float32, device=dev)
+        ws = [torch.empty(int(lib.axs6_linear_workspace_bytes(i, M, Nl, K)), dtype=torch.uint8, device=dev) for i in (0, 1, 2, 3)]
+        self.xq, self.wq, self.gq, self.part = ws
+        self.stream = torch.cuda.current_stream().cuda_stream
+
+    def fwd_mine(self):
+        st = self.lib.axs6_linear_fwd(self.x.data_ptr(), 1, K, self.w.data_ptr(), 0, K, self.bias.data_ptr(),
+                                      self.y_mine.data_ptr(), 1, self.Nl, self.M, self.Nl, K, BLOCK, 1, 1,
+                                      self.xq.data_ptr(), self.wq.data_ptr(), self.stream)
+        assert st == 0, st
+
+    def gather(self, dist, group):
+        dist.all_gather_into_tensor(self.y_blocks, self.y_mine)       # nothing runs beside it: the default group, all CTAs
+        self.lay_side_by_side()
+
+    def lay_side_by_side(self):
+        torch.cat(list(self.y_blocks.unbind(0)), dim=1, out=self.y)                        # (world, M, N/world) -> (M, N)
+
+    def _bwd(self, i, dx, dw, db, flags):
+        M, Nl = self.M, self.Nl
+        st = self.lib.axs6_linear_bwd(self.go.data_ptr(), 1, N, self.xq.data_ptr(), self.w.data_ptr(), 0, K, dx, 1, K, dw, K, db,
+                                      M, Nl, K, BLOCK, 1, flags, 1234, i * (M * N // 8), None, self.gq.data_ptr(),
+                                      self.wq.data_ptr(), self.part.data_ptr(), None, self.stream)
+        assert st == 0, st
+
+    def step(self, i, dist, group, collectives: bool, reserve: int):
+        self.fwd_mine()
+        if collectives:
+            self.gather(dist, group)
+        self._bwd(i, self.dx.data_ptr(), None, None, FLAG_QGRAD | FLAG_REUSE_WQ)
+        pending = dist.all_reduce(self.dx, group=group, async_op=True) if collectives else None
+        if reserve and collectives:
+            self.lib.axs6_tune(8, reserve)
+        self._bwd(i, None, self.dw.data_ptr(), self.db.data_ptr(), FLAG_QGRAD | FLAG_REUSE_GQ)
+        if reserve and collectives:
+            self.lib.axs6_tune(8, 0)
+        if pending is not None:
+            pending.wait()
+
+
+def _column_split(lib, dev, rank: int, world: int, dist, group, steps: int, reserve: int) -> dict:
+    """Times the column-split step (with and without its two collectives, max over ranks) and checks that the gathered
+    forward output equals, bit for bit, the forward of the whole weight matrix on one GPU."""
+    case = _ColumnCase(lib, dev, rank, world, 4200)
+    case.fwd_mine()
+    case.gather(dist, group)
+    whole = torch.empty(M_ROWS, N, dtype=torch.bfloat16, device=dev)
+    ws = [torch.empty(int(lib.axs6_linear_workspace_bytes(i, M_ROWS, N, K)), dtype=torch.uint8, device=dev) for i in (0, 1)]
+    st = lib.axs6_linear_fwd(case.x.data_ptr(), 1, K, case.w_full.data_ptr(), 0, K, torch.zeros(N, device=dev).data_ptr(),
+                             whole.data_ptr(), 1, N, M_ROWS, N, K, BLOCK, 1, 1, ws[0].data_ptr(), ws[1].data_ptr(), case.stream)
+    assert st == 0, st
+    torch.cuda.synchronize()
+    same = torch.tensor([1.0 if torch.equal(case.y, whole) else 0.0], dtype=torch.float64, device=dev)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    del whole, ws
+
+    def timed(collectives: bool, res: int) -> float:
+        for i in range(3):
+            case.step(i, dist, group, collectives, res)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            case.step(i, dist, group, collectives, res)
+        e1.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps
+
+    def alone(fn) -> float:
+        """One collective (or copy) by itself, max over ranks."""
+        for _ in range(2):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps
+
+    flops = 6.0 * M_ROWS * N * K                                  # whole job: every rank does 1/world of it
+    m_all, m_none = timed(True, reserve), timed(False, 0)
+    phases = {"all_gather_y_ms": alone(lambda: dist.all_gather_into_tensor(case.y_blocks, case.y_mine)),
+              "lay_blocks_side_by_side_ms": alone(case.lay_side_by_side),
+              "all_reduce_dx_alone_ms": alone(lambda: dist.all_reduce(case.dx, group=group))}
+    return {"columns_per_gpu": case.Nl, "rows": M_ROWS, "ms_per_step": m_all, "TFLOPs": flops / (m_all * 1e-3) / 1e12,
+            "compute_only": {"ms_per_step": m_none, "TFLOPs": flops / (m_none * 1e-3) / 1e12},
+            "gathered_forward_equals_one_gpu_forward": bool(same.item() == 1.0), "collectives_alone": phases,
+            "collectives": f"all-gather of the (M, N/{world}) bf16 column blocks of y + one copy that lays them side by side; "
+                           f"all-reduce of the bf16 partial dX ({M_ROWS}x{K}) under the dW product",
+            "wire_bytes_per_rank": {"all_gather_y": M_ROWS * case.Nl * 2, "all_reduce_dx": M_ROWS * K * 2}}
 
 
 def _rel(a, b) -> float:
@@ -345,6 +470,11 @@ def run(args, rank: int, world: int, dev, pk: dict, steps: int | None = None) ->
                   "compute_only": {"ms_per_step": m_c, "TFLOPs": flops_strong / (m_c * 1e-3) / 1e12,
                                    "note": "the same sharded step with the dW all-reduce switched off"}}
         del sc
+        torch.cuda.empty_cache()
+        try:
+            strong["column_split"] = _column_split(lib, dev, rank, world, dist, group, steps, reserve)
+        except Exception as e:
+            strong["column_split"] = {"error": repr(e)[:300]}
         torch.cuda.empty_cache()
 
     tflops = res_weak["TFLOPs"]
