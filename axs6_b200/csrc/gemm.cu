@@ -1139,6 +1139,7 @@ static int launch_gemm_packed(const void *a, const void *a_exps, int64_t lda, co
     q.a_exps = static_cast<const uint8_t *>(a_exps); q.b_exps = static_cast<const uint8_t *>(b_exps);
     q.a_nblk = (int)(a_cols / 32); q.b_nblk = (int)(b_cols / 32);
     q.a_rows = (int)a_rows; q.b_rows = (int)b_rows;
+    q.gather_arrivals = tune_value(9) == 1 ? 0 : 1;
     bool ok = true;
     if (a_exps) {
         if (a_cols % 64 || a_rows % 8) return AXS6_ERR_UNSUPPORTED;   // payload rows and exponent runs must be 16-byte multiples

@@ -37,6 +37,7 @@ struct PackedParams {
     const uint8_t *a_exps, *b_exps;     // exponent planes, pair-major (null: operand is bf16)
     int a_nblk, b_nblk;                 // blocks per row of the stored operand matrix
     int a_rows, b_rows;                 // rows of the stored operand matrix (K-major: M or N; MN-major: K)
+    int gather_arrivals;                // 1: the last decode warp of a CTA to finish a stage signals the leader for all 16
 };
 
 struct PairQ {
@@ -100,6 +101,7 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     constexpr int TN = 256;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(16) uint32_t lut[4096];                             // code pair -> two bf16 values (16 KB, static)
+    __shared__ uint32_t stage_done[PairQ::kStages];                          // decode warps of this CTA finished with a stage (running count)
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;             // MMA stages (1024-aligned)
     const uint32_t raw0 = base + S * kStage;                                 // raw stages: [A payload | B payload | A exps | B exps]
     const uint32_t bar0 = raw0 + R * kRaw;
@@ -125,8 +127,9 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
             // full: (leader's expect_tx arrival if a bf16 operand is loaded) + one arrival per decode warp of both CTAs
-            mbar_init(full_bar(s), (kAnyTma ? 1 : 0) + 2 * kDecodeWarps);
+            mbar_init(full_bar(s), (kAnyTma ? 1 : 0) + (q.gather_arrivals ? 2 : 2 * kDecodeWarps));
             mbar_init(empty_bar(s), 1);
+            stage_done[s] = 0u;
         }
         for (int s = 0; s < R; ++s) {
             mbar_init(rfull_bar(s), 1);
@@ -364,7 +367,18 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // decoded tile visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive_release_cluster(map_to_cta(full_bar(s), 0));
+                    // A cluster-scope release per warp and k-block is what the decode warps stalled on most.  With
+                    // gathered arrivals the warps count themselves in shared memory (CTA scope) and only the one that
+                    // completes the sixteen releases to the leader's barrier; the count runs on, a stage is not
+                    // decoded again before the tensor core has read it.
+                    bool signal = true;
+                    if (q.gather_arrivals) {
+                        uint32_t before;
+                        asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;"
+                                     : "=r"(before) : "r"(smem_u32(&stage_done[s])) : "memory");
+                        signal = (before % kDecodeWarps) == kDecodeWarps - 1;
+                    }
+                    if (signal) mbar_arrive_release_cluster(map_to_cta(full_bar(s), 0));
                     mbar_arrive(rempty_bar(rs));
                 }
                 if (++s == S) { s = 0; ph ^= 1u; }

@@ -127,6 +127,8 @@ int64_t axs6_query(int what);
  *           clusters: same results; measured 1-2 % slower alone, better only next to a kernel that holds SMs
  *   key 7   GEMM kernel: 1 single-CTA, 2 CTA pairs on 256 x 256 tiles, 3 CTA pairs on 256 x 512 tiles
  *   key 8   SMs the GEMM leaves free (for a collective on another stream)
+ *   key 9   1 = every decode warp of the quantise-on-load GEMM signals the leader CTA's stage barrier itself (32 cluster-scope
+ *           arrivals per k-block) instead of the last warp of each CTA doing it for all sixteen (2 per k-block)
  *   key 11  1 = general unpack / unpack-and-sum kernels only (no TMA-fed kernel)
  *   key 12  1 = general fake-quantise kernel only (no TMA-fed bf16 kernel)
  *   key 13  poll limit of the bounded waits inside axs6_unpack_sum's fast kernel (default 2^22 polls)
