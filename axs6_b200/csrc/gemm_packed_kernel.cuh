@@ -31,6 +31,8 @@
 // 7 producer/raw stage free) and all roles leave, as in the other kernels.
 
 constexpr int kDecodeWarps = 16;
+constexpr int kDecodeGroups = 4;                               // groups of decode warps; group g decodes k-blocks g, g + 4, ...
+constexpr int kGroupWarps = kDecodeWarps / kDecodeGroups;      // 4 warps = 128 threads, 4 half-blocks per thread and operand
 constexpr int kThreadsPacked = (6 + kDecodeWarps) * 32;       // 704
 
 struct PackedParams {
@@ -42,7 +44,7 @@ struct PackedParams {
 
 struct PairQ {
     static constexpr int kStages = 5;                              // decoded (MMA) stages
-    static constexpr int kRawStages = 3;                           // payload + exponent stages
+    static constexpr int kRawStages = 4;                           // payload + exponent stages: one per decode group (see the decode warps)
     static constexpr int kABytes = 128 * BK * 2, kBBytes = 128 * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;          // 32 KB
     static constexpr int kRawOp = 128 * 48;                        // payload tile of one operand: 6 KB
@@ -56,39 +58,52 @@ __device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_add
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// All-zero blocks (exponent 0) and blocks at the ends of the exponent range: fp32 product, one rounding.  Rare, and kept
+// out of line (loads and stores included) so that the decode loop stays small enough for the instruction cache.
+__device__ __noinline__ void decode_half_block_slow(uint32_t raw, uint32_t se, uint32_t dst0, uint32_t dst1)
+{
+    uint32_t w[3], o[8];
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[0]) : "r"(raw));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[1]) : "r"(raw + 4u));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[2]) : "r"(raw + 8u));
+    const float scale = axs6_scale_decode(se);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int bit = 6 * i, word = bit >> 5, off = bit & 31;
+        const uint32_t code = (off <= 26 ? (w[word] >> off) : __funnelshift_r(w[word], w[word + 1 < 3 ? word + 1 : 2], off)) & 63u;
+        const float y = axs6_decode_value(code >> 5, __uint_as_float(g_codebook_bits[code & 31u]), scale);
+        const uint32_t h = axs6_f32_to_bf16_bits(y);
+        if (i & 1) o[i >> 1] |= h << 16; else o[i >> 1] = h;
+    }
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst1), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+}
+
 // Decodes half a block: 16 codes = 12 payload bytes at shared address `raw` (4-byte aligned), exponent `se`, into
-// 16 bf16 values = 8 words.  `lut` is the pair table in static shared memory (its address folds into the load
-// instruction): entry (c1 << 6 | c0) holds the two table values of codes c0 (low half) and c1 (high half).
-__device__ __forceinline__ void decode_half_block(uint32_t raw, uint32_t se, const uint32_t *lut, uint32_t (&o)[8])
+// 16 bf16 values = 8 words.  `lut` is the code table in static shared memory with one copy per lane: entry
+// (code, lane) is word code * 32 + lane, so the 32 lookups of a warp always hit 32 different banks (`lane4` = lane * 4).
+__device__ __forceinline__ void decode_half_block(uint32_t raw, uint32_t se, const uint32_t *lut, uint32_t lane4, uint32_t (&o)[8])
 {
     uint32_t w[3];
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[0]) : "r"(raw));
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[1]) : "r"(raw + 4u));
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[2]) : "r"(raw + 8u));
-    if (se >= 8u && se <= 254u) {
-        const uint32_t kk = (se - 7u) * 0x00800080u;
+    const uint32_t kk = (se - 7u) * 0x00800080u;                  // the caller has checked 8 <= se <= 254
 #pragma unroll
-        for (int p = 0; p < 8; ++p) {
-            // byte offset of pair p's entry: its 12 bits start at bit 12 p of the 96-bit payload
-            const int bit = 12 * p, word = bit >> 5, off = bit & 31;
+    for (int pr = 0; pr < 8; ++pr) {
+        uint32_t v[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            // byte offset of the entry of value 2 pr + e: its code moved to bits 7..12, plus this lane's word
+            const int bit = 6 * (2 * pr + e), word = bit >> 5, off = bit & 31;
             uint32_t x;
-            if (off == 0) x = w[word] << 2;
-            else if (off <= 20) x = w[word] >> (off - 2);
-            else x = __funnelshift_r(w[word], w[word + 1 < 3 ? word + 1 : 2], off - 2);
-            const uint32_t v = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(lut) + (x & 0x3FFCu));
-            o[p] = v + kk;
+            if (off < 7) x = w[word] << (7 - off);
+            else if (off == 7) x = w[word];
+            else if (off <= 26) x = w[word] >> (off - 7);
+            else x = __funnelshift_r(w[word], w[word + 1 < 3 ? word + 1 : 2], off - 7);
+            v[e] = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(lut) + ((x & (0x3Fu << 7)) | lane4));
         }
-    } else {
-        // all-zero blocks (se = 0) and blocks at the ends of the exponent range: fp32 product, one rounding
-        const float scale = axs6_scale_decode(se);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const int bit = 6 * i, word = bit >> 5, off = bit & 31;
-            const uint32_t code = (off <= 26 ? (w[word] >> off) : __funnelshift_r(w[word], w[word + 1 < 3 ? word + 1 : 2], off)) & 63u;
-            const float y = axs6_decode_value(code >> 5, __uint_as_float(g_codebook_bits[code & 31u]), scale);
-            const uint32_t h = axs6_f32_to_bf16_bits(y);
-            if (i & 1) o[i >> 1] |= h << 16; else o[i >> 1] = h;
-        }
+        o[pr] = (v[1] << 16) + v[0] + kk;
     }
 }
 
@@ -100,7 +115,7 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     constexpr int S = PairQ::kStages, R = PairQ::kRawStages, kA2 = PairQ::kABytes, kStage = PairQ::kStageBytes, kRaw = PairQ::kRawBytes;
     constexpr int TN = 256;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(16) uint32_t lut[4096];                             // code pair -> two bf16 values (16 KB, static)
+    __shared__ __align__(128) uint32_t lut[64 * 32];                         // code -> bf16 bits, one copy per lane (8 KB, static)
     __shared__ uint32_t stage_done[PairQ::kStages];                          // decode warps of this CTA finished with a stage (running count)
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;             // MMA stages (1024-aligned)
     const uint32_t raw0 = base + S * kStage;                                 // raw stages: [A payload | B payload | A exps | B exps]
@@ -126,14 +141,15 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
-            // full: (leader's expect_tx arrival if a bf16 operand is loaded) + one arrival per decode warp of both CTAs
-            mbar_init(full_bar(s), (kAnyTma ? 1 : 0) + (q.gather_arrivals ? 2 : 2 * kDecodeWarps));
+            // full: (leader's expect_tx arrival if a bf16 operand is loaded) + one arrival per CTA (or per warp of the
+            // group that decoded the stage, both CTAs)
+            mbar_init(full_bar(s), (kAnyTma ? 1 : 0) + (q.gather_arrivals ? 2 : 2 * kGroupWarps));
             mbar_init(empty_bar(s), 1);
             stage_done[s] = 0u;
         }
         for (int s = 0; s < R; ++s) {
             mbar_init(rfull_bar(s), 1);
-            mbar_init(rempty_bar(s), kDecodeWarps);
+            mbar_init(rempty_bar(s), kGroupWarps);
         }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -141,15 +157,10 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     }
     {
         uint32_t *tl = lut;
-        for (int i = threadIdx.x; i < 4096; i += kThreadsPacked) {
-            uint32_t v[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int c = (i >> (6 * e)) & 63;
-                const uint32_t bits = g_codebook_bits[c & 31];
-                v[e] = ((uint32_t)axs6_f32_to_bf16_bits(__uint_as_float(bits)) - (120u << 7)) | ((uint32_t)(c >> 5) << 15);
-            }
-            tl[i] = v[0] | (v[1] << 16);
+        for (int i = threadIdx.x; i < 64 * 32; i += kThreadsPacked) {
+            const int c = i >> 5;
+            const uint32_t bits = g_codebook_bits[c & 31];
+            tl[i] = ((uint32_t)axs6_f32_to_bf16_bits(__uint_as_float(bits)) - (120u << 7)) | ((uint32_t)(c >> 5) << 15);
         }
     }
     if (warp == 1) {
@@ -303,32 +314,39 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         }
     } else if (kPacked) {
         // ------------------------------------------------------------------ decode (warps 6..21, both CTAs)
-        // thread dt owns half-block dt of the 512 half-blocks (16 values each) of a packed operand tile:
-        // block = dt >> 1 in row-major order of the raw tile, half = dt & 1
+        // A packed operand tile is 512 half-blocks of 16 values (block = hb >> 1 in row-major order of the raw tile,
+        // half = hb & 1).  The sixteen warps work as four groups: group g decodes the k-blocks g, g + 4, ... of the
+        // cluster's sequence, so that up to four stages are being filled at the same time and a warp pays its waits,
+        // fence and arrivals once per four half-blocks per operand.  Thread gt of a group owns half-blocks gt + 128 j.
+        // A parity wait tells two neighbouring phases of a barrier apart and no more, so a group must never wait
+        // for a phase while the one before it is still open: with one raw stage per group the fill it waits for
+        // follows the fill it has just consumed, and with at least as many decoded stages as groups the stage it
+        // wants back was handed to the tensor core before the stage it got back one turn earlier.
+        static_assert(PairQ::kRawStages == kDecodeGroups && PairQ::kStages >= kDecodeGroups, "stage counts against the decode groups");
+        static_assert(kGroupWarps * 32 * 4 == 512, "four half-blocks per thread and operand");
         const int dt = threadIdx.x - 6 * 32;
-        const int blk = dt >> 1, half = dt & 1;
-        struct Geo { uint32_t raw, exp, dst0, dst1; int row, col; };
-        auto geo = [&](bool mn) -> Geo {
+        const int grp = dt >> 7, gt = dt & 127;
+        const uint32_t lane4 = (uint32_t)lane << 2;
+        struct Geo { uint32_t raw, exp, dst0; int row, col; };
+        auto geo = [&](bool mn, int hb) -> Geo {
             Geo g;
-            g.raw = (uint32_t)blk * 24u + (uint32_t)half * 12u;
+            const int blk = hb >> 1, half = hb & 1;
+            g.raw = (uint32_t)hb * 12u;
             if (!mn) {               // tile row r = blk >> 1 (output index), j = blk & 1 of the two contraction blocks
                 const uint32_t r = (uint32_t)blk >> 1, j = (uint32_t)blk & 1u;
                 g.exp = (uint32_t)blk;
                 const uint32_t p0 = 4u * j + 2u * (uint32_t)half;
                 g.dst0 = r * 128u + (((p0) ^ (r & 7u)) << 4);
-                g.dst1 = r * 128u + (((p0 + 1u) ^ (r & 7u)) << 4);
                 g.row = (int)r; g.col = (int)j;
             } else {                 // k-row r = blk >> 2, b = blk & 3 of the four output blocks
                 const uint32_t r = (uint32_t)blk >> 2, b = (uint32_t)blk & 3u;
                 g.exp = (b >> 1) * 128u + r * 2u + (b & 1u);
                 const uint32_t p0 = 4u * (b & 1u) + 2u * (uint32_t)half;
                 g.dst0 = (b >> 1) * 8192u + r * 128u + (((p0) ^ (r & 7u)) << 4);
-                g.dst1 = (b >> 1) * 8192u + r * 128u + (((p0 + 1u) ^ (r & 7u)) << 4);
                 g.row = (int)r; g.col = (int)b;
             }
-            return g;
+            return g;                // the second 16-byte chunk of the half-block sits at dst0 ^ 16 (p0 is even)
         };
-        const Geo ga = geo(p.a_mn), gb = geo(p.b_mn);
         // is this thread's block inside the operand?  K-major: row o0 + row < rows, block 2 kb + col < nblk;
         // MN-major: k-row kb * 64 + row < rows, block o0 / 32 + col < nblk
         auto inside = [&](const Geo &g, bool mn, int rows, int nblk, int o0, int kb) -> bool {
@@ -336,51 +354,63 @@ gemm2q_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         };
         auto put = [&](uint32_t stage_half, const Geo &g, bool valid, uint32_t raw_op, uint32_t exp_op) {
             uint32_t o[8];
+            const uint32_t d0 = stage_half + g.dst0, d1 = stage_half + (g.dst0 ^ 16u);
             if (valid) {
                 uint32_t se;
                 asm volatile("ld.shared.u8 %0, [%1];" : "=r"(se) : "r"(exp_op + g.exp));
-                decode_half_block(raw_op + g.raw, se, lut, o);
+                if (se < 8u || se > 254u) {
+                    decode_half_block_slow(raw_op + g.raw, se, d0, d1);
+                    return;
+                }
+                decode_half_block(raw_op + g.raw, se, lut, lane4, o);
             } else {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) o[i] = 0u;
             }
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage_half + g.dst0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage_half + g.dst1), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(d0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(d1), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
         };
-        int s = 0, rs = 0;
+        int s = 0, rs = 0, turn = 0;
         uint32_t ph = 0, rph = 0;
         bool ok = true;
         for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
             const int m0 = (t / tiles_n) * 256 + (int)rank * 128;
             const int n0 = (t % tiles_n) * TN + (int)rank * 128;
             for (int kb = 0; kb < total_kb; ++kb) {
-                // one lane polls, the warp follows
-                int go = 1;
-                if (lane == 0) go = (mbar_wait(rfull_bar(rs), rph, 5) && mbar_wait(empty_bar(s), ph ^ 1u, 6)) ? 1 : 0;
-                go = __shfl_sync(0xFFFFFFFFu, go, 0);
-                if (!go) { ok = false; break; }
-                const uint32_t sa = base + s * kStage, sb = sa + kA2;
-                const uint32_t ra = raw0 + rs * kRaw, rb = ra + PairQ::kRawOp;
-                const uint32_t ea = ra + 2 * PairQ::kRawOp, eb = ea + PairQ::kExpOp;
-                if (QA) put(sa, ga, inside(ga, p.a_mn, q.a_rows, q.a_nblk, m0, kb), ra, ea);
-                if (QB) put(sb, gb, inside(gb, p.b_mn, q.b_rows, q.b_nblk, n0, kb), rb, eb);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // decoded tile visible to the tensor core's reads
-                __syncwarp();
-                if (lane == 0) {
-                    // A cluster-scope release per warp and k-block is what the decode warps stalled on most.  With
-                    // gathered arrivals the warps count themselves in shared memory (CTA scope) and only the one that
-                    // completes the sixteen releases to the leader's barrier; the count runs on, a stage is not
-                    // decoded again before the tensor core has read it.
-                    bool signal = true;
-                    if (q.gather_arrivals) {
-                        uint32_t before;
-                        asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;"
-                                     : "=r"(before) : "r"(smem_u32(&stage_done[s])) : "memory");
-                        signal = (before % kDecodeWarps) == kDecodeWarps - 1;
+                if (turn == grp) {
+                    // one lane polls, the warp follows
+                    int go = 1;
+                    if (lane == 0) go = (mbar_wait(rfull_bar(rs), rph, 5) && mbar_wait(empty_bar(s), ph ^ 1u, 6)) ? 1 : 0;
+                    go = __shfl_sync(0xFFFFFFFFu, go, 0);
+                    if (!go) { ok = false; break; }
+                    const uint32_t sa = base + s * kStage, sb = sa + kA2;
+                    const uint32_t ra = raw0 + rs * kRaw, rb = ra + PairQ::kRawOp;
+                    const uint32_t ea = ra + 2 * PairQ::kRawOp, eb = ea + PairQ::kExpOp;
+#pragma unroll 1
+                    for (int j = 0; j < 512 / (kGroupWarps * 32); ++j) {
+                        const int hb = gt + kGroupWarps * 32 * j;
+                        if (QA) { const Geo g = geo(p.a_mn, hb); put(sa, g, inside(g, p.a_mn, q.a_rows, q.a_nblk, m0, kb), ra, ea); }
+                        if (QB) { const Geo g = geo(p.b_mn, hb); put(sb, g, inside(g, p.b_mn, q.b_rows, q.b_nblk, n0, kb), rb, eb); }
                     }
-                    if (signal) mbar_arrive_release_cluster(map_to_cta(full_bar(s), 0));
-                    mbar_arrive(rempty_bar(rs));
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // decoded tile visible to the tensor core's reads
+                    __syncwarp();
+                    if (lane == 0) {
+                        // A cluster-scope release per warp and k-block is what the decode warps stalled on most.  With
+                        // gathered arrivals the warps of the group count themselves in shared memory (CTA scope) and only
+                        // the one that completes the group releases to the leader's barrier; the count runs on, a stage
+                        // is not decoded again before the tensor core has read it.
+                        bool signal = true;
+                        if (q.gather_arrivals) {
+                            uint32_t before;
+                            asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;"
+                                         : "=r"(before) : "r"(smem_u32(&stage_done[s])) : "memory");
+                            signal = (before % kGroupWarps) == kGroupWarps - 1;
+                        }
+                        if (signal) mbar_arrive_release_cluster(map_to_cta(full_bar(s), 0));
+                        mbar_arrive(rempty_bar(rs));
+                    }
                 }
+                if (++turn == kDecodeGroups) turn = 0;
                 if (++s == S) { s = 0; ph ^= 1u; }
                 if (++rs == R) { rs = 0; rph ^= 1u; }
             }
