@@ -114,6 +114,28 @@ def test_gemm_packed_against_unpacked_operands(M, N, K, a_mn, b_mn, which):
     assert rel(c32[torch.from_numpy(idx).cuda()].cpu(), torch.from_numpy(want)) < 1e-5
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1)])
+def test_gemm_packed_per_warp_arrivals_give_the_same_bits(a_mn, b_mn):
+    """axs6_tune(9, 1): every decode warp signals the stage barrier itself instead of the last warp of its group for
+    all four.  Same decoded stages, same products: the outputs must be identical, multi-wave shape included."""
+    lib = _lib.load()
+    M, N, K = 37 * 256, 3 * 256, 1024
+    a, b = _operands(M, N, K, a_mn, b_mn, 77 + 2 * a_mn + b_mn)
+    pa, pb = ops.pack_split(a), ops.pack_split(b)
+    want = ops.gemm_packed(pa, pb, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.bfloat16)
+    want_w = ops.gemm_packed(ops.unpack_split(pa, torch.bfloat16), pb, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.bfloat16)
+    gemm_status_ok()
+    assert lib.axs6_tune(9, 1) == 0
+    try:
+        got = ops.gemm_packed(pa, pb, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.bfloat16)
+        got_w = ops.gemm_packed(ops.unpack_split(pa, torch.bfloat16), pb, a_mn=bool(a_mn), b_mn=bool(b_mn), out_dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+    finally:
+        lib.axs6_tune(9, 0)
+    gemm_status_ok()
+    assert torch.equal(got, want) and torch.equal(got_w, want_w)
+
+
 def test_gemm_packed_zero_and_extreme_blocks_and_bias():
     """All-zero blocks (exponent byte 0: the smallest level times 2^-127, a bf16 denormal), tiny and huge block scales,
     and the bias epilogue."""
